@@ -1,0 +1,191 @@
+// Memory-bound kernels of the step: embedding gather, fused residual-add + RMSNorm (optionally on
+// selected rows), rotary encoding fused with the K/V page write, SiLU(gate) * up.
+// Every kernel is a template over the activation type (float for the 32-bit path, bf16 for the
+// serving path); arithmetic is fp32 in both.
+#include "common.cuh"
+
+namespace gf {
+
+// ----------------------------------------------------------------------------- embedding
+// out[t, :] = W[ids[t], :], copied in `unit`-byte words (16 when rows allow it).
+template <typename V>
+__global__ void embedding_kernel(const int* __restrict__ ids, const V* __restrict__ w,
+                                 V* __restrict__ out, int words_per_row) {
+  const int t = blockIdx.x;
+  const V* src = w + (size_t)ids[t] * words_per_row;
+  V* dst = out + (size_t)t * words_per_row;
+  for (int i = threadIdx.x; i < words_per_row; i += blockDim.x) dst[i] = src[i];
+}
+
+// ----------------------------------------------------------------------------- add + rmsnorm
+// s = x[src] (+ delta[src]) formed in fp32 and rounded once to T; normed = s * gamma / rms with
+// rms = sqrtf(sum(s^2) / H + eps).  `rows` (nullable) selects source rows.  One block per row; the
+// row is parked in shared memory as fp32 between the two passes.
+template <typename T, typename G>
+__global__ void add_rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ delta,
+                                   const G* __restrict__ gamma, const int* __restrict__ rows,
+                                   T* __restrict__ sum_out, T* __restrict__ normed, int H,
+                                   float eps) {
+  extern __shared__ float row[];
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const size_t src = (size_t)(rows ? rows[r] : r) * H;
+  const size_t dst = (size_t)r * H;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    float s = to_f32(x[src + j]);
+    if (delta) {
+      const T sv = from_f32<T>(s + to_f32(delta[src + j]));
+      s = to_f32(sv);
+      if (sum_out) sum_out[dst + j] = sv;
+    }
+    row[j] = s;
+    ss += s * s;
+  }
+  ss = block_sum(ss, scratch);
+  const float rms = sqrtf(ss / (float)H + eps);
+  for (int j = threadIdx.x; j < H; j += blockDim.x)
+    normed[dst + j] = from_f32<T>(row[j] * to_f32(gamma[j]) / rms);
+}
+
+// ----------------------------------------------------------------------------- rope + KV write
+// qkv[t] = [q heads | k heads | v heads], each head hd wide.  The first `rot` channels of every q
+// and k head are rotated in pairs (j, j + rot/2) by the angle of positions[t]; table row p holds
+// cos[0..rot/2) then sin[0..rot/2).  q is rotated in place.  If slot_mapping is given, rotated k
+// and plain v go to token slot slot_mapping[t] of the K and V pages (slot < 0: skipped).
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride,
+                                     const float* __restrict__ table, int rot,
+                                     const int* __restrict__ positions,
+                                     const int* __restrict__ slot_mapping, T* __restrict__ kpages,
+                                     T* __restrict__ vpages, int nh, int nkv, int hd) {
+  const int t = blockIdx.x;
+  T* rowp = qkv + (size_t)t * row_stride;
+  const int half = rot >> 1;
+  const int slot = slot_mapping ? slot_mapping[t] : -1;
+  T* kdst = slot >= 0 ? kpages + (size_t)slot * nkv * hd : nullptr;
+  T* vdst = slot >= 0 ? vpages + (size_t)slot * nkv * hd : nullptr;
+  const float* cs = table ? table + (size_t)positions[t] * rot : nullptr;
+  // rotated pairs of q and k heads
+  const int npairs = (nh + nkv) * half;
+  for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
+    const int head = i / half, j = i - head * half;
+    const float c = cs[j], s = cs[half + j];
+    T* h = rowp + (size_t)head * hd;
+    const float a = to_f32(h[j]), b = to_f32(h[j + half]);
+    const T lo = from_f32<T>(a * c - b * s), hi = from_f32<T>(a * s + b * c);
+    if (head < nh) {
+      h[j] = lo;
+      h[j + half] = hi;
+    } else if (kdst) {
+      T* kd = kdst + (size_t)(head - nh) * hd;
+      kd[j] = lo;
+      kd[j + half] = hi;
+    }
+  }
+  if (!kdst) return;
+  // channels of k beyond the rotated ones, and all of v
+  const int tail = hd - rot;
+  const int nk_tail = nkv * tail;
+  for (int i = threadIdx.x; i < nk_tail; i += blockDim.x) {
+    const int head = i / tail, j = rot + (i - head * tail);
+    kdst[(size_t)head * hd + j] = rowp[(size_t)(nh + head) * hd + j];
+  }
+  const T* vsrc = rowp + (size_t)(nh + nkv) * hd;
+  for (int i = threadIdx.x; i < nkv * hd; i += blockDim.x) vdst[i] = vsrc[i];
+}
+
+// ----------------------------------------------------------------------------- silu(gate) * up
+// gu[t] = [gate (I) | up (I)]; out[t, i] = gate * 1/(1+exp(-gate)) * up in fp32.
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I,
+                                size_t total) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / I, j = i - t * I;
+    const float g = to_f32(gu[t * 2 * I + j]), u = to_f32(gu[t * 2 * I + I + j]);
+    out[i] = from_f32<T>(g * (1.0f / (1.0f + expf(-g))) * u);
+  }
+}
+
+template <typename T, typename G>
+int launch_add_rmsnorm(const void* x, const void* delta, const void* gamma, const int* rows,
+                       void* sum_out, void* normed, int R, int H, float eps, cudaStream_t st) {
+  const size_t smem = (size_t)H * sizeof(float);
+  auto k = add_rmsnorm_kernel<T, G>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  k<<<R, threads, smem, st>>>((const T*)x, (const T*)delta, (const G*)gamma, rows, (T*)sum_out,
+                              (T*)normed, H, eps);
+  return launch_status();
+}
+
+}  // namespace gf
+
+using namespace gf;
+
+GF_EXPORT int gf_embedding(const int* ids, const void* w, void* out, int T, int H, int dtype,
+                           void* stream) {
+  if (T <= 0) return 0;
+  const size_t row_bytes = (size_t)H * (dtype == GF_F32 ? 4 : 2);
+  auto st = (cudaStream_t)stream;
+  const bool al16 = row_bytes % 16 == 0 && ((uintptr_t)w % 16 == 0) && ((uintptr_t)out % 16 == 0);
+  if (al16)
+    embedding_kernel<uint4><<<T, 128, 0, st>>>(ids, (const uint4*)w, (uint4*)out,
+                                               (int)(row_bytes / 16));
+  else if (dtype == GF_F32)
+    embedding_kernel<float><<<T, 128, 0, st>>>(ids, (const float*)w, (float*)out, H);
+  else
+    embedding_kernel<uint16_t><<<T, 128, 0, st>>>(ids, (const uint16_t*)w, (uint16_t*)out, H);
+  return launch_status();
+}
+
+GF_EXPORT int gf_add_rmsnorm(const void* x, const void* delta, const void* gamma, int gamma_dtype,
+                             float eps, const int* rows, void* sum_out, void* normed, int R, int H,
+                             int dtype, void* stream) {
+  if (R <= 0) return 0;
+  auto st = (cudaStream_t)stream;
+  if (dtype == GF_F32) {
+    if (gamma_dtype != GF_F32) return -2;
+    return launch_add_rmsnorm<float, float>(x, delta, gamma, rows, sum_out, normed, R, H, eps, st);
+  }
+  if (gamma_dtype == GF_F32)
+    return launch_add_rmsnorm<__nv_bfloat16, float>(x, delta, gamma, rows, sum_out, normed, R, H,
+                                                    eps, st);
+  return launch_add_rmsnorm<__nv_bfloat16, __nv_bfloat16>(x, delta, gamma, rows, sum_out, normed,
+                                                          R, H, eps, st);
+}
+
+GF_EXPORT int gf_rope_kv_write(void* qkv, int row_stride, const float* table, int rot,
+                               const int* positions, const int* slot_mapping, void* kpages,
+                               void* vpages, int T, int nh, int nkv, int hd, int dtype,
+                               void* stream) {
+  if (T <= 0) return 0;
+  auto st = (cudaStream_t)stream;
+  if (!table) rot = 0;
+  if (dtype == GF_F32)
+    rope_kv_write_kernel<float><<<T, 128, 0, st>>>((float*)qkv, row_stride, table, rot, positions,
+                                                   slot_mapping, (float*)kpages, (float*)vpages,
+                                                   nh, nkv, hd);
+  else
+    rope_kv_write_kernel<__nv_bfloat16><<<T, 128, 0, st>>>(
+        (__nv_bfloat16*)qkv, row_stride, table, rot, positions, slot_mapping,
+        (__nv_bfloat16*)kpages, (__nv_bfloat16*)vpages, nh, nkv, hd);
+  return launch_status();
+}
+
+GF_EXPORT int gf_silu_mul(const void* gu, void* out, int T, int I, int dtype, void* stream) {
+  const size_t total = (size_t)T * I;
+  if (total == 0) return 0;
+  auto st = (cudaStream_t)stream;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  if (dtype == GF_F32)
+    silu_mul_kernel<float><<<blocks, 256, 0, st>>>((const float*)gu, (float*)out, I, total);
+  else
+    silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)gu,
+                                                           (__nv_bfloat16*)out, I, total);
+  return launch_status();
+}

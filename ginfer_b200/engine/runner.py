@@ -1,0 +1,218 @@
+"""The step function: one batch of (request, its next tokens) through the model, from the cache.
+
+Reference: ``ginfer/engine/model_runner.cc``.  Its ``run(seqs, is_prefill)`` takes either whole
+prompts or single decode tokens, never both (``model_runner.cc:300-317``), builds ``input_ids``,
+``positions``, ``cu_seqlens``, ``slot_mapping`` and ``block_tables`` on the host and copies each
+separately (``:177-298``), and returns arg-max ids.  Here one step takes any mix of prompt
+portions and decode tokens, packs all per-step integers into one pinned buffer copied once, runs
+only the given tokens against what earlier steps left in the cache, and returns fp32 logits at the
+rows asked for.  Sampling is a separate stage.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from ..cache import CacheManager, CacheStorage, OutOfPages, plan_groups
+from ..parts.base import PagedKVBinding, StateBinding, StepContext
+from ..parts.model import DecoderModel
+
+
+@dataclass
+class StepEntry:
+    request_id: object
+    tokens: list[int]
+    want: list[int] = field(default_factory=list)    # indices into ``tokens``
+
+
+def _align4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, *, page_size: int, max_num_seqs: int,
+                 max_seq_len: int, num_pages: int | None = None,
+                 gpu_memory_utilization: float = 0.8, max_num_batched_tokens: int = 8192):
+        if model.device is None or model.device.type != "cuda":
+            raise RuntimeError("the model must be loaded on a CUDA device before a runner is made")
+        self.model = model
+        self.device = model.device
+        self.dtype = model.dtype
+        self.page_size = int(page_size)
+        self.max_seq_len = min(int(max_seq_len), model.plan.max_positions)
+        self.max_num_seqs = int(max_num_seqs)
+        self.max_num_batched_tokens = int(max_num_batched_tokens)
+        specs = model.cache_specs()
+        self.groups, self._group_of_cache = plan_groups(specs)
+        itemsize = torch.empty((), dtype=self.dtype).element_size()
+        if num_pages is None:
+            num_pages = self._pages_from_memory(gpu_memory_utilization, itemsize)
+        counts = [int(num_pages)] * len(self.groups)
+        self.cache = CacheManager([g.window for g in self.groups], counts, self.page_size,
+                                  self.max_num_seqs, self.max_seq_len)
+        self.storage = CacheStorage(specs, self.groups, counts, self.page_size,
+                                    self.max_num_seqs, self.dtype, self.device)
+        self.vocab_size = model.plan.vocab_size
+        self._host = None            # pinned staging for the step's integers
+        self._host_cap = 0
+        self._copied = torch.cuda.Event()     # the last copy out of the staging buffer
+        self._copy_pending = False
+        self.steps_run = 0
+
+    def _pages_from_memory(self, utilization: float, itemsize: int) -> int:
+        free, _total = torch.cuda.mem_get_info(self.device)
+        per_page = sum(g.bytes_per_page(self.page_size, itemsize) for g in self.groups) or 1
+        want = int(free * utilization) // per_page
+        # nobody needs more pages than every slot filled to max_seq_len
+        cap = self.max_num_seqs * (-(-self.max_seq_len // self.page_size))
+        return max(1, min(want, cap))
+
+    # ------------------------------------------------------------------ requests
+    def end(self, request_id) -> None:
+        """The request is finished: its pages and its slot are given back."""
+        if self.cache.has(request_id):
+            self.cache.release(request_id)
+
+    def preempt(self, request_id) -> None:
+        """Give the request's pages back but keep its slot; it will be computed again."""
+        self.cache.release(request_id, keep_slot=True)
+        self.storage.reset_slot(self.cache.get(request_id).slot)
+
+    # ------------------------------------------------------------------ the step
+    def _staging(self, n_ints: int) -> torch.Tensor:
+        if n_ints > self._host_cap:
+            self._host_cap = max(2 * n_ints, 4096)
+            self._host = torch.empty(self._host_cap, dtype=torch.int32, pin_memory=True)
+        return self._host
+
+    def prepare(self, entries: list[StepEntry]):
+        """Admit new requests, take pages, and lay out the step's integers on the host.
+        Returns ``(host_arrays, facts)``; nothing has touched the device yet."""
+        cache, P = self.cache, self.page_size
+        B = len(entries)
+        if B == 0:
+            raise ValueError("a step needs at least one entry")
+        if B > self.max_num_seqs:
+            raise ValueError(f"{B} entries in one step; max_num_seqs is {self.max_num_seqs}")
+        ids = [e.request_id for e in entries]
+        if len(set(ids)) != B:
+            raise ValueError("a request appears twice in one step")
+        q_lens = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=B)
+        if (q_lens <= 0).any():
+            raise ValueError("an entry brings no tokens")
+        T = int(q_lens.sum())
+        # pages: check the whole step before taking any
+        need = [0] * cache.num_groups
+        new = []
+        for e, n in zip(entries, q_lens):
+            if not cache.has(e.request_id):
+                new.append(e.request_id)
+            have = cache.get(e.request_id).num_tokens if cache.has(e.request_id) else 0
+            if have + int(n) > self.max_seq_len:
+                raise ValueError(f"request {e.request_id!r} would reach {have + int(n)} tokens; "
+                                 f"the limit is {self.max_seq_len}")
+            for g, k in enumerate(cache.pages_needed(e.request_id, int(n))):
+                need[g] += k
+        if len(new) > cache.slots.num_free:
+            raise RuntimeError(f"{len(new)} new requests but {cache.slots.num_free} free slots")
+        for g, (k, f) in enumerate(zip(need, cache.free_pages())):
+            if k > f:
+                raise OutOfPages(f"the step needs {k} pages of group {g}; {f} are free")
+        for rid in new:
+            rc = cache.admit(rid)
+            self.storage.reset_slot(rc.slot)
+        rcs = [cache.get(e.request_id) for e in entries]
+        q_starts = np.fromiter((rc.num_tokens for rc in rcs), dtype=np.int64, count=B)
+        for e, n in zip(entries, q_lens):
+            cache.reserve(e.request_id, int(n))
+
+        tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64).reshape(-1)
+                                 for e in entries])
+        if tokens.min() < 0 or tokens.max() >= self.vocab_size:
+            raise ValueError(f"token ids must lie in [0, {self.vocab_size})")
+        cu = np.zeros(B + 1, dtype=np.int64)
+        np.cumsum(q_lens, out=cu[1:])
+        seq_of_token = np.repeat(np.arange(B), q_lens)
+        positions = np.arange(T) - np.repeat(cu[:-1] - q_starts, q_lens)
+        kv_lens = q_starts + q_lens
+        slot_ids = np.fromiter((rc.slot for rc in rcs), dtype=np.int64, count=B)
+        rows = []
+        for b, e in enumerate(entries):
+            for w in e.want:
+                if not (0 <= int(w) < q_lens[b]):
+                    raise ValueError(f"request {e.request_id!r} wants logits at place {w} of "
+                                     f"{q_lens[b]} tokens")
+                rows.append(cu[b] + int(w))
+        logit_rows = np.asarray(rows, dtype=np.int64)
+        width = int(-(-int(kv_lens.max()) // P))
+        slots_of_token = slot_ids[seq_of_token]
+        slot_maps = [cache.slot_mapping(g, slots_of_token, positions)
+                     for g in range(cache.num_groups)]
+        tables = [cache.block_table(g, slot_ids, width) for g in range(cache.num_groups)]
+        arrays = dict(token_ids=tokens, positions=positions, seq_of_token=seq_of_token,
+                      cu_seqlens_q=cu, kv_lens=kv_lens, slot_ids=slot_ids, logit_rows=logit_rows)
+        for g in range(cache.num_groups):
+            arrays[f"slot_mapping{g}"] = slot_maps[g]
+            arrays[f"block_table{g}"] = tables[g]
+        facts = dict(T=T, B=B, q_lens=q_lens, q_starts=q_starts, slot_ids=slot_ids, width=width,
+                     max_q_len=int(q_lens.max()), max_kv_len=int(kv_lens.max()))
+        return arrays, facts
+
+    def upload(self, arrays: dict[str, np.ndarray]) -> dict[str, torch.Tensor]:
+        """One pinned buffer, one host-to-device copy; returns device views by name."""
+        total = sum(_align4(a.size) for a in arrays.values())
+        if self._copy_pending:                # do not overwrite what the last copy still reads
+            self._copied.synchronize()
+        host = self._staging(total)
+        hnp = host.numpy()
+        off, spans = 0, {}
+        for k, a in arrays.items():
+            n = a.size
+            hnp[off:off + n] = a.reshape(-1)
+            spans[k] = (off, n, a.shape)
+            off += _align4(n)
+        dev = host[:total].to(self.device, non_blocking=True)
+        self._copied.record()
+        self._copy_pending = True
+        return {k: dev[o:o + n].view(shape) for k, (o, n, shape) in spans.items()}
+
+    def make_context(self, dev: dict[str, torch.Tensor], facts: dict) -> StepContext:
+        return StepContext(
+            num_tokens=facts["T"], num_seqs=facts["B"], dtype=self.dtype, device=self.device,
+            token_ids=dev["token_ids"], positions=dev["positions"],
+            seq_of_token=dev["seq_of_token"], cu_seqlens_q=dev["cu_seqlens_q"],
+            kv_lens=dev["kv_lens"], slot_ids=dev["slot_ids"], logit_rows=dev["logit_rows"],
+            q_lens_host=[int(x) for x in facts["q_lens"]],
+            q_starts_host=[int(x) for x in facts["q_starts"]],
+            slot_ids_host=[int(x) for x in facts["slot_ids"]],
+            max_q_len=facts["max_q_len"], max_kv_len=facts["max_kv_len"],
+            decode_only=facts["max_q_len"] == 1)
+
+    def binder(self, dev: dict[str, torch.Tensor]):
+        def bind(entry):
+            cid = entry.cache
+            if self.storage.is_paged(cid):
+                g = self.storage.group_of(cid)
+                return PagedKVBinding(self.storage.pages_of(cid), dev[f"block_table{g}"],
+                                      dev[f"slot_mapping{g}"], self.page_size,
+                                      self.groups[g].window, entry.write_cache)
+            if cid in self.storage.state:
+                return StateBinding(self.storage.state[cid], entry.write_cache)
+            return None
+        return bind
+
+    @torch.no_grad()
+    def step(self, entries: list[StepEntry]) -> torch.Tensor:
+        """Run the entries' tokens as one batch; returns fp32 logits ``[wanted, vocab]`` on the
+        device, in the order of the entries and of each entry's ``want``."""
+        arrays, facts = self.prepare(entries)
+        with torch.cuda.device(self.device):
+            dev = self.upload(arrays)
+            ctx = self.make_context(dev, facts)
+            logits = self.model.forward(ctx, self.binder(dev))
+        for e, n in zip(entries, facts["q_lens"]):
+            self.cache.commit(e.request_id, int(n))
+        self.steps_run += 1
+        return logits

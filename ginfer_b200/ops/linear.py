@@ -1,0 +1,84 @@
+"""Matrix products ``y = x W^T (+ b)`` with ``W [out, in]`` as Hugging Face stores it (the
+reference reads the same memory as a column-major ``[in, out]`` view:
+``ginfer/core/layer/linear.cc:13-16``).
+
+float32: the hand-written FMA kernel of ``csrc/gemm_f32.cu`` (no reduced-precision mode).
+bfloat16: the tcgen05 kernel of ``csrc/gemm_bf16.cu`` where it takes the shape, else cuBLAS
+through ``torch`` (fp32 accumulation), which is what the reference uses for every product.
+"""
+from __future__ import annotations
+
+from ctypes import c_int, c_void_p
+
+import torch
+
+from . import _cuda, _fn, _ok, _p, _stream, silu_mul
+
+
+def gemm_f32(x: torch.Tensor, w: torch.Tensor, bias=None) -> torch.Tensor:
+    _cuda(x, w, bias)
+    assert x.dtype == torch.float32 and w.dtype == torch.float32
+    assert x.dim() == 2 and w.dim() == 2 and x.stride(1) == 1 and w.is_contiguous()
+    M, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == N
+    out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    f = _fn("gemm_f32", "gf_gemm_f32",
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _ok(f(_p(x), x.stride(0), _p(w), _p(bias), _p(out), N, M, N, K, _stream()), "gemm_f32")
+    return out
+
+
+class Linear:
+    """``y = x W^T + b``.  ``out_dtype`` float32 asks for fp32 results from bf16 operands (the
+    output head)."""
+
+    def __init__(self, weight: torch.Tensor, bias: torch.Tensor | None = None,
+                 out_dtype: torch.dtype | None = None):
+        _cuda(weight, bias)
+        self.weight = weight.contiguous()
+        self.bias = bias
+        self.out_features, self.in_features = weight.shape
+        self.dtype = weight.dtype
+        self.out_dtype = out_dtype or weight.dtype
+        if self.dtype == torch.float32:
+            if bias is not None:
+                self.bias = bias.float().contiguous()
+        elif self.dtype == torch.bfloat16:
+            # cuBLAS adds the bias in its fp32 epilogue; it wants the operands' dtype
+            self._bias_lib = None if bias is None else bias.to(torch.bfloat16).contiguous()
+            self._bias_f32 = None if bias is None else bias.float().contiguous()
+        else:
+            raise TypeError(f"Linear takes float32 or bfloat16 weights, not {self.dtype}")
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        if x.dtype != self.dtype:
+            raise TypeError(f"Linear holds {self.dtype} weights but got {x.dtype} input")
+        if self.dtype == torch.float32:
+            return gemm_f32(x, self.weight, self.bias)
+        from . import gemm_bf16
+        y = gemm_bf16.try_linear(x, self.weight, self._bias_f32, self.out_dtype)
+        if y is not None:
+            return y
+        if self.out_dtype == torch.float32:
+            y = torch.mm(x, self.weight.t(), out_dtype=torch.float32)
+            if self._bias_f32 is not None:
+                y += self._bias_f32
+            return y
+        if self._bias_lib is not None:
+            return torch.addmm(self._bias_lib, x, self.weight.t())
+        return torch.mm(x, self.weight.t())
+
+
+class GatedLinear:
+    """``silu(x W_g^T) * (x W_u^T)`` over joined weights, so ``x`` is read once."""
+
+    def __init__(self, gate: torch.Tensor, up: torch.Tensor):
+        assert gate.shape == up.shape and gate.dtype == up.dtype
+        self.intermediate = gate.shape[0]
+        self.proj = Linear(torch.cat([gate, up], dim=0))
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        return silu_mul(self.proj(x))

@@ -1,0 +1,71 @@
+"""Replay of the same requests under every way of cutting them into steps, in 32-bit and in
+bfloat16, against the plain implementation."""
+import os
+
+import pytest
+import torch
+
+import replay
+from tiny import CONFIGS, make_folder, prompt
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": [5, 17, 33, 70, 130, 49], "B": [1, 40, 90, 200, 66, 133], "C": [3, 64, 97, 35]}
+PAGE = {"A": 16, "B": 8, "C": 4}
+
+
+def _requests(name):
+    v = CONFIGS[name]["vocab_size"]
+    return {f"r{i}": prompt(n, v, seed=100 * i + n) for i, n in enumerate(LENGTHS[name])}
+
+
+def _storage(dtype):
+    return "bfloat16" if dtype == "bfloat16" else "float32"
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("models")
+    return {(n, s): make_folder(root, n, seed=1, storage=s)
+            for n in CONFIGS for s in ("float32", "bfloat16")}
+
+
+def _runner(model_dir, dtype, page, max_tokens):
+    from ginfer_b200.engine import ModelRunner
+    from ginfer_b200.engine.loading import load_model
+    model, _ = load_model(model_dir, dtype)
+    budget = -(-max_tokens // 64) * 64
+    return ModelRunner(model, page_size=page, max_num_seqs=4, max_seq_len=budget,
+                       num_pages=budget // page, max_num_batched_tokens=budget)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("cut", ["whole", "tail", "portions", "mixed"])
+def test_cuts_agree_with_plain(folders, name, dtype, cut):
+    model_dir = folders[(name, _storage(dtype))]
+    reqs = _requests(name)
+    if cut == "whole":
+        steps = replay.cut_whole(reqs)
+    elif cut == "tail":
+        steps = replay.cut_tail_decode(reqs)
+    elif cut == "portions":
+        steps = replay.cut_portions(reqs)
+    else:
+        steps, _ = replay.cut_mixed(reqs, seed=7)
+    max_tokens = replay.peak_tokens(steps)          # so few pages that they are used again
+    runner = _runner(model_dir, dtype, PAGE[name], max_tokens)
+    rows = replay.run_in_process(runner, steps)
+    replay.compare(rows, replay.plain_logits(model_dir, reqs), dtype, reqs)
+    assert not runner.cache.requests and all(
+        f == p.num_pages for f, p in zip(runner.cache.free_pages(), runner.cache.pools))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_program_mixed(folders, tmp_path, dtype):
+    """The same through ``bin/trace_run`` (page size 16, pool sized by --max-tokens)."""
+    model_dir = folders[("B", _storage(dtype))]
+    reqs = _requests("B")
+    steps, peak = replay.cut_mixed(reqs, seed=3)
+    rows = replay.run_trace_program(model_dir, dtype, steps, peak, str(tmp_path / "out"))
+    replay.compare(rows, replay.plain_logits(model_dir, reqs), dtype, reqs)

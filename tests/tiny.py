@@ -1,0 +1,77 @@
+"""Two tiny Qwen2 configurations that differ in every size and option, and helpers that make
+model folders for them in a temporary place."""
+from __future__ import annotations
+
+import json
+import os
+
+import torch
+
+TINY_A = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 2, "hidden_size": 64, "num_attention_heads": 4,
+    "num_key_value_heads": 2, "head_dim": 16, "intermediate_size": 128, "vocab_size": 256,
+    "rope_theta": 10000.0, "rms_norm_eps": 1e-6, "max_position_embeddings": 512,
+    "tie_word_embeddings": True, "use_sliding_window": False, "torch_dtype": "float32",
+    "eos_token_id": 255,
+}
+
+# every size and option differs from A; sizes are no powers of two
+TINY_B = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 3, "hidden_size": 96, "num_attention_heads": 3,
+    "num_key_value_heads": 1, "head_dim": 32, "intermediate_size": 224, "vocab_size": 389,
+    "rope_theta": 1000000.0, "rms_norm_eps": 1e-5, "max_position_embeddings": 640,
+    "tie_word_embeddings": False, "use_sliding_window": True, "sliding_window": 48,
+    "max_window_layers": 1, "torch_dtype": "float32", "eos_token_id": [7, 11],
+}
+
+# a third one with a head size of 48 (a step of 16 that is no power of two) and 5 heads in 5 groups
+TINY_C = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 2, "hidden_size": 80, "num_attention_heads": 5,
+    "num_key_value_heads": 5, "head_dim": 48, "intermediate_size": 176, "vocab_size": 301,
+    "rope_theta": 50000.0, "rms_norm_eps": 3e-6, "max_position_embeddings": 384,
+    "tie_word_embeddings": False, "use_sliding_window": True, "sliding_window": 33,
+    "max_window_layers": 0, "torch_dtype": "float32", "eos_token_id": 300,
+}
+
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+
+
+def sharpen(model_dir: str, q_scale: float = 12.0) -> None:
+    """Scale the q and k projections so that attention scores spread over several units: softmax
+    becomes peaked and a wrong mask, a missing key or a misplaced page changes the logits
+    visibly.  Rewritten with the ``safetensors`` package (not with the framework's writer)."""
+    from safetensors import safe_open
+    from safetensors.torch import save_file
+    path = os.path.join(model_dir, "model.safetensors")
+    tensors = {}
+    with safe_open(path, framework="pt") as f:
+        for k in f.keys():
+            t = f.get_tensor(k)
+            if k.endswith(("q_proj.weight", "k_proj.weight", "q_proj.bias", "k_proj.bias")):
+                t = (t.float() * q_scale).to(t.dtype)
+            tensors[k] = t.contiguous()
+    save_file(tensors, path)
+
+
+def make_folder(tmp_path, name: str, seed: int = 0, storage: str = "float32",
+                sharp: bool = True) -> str:
+    from ginfer_b200.weights import write_random_model
+    d = os.path.join(str(tmp_path), f"tiny_{name}_{storage}_{seed}")
+    if not os.path.exists(os.path.join(d, "model.safetensors")):
+        write_random_model(d, dict(CONFIGS[name]), seed, storage_dtype=storage)
+        if sharp:
+            sharpen(d)
+    return d
+
+
+def read_config(model_dir: str) -> dict:
+    with open(os.path.join(model_dir, "config.json")) as f:
+        return json.load(f)
+
+
+def prompt(n: int, vocab: int, seed: int) -> list[int]:
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()
