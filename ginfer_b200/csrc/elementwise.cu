@@ -18,13 +18,14 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const V* __restric
 }
 
 // ----------------------------------------------------------------------------- add + rmsnorm
-// s = x[src] (+ delta[src]) formed in fp32 and rounded once to T; normed = s * gamma / rms with
-// rms = sqrtf(sum(s^2) / H + eps).  `rows` (nullable) selects source rows.  One block per row; the
-// row is parked in shared memory as fp32 between the two passes.
-template <typename T, typename G>
-__global__ void add_rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ delta,
+// s = x[src] (+ delta[src]) formed and kept in fp32 (the residual stream is fp32 in both paths: x
+// is the activation type only for the embedding's output); normed = s * gamma / rms with
+// rms = sqrtf(sum(s^2) / H + eps), stored in the activation type.  `rows` (nullable) selects source
+// rows.  One block per row; the row is parked in shared memory between the two passes.
+template <typename XT, typename T, typename G>
+__global__ void add_rmsnorm_kernel(const XT* __restrict__ x, const T* __restrict__ delta,
                                    const G* __restrict__ gamma, const int* __restrict__ rows,
-                                   T* __restrict__ sum_out, T* __restrict__ normed, int H,
+                                   float* __restrict__ sum_out, T* __restrict__ normed, int H,
                                    float eps) {
   extern __shared__ float row[];
   __shared__ float scratch[33];
@@ -34,11 +35,8 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, const T* __restrict_
   float ss = 0.f;
   for (int j = threadIdx.x; j < H; j += blockDim.x) {
     float s = to_f32(x[src + j]);
-    if (delta) {
-      const T sv = from_f32<T>(s + to_f32(delta[src + j]));
-      s = to_f32(sv);
-      if (sum_out) sum_out[dst + j] = sv;
-    }
+    if (delta) s += to_f32(delta[src + j]);
+    if (sum_out) sum_out[dst + j] = s;
     row[j] = s;
     ss += s * s;
   }
@@ -108,18 +106,18 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
   }
 }
 
-template <typename T, typename G>
+template <typename XT, typename T, typename G>
 int launch_add_rmsnorm(const void* x, const void* delta, const void* gamma, const int* rows,
                        void* sum_out, void* normed, int R, int H, float eps, cudaStream_t st) {
   const size_t smem = (size_t)H * sizeof(float);
-  auto k = add_rmsnorm_kernel<T, G>;
+  auto k = add_rmsnorm_kernel<XT, T, G>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-  k<<<R, threads, smem, st>>>((const T*)x, (const T*)delta, (const G*)gamma, rows, (T*)sum_out,
-                              (T*)normed, H, eps);
+  k<<<R, threads, smem, st>>>((const XT*)x, (const T*)delta, (const G*)gamma, rows,
+                              (float*)sum_out, (T*)normed, H, eps);
   return launch_status();
 }
 
@@ -143,20 +141,27 @@ GF_EXPORT int gf_embedding(const int* ids, const void* w, void* out, int T, int 
   return launch_status();
 }
 
-GF_EXPORT int gf_add_rmsnorm(const void* x, const void* delta, const void* gamma, int gamma_dtype,
-                             float eps, const int* rows, void* sum_out, void* normed, int R, int H,
-                             int dtype, void* stream) {
+// x_dtype: type of x (fp32 residual stream, or the activation type); dtype: activation type of
+// delta and normed; sum_out (nullable) is fp32.
+GF_EXPORT int gf_add_rmsnorm(const void* x, int x_dtype, const void* delta, const void* gamma,
+                             int gamma_dtype, float eps, const int* rows, void* sum_out,
+                             void* normed, int R, int H, int dtype, void* stream) {
   if (R <= 0) return 0;
   auto st = (cudaStream_t)stream;
+  using bf = __nv_bfloat16;
+#define GF_GO(XT, T, G) \
+  return launch_add_rmsnorm<XT, T, G>(x, delta, gamma, rows, sum_out, normed, R, H, eps, st)
   if (dtype == GF_F32) {
-    if (gamma_dtype != GF_F32) return -2;
-    return launch_add_rmsnorm<float, float>(x, delta, gamma, rows, sum_out, normed, R, H, eps, st);
+    if (gamma_dtype != GF_F32 || x_dtype != GF_F32) return -2;
+    GF_GO(float, float, float);
   }
-  if (gamma_dtype == GF_F32)
-    return launch_add_rmsnorm<__nv_bfloat16, float>(x, delta, gamma, rows, sum_out, normed, R, H,
-                                                    eps, st);
-  return launch_add_rmsnorm<__nv_bfloat16, __nv_bfloat16>(x, delta, gamma, rows, sum_out, normed,
-                                                          R, H, eps, st);
+  if (x_dtype == GF_F32) {
+    if (gamma_dtype == GF_F32) GF_GO(float, bf, float);
+    GF_GO(float, bf, bf);
+  }
+  if (gamma_dtype == GF_F32) GF_GO(bf, bf, float);
+  GF_GO(bf, bf, bf);
+#undef GF_GO
 }
 
 GF_EXPORT int gf_rope_kv_write(void* qkv, int row_stride, const float* table, int rot,

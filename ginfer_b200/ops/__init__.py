@@ -75,18 +75,21 @@ def embedding(token_ids: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
 # ----------------------------------------------------------------------------- add + rmsnorm
 def add_rmsnorm(x: torch.Tensor, delta, gamma: torch.Tensor, eps: float, rows=None,
                 want_sum: bool = True):
-    """``s = x + delta`` (fp32 sum, rounded once); returns ``(s or None, s * gamma / rms(s))``.
-    Without ``delta`` and ``rows`` the returned ``s`` is ``x`` itself."""
+    """``s = x + delta`` in fp32; returns ``(s or None, s * gamma / rms(s))``.  ``x`` is the fp32
+    residual stream or an activation; ``delta`` and the normed output have the activation dtype
+    (that of ``delta``, else of ``x``).  Without ``delta`` and ``rows`` the returned ``s`` is
+    ``x`` itself."""
     _cuda(x, delta, gamma, rows)
     assert x.dim() == 2 and x.is_contiguous()
     H = x.shape[1]
+    act = x.dtype if delta is None else delta.dtype
     if delta is not None:
-        assert delta.shape == x.shape and delta.dtype == x.dtype and delta.is_contiguous()
+        assert delta.shape == x.shape and delta.is_contiguous()
     assert gamma.numel() == H and gamma.is_contiguous()
     R = x.shape[0] if rows is None else rows.numel()
     if rows is not None:
         assert rows.dtype == torch.int32 and rows.is_contiguous()
-    normed = torch.empty((R, H), dtype=x.dtype, device=x.device)
+    normed = torch.empty((R, H), dtype=act, device=x.device)
     s = None
     if want_sum:
         if delta is None and rows is None:
@@ -94,13 +97,13 @@ def add_rmsnorm(x: torch.Tensor, delta, gamma: torch.Tensor, eps: float, rows=No
         elif delta is None:
             s = x.index_select(0, rows.long())
         else:
-            s = torch.empty((R, H), dtype=x.dtype, device=x.device)
+            s = torch.empty((R, H), dtype=torch.float32, device=x.device)
     f = _fn("elementwise", "gf_add_rmsnorm",
-            [c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int,
-             c_int, c_int, c_void_p])
+            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p,
+             c_int, c_int, c_int, c_void_p])
     sum_ptr = _p(s) if (want_sum and delta is not None) else None
-    _ok(f(_p(x), _p(delta), _p(gamma), _code(gamma.dtype), float(eps), _p(rows), sum_ptr,
-          _p(normed), R, H, _code(x.dtype), _stream()), "add_rmsnorm")
+    _ok(f(_p(x), _code(x.dtype), _p(delta), _p(gamma), _code(gamma.dtype), float(eps), _p(rows),
+          sum_ptr, _p(normed), R, H, _code(act), _stream()), "add_rmsnorm")
     return s, normed
 
 

@@ -24,6 +24,24 @@ import numpy as np
 import torch
 
 
+# ----------------------------------------------------------------------------- stored precision
+class Stored:
+    """Which precision activations are *stored* in between parts.  The default stores nothing
+    rounded (pure float64).  ``Stored.bf16()`` rounds to bfloat16 wherever the bfloat16 serving
+    path of an engine writes an activation to memory: after a norm, a projection, the rotary
+    encoding, the attention output and the gated product.  The residual sum stays unrounded (it is
+    kept in 32-bit).  Arithmetic stays float64 either way."""
+    round = staticmethod(lambda t: t)
+
+    @classmethod
+    def bf16(cls):
+        cls.round = staticmethod(lambda t: t.to(torch.bfloat16).to(t.dtype))
+
+    @classmethod
+    def exact(cls):
+        cls.round = staticmethod(lambda t: t)
+
+
 # ----------------------------------------------------------------------------- reading a folder
 def read_model_folder(model_dir: str, dtype=torch.float64):
     """``(config dict, {tensor name: tensor as dtype})`` using the ``safetensors`` package."""
@@ -62,13 +80,13 @@ def rms_norm(x: torch.Tensor, gamma: torch.Tensor, eps: float) -> torch.Tensor:
     # ss = sum x^2; rms = sqrt(ss / H + eps); out = x * gamma / rms
     ss = (x * x).sum(dim=-1, keepdim=True)
     rms = torch.sqrt(ss / x.shape[-1] + eps)
-    return x * gamma / rms
+    return Stored.round(x * gamma / rms)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None = None) -> torch.Tensor:
     # ginfer/core/layer/linear.cc:13-35: y = x W^T (+ b), W stored [out, in]
     y = x @ w.t()
-    return y if b is None else y + b
+    return Stored.round(y if b is None else y + b)
 
 
 def rotary_cos_sin(positions: torch.Tensor, head_dim: int, theta: float):
@@ -89,7 +107,7 @@ def apply_rotary(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch
     half = x.shape[-1] // 2
     a, b = x[..., :half], x[..., half:]
     c, s = cos[:, None, :].to(x.dtype), sin[:, None, :].to(x.dtype)
-    return torch.cat([a * c - b * s, a * s + b * c], dim=-1)
+    return Stored.round(torch.cat([a * c - b * s, a * s + b * c], dim=-1))
 
 
 def visibility(num_tokens: int, window: int) -> torch.Tensor:
@@ -121,14 +139,14 @@ def gqa_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int
         s = s.masked_fill(~ok, float("-inf"))
         p = torch.softmax(s, dim=-1)
         out[:, n, :] = p @ v[:, kv, :]
-    return out
+    return Stored.round(out)
 
 
 def swiglu(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor):
     # ginfer/core/layer/transformer/feedforward.cc:22-25 and
     # ginfer/core/op/kernels/cuda/swiglu_kernel.cu:24-27: z = g * 1/(1+exp(-g)) * u; m = z W_d^T
     g, u = linear(x, w_gate), linear(x, w_up)
-    z = g * (1.0 / (1.0 + torch.exp(-g))) * u
+    z = Stored.round(g * (1.0 / (1.0 + torch.exp(-g))) * u)
     return linear(z, w_down)
 
 
@@ -183,7 +201,7 @@ def forward(w: dict, cfg: dict, token_ids, run=None) -> torch.Tensor:
     x = rms_norm(h, w["model.norm.weight"], float(cfg.get("rms_norm_eps", 1e-6)))
     head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) \
         else w["lm_head.weight"]
-    return linear(x, head)
+    return x @ head.t()            # logits are not stored in reduced precision
 
 
 # ----------------------------------------------------------------------------- choosing tokens

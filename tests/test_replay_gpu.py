@@ -56,7 +56,7 @@ def test_cuts_agree_with_plain(folders, name, dtype, cut):
     max_tokens = replay.peak_tokens(steps)          # so few pages that they are used again
     runner = _runner(model_dir, dtype, PAGE[name], max_tokens)
     rows = replay.run_in_process(runner, steps)
-    replay.compare(rows, replay.plain_logits(model_dir, reqs), dtype, reqs)
+    replay.compare(rows, replay.plain_logits(model_dir, reqs, dtype), dtype, reqs)
     assert not runner.cache.requests and all(
         f == p.num_pages for f, p in zip(runner.cache.free_pages(), runner.cache.pools))
 
@@ -68,4 +68,4 @@ def test_trace_program_mixed(folders, tmp_path, dtype):
     reqs = _requests("B")
     steps, peak = replay.cut_mixed(reqs, seed=3)
     rows = replay.run_trace_program(model_dir, dtype, steps, peak, str(tmp_path / "out"))
-    replay.compare(rows, replay.plain_logits(model_dir, reqs), dtype, reqs)
+    replay.compare(rows, replay.plain_logits(model_dir, reqs, dtype), dtype, reqs)
