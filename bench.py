@@ -1,0 +1,319 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B]
+
+The default run has the layer sizes of the Qwen2-1.5B shape (28 layers, hidden 1536, 12 heads,
+2 kv heads, head size 128, intermediate 8960, vocabulary 151936, untied head, q/k/v bias) with
+random bf16 weights, a batch of 8 requests with 512-token prompts, cache pages of 16 tokens and a
+context limit of 4096.  A "step" is one decode step of the whole batch.
+
+It prints ONE JSON line.  ``value``: decoded tokens a second, timed on the device with CUDA events
+around K steps of the engine's step function plus arg-max.  ``e2e``: the same through
+``Engine.step`` (scheduler, pinned host-to-device copy of the step's integers, sampling, read-back
+of the sampled ids), timed with the wall clock around synchronised steps.  ``prefill``: one
+2,048-token prompt in one step.  ``roofline``: the bytes a decode step has to read (every weight
+once, and the cache of the live requests) over its time, against the measured copy bandwidth.
+``points``: decoding at batch 1 and 64.
+
+Only one GPU is used; ``--gpus N`` with N > 1 prints a line that says so and exits with 2.
+``--impl reference`` reports why the reference cannot run here.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+QWEN2_1P5B = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 28, "hidden_size": 1536, "num_attention_heads": 12,
+    "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 8960, "vocab_size": 151936,
+    "rope_theta": 10000.0, "rms_norm_eps": 1e-6, "max_position_embeddings": 4096,
+    "tie_word_embeddings": False, "sliding_window": 4096, "use_sliding_window": False,
+    "torch_dtype": "bfloat16",
+}
+CONTEXT = 4096
+PROMPT = 512
+PREFILL_TOKENS = 2048
+PAGE = 16
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        out = dict(FALLBACK_PEAKS)
+        for k in out:
+            if isinstance(d.get(k), (int, float)):
+                out[k] = float(d[k])
+        return out, "measured"
+    except (OSError, ValueError):
+        return dict(FALLBACK_PEAKS), "fallback"
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0):
+        self.rows: list[list[str]] = []
+        self.proc = None
+        self.index = index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6:
+                self.rows.append(parts)
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks = sorted(int(r[0]) for r in self.rows if r[0].isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names)
+                   if any(r[2 + i].lower().startswith("active") for r in self.rows)]
+        mx = [int(r[1]) for r in self.rows if r[1].isdigit()]
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(self.rows)}
+
+
+# ----------------------------------------------------------------------------- sizes
+def linear_params_per_layer(c) -> int:
+    h, nh, nkv, hd, i = (c["hidden_size"], c["num_attention_heads"], c["num_key_value_heads"],
+                         c["head_dim"], c["intermediate_size"])
+    return (nh + 2 * nkv) * hd * h + h * nh * hd + 3 * i * h
+
+
+def weight_bytes(c, layers: int, itemsize: int = 2) -> int:
+    h, nh, nkv, hd = c["hidden_size"], c["num_attention_heads"], c["num_key_value_heads"], \
+        c["head_dim"]
+    per_layer = linear_params_per_layer(c) + (nh + 2 * nkv) * hd + 2 * h
+    head = c["vocab_size"] * h                      # the output head; the embedding is gathered
+    return (layers * per_layer + h + head) * itemsize
+
+
+def kv_bytes_per_token(c, layers: int, itemsize: int = 2) -> int:
+    return layers * 2 * c["num_key_value_heads"] * c["head_dim"] * itemsize
+
+
+def prefill_flops(c, layers: int, T: int, wanted_rows: int = 1) -> float:
+    lin = 2.0 * T * layers * linear_params_per_layer(c)
+    attn = layers * 4.0 * c["num_attention_heads"] * c["head_dim"] * (T * (T + 1) / 2)
+    head = 2.0 * wanted_rows * c["vocab_size"] * c["hidden_size"]
+    return lin + attn + head
+
+
+# ----------------------------------------------------------------------------- timed pieces
+def decode_device_timed(eng, batch: int, steps: int, warmup: int, seed: int):
+    """Prefill ``batch`` prompts of PROMPT tokens, then time ``steps`` decode steps (step function
+    plus arg-max) with CUDA events.  Returns (ms per step, launches in the timed region)."""
+    import torch
+
+    from ginfer_b200 import ops
+    from ginfer_b200.engine import StepEntry
+    runner = eng.runner
+    g = torch.Generator().manual_seed(seed)
+    V = runner.vocab_size
+    ids = [f"bench-{seed}-{b}" for b in range(batch)]
+    prompts = torch.randint(0, V, (batch, PROMPT), generator=g).tolist()
+    feed = torch.randint(0, V, (warmup + steps, batch), generator=g).tolist()
+    budget = eng.cfg.max_num_batched_tokens
+    per_step = max(1, budget // PROMPT)
+    for i in range(0, batch, per_step):
+        runner.step([StepEntry(ids[b], prompts[b], []) for b in range(i, min(batch, i + per_step))])
+    for s in range(warmup):
+        ops.argmax(runner.step([StepEntry(ids[b], [feed[s][b]], [0]) for b in range(batch)]))
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    l0 = ops.launch_count() + runner.graph_launches
+    start.record()
+    for s in range(warmup, warmup + steps):
+        ops.argmax(runner.step([StepEntry(ids[b], [feed[s][b]], [0]) for b in range(batch)]))
+    stop.record()
+    torch.cuda.synchronize()
+    launches = ops.launch_count() + runner.graph_launches - l0
+    ms = start.elapsed_time(stop) / steps
+    for rid in ids:
+        runner.end(rid)
+    return ms, launches
+
+
+def decode_end_to_end(eng, batch: int, steps: int, warmup: int, seed: int):
+    """The same through the public entry point: requests are added with host token ids,
+    ``Engine.step`` schedules, copies the step's integers from pinned memory, runs, samples and
+    reads the ids back.  Returns (ms per step, h2d bytes per step, d2h bytes per step)."""
+    import torch
+
+    from ginfer_b200.sampling import SamplingParams
+    g = torch.Generator().manual_seed(seed)
+    prompts = torch.randint(0, eng.runner.vocab_size, (batch, PROMPT), generator=g).tolist()
+    sp = SamplingParams(max_tokens=warmup + steps + 1, ignore_eos=True)
+    for p in prompts:
+        eng.add_request(p, sp)
+    while any(len(r.output) == 0 for r in eng.requests.values()):
+        eng.step()                                   # prompts
+    for _ in range(warmup):
+        eng.step()
+    torch.cuda.synchronize()
+    h0 = eng.runner.h2d_bytes
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        eng.step()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    h2d = (eng.runner.h2d_bytes - h0) / steps
+    while not eng.scheduler.is_finished():
+        eng.step()
+    eng.requests.clear()
+    return 1e3 * dt / steps, int(h2d), 4 * batch
+
+
+def prefill_timed(eng, tokens: int, reps: int, warmup: int, seed: int):
+    import torch
+
+    from ginfer_b200.engine import StepEntry
+    runner = eng.runner
+    g = torch.Generator().manual_seed(seed)
+    prompt = torch.randint(0, runner.vocab_size, (tokens,), generator=g).tolist()
+    times = []
+    for r in range(warmup + reps):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        runner.step([StepEntry("prefill", prompt, [tokens - 1])])
+        stop.record()
+        torch.cuda.synchronize()
+        runner.end("prefill")
+        if r >= warmup:
+            times.append(start.elapsed_time(stop))
+    times.sort()
+    return times[len(times) // 2]
+
+
+# ----------------------------------------------------------------------------- main
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=None,
+                    help="run fewer layers than the configuration has (both numbers are reported)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--enforce-eager", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "11Aln0/ginfer is a CMake/C++ project without setup.py or pyproject "
+                          "(pip: 'not installable'); its CMake downloads nine packages at "
+                          "configure time and there is no network"}))
+        return 0
+    if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        print(json.dumps({"error": "this engine runs on one GPU; --gpus N > 1 is not supported",
+                          "n_gpus": args.gpus}))
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+
+    from ginfer_b200.engine.llm import Engine
+    cfg = dict(QWEN2_1P5B)
+    full_layers = cfg["num_hidden_layers"]
+    layers = args.layers or full_layers
+    cfg["num_hidden_layers"] = layers
+    peaks, peak_src = load_peaks()
+    eng = Engine(config=cfg, weights_seed=0, dtype="bfloat16", max_num_batched_tokens=8192,
+                 max_num_seqs=64, max_seq_len=CONTEXT, kvcache_block_size=PAGE,
+                 num_kvcache_blocks=64 * (PROMPT + 256) // PAGE + PREFILL_TOKENS // PAGE + 64,
+                 enforce_eager=args.enforce_eager)
+    B = args.batch
+
+    clocks = ClockSampler()
+    clocks.start()
+    ms, launches = decode_device_timed(eng, B, args.steps, args.warmup, seed=1)
+    clock_info = clocks.stop()
+    e2e_ms, h2d, d2h = decode_end_to_end(eng, B, args.steps, args.warmup, seed=2)
+    pre_ms = prefill_timed(eng, PREFILL_TOKENS, reps=5, warmup=3, seed=3)
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            pms, _ = decode_device_timed(eng, b, min(args.steps, 64), args.warmup, seed=10 + b)
+            points[f"decode_b{b}"] = round(b / (pms * 1e-3), 1)
+
+    mean_ctx = PROMPT + args.warmup + args.steps / 2
+    step_bytes = weight_bytes(cfg, layers) + B * mean_ctx * kv_bytes_per_token(cfg, layers)
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    flops = prefill_flops(cfg, layers, PREFILL_TOKENS)
+    value = B / (ms * 1e-3)
+    line = {
+        "metric": "decode tok/s at batch 8 (one B200), Qwen2-1.5B shape",
+        "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random token ids, random-init weights N(0, 0.02)",
+        "impl": "ours",
+        "config": {
+            "model": "Qwen2-1.5B shape", "layers_run": layers, "layers_config": full_layers,
+            "hidden_size": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+            "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+            "intermediate_size": cfg["intermediate_size"], "vocab_size": cfg["vocab_size"],
+            "global_batch": B, "seq_len": CONTEXT, "prompt_len": PROMPT,
+            "kv_block": PAGE, "parallelism": "single GPU",
+            "l2": "inputs larger than L2 (3.1 GB of weights read per step)",
+            "cuda_graphs": not args.enforce_eager, "peaks": peak_src,
+        },
+        "e2e": {"value": round(B / (e2e_ms * 1e-3), 1), "unit": "tok/s",
+                "ms_per_step": round(e2e_ms, 4), "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "prefill": {"value": round(PREFILL_TOKENS / (pre_ms * 1e-3), 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(pre_ms, 3),
+                    "frac": round(flops / (pre_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1),
+                     "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clock_info,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

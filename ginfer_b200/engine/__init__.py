@@ -1,1 +1,3 @@
 from .runner import ModelRunner, StepEntry
+from .request import Request, RequestState
+from .scheduler import Scheduled, Scheduler

@@ -1,0 +1,134 @@
+"""The Python entry point: token ids in, generated token ids out.
+
+Reference: ``ginfer/engine/engine.{h,cc}``: ``Engine(Config)``, ``generate(prompts,
+SamplingParams)`` adds every prompt, loops ``step()`` until the scheduler is empty and returns the
+results in request order (``engine.cc:126-151``); ``step()`` is schedule, run, post-process, with
+prefill and decode throughput counted per step (``engine.cc:93-124,73-91``).  The reference
+returns text; this engine consumes and returns token ids (no tokenizer).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+
+import torch
+
+from ..config.engine_config import EngineConfig
+from ..sampling import Sampler, SamplingParams
+from .loading import load_model, random_model
+from .request import Request, RequestState
+from .runner import ModelRunner, StepEntry
+from .scheduler import Scheduler
+
+
+@dataclass
+class EngineStats:
+    """Counted as the reference does: a step with any prompt portion is a prefill step and
+    counts its tokens; other steps are decode steps and count their requests."""
+    prefill_tokens: int = 0
+    decode_tokens: int = 0
+    prefill_seconds: float = 0.0
+    decode_seconds: float = 0.0
+    steps: int = 0
+    preemptions: int = 0
+
+    def summary(self) -> dict:
+        return {
+            "prefill_tokens": self.prefill_tokens, "decode_tokens": self.decode_tokens,
+            "prefill_tok_per_s": self.prefill_tokens / self.prefill_seconds
+            if self.prefill_seconds else 0.0,
+            "decode_tok_per_s": self.decode_tokens / self.decode_seconds
+            if self.decode_seconds else 0.0,
+            "steps": self.steps, "preemptions": self.preemptions,
+        }
+
+
+class Engine:
+    def __init__(self, model_path: str | None = None, *, config: dict | None = None,
+                 weights_seed: int = 0, dtype: str = "bfloat16",
+                 max_num_batched_tokens: int = 8192, max_num_seqs: int = 64,
+                 max_seq_len: int = 4096, gpu_memory_utilization: float = 0.8,
+                 kvcache_block_size: int = 16, num_kvcache_blocks: int | None = None,
+                 enforce_eager: bool = False, device: str = "cuda:0", seed: int = 0):
+        """``model_path``: a folder with ``config.json`` and ``model.safetensors``; or give
+        ``config`` (a ``config.json`` as a dict) and ``weights_seed`` for random weights."""
+        self.cfg = EngineConfig(model_path or "<random>", dtype, max_num_batched_tokens,
+                                max_num_seqs, max_seq_len, gpu_memory_utilization,
+                                kvcache_block_size, num_kvcache_blocks, enforce_eager, device)
+        self.cfg.validate()
+        if model_path is not None:
+            self.model, self.model_config = load_model(model_path, dtype, device)
+        elif config is not None:
+            self.model, self.model_config = random_model(config, weights_seed, dtype, device)
+        else:
+            raise ValueError("give model_path or config")
+        self.runner = ModelRunner(
+            self.model, page_size=kvcache_block_size, max_num_seqs=max_num_seqs,
+            max_seq_len=max_seq_len, num_pages=num_kvcache_blocks,
+            gpu_memory_utilization=gpu_memory_utilization,
+            max_num_batched_tokens=max_num_batched_tokens, enforce_eager=enforce_eager)
+        self.scheduler = Scheduler(self.runner.cache, max_num_seqs, max_num_batched_tokens,
+                                   self.runner.max_seq_len, self.model.plan.eos_token_ids)
+        self.sampler = Sampler(device)
+        self.seed = int(seed)
+        self.stats = EngineStats()
+        self._next_id = 0
+        self.requests: dict[int, Request] = {}
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, prompt_ids: list[int], params: SamplingParams | None = None) -> int:
+        params = params or SamplingParams()
+        params.validate()
+        rid = self._next_id
+        self._next_id += 1
+        seed = params.seed if params.seed is not None else (self.seed * 1000003 + rid)
+        req = Request(rid, [int(t) for t in prompt_ids], params, seed=seed,
+                      arrival_time=time.perf_counter())
+        v = self.model.plan.vocab_size
+        if any(t < 0 or t >= v for t in req.prompt):
+            raise ValueError(f"prompt token ids must lie in [0, {v})")
+        self.scheduler.add(req)
+        self.requests[rid] = req
+        return rid
+
+    # ------------------------------------------------------------------ one step
+    def step(self) -> list[Request]:
+        """Schedule, run, sample, post-process; returns the requests that finished."""
+        t0 = time.perf_counter()
+        batch, dropped = self.scheduler.schedule()
+        finished = list(dropped)
+        if batch:
+            entries = [StepEntry(s.request.request_id,
+                                 s.request.tokens(s.start, s.start + s.num_tokens),
+                                 [s.num_tokens - 1] if s.sample else []) for s in batch]
+            logits = self.runner.step(entries)
+            picks = [s for s in batch if s.sample]
+            tokens = self.sampler.sample(
+                logits, [s.request.params.temperature for s in picks],
+                [s.request.seed for s in picks], [len(s.request.output) for s in picks])
+            finished += self.scheduler.postprocess(batch, tokens)
+            dt = time.perf_counter() - t0
+            if any(s.num_tokens > 1 for s in batch):
+                self.stats.prefill_tokens += sum(s.num_tokens for s in batch)
+                self.stats.prefill_seconds += dt
+            else:
+                self.stats.decode_tokens += len(batch)
+                self.stats.decode_seconds += dt
+            self.stats.steps += 1
+        self.stats.preemptions = self.scheduler.num_preemptions
+        return finished
+
+    # ------------------------------------------------------------------ the user's call
+    def generate(self, prompts: list[list[int]], sampling_params=None) -> list[list[int]]:
+        """Generate for every prompt (lists of token ids); returns the generated ids of each, in
+        the order of ``prompts``.  ``sampling_params``: one for all, or one per prompt."""
+        if sampling_params is None or isinstance(sampling_params, SamplingParams):
+            sampling_params = [sampling_params or SamplingParams()] * len(prompts)
+        if len(sampling_params) != len(prompts):
+            raise ValueError("one SamplingParams per prompt is needed")
+        ids = [self.add_request(p, sp) for p, sp in zip(prompts, sampling_params)]
+        while not self.scheduler.is_finished():
+            self.step()
+        out = [self.requests[i].output for i in ids]
+        self.last_requests = [self.requests.pop(i) for i in ids]
+        return out

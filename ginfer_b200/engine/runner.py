@@ -34,7 +34,8 @@ def _align4(n: int) -> int:
 class ModelRunner:
     def __init__(self, model: DecoderModel, *, page_size: int, max_num_seqs: int,
                  max_seq_len: int, num_pages: int | None = None,
-                 gpu_memory_utilization: float = 0.8, max_num_batched_tokens: int = 8192):
+                 gpu_memory_utilization: float = 0.8, max_num_batched_tokens: int = 8192,
+                 enforce_eager: bool = True):
         if model.device is None or model.device.type != "cuda":
             raise RuntimeError("the model must be loaded on a CUDA device before a runner is made")
         self.model = model
@@ -44,6 +45,7 @@ class ModelRunner:
         self.max_seq_len = min(int(max_seq_len), model.plan.max_positions)
         self.max_num_seqs = int(max_num_seqs)
         self.max_num_batched_tokens = int(max_num_batched_tokens)
+        self.enforce_eager = bool(enforce_eager)
         specs = model.cache_specs()
         self.groups, self._group_of_cache = plan_groups(specs)
         itemsize = torch.empty((), dtype=self.dtype).element_size()
@@ -60,6 +62,8 @@ class ModelRunner:
         self._copied = torch.cuda.Event()     # the last copy out of the staging buffer
         self._copy_pending = False
         self.steps_run = 0
+        self.h2d_bytes = 0            # bytes of step integers copied to the device so far
+        self.graph_launches = 0       # kernel launches replayed from CUDA graphs so far
 
     def _pages_from_memory(self, utilization: float, itemsize: int) -> int:
         free, _total = torch.cuda.mem_get_info(self.device)
@@ -78,7 +82,6 @@ class ModelRunner:
     def preempt(self, request_id) -> None:
         """Give the request's pages back but keep its slot; it will be computed again."""
         self.cache.release(request_id, keep_slot=True)
-        self.storage.reset_slot(self.cache.get(request_id).slot)
 
     # ------------------------------------------------------------------ the step
     def _staging(self, n_ints: int) -> torch.Tensor:
@@ -121,10 +124,13 @@ class ModelRunner:
             if k > f:
                 raise OutOfPages(f"the step needs {k} pages of group {g}; {f} are free")
         for rid in new:
-            rc = cache.admit(rid)
-            self.storage.reset_slot(rc.slot)
+            cache.admit(rid)
         rcs = [cache.get(e.request_id) for e in entries]
         q_starts = np.fromiter((rc.num_tokens for rc in rcs), dtype=np.int64, count=B)
+        if self.storage.state:
+            for rc in rcs:
+                if rc.num_tokens == 0:       # a sequence starts (again): its state starts at zero
+                    self.storage.reset_slot(rc.slot)
         for e, n in zip(entries, q_lens):
             cache.reserve(e.request_id, int(n))
 
@@ -174,6 +180,7 @@ class ModelRunner:
             spans[k] = (off, n, a.shape)
             off += _align4(n)
         dev = host[:total].to(self.device, non_blocking=True)
+        self.h2d_bytes += 4 * total
         self._copied.record()
         self._copy_pending = True
         return {k: dev[o:o + n].view(shape) for k, (o, n, shape) in spans.items()}

@@ -1,0 +1,218 @@
+"""Continuous batching with prompts fed in portions under a token budget.
+
+Reference: ``ginfer/engine/scheduler.cc:20-99``.  There a step is either all prompts (each whole)
+or all decode tokens; a prompt longer than the budget is never scheduled; when a decoding request
+cannot get a page the most recently admitted running request is preempted (its pages released,
+itself queued again and later computed from the start, ``scheduler.cc:47-56,73-77``); a request
+finishes on an EOS id (unless ``ignore_eos``) or at ``max_tokens`` (``scheduler.cc:83-98``).
+
+Here every step is one mixed batch, built in this order:
+
+1. every running request that is decoding gets its one token;
+2. running requests still in their prompt get a portion of it;
+3. waiting requests are admitted, oldest first, while a slot, budget and pages for a first
+   portion are there (a request that does not fit stops admission: no overtaking).
+
+The budget is ``max_num_batched_tokens`` tokens a step; a portion is whatever of the prompt is
+left, cut to the budget and to the pages that are free.
+
+When pages run out: a decoding request that needs a page takes it from the most recently admitted
+other running request, which is preempted: its pages go back, it keeps its slot and its sampling
+state, it is put at the *front* of the waiting queue and is later computed again from its first
+token (prompt and the output so far).  A request that is alone and still cannot get a page is
+finished with reason ``out_of_pages``; a prompt that could never fit the pool or ``max_seq_len``
+is refused when it is added.  Nothing spins.
+"""
+from __future__ import annotations
+
+import time
+from collections import deque
+from dataclasses import dataclass
+
+from ..cache.manager import CacheManager
+from .request import Request, RequestState
+
+
+@dataclass
+class Scheduled:
+    request: Request
+    start: int            # position of the first token of the portion
+    num_tokens: int
+    sample: bool          # the portion ends at the request's last token: a token is sampled
+
+
+class Scheduler:
+    def __init__(self, cache: CacheManager, max_num_seqs: int, max_num_batched_tokens: int,
+                 max_seq_len: int, eos_token_ids=()):
+        self.cache = cache
+        self.max_num_seqs = int(max_num_seqs)
+        self.max_num_batched_tokens = int(max_num_batched_tokens)
+        self.max_seq_len = int(max_seq_len)
+        self.eos = frozenset(int(e) for e in eos_token_ids)
+        self.waiting: deque[Request] = deque()
+        self.running: list[Request] = []          # in order of admission
+        self.num_preemptions = 0
+
+    # ------------------------------------------------------------------ queue
+    def is_finished(self) -> bool:
+        return not self.waiting and not self.running
+
+    def add(self, req: Request) -> None:
+        n = len(req.prompt)
+        if n == 0:
+            raise ValueError("a prompt needs at least one token")
+        if n + 1 > self.max_seq_len:
+            raise ValueError(f"prompt of {n} tokens leaves no room for output within "
+                             f"max_seq_len {self.max_seq_len}")
+        need = -(-n // self.cache.page_size)
+        for g, pool in enumerate(self.cache.pools):
+            if need > pool.num_pages and self.cache.windows[g] == 0:
+                raise ValueError(f"prompt of {n} tokens needs {need} pages; the pool of group "
+                                 f"{g} has {pool.num_pages}")
+        req.state = RequestState.WAITING
+        self.waiting.append(req)
+
+    # ------------------------------------------------------------------ one step
+    def _fit(self, req: Request, want: int, promised: list[int]) -> int:
+        """Largest portion <= ``want`` whose pages are free (beyond ``promised``)."""
+        if want <= 0:
+            return 0
+        if self.cache.can_reserve(req.request_id, want, promised):
+            return want
+        P = self.cache.page_size
+        have = req.num_computed
+        free = min(f - p for f, p in zip(self.cache.free_pages(), promised))
+        if free < 0:
+            return 0
+        # tokens until the pages held so far are full, plus what ``free`` more pages hold
+        rc = self.cache.requests.get(req.request_id)
+        held_end = (min(rc.next_page) if rc else 0) * P
+        room = max(0, held_end - have) + free * P
+        n = min(want, room)
+        while n > 0 and not self.cache.can_reserve(req.request_id, n, promised):
+            n -= 1
+        return n
+
+    def _promise(self, req: Request, n: int, promised: list[int]) -> None:
+        for g, k in enumerate(self.cache.pages_needed(req.request_id, n)):
+            promised[g] += k
+
+    def _preempt(self, victim: Request) -> None:
+        self.cache.release(victim.request_id, keep_slot=True)
+        victim.num_computed = 0
+        victim.state = RequestState.WAITING
+        victim.num_preemptions += 1
+        self.num_preemptions += 1
+        self.running.remove(victim)
+        self.waiting.appendleft(victim)
+
+    def _finish(self, req: Request, reason: str) -> None:
+        req.state = RequestState.FINISHED
+        req.finish_reason = reason
+        req.finish_time = time.perf_counter()
+        if req in self.running:
+            self.running.remove(req)
+        if self.cache.has(req.request_id):
+            self.cache.release(req.request_id)
+
+    def schedule(self) -> tuple[list[Scheduled], list[Request]]:
+        """Returns the step's batch and the requests finished without a step (out of pages)."""
+        budget = self.max_num_batched_tokens
+        promised = [0] * self.cache.num_groups
+        batch: list[Scheduled] = []
+        dropped: list[Request] = []
+
+        # 1. decoding requests, oldest first; a page may cost the youngest its place
+        for req in list(self.running):
+            if req.state is not RequestState.RUNNING or req.num_tokens - req.num_computed != 1:
+                continue
+            if budget <= 0:
+                break
+            while not self.cache.can_reserve(req.request_id, 1, promised):
+                victims = [r for r in self.running if r is not req
+                           and all(s.request is not r for s in batch)]
+                if victims:
+                    self._preempt(victims[-1])
+                elif len(self.running) > 1 or batch:
+                    break                      # others already hold this step's pages: wait
+                else:
+                    self._finish(req, "out_of_pages")
+                    dropped.append(req)
+                    break
+            if req.state is not RequestState.RUNNING or \
+                    not self.cache.can_reserve(req.request_id, 1, promised):
+                continue
+            self._promise(req, 1, promised)
+            batch.append(Scheduled(req, req.num_computed, 1, True))
+            budget -= 1
+
+        # 2. running requests still feeding their prompt
+        for req in list(self.running):
+            left = req.num_tokens - req.num_computed
+            if req.state is not RequestState.RUNNING or left <= 1 or budget <= 0:
+                continue
+            n = self._fit(req, min(left, budget), promised)
+            if n <= 0:
+                continue
+            self._promise(req, n, promised)
+            batch.append(Scheduled(req, req.num_computed, n, n == left))
+            budget -= n
+
+        # 3. admission, oldest first, no overtaking
+        while self.waiting and budget > 0 and len(self.running) < self.max_num_seqs:
+            req = self.waiting[0]
+            if not self.cache.has(req.request_id) and self.cache.slots.num_free == 0:
+                break
+            left = req.num_tokens
+            n = self._fit(req, min(left, budget), promised)
+            if n <= 0:
+                break
+            self.waiting.popleft()
+            if not self.cache.has(req.request_id):
+                self.cache.admit(req.request_id)
+            req.state = RequestState.RUNNING
+            self.running.append(req)
+            self._promise(req, n, promised)
+            batch.append(Scheduled(req, 0, n, n == left))
+            budget -= n
+
+        # nothing could move although requests are live: free the youngest's pages, or give up on
+        # a request that is alone
+        if not batch and not dropped and (self.running or self.waiting):
+            if len(self.running) > 1:
+                self._preempt(self.running[-1])
+                return self.schedule()
+            if self.running:
+                req = self.running[0]
+                self._finish(req, "out_of_pages")
+                dropped.append(req)
+            elif self.waiting:
+                req = self.waiting.popleft()
+                self._finish(req, "out_of_pages")
+                dropped.append(req)
+        return batch, dropped
+
+    def postprocess(self, batch: list[Scheduled], sampled: list[int]) -> list[Request]:
+        """``sampled``: one token for every entry of ``batch`` with ``sample`` set, in order.
+        Appends tokens, finishes requests, returns the finished ones."""
+        finished = []
+        it = iter(sampled)
+        now = time.perf_counter()
+        for s in batch:
+            req = s.request
+            req.num_computed = s.start + s.num_tokens
+            if not s.sample:
+                continue
+            tok = int(next(it))
+            req.output.append(tok)
+            if req.first_token_time is None:
+                req.first_token_time = now
+            if not req.params.ignore_eos and tok in self.eos:
+                self._finish(req, "eos")
+            elif len(req.output) >= req.params.max_tokens:
+                self._finish(req, "max_tokens")
+            elif req.num_tokens >= self.max_seq_len:
+                self._finish(req, "max_seq_len")
+            if req.state is RequestState.FINISHED:
+                finished.append(req)
+        return finished

@@ -46,18 +46,33 @@ def _ok(rc: int, what: str):
         raise RuntimeError(f"{what}: the kernel refused its arguments (code {rc})")
 
 
-_sigs_done: set = set()
+class _Counter:
+    """Kernel launches made through this module (each entry point launches one kernel unless it
+    says otherwise); read by the benchmark."""
+    launches = 0
 
 
-def _fn(lib_name: str, fn_name: str, argtypes, defines=()):
-    lib = load_library(lib_name, tuple(defines))
-    f = getattr(lib, fn_name)
+_fns: dict = {}
+
+
+def _fn(lib_name: str, fn_name: str, argtypes, defines=(), kernels: int = 1):
     key = (lib_name, tuple(defines), fn_name)
-    if key not in _sigs_done:
+    g = _fns.get(key)
+    if g is None:
+        lib = load_library(lib_name, tuple(defines))
+        f = getattr(lib, fn_name)
         f.argtypes = argtypes
         f.restype = c_int
-        _sigs_done.add(key)
-    return f
+
+        def g(*args, _f=f, _k=kernels):
+            _Counter.launches += _k
+            return _f(*args)
+        _fns[key] = g
+    return g
+
+
+def launch_count() -> int:
+    return _Counter.launches
 
 
 # ----------------------------------------------------------------------------- embedding

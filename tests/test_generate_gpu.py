@@ -1,0 +1,136 @@
+"""Generation through the Python entry point and the command line: greedy tokens equal the plain
+implementation's, temperature sampling follows the plain inverse-CDF rule, and neither depends on
+the batch, the token budget or a preemption."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_qwen2 as plain
+from tiny import CONFIGS, make_folder, prompt
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("gen")
+    return {n: make_folder(root, n, seed=4) for n in ("A", "B")}
+
+
+def _engine(d, dtype="float32", **kw):
+    from ginfer_b200.engine.llm import Engine
+    args = dict(model_path=d, dtype=dtype, max_num_seqs=4, max_num_batched_tokens=32,
+                max_seq_len=256, num_kvcache_blocks=40, kvcache_block_size=16)
+    args.update(kw)
+    return Engine(**args)
+
+
+@pytest.mark.parametrize("name,lengths,new", [("A", (5, 17, 33), 8), ("B", (1, 40, 90), 12)])
+def test_greedy_generation_equals_plain(folders, name, lengths, new):
+    from ginfer_b200.sampling import SamplingParams
+    d = folders[name]
+    cfg, w = plain.read_model_folder(d)
+    prompts = [prompt(n, cfg["vocab_size"], seed=n) for n in lengths]
+    want = [plain.greedy_generate(w, cfg, p, new) for p in prompts]
+    sp = SamplingParams(max_tokens=new, ignore_eos=True)
+    # a budget of 13 tokens a step: prompts go in portions beside decode tokens
+    eng = _engine(d, max_num_batched_tokens=13, kvcache_block_size=8 if name == "B" else 16)
+    assert eng.generate(prompts, sp) == want
+    assert eng.runner.cache.free_pages() == [40] * eng.runner.cache.num_groups
+    # so few pages that requests are preempted and computed again: same tokens
+    few = _engine(d, num_kvcache_blocks=9, max_num_batched_tokens=64)
+    assert few.generate(prompts, sp) == want
+    if name == "B":
+        assert few.stats.preemptions >= 1
+
+
+def test_eos_stops_generation(folders):
+    from ginfer_b200.sampling import SamplingParams
+    d = folders["A"]
+    cfg, w = plain.read_model_folder(d)
+    p = prompt(9, cfg["vocab_size"], seed=3)
+    free = plain.greedy_generate(w, cfg, p, 6)
+    cfg2 = dict(cfg)
+    cfg2["eos_token_id"] = free[2]
+    d2 = d + "_eos"
+    os.makedirs(d2, exist_ok=True)
+    json.dump(cfg2, open(os.path.join(d2, "config.json"), "w"))
+    if not os.path.exists(os.path.join(d2, "model.safetensors")):
+        os.link(os.path.join(d, "model.safetensors"), os.path.join(d2, "model.safetensors"))
+    eng = _engine(d2)
+    assert eng.generate([p], SamplingParams(max_tokens=6)) == [free[:free.index(free[2]) + 1]]
+    assert eng.last_requests[0].finish_reason == "eos"
+    assert eng.generate([p], SamplingParams(max_tokens=6, ignore_eos=True)) == [free]
+
+
+def test_temperature_sampling_follows_the_plain_rule_and_ignores_the_batch(folders):
+    from ginfer_b200.sampling import SamplingParams, uniform
+    d = folders["B"]
+    cfg, w = plain.read_model_folder(d)
+    prompts = [prompt(n, cfg["vocab_size"], seed=50 + n) for n in (1, 40, 90)]
+    sps = [SamplingParams(max_tokens=12, ignore_eos=True, temperature=0.8, seed=1000 + i)
+           for i in range(3)]
+    eng = _engine(d, kvcache_block_size=8, max_num_batched_tokens=13)
+    outs = eng.generate(prompts, sps)
+    # replay each request with the plain model: at every step the engine's token must be the
+    # plain inverse-CDF choice, unless u falls within rounding distance of a CDF step
+    for p, out, sp in zip(prompts, outs, sps):
+        ids = list(p)
+        for i, tok in enumerate(out):
+            logits = plain.forward(w, cfg, ids)[-1]
+            u = uniform(sp.seed, i)
+            pick = plain.temperature_token(logits, 0.8, u)
+            if tok != pick:
+                cdf = torch.cumsum(torch.softmax(logits.double() / 0.8, -1), 0)
+                lo, hi = sorted((tok, pick))
+                assert hi - lo == 1 and abs(float(cdf[lo]) - u) < 1e-5, (i, tok, pick)
+            ids.append(tok)
+    # alone, and with other seeds beside it: the same tokens
+    alone = _engine(d, kvcache_block_size=8)
+    assert alone.generate([prompts[1]], sps[1]) == [outs[1]]
+    other = [SamplingParams(max_tokens=12, ignore_eos=True, temperature=0.8, seed=5)] * 3
+    assert _engine(d, kvcache_block_size=8).generate(prompts, other) != outs
+
+
+def test_bfloat16_greedy_agrees_across_ways_of_batching(folders, tmp_path):
+    from ginfer_b200.sampling import SamplingParams
+    d = make_folder(tmp_path, "A", seed=4, storage="bfloat16")
+    cfg = CONFIGS["A"]
+    prompts = [prompt(n, cfg["vocab_size"], seed=n) for n in (5, 17, 33)]
+    sp = SamplingParams(max_tokens=8, ignore_eos=True)
+    together = _engine(d, "bfloat16").generate(prompts, sp)
+    chunked = _engine(d, "bfloat16", max_num_batched_tokens=7).generate(prompts, sp)
+    alone = [_engine(d, "bfloat16").generate([p], sp)[0] for p in prompts]
+    assert together == chunked == alone
+
+
+def test_command_line(folders, tmp_path):
+    d = folders["A"]
+    cfg, w = plain.read_model_folder(d)
+    prompts = [prompt(n, cfg["vocab_size"], seed=n) for n in (6, 11)]
+    f = tmp_path / "prompts.txt"
+    f.write_text(" ".join(map(str, prompts[0])) + "\n" + json.dumps(prompts[1]) + "\n")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "ginfer_generate"),
+                        "--model-path", d, "--dtype", "float32", "--prompt-ids", str(f),
+                        "--max-tokens", "5", "--ignore-eos", "--max-num-seqs", "2",
+                        "--max-seq-len", "64", "--num-kvcache-blocks", "8"],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [json.loads(x) for x in r.stdout.strip().splitlines()]
+    assert [ln["output_ids"] for ln in lines[:2]] == \
+        [plain.greedy_generate(w, cfg, p, 5) for p in prompts]
+    assert lines[2]["stats"]["decode_tokens"] > 0 and lines[2]["stats"]["avg_ttft_ms"] > 0
+
+
+def test_no_cpu_path():
+    from ginfer_b200 import ops
+    with pytest.raises(RuntimeError, match="CUDA device only"):
+        ops.embedding(torch.zeros(2, dtype=torch.int32), torch.zeros(4, 8))
+    from ginfer_b200.engine.loading import require_cuda
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        require_cuda("cpu")

@@ -1,0 +1,208 @@
+"""The scheduler's decisions on the host, with the cache manager and a stand-in for the model."""
+import random
+
+import pytest
+
+from ginfer_b200.cache.manager import CacheManager
+from ginfer_b200.engine.request import Request, RequestState
+from ginfer_b200.engine.scheduler import Scheduler
+from ginfer_b200.sampling import SamplingParams, uniform
+
+
+def _sched(pages=16, page=4, seqs=4, budget=16, max_len=64, eos=(), windows=(0,)):
+    cache = CacheManager(list(windows), pages, page, seqs, max_len)
+    return Scheduler(cache, seqs, budget, max_len, eos), cache
+
+
+def _next_token(req):
+    """A stand-in model: the next token is a function of the tokens so far (so a request that is
+    computed again after a preemption must get the same continuation)."""
+    h = 17
+    for i in range(req.num_tokens):
+        h = (h * 31 + req.token_at(i)) % 1009
+    return h % 97
+
+
+def _run_step(sched, cache, log=None):
+    batch, dropped = sched.schedule()
+    for s in batch:                                   # what the runner does with the pages
+        assert s.start == cache.get(s.request.request_id).num_tokens == s.request.num_computed
+        cache.reserve(s.request.request_id, s.num_tokens)
+    for s in batch:
+        cache.commit(s.request.request_id, s.num_tokens)
+    tokens = []
+    for s in batch:
+        if s.sample:
+            assert s.start + s.num_tokens == s.request.num_tokens
+            tokens.append(_next_token(s.request))
+    if log is not None:
+        log.append([(s.request.request_id, s.start, s.num_tokens, s.sample) for s in batch])
+    finished = sched.postprocess(batch, tokens)
+    cache.check()
+    return batch, dropped + finished
+
+
+def _req(i, n, max_tokens=4, **kw):
+    return Request(i, [(7 * i + j) % 50 for j in range(n)],
+                   SamplingParams(max_tokens=max_tokens, **kw))
+
+
+def test_prompt_is_cut_under_the_budget_and_decode_goes_first():
+    sched, cache = _sched(pages=32, budget=10)
+    a, b = _req(0, 23, max_tokens=3), _req(1, 4, max_tokens=6)
+    sched.add(a)
+    sched.add(b)
+    log = []
+    _run_step(sched, cache, log)
+    assert log[-1] == [(0, 0, 10, False)]            # b waits: the budget is spent
+    _run_step(sched, cache, log)
+    assert log[-1] == [(0, 10, 10, False)]
+    _run_step(sched, cache, log)
+    assert log[-1] == [(0, 20, 3, True), (1, 0, 4, True)]
+    _run_step(sched, cache, log)
+    assert log[-1] == [(0, 23, 1, True), (1, 4, 1, True)]      # both decode
+    while not sched.is_finished():
+        batch, _ = _run_step(sched, cache, log)
+        assert sum(n for _, _, n, _ in log[-1]) <= 10
+    assert len(a.output) == 3 and len(b.output) == 6
+    assert a.finish_reason == b.finish_reason == "max_tokens"
+    assert cache.free_pages() == [32] and cache.slots.num_free == 4
+
+
+def test_decode_tokens_come_before_prompt_portions():
+    sched, cache = _sched(pages=64, budget=8, max_len=128)
+    a = _req(0, 3, max_tokens=10)
+    sched.add(a)
+    _run_step(sched, cache)
+    b = _req(1, 30, max_tokens=2)
+    sched.add(b)
+    log = []
+    _run_step(sched, cache, log)
+    assert log[-1] == [(0, 3, 1, True), (1, 0, 7, False)]      # one decode token, then 7 of b
+
+
+def test_eos_finishes_unless_ignored_and_max_seq_len_stops():
+    sched, cache = _sched(eos=(_next_token(_req(0, 5)),))
+    a = _req(0, 5, max_tokens=9)
+    b = _req(1, 5, max_tokens=9, ignore_eos=True)
+    b.prompt = list(a.prompt)
+    sched.add(a)
+    sched.add(b)
+    while not sched.is_finished():
+        _run_step(sched, cache)
+    assert a.finish_reason == "eos" and len(a.output) == 1
+    assert b.finish_reason == "max_tokens" and len(b.output) == 9
+    sched, cache = _sched(max_len=8, pages=8)
+    c = _req(2, 6, max_tokens=50)
+    sched.add(c)
+    while not sched.is_finished():
+        _run_step(sched, cache)
+    assert c.finish_reason == "max_seq_len" and c.num_tokens == 8
+
+
+def test_prompts_that_can_never_fit_are_refused_when_added():
+    sched, _ = _sched(pages=4, page=4, max_len=64)
+    with pytest.raises(ValueError, match="pages"):
+        sched.add(_req(0, 17))
+    with pytest.raises(ValueError, match="max_seq_len"):
+        sched.add(_req(1, 64))
+    with pytest.raises(ValueError, match="at least one"):
+        sched.add(_req(2, 0))
+
+
+def test_out_of_pages_preempts_the_youngest_which_is_computed_again():
+    # 6 pages of 4 tokens; two requests of 9 tokens take 3 pages each; the first to need a
+    # fourth page takes it from the younger one
+    sched, cache = _sched(pages=6, page=4, budget=32, max_len=24)
+    a, b = _req(0, 9, max_tokens=8), _req(1, 9, max_tokens=8)
+    ref = []
+    for r in (_req(0, 9, max_tokens=8), _req(1, 9, max_tokens=8)):    # each alone
+        s2, c2 = _sched(pages=6, page=4, budget=32, max_len=24)
+        s2.add(r)
+        while not s2.is_finished():
+            _run_step(s2, c2)
+        ref.append(list(r.output))
+    sched.add(a)
+    sched.add(b)
+    steps = 0
+    while not sched.is_finished():
+        _run_step(sched, cache)
+        steps += 1
+        assert steps < 200
+    assert sched.num_preemptions >= 1 and b.num_preemptions >= 1 and a.num_preemptions == 0
+    assert [a.output, b.output] == ref                # preemption does not change the result
+    assert a.finish_reason == b.finish_reason == "max_tokens"
+    assert cache.free_pages() == [6] and cache.slots.num_free == 4
+
+
+def test_a_request_that_cannot_fit_even_alone_ends_with_out_of_pages():
+    sched, cache = _sched(pages=3, page=4, budget=32, max_len=64)
+    a = _req(0, 10, max_tokens=30)
+    sched.add(a)
+    steps = 0
+    while not sched.is_finished():
+        _run_step(sched, cache)
+        steps += 1
+        assert steps < 100
+    assert a.finish_reason == "out_of_pages" and a.state is RequestState.FINISHED
+    assert a.num_tokens == 12 + 1                     # 12 tokens cached, the 13th has no page
+    assert cache.free_pages() == [3]
+
+
+def test_slots_bound_the_live_requests_and_admission_is_in_order():
+    sched, cache = _sched(pages=64, seqs=2, budget=64, max_len=64)
+    reqs = [_req(i, 5, max_tokens=3) for i in range(5)]
+    for r in reqs:
+        sched.add(r)
+    order = []
+    while not sched.is_finished():
+        batch, _ = _run_step(sched, cache)
+        assert len(sched.running) <= 2
+        for s in batch:
+            if s.start == 0 and s.request.request_id not in order:
+                order.append(s.request.request_id)
+    assert order == [0, 1, 2, 3, 4]
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_workloads_finish_with_the_results_of_each_request_alone(seed):
+    rng = random.Random(seed)
+    page = rng.choice([2, 4, 8])
+    pages = rng.choice([10, 14, 40])
+    windows = rng.choice([(0,), (0, 12)])
+    budget = rng.choice([5, 16, 64])
+    max_len = pages * page
+    reqs = [_req(i, rng.randint(1, min(30, (pages - 1) * page)), max_tokens=rng.randint(1, 12))
+            for i in range(rng.randint(3, 9))]
+    alone = []
+    for r in reqs:
+        s2, c2 = _sched(pages=pages, page=page, seqs=3, budget=budget, max_len=max_len,
+                        windows=windows)
+        clone = Request(r.request_id, list(r.prompt), r.params)
+        s2.add(clone)
+        while not s2.is_finished():
+            _run_step(s2, c2)
+        alone.append((list(clone.output), clone.finish_reason))
+    sched, cache = _sched(pages=pages, page=page, seqs=3, budget=budget, max_len=max_len,
+                          windows=windows)
+    pending = list(reqs)
+    steps = 0
+    while pending or not sched.is_finished():
+        while pending and rng.random() < 0.5:
+            sched.add(pending.pop(0))
+        batch, _ = _run_step(sched, cache)
+        assert sum(s.num_tokens for s in batch) <= budget and len(sched.running) <= 3
+        steps += 1
+        assert steps < 2000, "the scheduler does not make progress"
+    for r, (out, why) in zip(reqs, alone):
+        if why != "out_of_pages" and r.finish_reason != "out_of_pages":
+            assert r.output == out and r.finish_reason == why
+    assert cache.free_pages() == [pages] * len(windows) and cache.slots.num_free == 3
+
+
+def test_sampling_numbers_depend_on_seed_and_index_only():
+    assert uniform(3, 5) == uniform(3, 5)
+    xs = [uniform(1, i) for i in range(2000)]
+    assert all(0.0 <= x < 1.0 for x in xs) and len(set(xs)) > 1990
+    assert abs(sum(xs) / len(xs) - 0.5) < 0.03
+    assert uniform(1, 7) != uniform(2, 7)
