@@ -1,0 +1,524 @@
+// bf16 grouped-query attention over the paged cache for the serving path, compiled for one head
+// size (-DGF_HEAD_DIM=<multiple of 16, at most 256>).
+//
+//  * gf_attn_decode: one query token per request.  One CTA per (request, kv head, split of the
+//    keys, chunk of 16 query heads): the query heads of a group share every K/V byte that is
+//    loaded (the reference's decode kernel reads K/V once per query head:
+//    ginfer/core/op/kernels/cuda/page_attn_kernel/flash_gqa_varlen_decode_kvcache.cu:272-335).
+//    Splits write fp32 partial results (running maximum, sum, unnormalised output) to scratch
+//    memory and gf_attn_decode's second kernel merges them.
+//  * gf_attn_prefill: any number of query tokens per request (portions of prompts, and single
+//    tokens beside them).  One CTA per (64 query rows of one head); keys are visited in tiles of 64
+//    through the block table.
+//
+// Both use mma.sync.m16n8k16 (bf16 in, fp32 accumulate) with operands staged in shared memory by
+// cp.async and read by ldmatrix.  Scores, the running maximum, the sum and the output accumulator
+// are fp32 (the reference keeps S, P, the maximum and O in bf16:
+// flash_gqa_varlen_kernel.cu:169-172,220-257); P is rounded to bf16 for the P*V product.
+// Visibility: the query at position p sees key c iff c <= p and (window == 0 or p - c < window).
+#include "common.cuh"
+
+#ifndef GF_HEAD_DIM
+#define GF_HEAD_DIM 128
+#endif
+
+namespace gf {
+
+constexpr int HD = GF_HEAD_DIM;
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16, <= 256");
+constexpr int ROW = HD + 8;          // padded smem row (elements): 16-byte chunks, odd chunk stride
+constexpr int KT = 64;               // keys per tile
+constexpr int NTHREADS = 128;
+constexpr int KCH = HD / 16;         // 16-wide chunks of the head size
+constexpr float LOG2E = 1.4426950408889634f;
+
+using bf16 = __nv_bfloat16;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool pred) {
+  const int n = pred ? 16 : 0;       // src-size 0: the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src),
+               "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Load keys [c0, c0 + KT) of one kv head into a [KT][ROW] tile; rows at or past `end` (or before
+// `begin`) are zero-filled and touch no page.
+__device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* __restrict__ pages,
+                                             const int* __restrict__ tbl, int c0, int begin,
+                                             int end, int page_size, size_t tok_stride, int kvh) {
+  constexpr int CH = HD / 8;                           // 16-byte chunks in a row
+  for (int i = threadIdx.x; i < KT * CH; i += NTHREADS) {
+    const int r = i / CH, ch = i - r * CH;
+    const int c = c0 + r;
+    const bool ok = c >= begin && c < end;
+    const bf16* src = pages;
+    if (ok) {
+      const int page = tbl[c / page_size];
+      src = pages + ((size_t)page * page_size + c % page_size) * tok_stride + (size_t)kvh * HD +
+            ch * 8;
+    }
+    cp_async16(dst + r * ROW + ch * 8, src, ok);
+  }
+}
+
+// S[16 x (8*NT)] += A(16 x HD) * K^T for the keys of rows [key0, key0 + 8*NT) of the tile.
+template <int NT>
+__device__ __forceinline__ void qk_tile(float (&s)[NT][4], const uint32_t (&qf)[KCH][4],
+                                        const bf16* ktile, int key0, int lane) {
+  static_assert(NT % 2 == 0, "");
+  const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+  for (int kc = 0; kc < KCH; ++kc) {
+#pragma unroll
+    for (int n2 = 0; n2 < NT / 2; ++n2) {
+      uint32_t b[4];
+      ldsm_x4(b, ktile + (key0 + n2 * 16 + (mi >> 1) * 8 + r) * ROW + kc * 16 + (mi & 1) * 8);
+      mma16816(s[2 * n2], qf[kc], b[0], b[1]);
+      mma16816(s[2 * n2 + 1], qf[kc], b[2], b[3]);
+    }
+  }
+}
+
+// O[16 x HD] += P(16 x 8*NT, bf16 from s) * V for the keys of rows [key0, key0 + 8*NT) of the tile.
+template <int NT>
+__device__ __forceinline__ void pv_tile(float (&o)[HD / 8][4], const float (&s)[NT][4],
+                                        const bf16* vtile, int key0, int lane) {
+  const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+  for (int kc = 0; kc < NT / 2; ++kc) {
+    uint32_t a[4];
+    a[0] = pack_bf16(s[2 * kc][0], s[2 * kc][1]);
+    a[1] = pack_bf16(s[2 * kc][2], s[2 * kc][3]);
+    a[2] = pack_bf16(s[2 * kc + 1][0], s[2 * kc + 1][1]);
+    a[3] = pack_bf16(s[2 * kc + 1][2], s[2 * kc + 1][3]);
+#pragma unroll
+    for (int n2 = 0; n2 < HD / 16; ++n2) {
+      uint32_t b[4];
+      ldsm_x4_t(b, vtile + (key0 + kc * 16 + (mi & 1) * 8 + r) * ROW + n2 * 16 + (mi >> 1) * 8);
+      mma16816(o[2 * n2], a, b[0], b[1]);
+      mma16816(o[2 * n2 + 1], a, b[2], b[3]);
+    }
+  }
+}
+
+// One online-softmax update of a warp's 16 rows over 8*NT keys.  s holds raw dot products on
+// entry and the probabilities on exit.  Columns are keys col0 + ...; row i of the pair (i = 0:
+// row g, i = 1: row g + 8) sees keys in [lo[i], hi[i]].  m and l are per-thread copies of the row
+// maximum (in log2 units) and a partial row sum.
+template <int NT>
+__device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[HD / 8][4],
+                                               float (&m)[2], float (&l)[2], int col0,
+                                               const int (&lo)[2], const int (&hi)[2],
+                                               float scale_log2, int lane) {
+  const int t = lane & 3;
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int j = 0; j < NT; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int c = col0 + 8 * j + 2 * t + (e & 1), i = e >> 1;
+      const float v = (c >= lo[i] && c <= hi[i]) ? s[j][e] * scale_log2 : -INFINITY;
+      s[j][e] = v;
+      mx[i] = fmaxf(mx[i], v);
+    }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+  }
+  float corr[2], mnew[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    mnew[i] = fmaxf(m[i], mx[i]);
+    corr[i] = mnew[i] == -INFINITY ? 1.f : exp2f(m[i] - mnew[i]);
+    m[i] = mnew[i];
+  }
+  float sum[2] = {0.f, 0.f};
+#pragma unroll
+  for (int j = 0; j < NT; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = e >> 1;
+      const float p = mnew[i] == -INFINITY ? 0.f : exp2f(s[j][e] - mnew[i]);
+      s[j][e] = p;
+      sum[i] += p;
+    }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) l[i] = l[i] * corr[i] + sum[i];
+#pragma unroll
+  for (int n = 0; n < HD / 8; ++n) {
+    o[n][0] *= corr[0];
+    o[n][1] *= corr[0];
+    o[n][2] *= corr[1];
+    o[n][3] *= corr[1];
+  }
+}
+
+// ================================================================================== decode
+// grid (splits, nkv * head_chunks, B); 4 warps, warp w owns keys [16w, 16w + 16) of every tile.
+// Partials: po [B, nh, splits, HD] fp32 unnormalised, pml [B, nh, splits, 2] = (max in log2 units,
+// sum).  With one split the normalised bf16 result goes straight to `out`.
+constexpr int DEC_STAGES = 3;
+
+__global__ void __launch_bounds__(NTHREADS)
+attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __restrict__ kpages,
+                   const bf16* __restrict__ vpages, const int* __restrict__ block_table,
+                   int table_stride, const int* __restrict__ cu_seqlens_q,
+                   const int* __restrict__ positions, bf16* __restrict__ out,
+                   float* __restrict__ po, float* __restrict__ pml, int nh, int nkv,
+                   int page_size, int window, float scale_log2, int splits) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* ks = reinterpret_cast<bf16*>(smem_raw);                 // [STAGES][KT][ROW]
+  bf16* vs = ks + DEC_STAGES * KT * ROW;                        // [STAGES][KT][ROW]
+  const int split = blockIdx.x, b = blockIdx.z;
+  const int G = nh / nkv;
+  const int chunks = (G + 15) / 16;
+  const int kvh = blockIdx.y / chunks, chunk = blockIdx.y - kvh * chunks;
+  const int h0 = kvh * G + chunk * 16;                          // first query head of this CTA
+  const int nrows = min(16, G - chunk * 16);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int row = cu_seqlens_q[b];
+  const int p = positions[row];
+  const int lo = window > 0 ? max(0, p - window + 1) : 0;
+  const int nkeys = p - lo + 1;
+  int per = (nkeys + splits - 1) / splits;
+  per = (per + KT - 1) / KT * KT;
+  const int begin = lo + split * per;
+  const int end = min(p + 1, begin + per);
+  const int* tbl = block_table + (size_t)b * table_stride;
+  const size_t tok_stride = (size_t)nkv * HD;
+
+  // query fragments straight from global memory: rows are the heads h0 + g and h0 + g + 8
+  uint32_t qf[KCH][4];
+  {
+    const bf16* qrow = q + (size_t)row * q_row_stride + (size_t)h0 * HD;
+#pragma unroll
+    for (int kc = 0; kc < KCH; ++kc) {
+      const int d = kc * 16 + 2 * t;
+      const uint32_t* r0 = reinterpret_cast<const uint32_t*>(qrow + (size_t)g * HD + d);
+      const uint32_t* r1 = reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * HD + d);
+      qf[kc][0] = g < nrows ? r0[0] : 0u;
+      qf[kc][1] = g + 8 < nrows ? r1[0] : 0u;
+      qf[kc][2] = g < nrows ? r0[4] : 0u;
+      qf[kc][3] = g + 8 < nrows ? r1[4] : 0u;
+    }
+  }
+  float o[HD / 8][4];
+#pragma unroll
+  for (int n = 0; n < HD / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  const int lo2[2] = {begin, begin}, hi2[2] = {end - 1, end - 1};
+
+  const int ntiles = begin < end ? (end - begin + KT - 1) / KT : 0;
+  for (int s = 0; s < DEC_STAGES - 1; ++s) {
+    if (s < ntiles) {
+      load_kv_tile(ks + s * KT * ROW, kpages, tbl, begin + s * KT, begin, end, page_size,
+                   tok_stride, kvh);
+      load_kv_tile(vs + s * KT * ROW, vpages, tbl, begin + s * KT, begin, end, page_size,
+                   tok_stride, kvh);
+    }
+    cp_async_commit();
+  }
+  for (int it = 0; it < ntiles; ++it) {
+    cp_async_wait<DEC_STAGES - 2>();
+    __syncthreads();
+    const int nxt = it + DEC_STAGES - 1;
+    if (nxt < ntiles) {
+      const int st = nxt % DEC_STAGES;
+      load_kv_tile(ks + st * KT * ROW, kpages, tbl, begin + nxt * KT, begin, end, page_size,
+                   tok_stride, kvh);
+      load_kv_tile(vs + st * KT * ROW, vpages, tbl, begin + nxt * KT, begin, end, page_size,
+                   tok_stride, kvh);
+    }
+    cp_async_commit();
+    const int st = it % DEC_STAGES;
+    const int col0 = begin + it * KT + warp * 16;
+    if (col0 < end) {
+      float s[2][4] = {};
+      qk_tile<2>(s, qf, ks + st * KT * ROW, warp * 16, lane);
+      softmax_update<2>(s, o, m, l, col0, lo2, hi2, scale_log2, lane);
+      pv_tile<2>(o, s, vs + st * KT * ROW, warp * 16, lane);
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // merge the four warps through shared memory (reusing the tile buffers)
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+  }
+  float* so = reinterpret_cast<float*>(smem_raw);               // [4][16][HD]
+  float* sm = so + 4 * 16 * HD;                                 // [4][16]
+  float* sl = sm + 4 * 16;                                      // [4][16]
+#pragma unroll
+  for (int n = 0; n < HD / 8; ++n) {
+    float* base = so + (warp * 16) * HD + n * 8 + 2 * t;
+    base[g * HD] = o[n][0];
+    base[g * HD + 1] = o[n][1];
+    base[(g + 8) * HD] = o[n][2];
+    base[(g + 8) * HD + 1] = o[n][3];
+  }
+  if (t == 0) {
+    sm[warp * 16 + g] = m[0];
+    sm[warp * 16 + g + 8] = m[1];
+    sl[warp * 16 + g] = l[0];
+    sl[warp * 16 + g + 8] = l[1];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < nrows * HD; i += NTHREADS) {
+    const int r = i / HD, d = i - r * HD;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, sm[w * 16 + r]);
+    float acc = 0.f, lsum = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float wgt = mm == -INFINITY ? 0.f : exp2f(sm[w * 16 + r] - mm);
+      acc += wgt * so[(w * 16 + r) * HD + d];
+      lsum += wgt * sl[w * 16 + r];
+    }
+    const int head = h0 + r;
+    if (splits == 1) {
+      out[((size_t)row * nh + head) * HD + d] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+    } else {
+      const size_t pi = ((size_t)b * nh + head) * splits + split;
+      po[pi * HD + d] = acc;
+      if (d == 0) {
+        pml[pi * 2] = mm;
+        pml[pi * 2 + 1] = lsum;
+      }
+    }
+  }
+}
+
+// grid (nh, B), HD threads... one thread per output channel (HD <= 256).
+__global__ void attn_decode_merge_kernel(const float* __restrict__ po,
+                                         const float* __restrict__ pml,
+                                         const int* __restrict__ cu_seqlens_q,
+                                         bf16* __restrict__ out, int nh, int splits) {
+  const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  const size_t base = ((size_t)b * nh + head) * splits;
+  float mm = -INFINITY;
+  for (int s = 0; s < splits; ++s) mm = fmaxf(mm, pml[(base + s) * 2]);
+  float acc = 0.f, lsum = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = pml[(base + s) * 2];
+    const float wgt = ms == -INFINITY ? 0.f : exp2f(ms - mm);
+    acc += wgt * po[(base + s) * HD + d];
+    lsum += wgt * pml[(base + s) * 2 + 1];
+  }
+  const int row = cu_seqlens_q[b];
+  out[((size_t)row * nh + head) * HD + d] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+}
+
+// ================================================================================== prefill
+// grid (q tiles, nh, B): 64 query rows of one head of one request; warp w owns rows 16w .. 16w+15.
+constexpr int PRE_STAGES = 2;
+constexpr int QT = 64;
+
+__global__ void __launch_bounds__(NTHREADS)
+attn_prefill_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __restrict__ kpages,
+                    const bf16* __restrict__ vpages, const int* __restrict__ block_table,
+                    int table_stride, const int* __restrict__ cu_seqlens_q,
+                    const int* __restrict__ kv_lens, bf16* __restrict__ out, int nh, int nkv,
+                    int page_size, int window, float scale_log2) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw);                 // [QT][ROW]
+  bf16* ks = qs + QT * ROW;                                     // [STAGES][KT][ROW]
+  bf16* vs = ks + PRE_STAGES * KT * ROW;
+  const int b = blockIdx.z, head = blockIdx.y;
+  const int q_begin = cu_seqlens_q[b], q_len = cu_seqlens_q[b + 1] - q_begin;
+  const int r0 = blockIdx.x * QT;
+  if (r0 >= q_len) return;
+  const int kv_len = kv_lens[b];
+  const int pos0 = kv_len - q_len;                              // position of the request's row 0
+  const int kvh = head / (nh / nkv);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2;
+  const int* tbl = block_table + (size_t)b * table_stride;
+  const size_t tok_stride = (size_t)nkv * HD;
+  const int rows = min(QT, q_len - r0);
+
+  // the tile's queries -> shared memory (rows past the request's end are zero)
+  {
+    constexpr int CH = HD / 8;
+    for (int i = threadIdx.x; i < QT * CH; i += NTHREADS) {
+      const int r = i / CH, ch = i - r * CH;
+      const bool ok = r < rows;
+      const bf16* src = ok ? q + (size_t)(q_begin + r0 + r) * q_row_stride + (size_t)head * HD +
+                                 ch * 8
+                           : q;
+      cp_async16(qs + r * ROW + ch * 8, src, ok);
+    }
+  }
+  // keys this tile can see: from the window's start of its first row to its last row's position
+  const int p_first = pos0 + r0, p_last = pos0 + r0 + rows - 1;
+  const int key_lo = window > 0 ? max(0, p_first - window + 1) : 0;
+  const int begin = key_lo / KT * KT, end = p_last + 1;
+  const int ntiles = (end - begin + KT - 1) / KT;
+  load_kv_tile(ks, kpages, tbl, begin, key_lo, end, page_size, tok_stride, kvh);
+  load_kv_tile(vs, vpages, tbl, begin, key_lo, end, page_size, tok_stride, kvh);
+  cp_async_commit();
+
+  uint32_t qf[KCH][4];
+  float o[HD / 8][4];
+#pragma unroll
+  for (int n = 0; n < HD / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  // visibility bounds of this thread's two rows (rows past the end see nothing)
+  int lo2[2], hi2[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = warp * 16 + g + 8 * i;
+    const int p = pos0 + r0 + r;
+    hi2[i] = r < rows ? p : -1;
+    lo2[i] = window > 0 ? max(0, p - window + 1) : 0;
+  }
+  const int warp_hi = min(p_last, pos0 + r0 + warp * 16 + 15);  // last key any row of the warp sees
+  const int warp_lo = window > 0 ? max(0, pos0 + r0 + warp * 16 - window + 1) : 0;
+
+  for (int it = 0; it < ntiles; ++it) {
+    cp_async_wait<0>();
+    __syncthreads();
+    if (it == 0) {
+      const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+      for (int kc = 0; kc < KCH; ++kc)
+        ldsm_x4(qf[kc], qs + (warp * 16 + (mi & 1) * 8 + r) * ROW + kc * 16 + (mi >> 1) * 8);
+    }
+    if (it + 1 < ntiles) {
+      const int st = (it + 1) % PRE_STAGES;
+      load_kv_tile(ks + st * KT * ROW, kpages, tbl, begin + (it + 1) * KT, key_lo, end, page_size,
+                   tok_stride, kvh);
+      load_kv_tile(vs + st * KT * ROW, vpages, tbl, begin + (it + 1) * KT, key_lo, end, page_size,
+                   tok_stride, kvh);
+    }
+    cp_async_commit();
+    const int st = it % PRE_STAGES;
+    const int col0 = begin + it * KT;
+    if (col0 <= warp_hi && col0 + KT > warp_lo && warp * 16 < rows) {
+      float s[8][4] = {};
+      qk_tile<8>(s, qf, ks + st * KT * ROW, 0, lane);
+      softmax_update<8>(s, o, m, l, col0, lo2, hi2, scale_log2, lane);
+      pv_tile<8>(o, s, vs + st * KT * ROW, 0, lane);
+    }
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+  }
+  const int t = lane & 3;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = warp * 16 + g + 8 * i;
+    if (r >= rows) continue;
+    const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
+    bf16* orow = out + ((size_t)(q_begin + r0 + r) * nh + head) * HD;
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) {
+      *reinterpret_cast<uint32_t*>(orow + n * 8 + 2 * t) =
+          pack_bf16(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
+    }
+  }
+}
+
+}  // namespace gf
+
+using namespace gf;
+
+GF_EXPORT int gf_attn_head_dim() { return HD; }
+
+// Bytes of scratch gf_attn_decode needs for B requests, nh heads and `splits` > 1 splits.
+GF_EXPORT long long gf_attn_decode_scratch_bytes(int B, int nh, int splits) {
+  return splits <= 1 ? 0 : (long long)B * nh * splits * (HD + 2) * (long long)sizeof(float);
+}
+
+// One query token per request (row cu_seqlens_q[b] of q / out).  scratch: fp32, at least
+// gf_attn_decode_scratch_bytes; may be null when splits == 1.
+GF_EXPORT int gf_attn_decode(const void* q, int q_row_stride, const void* kpages,
+                             const void* vpages, const int* block_table, int table_stride,
+                             const int* cu_seqlens_q, const int* positions, void* out,
+                             void* scratch, int B, int nh, int nkv, int page_size, int window,
+                             float scale, int splits, void* stream) {
+  if (B <= 0) return 0;
+  if (nh % nkv || splits < 1) return -3;
+  if (splits > 1 && !scratch) return -4;
+  auto st = (cudaStream_t)stream;
+  const int G = nh / nkv, chunks = (G + 15) / 16;
+  const size_t tiles = (size_t)2 * DEC_STAGES * KT * ROW * sizeof(bf16);
+  const size_t merge = (size_t)(4 * 16 * HD + 2 * 4 * 16) * sizeof(float);
+  const size_t smem = tiles > merge ? tiles : merge;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attr_done = true;
+  }
+  float* po = (float*)scratch;
+  float* pml = po ? po + (size_t)B * nh * splits * HD : nullptr;
+  dim3 grid(splits, nkv * chunks, B);
+  attn_decode_kernel<<<grid, NTHREADS, smem, st>>>(
+      (const bf16*)q, q_row_stride, (const bf16*)kpages, (const bf16*)vpages, block_table,
+      table_stride, cu_seqlens_q, positions, (bf16*)out, po, pml, nh, nkv, page_size, window,
+      scale * LOG2E, splits);
+  int rc = launch_status();
+  if (rc || splits == 1) return rc;
+  attn_decode_merge_kernel<<<dim3(nh, B), HD, 0, st>>>(po, pml, cu_seqlens_q, (bf16*)out, nh,
+                                                       splits);
+  return launch_status();
+}
+
+GF_EXPORT int gf_attn_prefill(const void* q, int q_row_stride, const void* kpages,
+                              const void* vpages, const int* block_table, int table_stride,
+                              const int* cu_seqlens_q, const int* kv_lens, void* out, int B,
+                              int max_q_len, int nh, int nkv, int page_size, int window,
+                              float scale, void* stream) {
+  if (B <= 0 || max_q_len <= 0) return 0;
+  if (nh % nkv) return -3;
+  auto st = (cudaStream_t)stream;
+  const size_t smem = (size_t)(QT + 2 * PRE_STAGES * KT) * ROW * sizeof(bf16);
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attr_done = true;
+  }
+  dim3 grid((max_q_len + QT - 1) / QT, nh, B);
+  attn_prefill_kernel<<<grid, NTHREADS, smem, st>>>(
+      (const bf16*)q, q_row_stride, (const bf16*)kpages, (const bf16*)vpages, block_table,
+      table_stride, cu_seqlens_q, kv_lens, (bf16*)out, nh, nkv, page_size, window, scale * LOG2E);
+  return launch_status();
+}

@@ -1,7 +1,81 @@
-"""bf16 attention kernels for the serving path: split-KV decode and tensor-core prefill."""
+"""bf16 attention kernels for the serving path (``csrc/attention_bf16.cu``): split-KV decode and
+tensor-core prefill over the paged cache.  The library is compiled for the model's head size."""
 from __future__ import annotations
+
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+KEY_TILE = 64
+TARGET_CTAS = 148 * 2          # two resident CTAs of the decode kernel per SM
+MAX_SPLITS = 64
+
+_scratch: dict = {}
+
+
+def supports(hd: int, nh: int, nkv: int) -> bool:
+    return hd % 16 == 0 and 16 <= hd <= 256 and nh % nkv == 0
+
+
+def decode_splits(batch: int, nh: int, nkv: int, max_keys: int) -> int:
+    """How many ways to split each request's keys so that the grid fills the GPU."""
+    chunks = (nh // nkv + 15) // 16
+    base = max(1, batch * nkv * chunks)
+    by_gpu = max(1, TARGET_CTAS // base)
+    by_len = max(1, -(-max_keys // KEY_TILE))
+    return int(min(by_gpu, by_len, MAX_SPLITS))
+
+
+def _scratch_for(nbytes: int, device) -> torch.Tensor:
+    key = (device.index if device.index is not None else torch.cuda.current_device())
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() * 4 < nbytes:
+        buf = torch.empty(max(nbytes // 4 + 1, 1 << 20), dtype=torch.float32, device=device)
+        _scratch[key] = buf
+    return buf
+
+
+def decode(qkv, pages, block_table, cu_seqlens_q, positions, B, nh, nkv, hd, scale, window,
+           page_size, splits, out=None, scratch=None):
+    from . import _fn, _ok, _p, _stream
+    defines = (f"GF_HEAD_DIM={hd}",)
+    if out is None:
+        out = torch.empty((qkv.shape[0], nh * hd), dtype=torch.bfloat16, device=qkv.device)
+    if splits > 1 and scratch is None:
+        scratch = _scratch_for(B * nh * splits * (hd + 2) * 4, qkv.device)
+    f = _fn("attention_bf16", "gf_attn_decode",
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p], defines,
+            kernels=2 if splits > 1 else 1)
+    _ok(f(_p(qkv), qkv.stride(0), _p(pages[0]), _p(pages[1]), _p(block_table),
+          block_table.stride(0), _p(cu_seqlens_q), _p(positions), _p(out), _p(scratch), B, nh,
+          nkv, page_size, int(window), float(scale), int(splits), _stream()), "attn_decode")
+    return out
+
+
+def prefill(qkv, pages, block_table, cu_seqlens_q, kv_lens, B, max_q_len, nh, nkv, hd, scale,
+            window, page_size):
+    from . import _fn, _ok, _p, _stream
+    out = torch.empty((qkv.shape[0], nh * hd), dtype=torch.bfloat16, device=qkv.device)
+    f = _fn("attention_bf16", "gf_attn_prefill",
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+            (f"GF_HEAD_DIM={hd}",))
+    _ok(f(_p(qkv), qkv.stride(0), _p(pages[0]), _p(pages[1]), _p(block_table),
+          block_table.stride(0), _p(cu_seqlens_q), _p(kv_lens), _p(out), B, int(max_q_len), nh,
+          nkv, page_size, int(window), float(scale), _stream()), "attn_prefill")
+    return out
 
 
 def try_run(qkv, pages, block_table, ctx, nh, nkv, hd, scale, window, page_size):
-    """Run a bf16 kernel if one takes this head size and batch shape; ``None`` otherwise."""
-    return None
+    """Run a bf16 kernel if one takes this head size; ``None`` hands the work to the plain
+    fp32-arithmetic kernel."""
+    if not supports(hd, nh, nkv):
+        return None
+    if ctx.decode_only:
+        keys = ctx.max_kv_len if window <= 0 else min(window, ctx.max_kv_len)
+        splits = ctx.extras.get("decode_splits") or decode_splits(ctx.num_seqs, nh, nkv, keys)
+        return decode(qkv, pages, block_table, ctx.cu_seqlens_q, ctx.positions, ctx.num_seqs, nh,
+                      nkv, hd, scale, window, page_size, splits)
+    return prefill(qkv, pages, block_table, ctx.cu_seqlens_q, ctx.kv_lens, ctx.num_seqs,
+                   ctx.max_q_len, nh, nkv, hd, scale, window, page_size)
