@@ -31,6 +31,18 @@ def _align4(n: int) -> int:
     return (n + 3) & ~3
 
 
+GRAPH_WIDTH_STEP = 64        # block-table widths of graph-replayed decode steps, in pages
+
+
+@dataclass
+class _DecodeGraph:
+    graph: object
+    ints: torch.Tensor            # static device buffer the graph's kernels read
+    spans: dict
+    logits: torch.Tensor
+    launches: int
+
+
 class ModelRunner:
     def __init__(self, model: DecoderModel, *, page_size: int, max_num_seqs: int,
                  max_seq_len: int, num_pages: int | None = None,
@@ -59,6 +71,8 @@ class ModelRunner:
         self.vocab_size = model.plan.vocab_size
         self._host = None            # pinned staging for the step's integers
         self._host_cap = 0
+        self._graphs: dict = {}
+        self._graph_pool = None
         self._copied = torch.cuda.Event()     # the last copy out of the staging buffer
         self._copy_pending = False
         self.steps_run = 0
@@ -153,6 +167,11 @@ class ModelRunner:
                 rows.append(cu[b] + int(w))
         logit_rows = np.asarray(rows, dtype=np.int64)
         width = int(-(-int(kv_lens.max()) // P))
+        decode_only = int(q_lens.max()) == 1
+        if decode_only and not self.enforce_eager:
+            # decode steps are replayed from CUDA graphs, one per (batch size, table width):
+            # widths come in steps of GRAPH_WIDTH_STEP pages so that few graphs are needed
+            width = min(cache.table_width, -(-width // GRAPH_WIDTH_STEP) * GRAPH_WIDTH_STEP)
         slots_of_token = slot_ids[seq_of_token]
         slot_maps = [cache.slot_mapping(g, slots_of_token, positions)
                      for g in range(cache.num_groups)]
@@ -166,8 +185,8 @@ class ModelRunner:
                      max_q_len=int(q_lens.max()), max_kv_len=int(kv_lens.max()))
         return arrays, facts
 
-    def upload(self, arrays: dict[str, np.ndarray]) -> dict[str, torch.Tensor]:
-        """One pinned buffer, one host-to-device copy; returns device views by name."""
+    def _pack(self, arrays: dict[str, np.ndarray]):
+        """Lay the arrays out in the pinned staging buffer; returns (host view, spans)."""
         total = sum(_align4(a.size) for a in arrays.values())
         if self._copy_pending:                # do not overwrite what the last copy still reads
             self._copied.synchronize()
@@ -179,10 +198,21 @@ class ModelRunner:
             hnp[off:off + n] = a.reshape(-1)
             spans[k] = (off, n, a.shape)
             off += _align4(n)
-        dev = host[:total].to(self.device, non_blocking=True)
-        self.h2d_bytes += 4 * total
+        return host[:total], spans
+
+    def upload(self, arrays: dict[str, np.ndarray], into: torch.Tensor | None = None
+               ) -> dict[str, torch.Tensor]:
+        """One pinned buffer, one host-to-device copy; returns device views by name.  ``into``:
+        an existing device buffer (of a CUDA graph) to copy into instead of a new one."""
+        host, spans = self._pack(arrays)
+        if into is None:
+            dev = host.to(self.device, non_blocking=True)
+        else:
+            dev = into
+            dev[:host.numel()].copy_(host, non_blocking=True)
         self._copied.record()
         self._copy_pending = True
+        self.h2d_bytes += 4 * host.numel()
         return {k: dev[o:o + n].view(shape) for k, (o, n, shape) in spans.items()}
 
     def make_context(self, dev: dict[str, torch.Tensor], facts: dict) -> StepContext:
@@ -210,15 +240,54 @@ class ModelRunner:
             return None
         return bind
 
+    def _graph_key(self, entries, facts):
+        """Decode steps in which every request wants its token's logits replay a CUDA graph."""
+        if self.enforce_eager or facts["max_q_len"] != 1 or self.storage.state:
+            return None
+        if any(len(e.want) != 1 for e in entries):
+            return None
+        return (facts["B"], facts["width"])
+
+    def _capture(self, key, arrays, facts) -> _DecodeGraph:
+        from .. import ops
+        total = sum(_align4(a.size) for a in arrays.values())
+        ints = torch.empty(total, dtype=torch.int32, device=self.device)
+        dev = self.upload(arrays, into=ints)
+        ctx = self.make_context(dev, facts)
+        # what the kernels may assume about lengths is the bucket's bound, not this step's
+        ctx.max_kv_len = min(facts["width"] * self.page_size, self.max_seq_len)
+        ctx.capturing = True
+        bind = self.binder(dev)
+        self.model.forward(ctx, bind)                 # once eagerly: libraries, handles, attributes
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        before = ops.launch_count()
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            logits = self.model.forward(ctx, bind)
+        return _DecodeGraph(graph, ints, {}, logits, ops.launch_count() - before)
+
     @torch.no_grad()
     def step(self, entries: list[StepEntry]) -> torch.Tensor:
         """Run the entries' tokens as one batch; returns fp32 logits ``[wanted, vocab]`` on the
-        device, in the order of the entries and of each entry's ``want``."""
+        device, in the order of the entries and of each entry's ``want``.  The tensor is valid
+        until the next call of ``step``."""
         arrays, facts = self.prepare(entries)
         with torch.cuda.device(self.device):
-            dev = self.upload(arrays)
-            ctx = self.make_context(dev, facts)
-            logits = self.model.forward(ctx, self.binder(dev))
+            key = self._graph_key(entries, facts)
+            if key is not None:
+                g = self._graphs.get(key)
+                if g is None:
+                    g = self._graphs[key] = self._capture(key, arrays, facts)
+                self.upload(arrays, into=g.ints)
+                g.graph.replay()
+                self.graph_launches += g.launches
+                logits = g.logits
+            else:
+                dev = self.upload(arrays)
+                ctx = self.make_context(dev, facts)
+                logits = self.model.forward(ctx, self.binder(dev))
         for e, n in zip(entries, facts["q_lens"]):
             self.cache.commit(e.request_id, int(n))
         self.steps_run += 1

@@ -22,6 +22,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--device", default="cuda:0")
     ap.add_argument("--page-size", type=int, default=TRACE_PAGE_SIZE)
     ap.add_argument("--max-live", type=int, default=TRACE_MAX_LIVE)
+    ap.add_argument("--enforce-eager", action="store_true",
+                    help="launch every kernel of a decode step instead of replaying a CUDA graph")
     return ap
 
 
@@ -44,7 +46,7 @@ def main(argv=None) -> int:
     runner = ModelRunner(model, page_size=args.page_size, max_num_seqs=args.max_live,
                          max_seq_len=min(budget, model.plan.max_positions),
                          num_pages=budget // args.page_size,
-                         max_num_batched_tokens=budget)
+                         max_num_batched_tokens=budget, enforce_eager=args.enforce_eager)
     for line in sys.stdin:
         line = line.strip()
         if not line:

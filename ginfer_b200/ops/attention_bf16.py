@@ -42,7 +42,13 @@ def decode(qkv, pages, block_table, cu_seqlens_q, positions, B, nh, nkv, hd, sca
     if out is None:
         out = torch.empty((qkv.shape[0], nh * hd), dtype=torch.bfloat16, device=qkv.device)
     if splits > 1 and scratch is None:
-        scratch = _scratch_for(B * nh * splits * (hd + 2) * 4, qkv.device)
+        nbytes = B * nh * splits * (hd + 2) * 4
+        if torch.cuda.is_current_stream_capturing():
+            # a graph keeps its own scratch (from the graph's memory pool): the shared buffer
+            # may be replaced by a larger one later
+            scratch = torch.empty(nbytes // 4, dtype=torch.float32, device=qkv.device)
+        else:
+            scratch = _scratch_for(nbytes, qkv.device)
     f = _fn("attention_bf16", "gf_attn_decode",
             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
              c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p], defines,

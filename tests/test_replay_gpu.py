@@ -30,13 +30,14 @@ def folders(tmp_path_factory):
             for n in CONFIGS for s in ("float32", "bfloat16")}
 
 
-def _runner(model_dir, dtype, page, max_tokens):
+def _runner(model_dir, dtype, page, max_tokens, eager=True):
     from ginfer_b200.engine import ModelRunner
     from ginfer_b200.engine.loading import load_model
     model, _ = load_model(model_dir, dtype)
     budget = -(-max_tokens // 64) * 64
     return ModelRunner(model, page_size=page, max_num_seqs=4, max_seq_len=budget,
-                       num_pages=budget // page, max_num_batched_tokens=budget)
+                       num_pages=budget // page, max_num_batched_tokens=budget,
+                       enforce_eager=eager)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -59,6 +60,34 @@ def test_cuts_agree_with_plain(folders, name, dtype, cut):
     replay.compare(rows, replay.plain_logits(model_dir, reqs, dtype), dtype, reqs)
     assert not runner.cache.requests and all(
         f == p.num_pages for f, p in zip(runner.cache.free_pages(), runner.cache.pools))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_decode_steps_replayed_from_cuda_graphs(folders, name, dtype):
+    """Long decoding, one token a step for two requests side by side, with decode steps replayed
+    from CUDA graphs (as serving does) and the block table growing past a graph's width."""
+    model_dir = folders[(name, _storage(dtype))]
+    v = CONFIGS[name]["vocab_size"]
+    reqs = {"x": prompt(300, v, seed=1), "y": prompt(180, v, seed=2)}
+    steps = [{"step": 0, "end": [], "entries": [
+        {"id": "x", "tokens": reqs["x"][:40], "want": list(range(40))},
+        {"id": "y", "tokens": reqs["y"][:3], "want": [0, 1, 2]}]}]
+    ax, ay = 40, 3
+    while ax < 300 or ay < 180:
+        ent = []
+        if ax < 300:
+            ent.append({"id": "x", "tokens": [reqs["x"][ax]], "want": [0]})
+            ax += 1
+        if ay < 180:
+            ent.append({"id": "y", "tokens": [reqs["y"][ay]], "want": [0]})
+            ay += 1
+        steps.append({"step": len(steps), "entries": ent, "end": []})
+    steps[-1]["end"] = ["x", "y"]
+    runner = _runner(model_dir, dtype, 4, 512, eager=False)
+    rows = replay.run_in_process(runner, steps)
+    assert len(runner._graphs) >= 2 and runner.graph_launches > 0
+    replay.compare(rows, replay.plain_logits(model_dir, reqs, dtype), dtype, reqs)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
