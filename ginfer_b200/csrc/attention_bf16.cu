@@ -187,6 +187,8 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[HD 
 // Partials: po [B, nh, splits, HD] fp32 unnormalised, pml [B, nh, splits, 2] = (max in log2 units,
 // sum).  With one split the normalised bf16 result goes straight to `out`.
 constexpr int DEC_STAGES = 3;
+constexpr int kMaxDecodeGroups = 1 << 16;     // (request, kv head, head chunk) triples with a counter
+__device__ unsigned int g_decode_done[kMaxDecodeGroups];
 
 __global__ void __launch_bounds__(NTHREADS)
 attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __restrict__ kpages,
@@ -194,8 +196,9 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
                    int table_stride, const int* __restrict__ cu_seqlens_q,
                    const int* __restrict__ positions, bf16* __restrict__ out,
                    float* __restrict__ po, float* __restrict__ pml, int nh, int nkv,
-                   int page_size, int window, float scale_log2, int splits) {
+                   int page_size, int window, float scale_log2, int splits, int fused_merge) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ bool last_split;
   bf16* ks = reinterpret_cast<bf16*>(smem_raw);                 // [STAGES][KT][ROW]
   bf16* vs = ks + DEC_STAGES * KT * ROW;                        // [STAGES][KT][ROW]
   const int split = blockIdx.x, b = blockIdx.z;
@@ -318,6 +321,34 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
         pml[pi * 2 + 1] = lsum;
       }
     }
+  }
+  if (splits == 1 || !fused_merge) return;
+  // the CTA that finishes this (request, kv head, chunk) last merges the splits' partial results
+  __threadfence();
+  __syncthreads();
+  const unsigned int group = (unsigned int)b * gridDim.y + blockIdx.y;
+  if (threadIdx.x == 0) {
+    const unsigned int done = atomicAdd(&g_decode_done[group], 1u);
+    last_split = done == (unsigned int)splits - 1;
+    if (last_split) g_decode_done[group] = 0;                   // ready for the next launch
+  }
+  __syncthreads();
+  if (!last_split) return;
+  __threadfence();
+  for (int i = threadIdx.x; i < nrows * HD; i += NTHREADS) {
+    const int r = i / HD, d = i - r * HD;
+    const int head = h0 + r;
+    const size_t base = ((size_t)b * nh + head) * splits;
+    float mm = -INFINITY;
+    for (int s2 = 0; s2 < splits; ++s2) mm = fmaxf(mm, __ldcg(pml + (base + s2) * 2));
+    float acc = 0.f, lsum = 0.f;
+    for (int s2 = 0; s2 < splits; ++s2) {
+      const float ms = __ldcg(pml + (base + s2) * 2);
+      const float wgt = ms == -INFINITY ? 0.f : exp2f(ms - mm);
+      acc += wgt * __ldcg(po + (base + s2) * HD + d);
+      lsum += wgt * __ldcg(pml + (base + s2) * 2 + 1);
+    }
+    out[((size_t)row * nh + head) * HD + d] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
   }
 }
 
@@ -489,12 +520,13 @@ GF_EXPORT int gf_attn_decode(const void* q, int q_row_stride, const void* kpages
   float* po = (float*)scratch;
   float* pml = po ? po + (size_t)B * nh * splits * HD : nullptr;
   dim3 grid(splits, nkv * chunks, B);
+  const int fused = (size_t)B * nkv * chunks <= (size_t)kMaxDecodeGroups ? 1 : 0;
   attn_decode_kernel<<<grid, NTHREADS, smem, st>>>(
       (const bf16*)q, q_row_stride, (const bf16*)kpages, (const bf16*)vpages, block_table,
       table_stride, cu_seqlens_q, positions, (bf16*)out, po, pml, nh, nkv, page_size, window,
-      scale * LOG2E, splits);
+      scale * LOG2E, splits, fused);
   int rc = launch_status();
-  if (rc || splits == 1) return rc;
+  if (rc || splits == 1 || fused) return rc;
   attn_decode_merge_kernel<<<dim3(nh, B), HD, 0, st>>>(po, pml, cu_seqlens_q, (bf16*)out, nh,
                                                        splits);
   return launch_status();

@@ -94,14 +94,13 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride,
 }
 
 // ----------------------------------------------------------------------------- silu(gate) * up
-// gu[t] = [gate (I) | up (I)]; out[t, i] = gate * 1/(1+exp(-gate)) * up in fp32.
+// gu[t] holds gate and up interleaved (gate_0, up_0, gate_1, up_1, ...), as the joined product of
+// row-interleaved weights writes them; out[t, i] = gate * 1/(1+exp(-gate)) * up in fp32.
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I,
-                                size_t total) {
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, size_t total) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (size_t)gridDim.x * blockDim.x) {
-    const size_t t = i / I, j = i - t * I;
-    const float g = to_f32(gu[t * 2 * I + j]), u = to_f32(gu[t * 2 * I + I + j]);
+    const float g = to_f32(gu[2 * i]), u = to_f32(gu[2 * i + 1]);
     out[i] = from_f32<T>(g * (1.0f / (1.0f + expf(-g))) * u);
   }
 }
@@ -188,9 +187,9 @@ GF_EXPORT int gf_silu_mul(const void* gu, void* out, int T, int I, int dtype, vo
   auto st = (cudaStream_t)stream;
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   if (dtype == GF_F32)
-    silu_mul_kernel<float><<<blocks, 256, 0, st>>>((const float*)gu, (float*)out, I, total);
+    silu_mul_kernel<float><<<blocks, 256, 0, st>>>((const float*)gu, (float*)out, total);
   else
     silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)gu,
-                                                           (__nv_bfloat16*)out, I, total);
+                                                           (__nv_bfloat16*)out, total);
   return launch_status();
 }

@@ -1,0 +1,430 @@
+// bf16 matrix products on the 5th-generation tensor cores: out[M, N] = x[M, K] * W[N, K]^T with fp32
+// accumulation in tensor memory, operands staged in shared memory by TMA.
+//
+// The weight matrix is the A operand: a CTA owns 128 rows of W (TMEM lanes) and BN tokens (TMEM
+// columns, BN = 16 .. 256), so the same kernel serves prefill (BN = 256) and decode, where a batch
+// of 8 .. 64 tokens would waste a 128-row tile if tokens were the A operand.  Both operands are
+// K-major in global memory (x [M, K] and W [N, K] as Hugging Face stores it), so no transposition
+// is needed; TMA writes 128-byte-swizzled [rows][64] tiles that the UMMA descriptors name directly.
+//
+// Roles (192 threads): warp 0 issues TMA loads through a ring of STAGES stages; warp 1 allocates
+// tensor memory and issues tcgen05.mma (one thread), releasing stages with tcgen05.commit; warps
+// 2..5 read the accumulator back with tcgen05.ld and run the epilogue:
+//   EPI_STORE  out = acc (+ bias[n]) as bf16 or fp32
+//   EPI_SILU   W rows are interleaved (gate_i, up_i): out[m, i] = silu(bf16(gate)) * bf16(up)
+// With split_k > 1 every split parks its fp32 partial tile in a workspace and the split that
+// finishes a tile last (counted with an atomic it resets) sums the partials in split order and
+// runs the epilogue: deterministic, and small-N products of a decode step still fill the GPU.
+//
+// The reference calls cuBLASLt for every product (ginfer/core/op/kernels/cuda/gemm_kernel/
+// gemm_kernel.cu:93-156, bias in the epilogue :112-121, fp32 compute :100) and has a separate
+// SwiGLU kernel (swiglu_kernel.cu:6-31).
+//
+// Every wait on an mbarrier is bounded: after kSpinLimit polls the waiter records an error code in
+// *err and leaves its loop; all roles then meet at the final barrier and tensor memory is freed.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace gf {
+
+using bf16 = __nv_bfloat16;
+
+constexpr int BM = 128;            // W rows per CTA = TMEM lanes
+constexpr int BK = 64;             // K elements per stage: one 128-byte swizzle row of bf16
+constexpr int UMMA_K = 16;
+constexpr int NTHREADS = 192;
+constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr int EPI_STORE = 0, EPI_SILU = 2;
+constexpr int kMaxTiles = 1 << 16;
+__device__ unsigned int g_tile_done[kMaxTiles];
+
+__host__ __device__ constexpr int stages_for(int bn) {
+  // ring of (16 KB + bn * 128 B) stages within ~200 KB, at most 8
+  return (200 * 1024) / (BM * BK * 2 + bn * BK * 2) > 8 ? 8
+                                                        : (200 * 1024) / (BM * BK * 2 + bn * BK * 2);
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+// Bounded wait: false (and *err = code) if the phase did not complete within the limit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, int code) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if (spin > 1024) __nanosleep(64);
+  }
+  if (err) atomicExch(err, code);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar,
+                                            int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+// K-major operand tile of [rows][64] bf16 written by TMA with 128-byte swizzle: rows are 128 bytes
+// apart, groups of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1 (sm_100),
+// layout type 2 (SWIZZLE_128B).  The tile base is 1024-byte aligned.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);          // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                           // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;                 // stride byte offset
+  d |= (uint64_t)1 << 46;                           // descriptor version
+  d |= (uint64_t)2 << 61;                           // SWIZZLE_128B
+  return d;
+}
+// D fp32, A and B bf16, both K-major, M = 128, N = bn.
+__host__ __device__ constexpr uint32_t umma_idesc(int bn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) |
+         ((uint32_t)(BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                     uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+               ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <typename OUT> __device__ __forceinline__ void store_out(OUT* p, float v);
+template <> __device__ __forceinline__ void store_out<bf16>(bf16* p, float v) {
+  *p = __float2bfloat16_rn(v);
+}
+template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
+
+// Epilogue of 16 accumulator columns (tokens m_base .. m_base + 15) of W row n for one thread.
+template <int EPI, typename OUT>
+__device__ __forceinline__ void epilogue16(float (&v)[16], OUT* __restrict__ out, int ldo,
+                                           const float* __restrict__ bias, int n, int m_base,
+                                           int M, int N, int lane) {
+  if (EPI == EPI_STORE) {
+    const float b = (bias && n < N) ? bias[n] : 0.f;
+    if (n < N) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if (m_base + j < M) store_out<OUT>(out + (size_t)(m_base + j) * ldo + n, v[j] + b);
+    }
+  } else {
+    // rows come in pairs (gate, up) on adjacent lanes; each lane finishes every other token
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float mine = __bfloat162float(__float2bfloat16_rn(v[j]));
+      const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+      if ((j & 1) == (lane & 1)) {
+        const float g = (lane & 1) ? other : mine, u = (lane & 1) ? mine : other;
+        const int pair = n >> 1;
+        if ((n | 1) < N && m_base + j < M)
+          store_out<OUT>(out + (size_t)(m_base + j) * ldo + pair,
+                         g * (1.0f / (1.0f + expf(-g))) * u);
+      }
+    }
+  }
+}
+
+template <int BN, int EPI, typename OUT>
+__global__ void __launch_bounds__(NTHREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+               const float* __restrict__ bias, OUT* __restrict__ out, int ldo, int M, int N, int K,
+               int split_k, float* __restrict__ workspace, int* __restrict__ err) {
+  constexpr int STAGES = stages_for(BN);
+  constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  extern __shared__ __align__(1024) unsigned char smem[];
+  unsigned char* tiles = (unsigned char*)(((uintptr_t)smem + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(tiles + STAGES * (A_BYTES + B_BYTES));
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;
+  uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
+  __shared__ bool is_last;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BM, m0 = blockIdx.y * BN, split = blockIdx.z;
+  const int nkb_all = (K + BK - 1) / BK;
+  const int per = (nkb_all + split_k - 1) / split_k;
+  const int kb0 = split * per, kb1 = min(nkb_all, kb0 + per);
+  const int nkb = max(0, kb1 - kb0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    mbar_init(acc_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_w) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_x) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % STAGES;
+        if (!mbar_wait(empty + s, ((i / STAGES) & 1) ^ 1, err, 1)) break;
+        mbar_expect_tx(full + s, A_BYTES + B_BYTES);
+        unsigned char* a = tiles + s * (A_BYTES + B_BYTES);
+        tma_load_2d(a, &tmap_w, full + s, (kb0 + i) * BK, n0);
+        tma_load_2d(a + A_BYTES, &tmap_x, full + s, (kb0 + i) * BK, m0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(BN);
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int s = i % STAGES;
+        ok = mbar_wait(full + s, (i / STAGES) & 1, err, 2);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a = smem_u32(tiles + s * (A_BYTES + B_BYTES));
+        const uint64_t ad = umma_desc(a), bd = umma_desc(a + A_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k)
+          umma(tmem, ad + (uint64_t)(k * UMMA_K * 2 >> 4), bd + (uint64_t)(k * UMMA_K * 2 >> 4),
+               idesc, (i > 0 || k > 0) ? 1u : 0u);
+        umma_commit(empty + s);            // the stage is free once these MMAs have read it
+      }
+      umma_commit(acc_full);               // the accumulator is complete
+    }
+  } else {
+    // epilogue warps: TMEM lanes (warp % 4) * 32 .. + 31
+    const int q = warp & 3;
+    const int n = n0 + q * 32 + lane;
+    const bool ok = mbar_wait(acc_full, 0, err, 3);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+      const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16);
+      if (split_k == 1) {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+          if (m0 + c >= M) break;
+          float v[16];
+          if (nkb > 0) {
+            tmem_ld16(taddr + c, v);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = 0.f;
+          }
+          epilogue16<EPI, OUT>(v, out, ldo, bias, n, m0 + c, M, N, lane);
+        }
+      } else {
+        // park this split's partial tile: workspace[tile][split][row (128)][col (BN)]
+        const size_t tile = (size_t)blockIdx.y * gridDim.x + blockIdx.x;
+        float* mine = workspace + ((tile * split_k + split) * BM + (q * 32 + lane)) * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+          if (m0 + c >= M) break;
+          float v[16];
+          if (nkb > 0) {
+            tmem_ld16(taddr + c, v);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = 0.f;
+          }
+#pragma unroll
+          for (int j = 0; j < 16; j += 4)
+            __stcg(reinterpret_cast<float4*>(mine + c + j), make_float4(v[j], v[j + 1], v[j + 2],
+                                                                        v[j + 3]));
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem),
+                 "r"(TMEM_COLS)
+                 : "memory");
+  }
+  if (split_k == 1) return;
+
+  // the split that finishes this tile last adds the partials up in split order
+  __threadfence();
+  __syncthreads();
+  const unsigned int tile = blockIdx.y * gridDim.x + blockIdx.x;
+  if (threadIdx.x == 0) {
+    const unsigned int done = atomicAdd(&g_tile_done[tile], 1u);
+    is_last = done == (unsigned int)split_k - 1;
+    if (is_last) g_tile_done[tile] = 0;
+  }
+  __syncthreads();
+  if (!is_last || warp < 2) return;
+  __threadfence();
+  const int q = warp & 3;
+  const int row = q * 32 + lane, n = n0 + row;
+  const float* base = workspace + ((size_t)tile * split_k * BM + row) * BN;
+#pragma unroll 1
+  for (int c = 0; c < BN; c += 16) {
+    if (m0 + c >= M) break;
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = 0.f;
+    for (int s = 0; s < split_k; ++s) {
+      const float* p = base + (size_t)s * BM * BN + c;
+#pragma unroll
+      for (int j = 0; j < 16; j += 4) {
+        const float4 t = __ldcg(reinterpret_cast<const float4*>(p + j));
+        v[j] += t.x;
+        v[j + 1] += t.y;
+        v[j + 2] += t.z;
+        v[j + 3] += t.w;
+      }
+    }
+    epilogue16<EPI, OUT>(v, out, ldo, bias, n, m0 + c, M, N, lane);
+  }
+}
+
+// ----------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+            cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// rows x cols bf16, row-major with `ld` elements between rows; box = box_rows x 64, 128B swizzle
+static bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
+            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int EPI, typename OUT>
+static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* out,
+                  int ldo, int M, int N, int K, int split_k, float* workspace, int* err,
+                  cudaStream_t st) {
+  constexpr int STAGES = stages_for(BN);
+  const size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) +
+                      (2 * STAGES + 1) * sizeof(uint64_t) + 16;
+  auto k = gemm_tc_kernel<BN, EPI, OUT>;
+  static bool done = false;
+  if (!done) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    done = true;
+  }
+  dim3 grid((N + BM - 1) / BM, (M + BN - 1) / BN, split_k);
+  k<<<grid, NTHREADS, smem, st>>>(mw, mx, bias, (OUT*)out, ldo, M, N, K, split_k, workspace, err);
+  return launch_status();
+}
+
+template <int EPI, typename OUT>
+static int dispatch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const float* bias,
+                       void* out, int ldo, int M, int N, int K, int split_k, float* workspace,
+                       int* err, cudaStream_t st) {
+  switch (bn) {
+    case 16: return launch<16, EPI, OUT>(mw, mx, bias, out, ldo, M, N, K, split_k, workspace, err, st);
+    case 32: return launch<32, EPI, OUT>(mw, mx, bias, out, ldo, M, N, K, split_k, workspace, err, st);
+    case 64: return launch<64, EPI, OUT>(mw, mx, bias, out, ldo, M, N, K, split_k, workspace, err, st);
+    case 128: return launch<128, EPI, OUT>(mw, mx, bias, out, ldo, M, N, K, split_k, workspace, err, st);
+    case 256: return launch<256, EPI, OUT>(mw, mx, bias, out, ldo, M, N, K, split_k, workspace, err, st);
+  }
+  return -7;
+}
+
+}  // namespace gf
+
+using namespace gf;
+
+GF_EXPORT int gf_gemm_bf16_token_tile(int M) {
+  return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+}
+
+// fp32 words of workspace that split_k > 1 needs.
+GF_EXPORT long long gf_gemm_bf16_workspace_words(int M, int N, int split_k) {
+  if (split_k <= 1) return 0;
+  const int bn = gf_gemm_bf16_token_tile(M);
+  const long long tiles = (long long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
+  return tiles * split_k * BM * bn;
+}
+
+// out[M, *] = x[M, K] * W[N, K]^T.  epi 0: out[m, n] = acc + bias[n]; epi 2: W rows interleaved
+// (gate_i, up_i), out[m, i] = silu(gate) * up, N even.  out_f32: fp32 output (epi 0 only).
+// ldx, ldo in elements.  err: a device int that receives a non-zero code if a wait ran out.
+// Returns -6 when the shape or alignment cannot be served (the caller uses another product).
+GF_EXPORT int gf_gemm_bf16_tc(const void* x, int ldx, const void* w, const float* bias, void* out,
+                              int ldo, int M, int N, int K, int epi, int out_f32, int split_k,
+                              void* workspace, int* err, void* stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 || ldx % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return -6;
+  if (epi == EPI_SILU && ((N & 1) || out_f32)) return -6;
+  if (epi != EPI_STORE && epi != EPI_SILU) return -6;
+  const int bn = gf_gemm_bf16_token_tile(M);
+  if (split_k < 1) split_k = 1;
+  const long long tiles = (long long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
+  if (split_k > 1 && (!workspace || tiles > kMaxTiles)) return -6;
+  CUtensorMap mw, mx;
+  if (!make_map(&mw, w, N, K, K, BM) || !make_map(&mx, x, M, K, ldx, bn)) return -6;
+  auto st = (cudaStream_t)stream;
+  float* ws = (float*)workspace;
+  if (epi == EPI_SILU)
+    return dispatch_bn<EPI_SILU, bf16>(bn, mw, mx, bias, out, ldo, M, N, K, split_k, ws, err, st);
+  if (out_f32)
+    return dispatch_bn<EPI_STORE, float>(bn, mw, mx, bias, out, ldo, M, N, K, split_k, ws, err, st);
+  return dispatch_bn<EPI_STORE, bf16>(bn, mw, mx, bias, out, ldo, M, N, K, split_k, ws, err, st);
+}

@@ -39,12 +39,67 @@ __device__ int row_argmax(const float* __restrict__ x, int V, float* sval, int* 
   return r;
 }
 
-__global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
+// Arg-max of long rows in two stages inside one launch: every block reduces one chunk of a row and
+// parks its (value, index); the block that finishes a row last (counted with an atomic that it
+// resets for the next launch) reduces the parked pairs.  kMaxRows bounds the counters.
+constexpr int kChunk = 4096;
+constexpr int kMaxRows = 4096;
+__device__ unsigned int g_row_done[kMaxRows];
+
+__global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V,
+                              float* __restrict__ pval, int* __restrict__ pidx) {
   __shared__ float sval[kThreads / 32];
   __shared__ int sidx[kThreads / 32];
-  float mx;
-  const int r = row_argmax(logits + (size_t)blockIdx.x * V, V, sval, sidx, &mx);
-  if (threadIdx.x == 0) out[blockIdx.x] = r;
+  __shared__ bool last;
+  const int row = blockIdx.y, chunk = blockIdx.x, nchunks = gridDim.x;
+  const float* x = logits + (size_t)row * V;
+  const int j0 = chunk * kChunk, j1 = min(V, j0 + kChunk);
+  float v = -INFINITY;
+  int idx = 0x7fffffff;
+  for (int j = j0 + threadIdx.x; j < j1; j += blockDim.x) better(v, idx, x[j], j);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    better(v, idx, ov, oi);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { sval[warp] = v; sidx[warp] = idx; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (blockDim.x >> 5); ++w) better(v, idx, sval[w], sidx[w]);
+    if (nchunks == 1) {
+      out[row] = idx == 0x7fffffff ? 0 : idx;
+      last = false;
+    } else {
+      pval[(size_t)row * nchunks + chunk] = v;
+      pidx[(size_t)row * nchunks + chunk] = idx;
+      __threadfence();
+      const unsigned int done = atomicAdd(&g_row_done[row], 1u);
+      last = done == (unsigned int)nchunks - 1;
+    }
+  }
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  v = -INFINITY;
+  idx = 0x7fffffff;
+  for (int c = threadIdx.x; c < nchunks; c += blockDim.x)
+    better(v, idx, __ldcg(pval + (size_t)row * nchunks + c), __ldcg(pidx + (size_t)row * nchunks + c));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    better(v, idx, ov, oi);
+  }
+  __syncthreads();
+  if (lane == 0) { sval[warp] = v; sidx[warp] = idx; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (blockDim.x >> 5); ++w) better(v, idx, sval[w], sidx[w]);
+    out[row] = idx == 0x7fffffff ? 0 : idx;
+    g_row_done[row] = 0;                       // ready for the next launch
+  }
 }
 
 // temperature[r] <= 0: arg-max.  Otherwise w_j = expf((x_j - max) / temperature); thread i owns the
@@ -107,9 +162,15 @@ __global__ void sample_kernel(const float* __restrict__ logits, const float* __r
 
 using namespace gf;
 
-GF_EXPORT int gf_argmax(const float* logits, int* out, int R, int V, void* stream) {
+// scratch: room for 2 * R * ceil(V / 4096) 32-bit words (parked pairs); may be null when V <= 4096.
+GF_EXPORT int gf_argmax(const float* logits, int* out, int R, int V, void* scratch, void* stream) {
   if (R <= 0) return 0;
-  argmax_kernel<<<R, kThreads, 0, (cudaStream_t)stream>>>(logits, out, V);
+  if (R > kMaxRows) return -5;
+  const int nchunks = (V + kChunk - 1) / kChunk;
+  if (nchunks > 1 && !scratch) return -4;
+  float* pval = (float*)scratch;
+  int* pidx = (int*)scratch + (size_t)R * nchunks;
+  argmax_kernel<<<dim3(nchunks, R), kThreads, 0, (cudaStream_t)stream>>>(logits, out, V, pval, pidx);
   return launch_status();
 }
 

@@ -14,6 +14,7 @@ from dataclasses import dataclass, field
 import torch
 
 from ..config.engine_config import EngineConfig
+from ..ops import gemm_bf16
 from ..sampling import Sampler, SamplingParams
 from .loading import load_model, random_model
 from .request import Request, RequestState
@@ -106,6 +107,7 @@ class Engine:
             tokens = self.sampler.sample(
                 logits, [s.request.params.temperature for s in picks],
                 [s.request.seed for s in picks], [len(s.request.output) for s in picks])
+            gemm_bf16.check_errors(self.cfg.device)
             finished += self.scheduler.postprocess(batch, tokens)
             dt = time.perf_counter() - t0
             if any(s.num_tokens > 1 for s in batch):

@@ -37,6 +37,7 @@ def main(argv=None) -> int:
         return 2
     import torch
 
+    from ..ops import gemm_bf16
     from .loading import load_model
     from .runner import ModelRunner, StepEntry
 
@@ -59,6 +60,7 @@ def main(argv=None) -> int:
             logits = runner.step(entries)
             if logits.shape[0]:
                 arr = logits.to(torch.float32).cpu().numpy().astype("<f4", copy=False)
+                gemm_bf16.check_errors(args.device)
                 tmp = os.path.join(args.out, f".{step}.f32.tmp")
                 arr.tofile(tmp)
                 os.replace(tmp, os.path.join(args.out, f"{step}.f32"))

@@ -145,6 +145,7 @@ def rope_kv_write(qkv: torch.Tensor, table, rotary_dim: int, positions: torch.Te
 
 # ----------------------------------------------------------------------------- silu * up
 def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """``gate_up [T, 2 I]`` with gate and up interleaved (g0, u0, g1, u1, ...) -> ``[T, I]``."""
     _cuda(gate_up)
     assert gate_up.dim() == 2 and gate_up.is_contiguous() and gate_up.shape[1] % 2 == 0
     T, I = gate_up.shape[0], gate_up.shape[1] // 2
@@ -190,13 +191,27 @@ def paged_attention(qkv: torch.Tensor, pages: torch.Tensor, block_table: torch.T
 
 
 # ----------------------------------------------------------------------------- sampling
+_argmax_scratch: dict = {}
+
+
 def argmax(logits: torch.Tensor) -> torch.Tensor:
     _cuda(logits)
     assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous()
     R, V = logits.shape
     out = torch.empty((R,), dtype=torch.int32, device=logits.device)
-    f = _fn("sampling", "gf_argmax", [c_void_p, c_void_p, c_int, c_int, c_void_p])
-    _ok(f(_p(logits), _p(out), R, V, _stream()), "argmax")
+    words = 2 * R * (-(-V // 4096))
+    if torch.cuda.is_current_stream_capturing():
+        scratch = torch.empty(words, dtype=torch.int32, device=logits.device)
+    else:
+        scratch = _argmax_scratch.get(logits.device)
+        if scratch is None or scratch.numel() < words:
+            scratch = torch.empty(max(words, 1 << 16), dtype=torch.int32, device=logits.device)
+            _argmax_scratch[logits.device] = scratch
+    f = _fn("sampling", "gf_argmax", [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p])
+    rc = f(_p(logits), _p(out), R, V, _p(scratch), _stream())
+    if rc == -5:
+        raise ValueError(f"argmax takes at most 4096 rows at a time, got {R}")
+    _ok(rc, "argmax")
     return out
 
 

@@ -52,7 +52,7 @@ def decode(qkv, pages, block_table, cu_seqlens_q, positions, B, nh, nkv, hd, sca
     f = _fn("attention_bf16", "gf_attn_decode",
             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
              c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p], defines,
-            kernels=2 if splits > 1 else 1)
+            kernels=1)
     _ok(f(_p(qkv), qkv.stride(0), _p(pages[0]), _p(pages[1]), _p(block_table),
           block_table.stride(0), _p(cu_seqlens_q), _p(positions), _p(out), _p(scratch), B, nh,
           nkv, page_size, int(window), float(scale), int(splits), _stream()), "attn_decode")

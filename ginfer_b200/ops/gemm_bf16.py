@@ -1,7 +1,94 @@
-"""bf16 matrix products on the 5th-generation tensor cores (``csrc/gemm_bf16.cu``)."""
+"""bf16 matrix products on the 5th-generation tensor cores (``csrc/gemm_bf16.cu``: tcgen05.mma with
+the accumulator in tensor memory, operands staged by TMA)."""
 from __future__ import annotations
+
+from ctypes import c_int, c_void_p
+
+import torch
+
+NUM_SMS = 148
+_state: dict = {}
+
+
+def _dev_state(device):
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    st = _state.get(key)
+    if st is None:
+        st = {"err": torch.zeros(1, dtype=torch.int32, device=device), "ws": None}
+        _state[key] = st
+    return st
+
+
+def check_errors(device="cuda:0") -> None:
+    """Raise if a kernel gave up a bounded wait since the last check (reads one int back)."""
+    st = _state.get(torch.device(device).index or 0)
+    if st is None:
+        return
+    code = int(st["err"].item())
+    if code:
+        st["err"].zero_()
+        raise RuntimeError(f"gemm_bf16: a wait inside the tcgen05 kernel ran out (role {code}: "
+                           "1 = TMA producer, 2 = MMA issuer, 3 = epilogue)")
+
+
+def token_tile(M: int) -> int:
+    return 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
+
+
+def split_k_for(M: int, N: int, K: int) -> int:
+    """Split the K range of products whose tiles alone would leave most SMs idle."""
+    tiles = -(-N // 128) * -(-M // token_tile(M))
+    nkb = -(-K // 64)
+    if tiles * 4 >= NUM_SMS * 3 or nkb < 4:
+        return 1
+    return max(1, min(-(-NUM_SMS // tiles), nkb // 2, 16))
+
+
+def _workspace(words: int, device) -> torch.Tensor:
+    if torch.cuda.is_current_stream_capturing():
+        return torch.empty(words, dtype=torch.float32, device=device)
+    st = _dev_state(device)
+    if st["ws"] is None or st["ws"].numel() < words:
+        st["ws"] = torch.empty(max(words, 1 << 22), dtype=torch.float32, device=device)
+    return st["ws"]
+
+
+def supports(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    K = weight.shape[1]
+    return (K % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def gemm(x, weight, bias_f32=None, out_dtype=torch.bfloat16, epi: int = 0, split_k=None):
+    """``x [M, K] @ weight[N, K]^T``; ``epi`` 0: (+ bias) -> ``[M, N]``; ``epi`` 2: weight rows
+    are interleaved (gate_i, up_i) and the result is ``silu(gate) * up`` -> ``[M, N / 2]``.
+    Returns ``None`` if the kernel cannot serve the shape."""
+    from . import _fn, _ok, _p, _stream
+    if not supports(x, weight):
+        return None
+    M, K = x.shape
+    N = weight.shape[0]
+    cols = N // 2 if epi == 2 else N
+    out = torch.empty((M, cols), dtype=out_dtype, device=x.device)
+    if M == 0:
+        return out
+    sk = split_k_for(M, N, K) if split_k is None else int(split_k)
+    ws = None
+    if sk > 1:
+        bn = token_tile(M)
+        ws = _workspace(-(-N // 128) * -(-M // bn) * sk * 128 * bn, x.device)
+    st = _dev_state(x.device)
+    f = _fn("gemm_bf16", "gf_gemm_bf16_tc",
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+             c_int, c_int, c_void_p, c_void_p, c_void_p])
+    rc = f(_p(x), x.stride(0), _p(weight), _p(bias_f32), _p(out), cols, M, N, K, int(epi),
+           1 if out_dtype == torch.float32 else 0, sk, _p(ws), _p(st["err"]), _stream())
+    if rc in (-6, -7):
+        return None
+    _ok(rc, "gemm_bf16_tc")
+    return out
 
 
 def try_linear(x, weight, bias_f32, out_dtype):
     """Run the tcgen05 kernel if it takes this shape; ``None`` hands the product to cuBLAS."""
-    return None
+    return gemm(x, weight, bias_f32, out_dtype, epi=0)

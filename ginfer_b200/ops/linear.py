@@ -73,12 +73,21 @@ class Linear:
 
 
 class GatedLinear:
-    """``silu(x W_g^T) * (x W_u^T)`` over joined weights, so ``x`` is read once."""
+    """``silu(x W_g^T) * (x W_u^T)``.  The two matrices are joined row by row (gate_0, up_0,
+    gate_1, up_1, ...) so that ``x`` is read once and a gate meets its up value in neighbouring
+    accumulator rows: the tcgen05 kernel combines them in its epilogue and writes only the
+    product.  Gate and up are rounded to the activation dtype before they are combined, whichever
+    kernel runs, so the result does not depend on the kernel chosen."""
 
     def __init__(self, gate: torch.Tensor, up: torch.Tensor):
         assert gate.shape == up.shape and gate.dtype == up.dtype
-        self.intermediate = gate.shape[0]
-        self.proj = Linear(torch.cat([gate, up], dim=0))
+        self.intermediate, k = gate.shape
+        self.proj = Linear(torch.stack([gate, up], dim=1).reshape(2 * self.intermediate, k))
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        if x.dtype == torch.bfloat16:
+            from . import gemm_bf16
+            z = gemm_bf16.gemm(x, self.proj.weight, None, torch.bfloat16, epi=2)
+            if z is not None:
+                return z
         return silu_mul(self.proj(x))
