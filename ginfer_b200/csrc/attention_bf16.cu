@@ -6,7 +6,8 @@
 //    loaded (the reference's decode kernel reads K/V once per query head:
 //    ginfer/core/op/kernels/cuda/page_attn_kernel/flash_gqa_varlen_decode_kvcache.cu:272-335).
 //    Splits write fp32 partial results (running maximum, sum, unnormalised output) to scratch
-//    memory and gf_attn_decode's second kernel merges them.
+//    memory; the CTA that finishes a (request, kv head) last merges them (a second kernel does it
+//    when there are more such groups than counters).
 //  * gf_attn_prefill: any number of query tokens per request (portions of prompts, and single
 //    tokens beside them).  One CTA per (64 query rows of one head); keys are visited in tiles of 64
 //    through the block table.
@@ -69,23 +70,39 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Load keys [c0, c0 + KT) of one kv head into a [KT][ROW] tile; rows at or past `end` (or before
-// `begin`) are zero-filled and touch no page.
-__device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* __restrict__ pages,
-                                             const int* __restrict__ tbl, int c0, int begin,
-                                             int end, int page_size, size_t tok_stride, int kvh) {
+// Load keys [c0, c0 + KT) of one kv head into [KT][ROW] tiles of K and V; rows at or past `end` (or
+// before `begin`) are zero-filled and touch no page.  The block-table look-ups of all of a thread's
+// rows are issued first, so that they overlap instead of each waiting for the one before.
+__device__ __forceinline__ void load_kv_tiles(bf16* kdst, bf16* vdst,
+                                              const bf16* __restrict__ kpages,
+                                              const bf16* __restrict__ vpages,
+                                              const int* __restrict__ tbl, int c0, int begin,
+                                              int end, int page_size, size_t tok_stride, int kvh) {
   constexpr int CH = HD / 8;                           // 16-byte chunks in a row
-  for (int i = threadIdx.x; i < KT * CH; i += NTHREADS) {
+  constexpr int ITERS = (KT * CH + NTHREADS - 1) / NTHREADS;
+  long long off[ITERS];                                // element offset of the chunk, -1: no load
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int i = threadIdx.x + it * NTHREADS;
     const int r = i / CH, ch = i - r * CH;
     const int c = c0 + r;
-    const bool ok = c >= begin && c < end;
-    const bf16* src = pages;
+    const bool ok = i < KT * CH && c >= begin && c < end;
+    off[it] = -1;
     if (ok) {
-      const int page = tbl[c / page_size];
-      src = pages + ((size_t)page * page_size + c % page_size) * tok_stride + (size_t)kvh * HD +
-            ch * 8;
+      const int page = __ldg(tbl + c / page_size);
+      off[it] = ((long long)page * page_size + c % page_size) * (long long)tok_stride +
+                (long long)kvh * HD + ch * 8;
     }
-    cp_async16(dst + r * ROW + ch * 8, src, ok);
+  }
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int i = threadIdx.x + it * NTHREADS;
+    if (i < KT * CH) {
+      const int r = i / CH, ch = i - r * CH;
+      const bool ok = off[it] >= 0;
+      cp_async16(kdst + r * ROW + ch * 8, ok ? kpages + off[it] : kpages, ok);
+      cp_async16(vdst + r * ROW + ch * 8, ok ? vpages + off[it] : vpages, ok);
+    }
   }
 }
 
@@ -208,6 +225,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
   const int h0 = kvh * G + chunk * 16;                          // first query head of this CTA
   const int nrows = min(16, G - chunk * 16);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  pdl_trigger();
+  pdl_wait();
   const int row = cu_seqlens_q[b];
   const int p = positions[row];
   const int lo = window > 0 ? max(0, p - window + 1) : 0;
@@ -242,12 +261,9 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
 
   const int ntiles = begin < end ? (end - begin + KT - 1) / KT : 0;
   for (int s = 0; s < DEC_STAGES - 1; ++s) {
-    if (s < ntiles) {
-      load_kv_tile(ks + s * KT * ROW, kpages, tbl, begin + s * KT, begin, end, page_size,
-                   tok_stride, kvh);
-      load_kv_tile(vs + s * KT * ROW, vpages, tbl, begin + s * KT, begin, end, page_size,
-                   tok_stride, kvh);
-    }
+    if (s < ntiles)
+      load_kv_tiles(ks + s * KT * ROW, vs + s * KT * ROW, kpages, vpages, tbl, begin + s * KT,
+                    begin, end, page_size, tok_stride, kvh);
     cp_async_commit();
   }
   for (int it = 0; it < ntiles; ++it) {
@@ -256,10 +272,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
     const int nxt = it + DEC_STAGES - 1;
     if (nxt < ntiles) {
       const int st = nxt % DEC_STAGES;
-      load_kv_tile(ks + st * KT * ROW, kpages, tbl, begin + nxt * KT, begin, end, page_size,
-                   tok_stride, kvh);
-      load_kv_tile(vs + st * KT * ROW, vpages, tbl, begin + nxt * KT, begin, end, page_size,
-                   tok_stride, kvh);
+      load_kv_tiles(ks + st * KT * ROW, vs + st * KT * ROW, kpages, vpages, tbl, begin + nxt * KT,
+                    begin, end, page_size, tok_stride, kvh);
     }
     cp_async_commit();
     const int st = it % DEC_STAGES;
@@ -335,20 +349,40 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
   __syncthreads();
   if (!last_split) return;
   __threadfence();
-  for (int i = threadIdx.x; i < nrows * HD; i += NTHREADS) {
-    const int r = i / HD, d = i - r * HD;
-    const int head = h0 + r;
-    const size_t base = ((size_t)b * nh + head) * splits;
+  // weights of the splits first (through shared memory), then every thread adds up its channels
+  // with independent loads; splits past the request's keys hold nothing and are passed over
+  const int used = min(splits, per > 0 ? (nkeys + per - 1) / per : 0);
+  float* w = reinterpret_cast<float*>(smem_raw);                 // [16][used]: weight of a split
+  float* linv = w + 16 * used;                                   // [16]: 1 / total sum
+  __syncthreads();
+  for (int i = threadIdx.x; i < nrows * used; i += NTHREADS) {
+    const int r = i / used, s2 = i - r * used;
+    const size_t base = ((size_t)b * nh + h0 + r) * splits;
+    w[r * used + s2] = __ldcg(pml + (base + s2) * 2);            // the split's maximum for now
+  }
+  __syncthreads();
+  if (threadIdx.x < nrows) {
+    const int r = threadIdx.x;
+    const size_t base = ((size_t)b * nh + h0 + r) * splits;
     float mm = -INFINITY;
-    for (int s2 = 0; s2 < splits; ++s2) mm = fmaxf(mm, __ldcg(pml + (base + s2) * 2));
-    float acc = 0.f, lsum = 0.f;
-    for (int s2 = 0; s2 < splits; ++s2) {
-      const float ms = __ldcg(pml + (base + s2) * 2);
+    for (int s2 = 0; s2 < used; ++s2) mm = fmaxf(mm, w[r * used + s2]);
+    float lsum = 0.f;
+    for (int s2 = 0; s2 < used; ++s2) {
+      const float ms = w[r * used + s2];
       const float wgt = ms == -INFINITY ? 0.f : exp2f(ms - mm);
-      acc += wgt * __ldcg(po + (base + s2) * HD + d);
+      w[r * used + s2] = wgt;
       lsum += wgt * __ldcg(pml + (base + s2) * 2 + 1);
     }
-    out[((size_t)row * nh + head) * HD + d] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+    linv[r] = lsum > 0.f ? 1.f / lsum : 0.f;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < nrows * HD; i += NTHREADS) {
+    const int r = i / HD, d = i - r * HD;
+    const float* p = po + ((size_t)b * nh + h0 + r) * splits * HD + d;
+    float acc = 0.f;
+#pragma unroll 4
+    for (int s2 = 0; s2 < used; ++s2) acc += w[r * used + s2] * __ldcg(p + (size_t)s2 * HD);
+    out[((size_t)row * nh + h0 + r) * HD + d] = __float2bfloat16_rn(acc * linv[r]);
   }
 }
 
@@ -358,6 +392,8 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ po,
                                          const int* __restrict__ cu_seqlens_q,
                                          bf16* __restrict__ out, int nh, int splits) {
   const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  pdl_trigger();
+  pdl_wait();
   const size_t base = ((size_t)b * nh + head) * splits;
   float mm = -INFINITY;
   for (int s = 0; s < splits; ++s) mm = fmaxf(mm, pml[(base + s) * 2]);
@@ -388,6 +424,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __
   bf16* ks = qs + QT * ROW;                                     // [STAGES][KT][ROW]
   bf16* vs = ks + PRE_STAGES * KT * ROW;
   const int b = blockIdx.z, head = blockIdx.y;
+  pdl_trigger();
+  pdl_wait();
   const int q_begin = cu_seqlens_q[b], q_len = cu_seqlens_q[b + 1] - q_begin;
   const int r0 = blockIdx.x * QT;
   if (r0 >= q_len) return;
@@ -416,8 +454,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __
   const int key_lo = window > 0 ? max(0, p_first - window + 1) : 0;
   const int begin = key_lo / KT * KT, end = p_last + 1;
   const int ntiles = (end - begin + KT - 1) / KT;
-  load_kv_tile(ks, kpages, tbl, begin, key_lo, end, page_size, tok_stride, kvh);
-  load_kv_tile(vs, vpages, tbl, begin, key_lo, end, page_size, tok_stride, kvh);
+  load_kv_tiles(ks, vs, kpages, vpages, tbl, begin, key_lo, end, page_size, tok_stride, kvh);
   cp_async_commit();
 
   uint32_t qf[KCH][4];
@@ -448,10 +485,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __
     }
     if (it + 1 < ntiles) {
       const int st = (it + 1) % PRE_STAGES;
-      load_kv_tile(ks + st * KT * ROW, kpages, tbl, begin + (it + 1) * KT, key_lo, end, page_size,
-                   tok_stride, kvh);
-      load_kv_tile(vs + st * KT * ROW, vpages, tbl, begin + (it + 1) * KT, key_lo, end, page_size,
-                   tok_stride, kvh);
+      load_kv_tiles(ks + st * KT * ROW, vs + st * KT * ROW, kpages, vpages, tbl,
+                    begin + (it + 1) * KT, key_lo, end, page_size, tok_stride, kvh);
     }
     cp_async_commit();
     const int st = it % PRE_STAGES;
@@ -488,6 +523,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __
 
 using namespace gf;
 
+GF_DEFINE_PDL_SWITCH
+
 GF_EXPORT int gf_attn_head_dim() { return HD; }
 
 // Bytes of scratch gf_attn_decode needs for B requests, nh heads and `splits` > 1 splits.
@@ -521,15 +558,13 @@ GF_EXPORT int gf_attn_decode(const void* q, int q_row_stride, const void* kpages
   float* pml = po ? po + (size_t)B * nh * splits * HD : nullptr;
   dim3 grid(splits, nkv * chunks, B);
   const int fused = (size_t)B * nkv * chunks <= (size_t)kMaxDecodeGroups ? 1 : 0;
-  attn_decode_kernel<<<grid, NTHREADS, smem, st>>>(
-      (const bf16*)q, q_row_stride, (const bf16*)kpages, (const bf16*)vpages, block_table,
-      table_stride, cu_seqlens_q, positions, (bf16*)out, po, pml, nh, nkv, page_size, window,
-      scale * LOG2E, splits, fused);
-  int rc = launch_status();
+  int rc = launch_kernel(attn_decode_kernel, grid, dim3(NTHREADS), smem, st, (const bf16*)q,
+                         q_row_stride, (const bf16*)kpages, (const bf16*)vpages, block_table,
+                         table_stride, cu_seqlens_q, positions, (bf16*)out, po, pml, nh, nkv,
+                         page_size, window, scale * LOG2E, splits, fused);
   if (rc || splits == 1 || fused) return rc;
-  attn_decode_merge_kernel<<<dim3(nh, B), HD, 0, st>>>(po, pml, cu_seqlens_q, (bf16*)out, nh,
-                                                       splits);
-  return launch_status();
+  return launch_kernel(attn_decode_merge_kernel, dim3(nh, B), dim3(HD), 0, st, (const float*)po,
+                       (const float*)pml, cu_seqlens_q, (bf16*)out, nh, splits);
 }
 
 GF_EXPORT int gf_attn_prefill(const void* q, int q_row_stride, const void* kpages,
@@ -549,8 +584,8 @@ GF_EXPORT int gf_attn_prefill(const void* q, int q_row_stride, const void* kpage
     attr_done = true;
   }
   dim3 grid((max_q_len + QT - 1) / QT, nh, B);
-  attn_prefill_kernel<<<grid, NTHREADS, smem, st>>>(
-      (const bf16*)q, q_row_stride, (const bf16*)kpages, (const bf16*)vpages, block_table,
-      table_stride, cu_seqlens_q, kv_lens, (bf16*)out, nh, nkv, page_size, window, scale * LOG2E);
-  return launch_status();
+  return launch_kernel(attn_prefill_kernel, grid, dim3(NTHREADS), smem, st, (const bf16*)q,
+                       q_row_stride, (const bf16*)kpages, (const bf16*)vpages, block_table,
+                       table_stride, cu_seqlens_q, kv_lens, (bf16*)out, nh, nkv, page_size, window,
+                       scale * LOG2E);
 }

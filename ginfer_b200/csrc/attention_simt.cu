@@ -85,6 +85,8 @@ __global__ void paged_attention_simt_kernel(
 
 using namespace gf;
 
+GF_DEFINE_PDL_SWITCH
+
 // q: rows of q_row_stride elements whose first nh*hd hold the query heads.  kpages/vpages:
 // [num_pages, page_size, nkv, hd].  out: [T, nh, hd] packed.  Returns -3 for head sizes it refuses.
 GF_EXPORT int gf_paged_attention_simt(const void* q, int q_row_stride, const void* kpages,

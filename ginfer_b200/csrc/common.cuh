@@ -52,4 +52,57 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 
 inline int launch_status() { return (int)cudaGetLastError(); }
 
+// ---- programmatic dependent launch -------------------------------------------------------------
+// A kernel launched with the attribute may start while its predecessor in the stream still runs;
+// it must call pdl_wait() before it reads (or overwrites) anything the predecessor touches, and
+// may do independent work first (set-up, loading weights).  pdl_trigger() lets the successor start.
+// Launched without the attribute, both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+inline int& pdl_flag() {
+  static int enabled = 1;
+  return enabled;
+}
+
+// cluster_z > 1 launches thread-block clusters of (1, 1, cluster_z).
+template <typename... KArgs, typename... Args>
+inline int launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, int cluster_z, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (pdl_flag()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster_z > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = 1;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = (unsigned)cluster_z;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                         cudaStream_t stream, Args... args) {
+  return launch_kernel_cluster(kernel, grid, block, smem, stream, 1, args...);
+}
+
 }  // namespace gf
+
+// Every library exports this switch for programmatic dependent launch (on by default).
+#define GF_DEFINE_PDL_SWITCH \
+  GF_EXPORT void gf_set_pdl(int on) { gf::pdl_flag() = on ? 1 : 0; }

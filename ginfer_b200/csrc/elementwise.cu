@@ -12,6 +12,8 @@ template <typename V>
 __global__ void embedding_kernel(const int* __restrict__ ids, const V* __restrict__ w,
                                  V* __restrict__ out, int words_per_row) {
   const int t = blockIdx.x;
+  pdl_trigger();
+  pdl_wait();
   const V* src = w + (size_t)ids[t] * words_per_row;
   V* dst = out + (size_t)t * words_per_row;
   for (int i = threadIdx.x; i < words_per_row; i += blockDim.x) dst[i] = src[i];
@@ -27,12 +29,17 @@ __global__ void add_rmsnorm_kernel(const XT* __restrict__ x, const T* __restrict
                                    const G* __restrict__ gamma, const int* __restrict__ rows,
                                    float* __restrict__ sum_out, T* __restrict__ normed, int H,
                                    float eps) {
-  extern __shared__ float row[];
+  extern __shared__ float row[];                    // the row, then gamma: 2 * H floats
   __shared__ float scratch[33];
+  float* gam = row + H;
   const int r = blockIdx.x;
+  pdl_trigger();
+  for (int j = threadIdx.x; j < H; j += blockDim.x) gam[j] = to_f32(gamma[j]);   // weights: no wait
+  pdl_wait();
   const size_t src = (size_t)(rows ? rows[r] : r) * H;
   const size_t dst = (size_t)r * H;
   float ss = 0.f;
+#pragma unroll 4
   for (int j = threadIdx.x; j < H; j += blockDim.x) {
     float s = to_f32(x[src + j]);
     if (delta) s += to_f32(delta[src + j]);
@@ -42,8 +49,9 @@ __global__ void add_rmsnorm_kernel(const XT* __restrict__ x, const T* __restrict
   }
   ss = block_sum(ss, scratch);
   const float rms = sqrtf(ss / (float)H + eps);
+#pragma unroll 4
   for (int j = threadIdx.x; j < H; j += blockDim.x)
-    normed[dst + j] = from_f32<T>(row[j] * to_f32(gamma[j]) / rms);
+    normed[dst + j] = from_f32<T>(row[j] * gam[j] / rms);
 }
 
 // ----------------------------------------------------------------------------- rope + KV write
@@ -58,13 +66,16 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride,
                                      const int* __restrict__ slot_mapping, T* __restrict__ kpages,
                                      T* __restrict__ vpages, int nh, int nkv, int hd) {
   const int t = blockIdx.x;
+  pdl_trigger();
+  pdl_wait();
   T* rowp = qkv + (size_t)t * row_stride;
   const int half = rot >> 1;
   const int slot = slot_mapping ? slot_mapping[t] : -1;
   T* kdst = slot >= 0 ? kpages + (size_t)slot * nkv * hd : nullptr;
   T* vdst = slot >= 0 ? vpages + (size_t)slot * nkv * hd : nullptr;
   const float* cs = table ? table + (size_t)positions[t] * rot : nullptr;
-  // rotated pairs of q and k heads
+  // The launch gives one thread per rotated pair and per copied channel when they number at most
+  // 1024, so the loops below run once and a thread's loads are all issued before its stores.
   const int npairs = (nh + nkv) * half;
   for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
     const int head = i / half, j = i - head * half;
@@ -98,6 +109,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride,
 // row-interleaved weights writes them; out[t, i] = gate * 1/(1+exp(-gate)) * up in fp32.
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, size_t total) {
+  pdl_trigger();
+  pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (size_t)gridDim.x * blockDim.x) {
     const float g = to_f32(gu[2 * i]), u = to_f32(gu[2 * i + 1]);
@@ -108,21 +121,22 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, s
 template <typename XT, typename T, typename G>
 int launch_add_rmsnorm(const void* x, const void* delta, const void* gamma, const int* rows,
                        void* sum_out, void* normed, int R, int H, float eps, cudaStream_t st) {
-  const size_t smem = (size_t)H * sizeof(float);
+  const size_t smem = (size_t)2 * H * sizeof(float);
   auto k = add_rmsnorm_kernel<XT, T, G>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-  k<<<R, threads, smem, st>>>((const XT*)x, (const T*)delta, (const G*)gamma, rows,
-                              (float*)sum_out, (T*)normed, H, eps);
-  return launch_status();
+  return launch_kernel(k, dim3(R), dim3(threads), smem, st, (const XT*)x, (const T*)delta,
+                       (const G*)gamma, rows, (float*)sum_out, (T*)normed, H, eps);
 }
 
 }  // namespace gf
 
 using namespace gf;
+
+GF_DEFINE_PDL_SWITCH
 
 GF_EXPORT int gf_embedding(const int* ids, const void* w, void* out, int T, int H, int dtype,
                            void* stream) {
@@ -131,13 +145,13 @@ GF_EXPORT int gf_embedding(const int* ids, const void* w, void* out, int T, int 
   auto st = (cudaStream_t)stream;
   const bool al16 = row_bytes % 16 == 0 && ((uintptr_t)w % 16 == 0) && ((uintptr_t)out % 16 == 0);
   if (al16)
-    embedding_kernel<uint4><<<T, 128, 0, st>>>(ids, (const uint4*)w, (uint4*)out,
-                                               (int)(row_bytes / 16));
-  else if (dtype == GF_F32)
-    embedding_kernel<float><<<T, 128, 0, st>>>(ids, (const float*)w, (float*)out, H);
-  else
-    embedding_kernel<uint16_t><<<T, 128, 0, st>>>(ids, (const uint16_t*)w, (uint16_t*)out, H);
-  return launch_status();
+    return launch_kernel(embedding_kernel<uint4>, dim3(T), dim3(128), 0, st, ids, (const uint4*)w,
+                         (uint4*)out, (int)(row_bytes / 16));
+  if (dtype == GF_F32)
+    return launch_kernel(embedding_kernel<float>, dim3(T), dim3(128), 0, st, ids, (const float*)w,
+                         (float*)out, H);
+  return launch_kernel(embedding_kernel<uint16_t>, dim3(T), dim3(128), 0, st, ids,
+                       (const uint16_t*)w, (uint16_t*)out, H);
 }
 
 // x_dtype: type of x (fp32 residual stream, or the activation type); dtype: activation type of
@@ -170,15 +184,17 @@ GF_EXPORT int gf_rope_kv_write(void* qkv, int row_stride, const float* table, in
   if (T <= 0) return 0;
   auto st = (cudaStream_t)stream;
   if (!table) rot = 0;
+  int work = (nh + nkv) * (rot / 2);
+  if (nkv * hd > work) work = nkv * hd;
+  int threads = (work + 31) / 32 * 32;
+  threads = threads < 32 ? 32 : threads > 1024 ? 1024 : threads;
   if (dtype == GF_F32)
-    rope_kv_write_kernel<float><<<T, 128, 0, st>>>((float*)qkv, row_stride, table, rot, positions,
-                                                   slot_mapping, (float*)kpages, (float*)vpages,
-                                                   nh, nkv, hd);
-  else
-    rope_kv_write_kernel<__nv_bfloat16><<<T, 128, 0, st>>>(
-        (__nv_bfloat16*)qkv, row_stride, table, rot, positions, slot_mapping,
-        (__nv_bfloat16*)kpages, (__nv_bfloat16*)vpages, nh, nkv, hd);
-  return launch_status();
+    return launch_kernel(rope_kv_write_kernel<float>, dim3(T), dim3(threads), 0, st, (float*)qkv,
+                         row_stride, table, rot, positions, slot_mapping, (float*)kpages,
+                         (float*)vpages, nh, nkv, hd);
+  return launch_kernel(rope_kv_write_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, st,
+                       (__nv_bfloat16*)qkv, row_stride, table, rot, positions, slot_mapping,
+                       (__nv_bfloat16*)kpages, (__nv_bfloat16*)vpages, nh, nkv, hd);
 }
 
 GF_EXPORT int gf_silu_mul(const void* gu, void* out, int T, int I, int dtype, void* stream) {
@@ -187,9 +203,8 @@ GF_EXPORT int gf_silu_mul(const void* gu, void* out, int T, int I, int dtype, vo
   auto st = (cudaStream_t)stream;
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   if (dtype == GF_F32)
-    silu_mul_kernel<float><<<blocks, 256, 0, st>>>((const float*)gu, (float*)out, total);
-  else
-    silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)gu,
-                                                           (__nv_bfloat16*)out, total);
-  return launch_status();
+    return launch_kernel(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, st, (const float*)gu,
+                         (float*)out, total);
+  return launch_kernel(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, st,
+                       (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, total);
 }

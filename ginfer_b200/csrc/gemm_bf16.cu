@@ -12,9 +12,13 @@
 // 2..5 read the accumulator back with tcgen05.ld and run the epilogue:
 //   EPI_STORE  out = acc (+ bias[n]) as bf16 or fp32
 //   EPI_SILU   W rows are interleaved (gate_i, up_i): out[m, i] = silu(bf16(gate)) * bf16(up)
-// With split_k > 1 every split parks its fp32 partial tile in a workspace and the split that
-// finishes a tile last (counted with an atomic it resets) sums the partials in split order and
-// runs the epilogue: deterministic, and small-N products of a decode step still fill the GPU.
+// Products whose tiles alone would leave most SMs idle (the small-N products of a decode step) split
+// the K range, deterministically, in one of two ways.  Cluster mode (split_k 2, 4 or 8): the splits
+// of a tile form a thread-block cluster, park their fp32 partial tiles in their own shared memory,
+// and after a cluster barrier each CTA sums a band of rows over all peers through distributed
+// shared memory, in rank order, and runs the epilogue for it.  Workspace mode (any split_k): the
+// partials go to global memory and the split that finishes a tile last (counted with an atomic it
+// resets) sums them in split order.
 //
 // The reference calls cuBLASLt for every product (ginfer/core/op/kernels/cuda/gemm_kernel/
 // gemm_kernel.cu:93-156, bias in the epilogue :112-121, fp32 compute :100) and has a separate
@@ -40,9 +44,12 @@ constexpr int kMaxTiles = 1 << 16;
 __device__ unsigned int g_tile_done[kMaxTiles];
 
 __host__ __device__ constexpr int stages_for(int bn) {
-  // ring of (16 KB + bn * 128 B) stages within ~200 KB, at most 8
-  return (200 * 1024) / (BM * BK * 2 + bn * BK * 2) > 8 ? 8
-                                                        : (200 * 1024) / (BM * BK * 2 + bn * BK * 2);
+  // Ring of (16 KB + bn * 128 B) stages.  Small token tiles (decode) stay within ~110 KB so that
+  // two CTAs, of this product or of the next one in the stream, share an SM; large ones take
+  // ~200 KB.  At most 8 stages.
+  const int budget = bn <= 64 ? 110 * 1024 : 200 * 1024;
+  const int n = budget / (BM * BK * 2 + bn * BK * 2);
+  return n > 8 ? 8 : n;
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -161,7 +168,27 @@ __device__ __forceinline__ void epilogue16(float (&v)[16], OUT* __restrict__ out
   }
 }
 
-template <int BN, int EPI, typename OUT>
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float4 ld_dsmem_f4(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(remote)
+               : "memory");
+  return v;
+}
+
+template <int BN, int EPI, typename OUT, bool CLUSTER>
 __global__ void __launch_bounds__(NTHREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                const float* __restrict__ bias, OUT* __restrict__ out, int ldo, int M, int N, int K,
@@ -184,6 +211,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   const int kb0 = split * per, kb1 = min(nkb_all, kb0 + per);
   const int nkb = max(0, kb1 - kb0);
 
+  pdl_trigger();
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full + s, 1);
@@ -207,7 +235,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int i = 0; i < nkb; ++i) {
+      // Weights do not depend on the kernel before this one: fill the ring with them first, then
+      // wait for that kernel and add the activations to the same stages.
+      const int pre = nkb < STAGES ? nkb : STAGES;
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(full + i, A_BYTES + B_BYTES);
+        tma_load_2d(tiles + i * (A_BYTES + B_BYTES), &tmap_w, full + i, (kb0 + i) * BK, n0);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d(tiles + i * (A_BYTES + B_BYTES) + A_BYTES, &tmap_x, full + i, (kb0 + i) * BK,
+                    m0);
+      for (int i = pre; i < nkb; ++i) {
         const int s = i % STAGES;
         if (!mbar_wait(empty + s, ((i / STAGES) & 1) ^ 1, err, 1)) break;
         mbar_expect_tx(full + s, A_BYTES + B_BYTES);
@@ -239,6 +278,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     // epilogue warps: TMEM lanes (warp % 4) * 32 .. + 31
     const int q = warp & 3;
     const int n = n0 + q * 32 + lane;
+    pdl_wait();                            // nothing is written before the kernel ahead is done
     const bool ok = mbar_wait(acc_full, 0, err, 3);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ok) {
@@ -255,6 +295,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             for (int j = 0; j < 16; ++j) v[j] = 0.f;
           }
           epilogue16<EPI, OUT>(v, out, ldo, bias, n, m0 + c, M, N, lane);
+        }
+      } else if (CLUSTER) {
+        // park this split's partial tile in shared memory (the ring is drained by now):
+        // red[row (128)][RED_LD], rows padded so that float4 stores do not collide
+        float* mine = reinterpret_cast<float*>(tiles) + (size_t)(q * 32 + lane) * (BN + 4);
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+          float v[16];
+          if (nkb > 0 && m0 + c < M) {
+            tmem_ld16(taddr + c, v);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = 0.f;
+          }
+#pragma unroll
+          for (int j = 0; j < 16; j += 4)
+            *reinterpret_cast<float4*>(mine + c + j) = make_float4(v[j], v[j + 1], v[j + 2],
+                                                                    v[j + 3]);
         }
       } else {
         // park this split's partial tile: workspace[tile][split][row (128)][col (BN)]
@@ -286,6 +344,60 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                  : "memory");
   }
   if (split_k == 1) return;
+
+  if (CLUSTER) {
+    // every CTA of the cluster sums a band of rows over all peers, in rank order
+    pdl_wait();
+    cluster_sync();
+    const int rank = (int)cluster_rank();
+    const int band = BM / split_k;                    // split_k is 2, 4 or 8
+    constexpr int QUADS = BN / 4;                     // a unit of work: one row (pair), 4 tokens
+    const uint32_t red = smem_u32(tiles);
+    if (EPI == EPI_STORE) {
+      for (int u = threadIdx.x; u < band * QUADS; u += NTHREADS) {
+        const int row = rank * band + u % band, c = (u / band) * 4;
+        const int n = n0 + row;
+        if (m0 + c >= M || n >= N) continue;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+        for (int p = 0; p < split_k; ++p) {
+          const float4 t = ld_dsmem_f4(red + (uint32_t)((row * (BN + 4) + c) * 4), p);
+          v.x += t.x, v.y += t.y, v.z += t.z, v.w += t.w;
+        }
+        const float b = bias ? bias[n] : 0.f;
+        const float vv[4] = {v.x + b, v.y + b, v.z + b, v.w + b};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (m0 + c + j < M) store_out<OUT>(out + (size_t)(m0 + c + j) * ldo + n, vv[j]);
+      }
+    } else {
+      const int pairs = band / 2;
+      for (int u = threadIdx.x; u < pairs * QUADS; u += NTHREADS) {
+        const int row = rank * band + 2 * (u % pairs), c = (u / pairs) * 4;
+        const int pair = (n0 + row) >> 1;
+        if (m0 + c >= M || n0 + row + 1 >= N) continue;
+        float4 g = make_float4(0.f, 0.f, 0.f, 0.f), up = g;
+#pragma unroll 8
+        for (int p = 0; p < split_k; ++p) {
+          const float4 a = ld_dsmem_f4(red + (uint32_t)((row * (BN + 4) + c) * 4), p);
+          const float4 b = ld_dsmem_f4(red + (uint32_t)(((row + 1) * (BN + 4) + c) * 4), p);
+          g.x += a.x, g.y += a.y, g.z += a.z, g.w += a.w;
+          up.x += b.x, up.y += b.y, up.z += b.z, up.w += b.w;
+        }
+        const float gv[4] = {g.x, g.y, g.z, g.w}, uv[4] = {up.x, up.y, up.z, up.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float gg = __bfloat162float(__float2bfloat16_rn(gv[j]));
+          const float uu = __bfloat162float(__float2bfloat16_rn(uv[j]));
+          if (m0 + c + j < M)
+            store_out<OUT>(out + (size_t)(m0 + c + j) * ldo + pair,
+                           gg * (1.0f / (1.0f + expf(-gg))) * uu);
+        }
+      }
+    }
+    cluster_sync();                                   // nobody leaves while a peer still reads it
+    return;
+  }
 
   // the split that finishes this tile last adds the partials up in split order
   __threadfence();
@@ -354,14 +466,15 @@ static bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int 
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, int EPI, typename OUT>
-static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* out,
-                  int ldo, int M, int N, int K, int split_k, float* workspace, int* err,
-                  cudaStream_t st) {
+template <int BN, int EPI, typename OUT, bool CLUSTER>
+static int launch_mode(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* out,
+                       int ldo, int M, int N, int K, int split_k, float* workspace, int* err,
+                       cudaStream_t st) {
   constexpr int STAGES = stages_for(BN);
-  const size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) +
-                      (2 * STAGES + 1) * sizeof(uint64_t) + 16;
-  auto k = gemm_tc_kernel<BN, EPI, OUT>;
+  const size_t ring = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2);
+  const size_t red = CLUSTER ? (size_t)BM * (BN + 4) * sizeof(float) : 0;
+  const size_t smem = 1024 + (ring > red ? ring : red) + (2 * STAGES + 1) * sizeof(uint64_t) + 16;
+  auto k = gemm_tc_kernel<BN, EPI, OUT, CLUSTER>;
   static bool done = false;
   if (!done) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -369,8 +482,19 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* bia
     done = true;
   }
   dim3 grid((N + BM - 1) / BM, (M + BN - 1) / BN, split_k);
-  k<<<grid, NTHREADS, smem, st>>>(mw, mx, bias, (OUT*)out, ldo, M, N, K, split_k, workspace, err);
-  return launch_status();
+  return launch_kernel_cluster(k, grid, dim3(NTHREADS), smem, st, CLUSTER ? split_k : 1, mw, mx,
+                               bias, (OUT*)out, ldo, M, N, K, split_k, workspace, err);
+}
+
+template <int BN, int EPI, typename OUT>
+static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* out,
+                  int ldo, int M, int N, int K, int split_k, float* workspace, int* err,
+                  cudaStream_t st) {
+  if (split_k > 1 && !workspace)
+    return launch_mode<BN, EPI, OUT, true>(mw, mx, bias, out, ldo, M, N, K, split_k, workspace,
+                                           err, st);
+  return launch_mode<BN, EPI, OUT, false>(mw, mx, bias, out, ldo, M, N, K, split_k, workspace, err,
+                                          st);
 }
 
 template <int EPI, typename OUT>
@@ -391,6 +515,8 @@ static int dispatch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, con
 
 using namespace gf;
 
+GF_DEFINE_PDL_SWITCH
+
 GF_EXPORT int gf_gemm_bf16_token_tile(int M) {
   return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
 }
@@ -405,7 +531,8 @@ GF_EXPORT long long gf_gemm_bf16_workspace_words(int M, int N, int split_k) {
 
 // out[M, *] = x[M, K] * W[N, K]^T.  epi 0: out[m, n] = acc + bias[n]; epi 2: W rows interleaved
 // (gate_i, up_i), out[m, i] = silu(gate) * up, N even.  out_f32: fp32 output (epi 0 only).
-// ldx, ldo in elements.  err: a device int that receives a non-zero code if a wait ran out.
+// ldx, ldo in elements.  split_k > 1 with a workspace: workspace mode; without: cluster mode
+// (split_k 2, 4 or 8).  err: a device int that receives a non-zero code if a wait ran out.
 // Returns -6 when the shape or alignment cannot be served (the caller uses another product).
 GF_EXPORT int gf_gemm_bf16_tc(const void* x, int ldx, const void* w, const float* bias, void* out,
                               int ldo, int M, int N, int K, int epi, int out_f32, int split_k,
@@ -417,7 +544,9 @@ GF_EXPORT int gf_gemm_bf16_tc(const void* x, int ldx, const void* w, const float
   const int bn = gf_gemm_bf16_token_tile(M);
   if (split_k < 1) split_k = 1;
   const long long tiles = (long long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
-  if (split_k > 1 && (!workspace || tiles > kMaxTiles)) return -6;
+  // split_k > 1 without a workspace asks for cluster mode
+  if (split_k > 1 && !workspace && split_k != 2 && split_k != 4 && split_k != 8) return -6;
+  if (split_k > 1 && workspace && tiles > kMaxTiles) return -6;
   CUtensorMap mw, mx;
   if (!make_map(&mw, w, N, K, K, BM) || !make_map(&mx, x, M, K, ldx, bn)) return -6;
   auto st = (cudaStream_t)stream;

@@ -58,6 +58,8 @@ gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W,
 
 using namespace gf;
 
+GF_DEFINE_PDL_SWITCH
+
 GF_EXPORT int gf_gemm_f32(const float* A, int lda, const float* W, const float* bias, float* C,
                           int ldc, int M, int N, int K, void* stream) {
   if (M <= 0 || N <= 0) return 0;

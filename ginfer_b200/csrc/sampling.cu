@@ -52,6 +52,8 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict_
   __shared__ int sidx[kThreads / 32];
   __shared__ bool last;
   const int row = blockIdx.y, chunk = blockIdx.x, nchunks = gridDim.x;
+  pdl_trigger();
+  pdl_wait();
   const float* x = logits + (size_t)row * V;
   const int j0 = chunk * kChunk, j1 = min(V, j0 + kChunk);
   float v = -INFINITY;
@@ -162,6 +164,8 @@ __global__ void sample_kernel(const float* __restrict__ logits, const float* __r
 
 using namespace gf;
 
+GF_DEFINE_PDL_SWITCH
+
 // scratch: room for 2 * R * ceil(V / 4096) 32-bit words (parked pairs); may be null when V <= 4096.
 GF_EXPORT int gf_argmax(const float* logits, int* out, int R, int V, void* scratch, void* stream) {
   if (R <= 0) return 0;
@@ -170,8 +174,8 @@ GF_EXPORT int gf_argmax(const float* logits, int* out, int R, int V, void* scrat
   if (nchunks > 1 && !scratch) return -4;
   float* pval = (float*)scratch;
   int* pidx = (int*)scratch + (size_t)R * nchunks;
-  argmax_kernel<<<dim3(nchunks, R), kThreads, 0, (cudaStream_t)stream>>>(logits, out, V, pval, pidx);
-  return launch_status();
+  return launch_kernel(argmax_kernel, dim3(nchunks, R), dim3(kThreads), 0, (cudaStream_t)stream,
+                       logits, out, V, pval, pidx);
 }
 
 GF_EXPORT int gf_sample(const float* logits, const float* temperature, const float* u, int* out,

@@ -12,7 +12,7 @@ from ctypes import c_float, c_int, c_void_p
 
 import torch
 
-from .build import BuildError, build_all, load_library  # noqa: F401
+from .build import BuildError, build_all, load_library, set_pdl  # noqa: F401
 
 _CODES = {torch.float32: 0, torch.bfloat16: 1}
 

@@ -138,14 +138,30 @@ def compile_library(name: str, defines: tuple[str, ...] = (), verbose: bool = Tr
     return so
 
 
+_pdl_enabled = os.environ.get("GINFER_B200_PDL", "1") != "0"
+
+
 def load_library(name: str, defines: tuple[str, ...] = ()) -> ctypes.CDLL:
     key = name + "|" + "|".join(defines)
     with _lock:
         lib = _loaded.get(key)
         if lib is None:
             lib = ctypes.CDLL(compile_library(name, defines))
+            if hasattr(lib, "gf_set_pdl"):
+                lib.gf_set_pdl(ctypes.c_int(1 if _pdl_enabled else 0))
             _loaded[key] = lib
         return lib
+
+
+def set_pdl(enabled: bool) -> None:
+    """Switch programmatic dependent launch on or off for every kernel library (those loaded and
+    those yet to be).  On by default; ``GINFER_B200_PDL=0`` in the environment turns it off."""
+    global _pdl_enabled
+    with _lock:
+        _pdl_enabled = bool(enabled)
+        for lib in _loaded.values():
+            if hasattr(lib, "gf_set_pdl"):
+                lib.gf_set_pdl(ctypes.c_int(1 if _pdl_enabled else 0))
 
 
 # every library the framework can ask for: (source name, defines)

@@ -36,12 +36,14 @@ def token_tile(M: int) -> int:
 
 
 def split_k_for(M: int, N: int, K: int) -> int:
-    """Split the K range of products whose tiles alone would leave most SMs idle."""
+    """Split the K range of products whose tiles alone would leave most SMs idle: 2, 4 or 8
+    splits, which form a thread-block cluster and add up through distributed shared memory."""
     tiles = -(-N // 128) * -(-M // token_tile(M))
     nkb = -(-K // 64)
-    if tiles * 4 >= NUM_SMS * 3 or nkb < 4:
-        return 1
-    return max(1, min(-(-NUM_SMS // tiles), nkb // 2, 16))
+    split = 1
+    while split < 8 and tiles * split * 2 <= NUM_SMS + NUM_SMS // 4 and nkb // (split * 2) >= 2:
+        split *= 2
+    return split
 
 
 def _workspace(words: int, device) -> torch.Tensor:
@@ -59,10 +61,13 @@ def supports(x: torch.Tensor, weight: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
-def gemm(x, weight, bias_f32=None, out_dtype=torch.bfloat16, epi: int = 0, split_k=None):
+def gemm(x, weight, bias_f32=None, out_dtype=torch.bfloat16, epi: int = 0, split_k=None,
+         through_workspace: bool = False):
     """``x [M, K] @ weight[N, K]^T``; ``epi`` 0: (+ bias) -> ``[M, N]``; ``epi`` 2: weight rows
     are interleaved (gate_i, up_i) and the result is ``silu(gate) * up`` -> ``[M, N / 2]``.
-    Returns ``None`` if the kernel cannot serve the shape."""
+    ``split_k``: None picks it; 2, 4 or 8 add up inside a cluster; with ``through_workspace`` any
+    number of splits adds up through global memory.  Returns ``None`` if the kernel cannot serve
+    the shape."""
     from . import _fn, _ok, _p, _stream
     if not supports(x, weight):
         return None
@@ -74,7 +79,7 @@ def gemm(x, weight, bias_f32=None, out_dtype=torch.bfloat16, epi: int = 0, split
         return out
     sk = split_k_for(M, N, K) if split_k is None else int(split_k)
     ws = None
-    if sk > 1:
+    if sk > 1 and through_workspace:
         bn = token_tile(M)
         ws = _workspace(-(-N // 128) * -(-M // bn) * sk * 128 * bn, x.device)
     st = _dev_state(x.device)

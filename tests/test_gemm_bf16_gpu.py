@@ -26,9 +26,9 @@ def test_product_and_bias(M, N, K, bias):
     w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
     b = torch.randn(N, generator=g).to(DEV) if bias else None
     want = _ref(x, w, b)
-    for split_k in (None, 1, 3):
-        got = gemm_bf16.gemm(x, w, b, torch.bfloat16, split_k=split_k)
-        assert got is not None
+    for split_k, ws in ((None, False), (1, False), (2, False), (4, False), (8, False), (3, True)):
+        got = gemm_bf16.gemm(x, w, b, torch.bfloat16, split_k=split_k, through_workspace=ws)
+        assert got is not None, (split_k, ws)
         torch.testing.assert_close(got.double(), want, atol=2e-2, rtol=1e-2)
     got32 = gemm_bf16.gemm(x, w, b, torch.float32)
     torch.testing.assert_close(got32.double(), want, atol=1e-3, rtol=1e-4)
@@ -50,8 +50,9 @@ def test_gated_epilogue(M, I, K):
     gg = _ref(x, gate).to(torch.bfloat16).double()      # gate and up are rounded as a product's
     uu = _ref(x, up).to(torch.bfloat16).double()        # output would be, then combined in fp32
     want = gg / (1 + torch.exp(-gg)) * uu
-    for split_k in (None, 2):
-        got = gemm_bf16.gemm(x, inter, None, torch.bfloat16, epi=2, split_k=split_k)
+    for split_k, ws in ((None, False), (2, False), (8, False), (5, True)):
+        got = gemm_bf16.gemm(x, inter, None, torch.bfloat16, epi=2, split_k=split_k,
+                             through_workspace=ws)
         assert got is not None and got.shape == (M, I)
         torch.testing.assert_close(got.double(), want, atol=2e-2, rtol=2e-2)
     gemm_bf16.check_errors()
