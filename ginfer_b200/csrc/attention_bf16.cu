@@ -9,8 +9,8 @@
 //    memory; the CTA that finishes a (request, kv head) last merges them (a second kernel does it
 //    when there are more such groups than counters).
 //  * gf_attn_prefill: any number of query tokens per request (portions of prompts, and single
-//    tokens beside them).  One CTA per (64 query rows of one head); keys are visited in tiles of 64
-//    through the block table.
+//    tokens beside them).  One CTA per (128 query rows of one head; 64 for head sizes above 128);
+//    keys are visited in tiles of 64 through the block table.
 //
 // Both use mma.sync.m16n8k16 (bf16 in, fp32 accumulate) with operands staged in shared memory by
 // cp.async and read by ldmatrix.  Scores, the running maximum, the sum and the output accumulator
@@ -77,7 +77,8 @@ __device__ __forceinline__ void load_kv_tiles(bf16* kdst, bf16* vdst,
                                               const bf16* __restrict__ kpages,
                                               const bf16* __restrict__ vpages,
                                               const int* __restrict__ tbl, int c0, int begin,
-                                              int end, int page_size, size_t tok_stride, int kvh) {
+                                              int end, int page_size, int page_shift,
+                                              size_t tok_stride, int kvh) {
   constexpr int CH = HD / 8;                           // 16-byte chunks in a row
   constexpr int ITERS = (KT * CH + NTHREADS - 1) / NTHREADS;
   long long off[ITERS];                                // element offset of the chunk, -1: no load
@@ -89,9 +90,12 @@ __device__ __forceinline__ void load_kv_tiles(bf16* kdst, bf16* vdst,
     const bool ok = i < KT * CH && c >= begin && c < end;
     off[it] = -1;
     if (ok) {
-      const int page = __ldg(tbl + c / page_size);
-      off[it] = ((long long)page * page_size + c % page_size) * (long long)tok_stride +
-                (long long)kvh * HD + ch * 8;
+      // page_shift >= 0: the page size is a power of two
+      const int lp = page_shift >= 0 ? c >> page_shift : c / page_size;
+      const int in_page = page_shift >= 0 ? c & (page_size - 1) : c - lp * page_size;
+      const int page = __ldg(tbl + lp);
+      off[it] = ((long long)page * page_size + in_page) * (long long)tok_stride +
+                (long long)(kvh * HD + ch * 8);
     }
   }
 #pragma unroll
@@ -237,6 +241,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
   const int end = min(p + 1, begin + per);
   const int* tbl = block_table + (size_t)b * table_stride;
   const size_t tok_stride = (size_t)nkv * HD;
+  const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
 
   // query fragments straight from global memory: rows are the heads h0 + g and h0 + g + 8
   uint32_t qf[KCH][4];
@@ -263,7 +268,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
   for (int s = 0; s < DEC_STAGES - 1; ++s) {
     if (s < ntiles)
       load_kv_tiles(ks + s * KT * ROW, vs + s * KT * ROW, kpages, vpages, tbl, begin + s * KT,
-                    begin, end, page_size, tok_stride, kvh);
+                    begin, end, page_size, page_shift, tok_stride, kvh);
     cp_async_commit();
   }
   for (int it = 0; it < ntiles; ++it) {
@@ -273,7 +278,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
     if (nxt < ntiles) {
       const int st = nxt % DEC_STAGES;
       load_kv_tiles(ks + st * KT * ROW, vs + st * KT * ROW, kpages, vpages, tbl, begin + nxt * KT,
-                    begin, end, page_size, tok_stride, kvh);
+                    begin, end, page_size, page_shift, tok_stride, kvh);
     }
     cp_async_commit();
     const int st = it % DEC_STAGES;
@@ -409,9 +414,17 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ po,
 }
 
 // ================================================================================== prefill
-// grid (q tiles, nh, B): 64 query rows of one head of one request; warp w owns rows 16w .. 16w+15.
+// grid (q tiles, nh, B): QT query rows of one head of one request.  Warp w owns rows
+// 16 * MT * w .. + 16 * MT - 1: with MT = 2 every K/V fragment read from shared memory feeds two
+// row tiles (four MMAs), which is what keeps the tensor pipe busier than the shared-memory pipe.
+// Head sizes above 128 keep one row tile per warp (the output accumulator would not fit twice).
 constexpr int PRE_STAGES = 2;
-constexpr int QT = 64;
+#ifndef GF_ATTN_MT
+#define GF_ATTN_MT 2
+#endif
+constexpr int MT = HD <= 128 ? GF_ATTN_MT : 1;
+constexpr int WROWS = 16 * MT;                 // query rows per warp
+constexpr int QT = 4 * WROWS;                  // query rows per CTA
 
 __global__ void __launch_bounds__(NTHREADS)
 attn_prefill_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __restrict__ kpages,
@@ -427,7 +440,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __
   pdl_trigger();
   pdl_wait();
   const int q_begin = cu_seqlens_q[b], q_len = cu_seqlens_q[b + 1] - q_begin;
-  const int r0 = blockIdx.x * QT;
+  // later row tiles see more keys: they are handed out first so that the long ones do not trail
+  const int r0 = (int)(gridDim.x - 1 - blockIdx.x) * QT;
   if (r0 >= q_len) return;
   const int kv_len = kv_lens[b];
   const int pos0 = kv_len - q_len;                              // position of the request's row 0
@@ -435,6 +449,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2;
   const int* tbl = block_table + (size_t)b * table_stride;
   const size_t tok_stride = (size_t)nkv * HD;
+  const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
   const int rows = min(QT, q_len - r0);
 
   // the tile's queries -> shared memory (rows past the request's end are zero)
@@ -454,67 +469,111 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __
   const int key_lo = window > 0 ? max(0, p_first - window + 1) : 0;
   const int begin = key_lo / KT * KT, end = p_last + 1;
   const int ntiles = (end - begin + KT - 1) / KT;
-  load_kv_tiles(ks, vs, kpages, vpages, tbl, begin, key_lo, end, page_size, tok_stride, kvh);
+  load_kv_tiles(ks, vs, kpages, vpages, tbl, begin, key_lo, end, page_size, page_shift, tok_stride, kvh);
   cp_async_commit();
 
-  uint32_t qf[KCH][4];
-  float o[HD / 8][4];
+  float o[MT][HD / 8][4];
+  float m[MT][2], l[MT][2];
+  int lo2[MT][2], hi2[MT][2];                  // visibility bounds of this thread's rows
 #pragma unroll
-  for (int n = 0; n < HD / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-  // visibility bounds of this thread's two rows (rows past the end see nothing)
-  int lo2[2], hi2[2];
+  for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int r = warp * 16 + g + 8 * i;
-    const int p = pos0 + r0 + r;
-    hi2[i] = r < rows ? p : -1;
-    lo2[i] = window > 0 ? max(0, p - window + 1) : 0;
+    for (int n = 0; n < HD / 8; ++n) o[mt][n][0] = o[mt][n][1] = o[mt][n][2] = o[mt][n][3] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      m[mt][i] = -INFINITY;
+      l[mt][i] = 0.f;
+      const int r = warp * WROWS + mt * 16 + g + 8 * i;
+      const int p = pos0 + r0 + r;
+      hi2[mt][i] = r < rows ? p : -1;          // rows past the end see nothing
+      lo2[mt][i] = window > 0 ? max(0, p - window + 1) : 0;
+    }
   }
-  const int warp_hi = min(p_last, pos0 + r0 + warp * 16 + 15);  // last key any row of the warp sees
-  const int warp_lo = window > 0 ? max(0, pos0 + r0 + warp * 16 - window + 1) : 0;
+  const int warp_hi = min(p_last, pos0 + r0 + warp * WROWS + WROWS - 1);
+  const int warp_lo = window > 0 ? max(0, pos0 + r0 + warp * WROWS - window + 1) : 0;
+  const int mi = lane >> 3, lr = lane & 7;
+  const bf16* qw = qs + (warp * WROWS + (mi & 1) * 8 + lr) * ROW + (mi >> 1) * 8;
 
   for (int it = 0; it < ntiles; ++it) {
     cp_async_wait<0>();
     __syncthreads();
-    if (it == 0) {
-      const int mi = lane >> 3, r = lane & 7;
-#pragma unroll
-      for (int kc = 0; kc < KCH; ++kc)
-        ldsm_x4(qf[kc], qs + (warp * 16 + (mi & 1) * 8 + r) * ROW + kc * 16 + (mi >> 1) * 8);
-    }
     if (it + 1 < ntiles) {
       const int st = (it + 1) % PRE_STAGES;
       load_kv_tiles(ks + st * KT * ROW, vs + st * KT * ROW, kpages, vpages, tbl,
-                    begin + (it + 1) * KT, key_lo, end, page_size, tok_stride, kvh);
+                    begin + (it + 1) * KT, key_lo, end, page_size, page_shift, tok_stride, kvh);
     }
     cp_async_commit();
     const int st = it % PRE_STAGES;
     const int col0 = begin + it * KT;
-    if (col0 <= warp_hi && col0 + KT > warp_lo && warp * 16 < rows) {
-      float s[8][4] = {};
-      qk_tile<8>(s, qf, ks + st * KT * ROW, 0, lane);
-      softmax_update<8>(s, o, m, l, col0, lo2, hi2, scale_log2, lane);
-      pv_tile<8>(o, s, vs + st * KT * ROW, 0, lane);
+    if (!(col0 <= warp_hi && col0 + KT > warp_lo && warp * WROWS < rows)) continue;
+    const bf16* kt = ks + st * KT * ROW;
+    const bf16* vt = vs + st * KT * ROW;
+    float s[MT][8][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s[mt][j][0] = s[mt][j][1] = s[mt][j][2] = s[mt][j][3] = 0.f;
+    // S = Q K^T: one K fragment (two key tiles) feeds every row tile of the warp
+#pragma unroll
+    for (int kc = 0; kc < KCH; ++kc) {
+      uint32_t a[MT][4];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) ldsm_x4(a[mt], qw + mt * 16 * ROW + kc * 16);
+#pragma unroll
+      for (int n2 = 0; n2 < 4; ++n2) {
+        uint32_t kb[4];
+        ldsm_x4(kb, kt + (n2 * 16 + (mi >> 1) * 8 + lr) * ROW + kc * 16 + (mi & 1) * 8);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          mma16816(s[mt][2 * n2], a[mt], kb[0], kb[1]);
+          mma16816(s[mt][2 * n2 + 1], a[mt], kb[2], kb[3]);
+        }
+      }
+    }
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+      softmax_update<8>(s[mt], o[mt], m[mt], l[mt], col0, lo2[mt], hi2[mt], scale_log2, lane);
+    // O += P V
+#pragma unroll
+    for (int kc = 0; kc < 4; ++kc) {
+      uint32_t a[MT][4];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        a[mt][0] = pack_bf16(s[mt][2 * kc][0], s[mt][2 * kc][1]);
+        a[mt][1] = pack_bf16(s[mt][2 * kc][2], s[mt][2 * kc][3]);
+        a[mt][2] = pack_bf16(s[mt][2 * kc + 1][0], s[mt][2 * kc + 1][1]);
+        a[mt][3] = pack_bf16(s[mt][2 * kc + 1][2], s[mt][2 * kc + 1][3]);
+      }
+#pragma unroll
+      for (int n2 = 0; n2 < HD / 16; ++n2) {
+        uint32_t vb[4];
+        ldsm_x4_t(vb, vt + (kc * 16 + (mi & 1) * 8 + lr) * ROW + n2 * 16 + (mi >> 1) * 8);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          mma16816(o[mt][2 * n2], a[mt], vb[0], vb[1]);
+          mma16816(o[mt][2 * n2 + 1], a[mt], vb[2], vb[3]);
+        }
+      }
     }
   }
   cp_async_wait<0>();
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
-    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
-  }
   const int t = lane & 3;
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int r = warp * 16 + g + 8 * i;
-    if (r >= rows) continue;
-    const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
-    bf16* orow = out + ((size_t)(q_begin + r0 + r) * nh + head) * HD;
+  for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
-    for (int n = 0; n < HD / 8; ++n) {
-      *reinterpret_cast<uint32_t*>(orow + n * 8 + 2 * t) =
-          pack_bf16(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
+    for (int i = 0; i < 2; ++i) {
+      float li = l[mt][i];
+      li += __shfl_xor_sync(0xffffffffu, li, 1);
+      li += __shfl_xor_sync(0xffffffffu, li, 2);
+      const int r = warp * WROWS + mt * 16 + g + 8 * i;
+      if (r >= rows) continue;
+      const float inv = li > 0.f ? 1.f / li : 0.f;
+      bf16* orow = out + ((size_t)(q_begin + r0 + r) * nh + head) * HD;
+#pragma unroll
+      for (int n = 0; n < HD / 8; ++n) {
+        *reinterpret_cast<uint32_t*>(orow + n * 8 + 2 * t) =
+            pack_bf16(o[mt][n][2 * i] * inv, o[mt][n][2 * i + 1] * inv);
+      }
     }
   }
 }

@@ -104,6 +104,66 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride,
   for (int i = threadIdx.x; i < nkv * hd; i += blockDim.x) vdst[i] = vsrc[i];
 }
 
+// The same with 16-byte accesses: a thread rotates VEC consecutive pairs (VEC = 8 bf16 or 4 fp32)
+// or copies VEC channels.  Needs rot/2, hd and the row stride to be multiples of VEC and 16-byte
+// aligned pointers; the launcher checks.
+template <typename T>
+__global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, int row_stride,
+                                         const float* __restrict__ table, int rot,
+                                         const int* __restrict__ positions,
+                                         const int* __restrict__ slot_mapping,
+                                         T* __restrict__ kpages, T* __restrict__ vpages, int nh,
+                                         int nkv, int hd) {
+  constexpr int VEC = 16 / (int)sizeof(T);
+  const int t = blockIdx.x;
+  pdl_trigger();
+  pdl_wait();
+  T* rowp = qkv + (size_t)t * row_stride;
+  const int half = rot >> 1;
+  const int slot = slot_mapping ? slot_mapping[t] : -1;
+  T* kdst = slot >= 0 ? kpages + (size_t)slot * nkv * hd : nullptr;
+  T* vdst = slot >= 0 ? vpages + (size_t)slot * nkv * hd : nullptr;
+  const float* cs = table ? table + (size_t)positions[t] * rot : nullptr;
+  const int per_head = half / VEC;
+  const int nrot = (nh + nkv) * per_head;                 // vector pairs to rotate
+  const int tailv = (hd - rot) / VEC;                     // unrotated vectors per k head
+  const int ncopy = kdst ? nkv * tailv + nkv * hd / VEC : 0;
+  for (int i = threadIdx.x; i < nrot + ncopy; i += blockDim.x) {
+    if (i < nrot) {
+      const int head = i / per_head, j = (i - head * per_head) * VEC;
+      T* h = rowp + (size_t)head * hd;
+      const uint4 ra = *reinterpret_cast<const uint4*>(h + j);
+      const uint4 rb = *reinterpret_cast<const uint4*>(h + j + half);
+      const T* a = reinterpret_cast<const T*>(&ra);
+      const T* b = reinterpret_cast<const T*>(&rb);
+      T lo[VEC], hi[VEC];
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        const float c = cs[j + k], s = cs[half + j + k];
+        const float x = to_f32(a[k]), y = to_f32(b[k]);
+        lo[k] = from_f32<T>(x * c - y * s);
+        hi[k] = from_f32<T>(x * s + y * c);
+      }
+      T* dst = head < nh ? h : (kdst ? kdst + (size_t)(head - nh) * hd : nullptr);
+      if (dst) {
+        *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<const uint4*>(lo);
+        *reinterpret_cast<uint4*>(dst + j + half) = *reinterpret_cast<const uint4*>(hi);
+      }
+    } else {
+      const int c = i - nrot;
+      if (c < nkv * tailv) {
+        const int head = c / tailv, j = rot + (c - head * tailv) * VEC;
+        *reinterpret_cast<uint4*>(kdst + (size_t)head * hd + j) =
+            *reinterpret_cast<const uint4*>(rowp + (size_t)(nh + head) * hd + j);
+      } else {
+        const int j = (c - nkv * tailv) * VEC;
+        *reinterpret_cast<uint4*>(vdst + j) =
+            *reinterpret_cast<const uint4*>(rowp + (size_t)(nh + nkv) * hd + j);
+      }
+    }
+  }
+}
+
 // ----------------------------------------------------------------------------- silu(gate) * up
 // gu[t] holds gate and up interleaved (gate_0, up_0, gate_1, up_1, ...), as the joined product of
 // row-interleaved weights writes them; out[t, i] = gate * 1/(1+exp(-gate)) * up in fp32.
@@ -111,7 +171,25 @@ template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, size_t total) {
   pdl_trigger();
   pdl_wait();
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+  // 16 bytes of (gate, up) pairs per load: 4 pairs of bf16, 2 pairs of fp32
+  constexpr int PAIRS = 16 / (2 * (int)sizeof(T));
+  const size_t nvec = total / PAIRS;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const uint4 raw = reinterpret_cast<const uint4*>(gu)[i];
+    const T* p = reinterpret_cast<const T*>(&raw);
+    T res[PAIRS];
+#pragma unroll
+    for (int k = 0; k < PAIRS; ++k) {
+      const float g = to_f32(p[2 * k]), u = to_f32(p[2 * k + 1]);
+      res[k] = from_f32<T>(g * (1.0f / (1.0f + expf(-g))) * u);
+    }
+    if (sizeof(T) == 2)
+      reinterpret_cast<uint2*>(out)[i] = *reinterpret_cast<const uint2*>(res);
+    else
+      reinterpret_cast<uint2*>(out)[i] = *reinterpret_cast<const uint2*>(res);
+  }
+  for (size_t i = nvec * PAIRS + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (size_t)gridDim.x * blockDim.x) {
     const float g = to_f32(gu[2 * i]), u = to_f32(gu[2 * i + 1]);
     out[i] = from_f32<T>(g * (1.0f / (1.0f + expf(-g))) * u);
@@ -184,6 +262,23 @@ GF_EXPORT int gf_rope_kv_write(void* qkv, int row_stride, const float* table, in
   if (T <= 0) return 0;
   auto st = (cudaStream_t)stream;
   if (!table) rot = 0;
+  const int vec = dtype == GF_F32 ? 4 : 8;
+  const size_t esz = dtype == GF_F32 ? 4 : 2;
+  const bool can_vec = (rot / 2) % vec == 0 && hd % vec == 0 && row_stride % vec == 0 &&
+                       ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)kpages % 16 == 0) &&
+                       ((uintptr_t)vpages % 16 == 0) && ((size_t)nkv * hd * esz) % 16 == 0;
+  if (can_vec) {
+    int work = (nh + nkv) * (rot / 2 / vec) + nkv * ((hd - rot) / vec) + nkv * hd / vec;
+    int threads = (work + 31) / 32 * 32;
+    threads = threads < 32 ? 32 : threads > 256 ? 256 : threads;
+    if (dtype == GF_F32)
+      return launch_kernel(rope_kv_write_vec_kernel<float>, dim3(T), dim3(threads), 0, st,
+                           (float*)qkv, row_stride, table, rot, positions, slot_mapping,
+                           (float*)kpages, (float*)vpages, nh, nkv, hd);
+    return launch_kernel(rope_kv_write_vec_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, st,
+                         (__nv_bfloat16*)qkv, row_stride, table, rot, positions, slot_mapping,
+                         (__nv_bfloat16*)kpages, (__nv_bfloat16*)vpages, nh, nkv, hd);
+  }
   int work = (nh + nkv) * (rot / 2);
   if (nkv * hd > work) work = nkv * hd;
   int threads = (work + 31) / 32 * 32;
@@ -201,7 +296,8 @@ GF_EXPORT int gf_silu_mul(const void* gu, void* out, int T, int I, int dtype, vo
   const size_t total = (size_t)T * I;
   if (total == 0) return 0;
   auto st = (cudaStream_t)stream;
-  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  const size_t want = (total / 2 + 255) / 256 + 1;
+  const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
   if (dtype == GF_F32)
     return launch_kernel(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, st, (const float*)gu,
                          (float*)out, total);

@@ -94,6 +94,12 @@ def gemm(x, weight, bias_f32=None, out_dtype=torch.bfloat16, epi: int = 0, split
     return out
 
 
+MAX_TOKENS = 64     # beyond this many tokens a plain product goes to cuBLAS, which is faster there
+
+
 def try_linear(x, weight, bias_f32, out_dtype):
-    """Run the tcgen05 kernel if it takes this shape; ``None`` hands the product to cuBLAS."""
+    """Run the tcgen05 kernel where it is the faster one (the small batches of decode steps and
+    short prompt portions); ``None`` hands the product to cuBLAS."""
+    if x.shape[0] > MAX_TOKENS:
+        return None
     return gemm(x, weight, bias_f32, out_dtype, epi=0)

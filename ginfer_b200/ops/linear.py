@@ -87,7 +87,8 @@ class GatedLinear:
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         if x.dtype == torch.bfloat16:
             from . import gemm_bf16
-            z = gemm_bf16.gemm(x, self.proj.weight, None, torch.bfloat16, epi=2)
-            if z is not None:
-                return z
+            if x.shape[0] <= gemm_bf16.MAX_TOKENS:
+                z = gemm_bf16.gemm(x, self.proj.weight, None, torch.bfloat16, epi=2)
+                if z is not None:
+                    return z
         return silu_mul(self.proj(x))
