@@ -91,6 +91,28 @@ def test_decode_steps_replayed_from_cuda_graphs(folders, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("eager", [True, False])
+def test_first_tokens_one_by_one(folders, name, dtype, eager):
+    """A sequence fed one token at a time from its very first token (position 0, the first page,
+    the first page edge, the window filling up), two requests side by side that start at
+    different steps."""
+    model_dir = folders[(name, _storage(dtype))]
+    v = CONFIGS[name]["vocab_size"]
+    reqs = {"p": prompt(70, v, seed=11), "q": prompt(45, v, seed=12)}
+    steps = []
+    for i in range(70):
+        ent = [{"id": "p", "tokens": [reqs["p"][i]], "want": [0]}]
+        if 5 <= i < 50:
+            ent.append({"id": "q", "tokens": [reqs["q"][i - 5]], "want": [0]})
+        steps.append({"step": i, "entries": ent, "end": ["q"] if i == 49 else []})
+    steps[-1]["end"] = ["p"]
+    runner = _runner(model_dir, dtype, PAGE[name], 192, eager=eager)
+    rows = replay.run_in_process(runner, steps)
+    replay.compare(rows, replay.plain_logits(model_dir, reqs, dtype), dtype, reqs)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_program_mixed(folders, tmp_path, dtype):
     """The same through ``bin/trace_run`` (page size 16, pool sized by --max-tokens)."""
     model_dir = folders[("B", _storage(dtype))]
