@@ -648,3 +648,62 @@ GF_EXPORT int gf_attn_prefill(const void* q, int q_row_stride, const void* kpage
                        table_stride, cu_seqlens_q, kv_lens, (bf16*)out, nh, nkv, page_size, window,
                        scale * LOG2E);
 }
+
+// ----------------------------------------------------------------------------- no allocation
+// gf_attn_decode with scratch of its own; see attention_no_alloc.h for who needs it and the rules.
+#include <stdio.h>
+
+#include "attention_no_alloc.h"
+
+namespace {
+
+// The scratch of gf_attn_decode_static.  In host code this name is only a handle for
+// cudaGetSymbolAddress, never an address a kernel could use.
+static __device__ __align__(256) unsigned char g_static_scratch[GF_ATTN_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_addr[kMaxDevices] = {};     // device address per device, found on first use
+thread_local char g_static_error[256] = "";
+
+}  // namespace
+
+GF_EXPORT const char* gf_attn_decode_static_error(void) { return g_static_error; }
+
+GF_EXPORT int gf_attn_decode_static(const void* q, int q_row_stride, const void* kpages,
+                                    const void* vpages, const int* block_table, int table_stride,
+                                    const int* cu_seqlens_q, const int* positions, void* out,
+                                    int B, int nh, int nkv, int page_size, int window, float scale,
+                                    int splits, void* stream) {
+  g_static_error[0] = 0;
+  const long long need = gf_attn_decode_scratch_bytes(B, nh, splits);
+  if (need > (long long)GF_ATTN_STATIC_SCRATCH_BYTES) {
+    snprintf(g_static_error, sizeof g_static_error,
+             "gf_attn_decode_static: %d requests x %d heads x %d splits x head size %d need %lld "
+             "bytes of scratch; the built-in array holds %u",
+             B, nh, splits, HD, need, (unsigned)GF_ATTN_STATIC_SCRATCH_BYTES);
+    return GF_ATTN_STATIC_TOO_LARGE;
+  }
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    snprintf(g_static_error, sizeof g_static_error,
+             "gf_attn_decode_static: no usable current device (cudaGetDevice: %s, device %d)",
+             cudaGetErrorString(e), dev);
+    return e != cudaSuccess ? (int)e : -9;
+  }
+  if (!g_static_scratch_addr[dev]) {
+    // once per device, with that device current: the array's address on this device
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || !p) {
+      snprintf(g_static_error, sizeof g_static_error,
+               "gf_attn_decode_static: cudaGetSymbolAddress failed on device %d: %s", dev,
+               cudaGetErrorString(e));
+      return e != cudaSuccess ? (int)e : -9;
+    }
+    g_static_scratch_addr[dev] = p;
+  }
+  return gf_attn_decode(q, q_row_stride, kpages, vpages, block_table, table_stride, cu_seqlens_q,
+                        positions, out, splits > 1 ? g_static_scratch_addr[dev] : nullptr, B, nh,
+                        nkv, page_size, window, scale, splits, stream);
+}
