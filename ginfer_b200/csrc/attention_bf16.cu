@@ -71,41 +71,60 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // Load keys [c0, c0 + KT) of one kv head into [KT][ROW] tiles of K and V; rows at or past `end` (or
-// before `begin`) are zero-filled and touch no page.  The block-table look-ups of all of a thread's
-// rows are issued first, so that they overlap instead of each waiting for the one before.
+// before `begin`) are zero-filled and touch no page.  `tbl[lp - lp_base]` is the physical page of
+// logical page lp: the kernels copy the part of the request's block table they need into shared
+// memory first (lp_base = its first entry), so a tile's loads do not wait for look-ups in global
+// memory; the look-ups of all of a thread's rows are issued before its copies.
 __device__ __forceinline__ void load_kv_tiles(bf16* kdst, bf16* vdst,
                                               const bf16* __restrict__ kpages,
                                               const bf16* __restrict__ vpages,
-                                              const int* __restrict__ tbl, int c0, int begin,
-                                              int end, int page_size, int page_shift,
+                                              const int* tbl, int lp_base, int c0,
+                                              int begin, int end, int page_size, int page_shift,
                                               size_t tok_stride, int kvh) {
   constexpr int CH = HD / 8;                           // 16-byte chunks in a row
-  constexpr int ITERS = (KT * CH + NTHREADS - 1) / NTHREADS;
-  long long off[ITERS];                                // element offset of the chunk, -1: no load
+  if constexpr (NTHREADS % CH == 0) {
+    // a thread keeps its chunk column and walks down the rows in steps of NTHREADS / CH
+    constexpr int RSTEP = NTHREADS / CH, ITERS = KT / RSTEP;
+    const int ch = threadIdx.x % CH, rb = threadIdx.x / CH;
+    const unsigned col = (unsigned)(kvh * HD + ch * 8);
+    const unsigned stride = (unsigned)tok_stride;
+    unsigned slot[ITERS];
+    bool ok[ITERS];
 #pragma unroll
-  for (int it = 0; it < ITERS; ++it) {
-    const int i = threadIdx.x + it * NTHREADS;
-    const int r = i / CH, ch = i - r * CH;
-    const int c = c0 + r;
-    const bool ok = i < KT * CH && c >= begin && c < end;
-    off[it] = -1;
-    if (ok) {
-      // page_shift >= 0: the page size is a power of two
-      const int lp = page_shift >= 0 ? c >> page_shift : c / page_size;
-      const int in_page = page_shift >= 0 ? c & (page_size - 1) : c - lp * page_size;
-      const int page = __ldg(tbl + lp);
-      off[it] = ((long long)page * page_size + in_page) * (long long)tok_stride +
-                (long long)(kvh * HD + ch * 8);
+    for (int it = 0; it < ITERS; ++it) {
+      const int c = c0 + rb + it * RSTEP;
+      ok[it] = c >= begin && c < end;
+      slot[it] = 0;
+      if (ok[it]) {
+        const int lp = page_shift >= 0 ? c >> page_shift : c / page_size;
+        const int in_page = page_shift >= 0 ? c & (page_size - 1) : c - lp * page_size;
+        slot[it] = (unsigned)tbl[lp - lp_base] * (unsigned)page_size + (unsigned)in_page;
+      }
     }
-  }
 #pragma unroll
-  for (int it = 0; it < ITERS; ++it) {
-    const int i = threadIdx.x + it * NTHREADS;
-    if (i < KT * CH) {
+    for (int it = 0; it < ITERS; ++it) {
+      const size_t off = (size_t)slot[it] * stride + col;        // one wide multiply
+      const int r = rb + it * RSTEP;
+      cp_async16(kdst + r * ROW + ch * 8, kpages + off, ok[it]);
+      cp_async16(vdst + r * ROW + ch * 8, vpages + off, ok[it]);
+    }
+  } else {
+    constexpr int ITERS = (KT * CH + NTHREADS - 1) / NTHREADS;
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      const int i = threadIdx.x + it * NTHREADS;
+      if (i >= KT * CH) break;
       const int r = i / CH, ch = i - r * CH;
-      const bool ok = off[it] >= 0;
-      cp_async16(kdst + r * ROW + ch * 8, ok ? kpages + off[it] : kpages, ok);
-      cp_async16(vdst + r * ROW + ch * 8, ok ? vpages + off[it] : vpages, ok);
+      const int c = c0 + r;
+      const bool ok = c >= begin && c < end;
+      size_t off = 0;
+      if (ok) {
+        const int lp = c / page_size;
+        off = ((size_t)tbl[lp - lp_base] * page_size + (c - lp * page_size)) * tok_stride +
+              (size_t)(kvh * HD + ch * 8);
+      }
+      cp_async16(kdst + r * ROW + ch * 8, kpages + off, ok);
+      cp_async16(vdst + r * ROW + ch * 8, vpages + off, ok);
     }
   }
 }
@@ -154,7 +173,14 @@ __device__ __forceinline__ void pv_tile(float (&o)[HD / 8][4], const float (&s)[
 // entry and the probabilities on exit.  Columns are keys col0 + ...; row i of the pair (i = 0:
 // row g, i = 1: row g + 8) sees keys in [lo[i], hi[i]].  m and l are per-thread copies of the row
 // maximum (in log2 units) and a partial row sum.
-template <int NT>
+__device__ __forceinline__ float fast_exp2(float x) {   // 2^x; -inf -> 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// MASKED = false: every column is visible to both rows (an interior tile): no comparisons.
+template <int NT, bool MASKED>
 __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[HD / 8][4],
                                                float (&m)[2], float (&l)[2], int col0,
                                                const int (&lo)[2], const int (&hi)[2],
@@ -165,8 +191,12 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[HD 
   for (int j = 0; j < NT; ++j)
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const int c = col0 + 8 * j + 2 * t + (e & 1), i = e >> 1;
-      const float v = (c >= lo[i] && c <= hi[i]) ? s[j][e] * scale_log2 : -INFINITY;
+      const int i = e >> 1;
+      float v = s[j][e] * scale_log2;
+      if (MASKED) {
+        const int c = col0 + 8 * j + 2 * t + (e & 1);
+        v = (c >= lo[i] && c <= hi[i]) ? v : -INFINITY;
+      }
       s[j][e] = v;
       mx[i] = fmaxf(mx[i], v);
     }
@@ -175,11 +205,12 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[HD 
     mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
     mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
   }
-  float corr[2], mnew[2];
+  float corr[2], mnew[2], msub[2];
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     mnew[i] = fmaxf(m[i], mx[i]);
-    corr[i] = mnew[i] == -INFINITY ? 1.f : exp2f(m[i] - mnew[i]);
+    msub[i] = mnew[i] == -INFINITY ? 0.f : mnew[i];      // keeps -inf - -inf out of the exponent
+    corr[i] = fast_exp2(m[i] - msub[i]);                 // m = -inf: 0 (nothing accumulated yet)
     m[i] = mnew[i];
   }
   float sum[2] = {0.f, 0.f};
@@ -188,18 +219,21 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[HD 
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const int i = e >> 1;
-      const float p = mnew[i] == -INFINITY ? 0.f : exp2f(s[j][e] - mnew[i]);
+      const float p = fast_exp2(s[j][e] - msub[i]);
       s[j][e] = p;
       sum[i] += p;
     }
 #pragma unroll
   for (int i = 0; i < 2; ++i) l[i] = l[i] * corr[i] + sum[i];
+  // the accumulator is rescaled only when some row of the warp got a new maximum
+  if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
 #pragma unroll
-  for (int n = 0; n < HD / 8; ++n) {
-    o[n][0] *= corr[0];
-    o[n][1] *= corr[0];
-    o[n][2] *= corr[1];
-    o[n][3] *= corr[1];
+    for (int n = 0; n < HD / 8; ++n) {
+      o[n][0] *= corr[0];
+      o[n][1] *= corr[0];
+      o[n][2] *= corr[1];
+      o[n][3] *= corr[1];
+    }
   }
 }
 
@@ -208,6 +242,7 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[HD 
 // Partials: po [B, nh, splits, HD] fp32 unnormalised, pml [B, nh, splits, 2] = (max in log2 units,
 // sum).  With one split the normalised bf16 result goes straight to `out`.
 constexpr int DEC_STAGES = 3;
+constexpr int kMaxTableCopy = 4096;   // block-table entries a CTA copies to shared memory at most
 constexpr int kMaxDecodeGroups = 1 << 16;     // (request, kv head, head chunk) triples with a counter
 __device__ unsigned int g_decode_done[kMaxDecodeGroups];
 
@@ -217,7 +252,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
                    int table_stride, const int* __restrict__ cu_seqlens_q,
                    const int* __restrict__ positions, bf16* __restrict__ out,
                    float* __restrict__ po, float* __restrict__ pml, int nh, int nkv,
-                   int page_size, int window, float scale_log2, int splits, int fused_merge) {
+                   int page_size, int window, float scale_log2, int splits, int fused_merge,
+                   int tbl_off, int tbl_cap) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ bool last_split;
   bf16* ks = reinterpret_cast<bf16*>(smem_raw);                 // [STAGES][KT][ROW]
@@ -265,10 +301,22 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
   const int lo2[2] = {begin, begin}, hi2[2] = {end - 1, end - 1};
 
   const int ntiles = begin < end ? (end - begin + KT - 1) / KT : 0;
+  // this split's block-table entries -> shared memory
+  int lp_base = 0;
+  if (ntiles > 0) {
+    const int lp0 = begin / page_size, nlp = (end - 1) / page_size - lp0 + 1;
+    if (nlp <= tbl_cap) {
+      int* stbl = reinterpret_cast<int*>(smem_raw + tbl_off);
+      for (int i = threadIdx.x; i < nlp; i += NTHREADS) stbl[i] = tbl[lp0 + i];
+      __syncthreads();
+      tbl = stbl;
+      lp_base = lp0;
+    }
+  }
   for (int s = 0; s < DEC_STAGES - 1; ++s) {
     if (s < ntiles)
-      load_kv_tiles(ks + s * KT * ROW, vs + s * KT * ROW, kpages, vpages, tbl, begin + s * KT,
-                    begin, end, page_size, page_shift, tok_stride, kvh);
+      load_kv_tiles(ks + s * KT * ROW, vs + s * KT * ROW, kpages, vpages, tbl, lp_base,
+                    begin + s * KT, begin, end, page_size, page_shift, tok_stride, kvh);
     cp_async_commit();
   }
   for (int it = 0; it < ntiles; ++it) {
@@ -277,8 +325,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
     const int nxt = it + DEC_STAGES - 1;
     if (nxt < ntiles) {
       const int st = nxt % DEC_STAGES;
-      load_kv_tiles(ks + st * KT * ROW, vs + st * KT * ROW, kpages, vpages, tbl, begin + nxt * KT,
-                    begin, end, page_size, page_shift, tok_stride, kvh);
+      load_kv_tiles(ks + st * KT * ROW, vs + st * KT * ROW, kpages, vpages, tbl, lp_base,
+                    begin + nxt * KT, begin, end, page_size, page_shift, tok_stride, kvh);
     }
     cp_async_commit();
     const int st = it % DEC_STAGES;
@@ -286,7 +334,10 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
     if (col0 < end) {
       float s[2][4] = {};
       qk_tile<2>(s, qf, ks + st * KT * ROW, warp * 16, lane);
-      softmax_update<2>(s, o, m, l, col0, lo2, hi2, scale_log2, lane);
+      if (col0 + 16 <= end)
+        softmax_update<2, false>(s, o, m, l, col0, lo2, hi2, scale_log2, lane);
+      else
+        softmax_update<2, true>(s, o, m, l, col0, lo2, hi2, scale_log2, lane);
       pv_tile<2>(o, s, vs + st * KT * ROW, warp * 16, lane);
     }
   }
@@ -420,7 +471,7 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ po,
 // Head sizes above 128 keep one row tile per warp (the output accumulator would not fit twice).
 constexpr int PRE_STAGES = 2;
 #ifndef GF_ATTN_MT
-#define GF_ATTN_MT 2
+#define GF_ATTN_MT 1
 #endif
 constexpr int MT = HD <= 128 ? GF_ATTN_MT : 1;
 constexpr int WROWS = 16 * MT;                 // query rows per warp
@@ -431,7 +482,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __
                     const bf16* __restrict__ vpages, const int* __restrict__ block_table,
                     int table_stride, const int* __restrict__ cu_seqlens_q,
                     const int* __restrict__ kv_lens, bf16* __restrict__ out, int nh, int nkv,
-                    int page_size, int window, float scale_log2) {
+                    int page_size, int window, float scale_log2, int tbl_off, int tbl_cap) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);                 // [QT][ROW]
   bf16* ks = qs + QT * ROW;                                     // [STAGES][KT][ROW]
@@ -469,7 +520,18 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __
   const int key_lo = window > 0 ? max(0, p_first - window + 1) : 0;
   const int begin = key_lo / KT * KT, end = p_last + 1;
   const int ntiles = (end - begin + KT - 1) / KT;
-  load_kv_tiles(ks, vs, kpages, vpages, tbl, begin, key_lo, end, page_size, page_shift, tok_stride, kvh);
+  int lp_base = 0;
+  {
+    const int lp0 = key_lo / page_size, nlp = (end - 1) / page_size - lp0 + 1;
+    if (nlp <= tbl_cap) {
+      int* stbl = reinterpret_cast<int*>(smem_raw + tbl_off);
+      for (int i = threadIdx.x; i < nlp; i += NTHREADS) stbl[i] = tbl[lp0 + i];
+      __syncthreads();
+      tbl = stbl;
+      lp_base = lp0;
+    }
+  }
+  load_kv_tiles(ks, vs, kpages, vpages, tbl, lp_base, begin, key_lo, end, page_size, page_shift, tok_stride, kvh);
   cp_async_commit();
 
   float o[MT][HD / 8][4];
@@ -499,7 +561,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __
     __syncthreads();
     if (it + 1 < ntiles) {
       const int st = (it + 1) % PRE_STAGES;
-      load_kv_tiles(ks + st * KT * ROW, vs + st * KT * ROW, kpages, vpages, tbl,
+      load_kv_tiles(ks + st * KT * ROW, vs + st * KT * ROW, kpages, vpages, tbl, lp_base,
                     begin + (it + 1) * KT, key_lo, end, page_size, page_shift, tok_stride, kvh);
     }
     cp_async_commit();
@@ -530,9 +592,19 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __
         }
       }
     }
+    // interior tile: every row of the warp sees all of its keys
+    const int first_p = pos0 + r0 + warp * WROWS;
+    const bool interior = col0 + KT - 1 <= first_p && warp * WROWS + WROWS <= rows &&
+                          (window <= 0 || col0 >= first_p + WROWS - 1 - window + 1);
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-      softmax_update<8>(s[mt], o[mt], m[mt], l[mt], col0, lo2[mt], hi2[mt], scale_log2, lane);
+    for (int mt = 0; mt < MT; ++mt) {
+      if (interior)
+        softmax_update<8, false>(s[mt], o[mt], m[mt], l[mt], col0, lo2[mt], hi2[mt], scale_log2,
+                                 lane);
+      else
+        softmax_update<8, true>(s[mt], o[mt], m[mt], l[mt], col0, lo2[mt], hi2[mt], scale_log2,
+                                lane);
+    }
     // O += P V
 #pragma unroll
     for (int kc = 0; kc < 4; ++kc) {
@@ -605,11 +677,14 @@ GF_EXPORT int gf_attn_decode(const void* q, int q_row_stride, const void* kpages
   const int G = nh / nkv, chunks = (G + 15) / 16;
   const size_t tiles = (size_t)2 * DEC_STAGES * KT * ROW * sizeof(bf16);
   const size_t merge = (size_t)(4 * 16 * HD + 2 * 4 * 16) * sizeof(float);
-  const size_t smem = tiles > merge ? tiles : merge;
+  const size_t work = ((tiles > merge ? tiles : merge) + 15) / 16 * 16;
+  const int tbl_cap = table_stride < kMaxTableCopy ? table_stride : kMaxTableCopy;
+  const size_t smem = work + (size_t)tbl_cap * sizeof(int);
   static bool attr_done = false;
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)(work + kMaxTableCopy * sizeof(int)));
     if (e != cudaSuccess) return (int)e;
     attr_done = true;
   }
@@ -620,7 +695,7 @@ GF_EXPORT int gf_attn_decode(const void* q, int q_row_stride, const void* kpages
   int rc = launch_kernel(attn_decode_kernel, grid, dim3(NTHREADS), smem, st, (const bf16*)q,
                          q_row_stride, (const bf16*)kpages, (const bf16*)vpages, block_table,
                          table_stride, cu_seqlens_q, positions, (bf16*)out, po, pml, nh, nkv,
-                         page_size, window, scale * LOG2E, splits, fused);
+                         page_size, window, scale * LOG2E, splits, fused, (int)work, tbl_cap);
   if (rc || splits == 1 || fused) return rc;
   return launch_kernel(attn_decode_merge_kernel, dim3(nh, B), dim3(HD), 0, st, (const float*)po,
                        (const float*)pml, cu_seqlens_q, (bf16*)out, nh, splits);
@@ -634,11 +709,14 @@ GF_EXPORT int gf_attn_prefill(const void* q, int q_row_stride, const void* kpage
   if (B <= 0 || max_q_len <= 0) return 0;
   if (nh % nkv) return -3;
   auto st = (cudaStream_t)stream;
-  const size_t smem = (size_t)(QT + 2 * PRE_STAGES * KT) * ROW * sizeof(bf16);
+  const size_t work = (size_t)(QT + 2 * PRE_STAGES * KT) * ROW * sizeof(bf16);
+  const int tbl_cap = table_stride < kMaxTableCopy ? table_stride : kMaxTableCopy;
+  const size_t smem = work + (size_t)tbl_cap * sizeof(int);
   static bool attr_done = false;
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)(work + kMaxTableCopy * sizeof(int)));
     if (e != cudaSuccess) return (int)e;
     attr_done = true;
   }
@@ -646,7 +724,7 @@ GF_EXPORT int gf_attn_prefill(const void* q, int q_row_stride, const void* kpage
   return launch_kernel(attn_prefill_kernel, grid, dim3(NTHREADS), smem, st, (const bf16*)q,
                        q_row_stride, (const bf16*)kpages, (const bf16*)vpages, block_table,
                        table_stride, cu_seqlens_q, kv_lens, (bf16*)out, nh, nkv, page_size, window,
-                       scale * LOG2E);
+                       scale * LOG2E, (int)work, tbl_cap);
 }
 
 // ----------------------------------------------------------------------------- no allocation
