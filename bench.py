@@ -195,7 +195,7 @@ def decode_end_to_end(eng, batch: int, steps: int, warmup: int, seed: int):
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
     h2d = (eng.runner.h2d_bytes - h0) / steps
-    while not eng.scheduler.is_finished():
+    while not eng.is_idle():
         eng.step()
     eng.requests.clear()
     return 1e3 * dt / steps, int(h2d), 4 * batch

@@ -11,6 +11,7 @@ from __future__ import annotations
 import time
 from dataclasses import dataclass, field
 
+import numpy as np
 import torch
 
 from ..config.engine_config import EngineConfig
@@ -44,15 +45,24 @@ class EngineStats:
         }
 
 
+@dataclass
+class _Flight:
+    """A step that has been launched: its batch and the sampled tokens on their way."""
+    batch: list
+    pending: object
+
+
 class Engine:
     def __init__(self, model_path: str | None = None, *, config: dict | None = None,
                  weights_seed: int = 0, dtype: str = "bfloat16",
                  max_num_batched_tokens: int = 8192, max_num_seqs: int = 64,
                  max_seq_len: int = 4096, gpu_memory_utilization: float = 0.8,
                  kvcache_block_size: int = 16, num_kvcache_blocks: int | None = None,
-                 enforce_eager: bool = False, device: str = "cuda:0", seed: int = 0):
+                 enforce_eager: bool = False, device: str = "cuda:0", seed: int = 0,
+                 pipeline: bool = True):
         """``model_path``: a folder with ``config.json`` and ``model.safetensors``; or give
-        ``config`` (a ``config.json`` as a dict) and ``weights_seed`` for random weights."""
+        ``config`` (a ``config.json`` as a dict) and ``weights_seed`` for random weights.
+        ``pipeline``: prepare each step on the host while the device runs the one before."""
         self.cfg = EngineConfig(model_path or "<random>", dtype, max_num_batched_tokens,
                                 max_num_seqs, max_seq_len, gpu_memory_utilization,
                                 kvcache_block_size, num_kvcache_blocks, enforce_eager, device)
@@ -72,6 +82,8 @@ class Engine:
                                    self.runner.max_seq_len, self.model.plan.eos_token_ids)
         self.sampler = Sampler(device)
         self.seed = int(seed)
+        self.pipeline = bool(pipeline)
+        self._flight = None
         self.stats = EngineStats()
         self._next_id = 0
         self.requests: dict[int, Request] = {}
@@ -93,30 +105,72 @@ class Engine:
         return rid
 
     # ------------------------------------------------------------------ one step
+    def _entries(self, batch):
+        """Step entries of a scheduled batch; a token not known yet stands as 0 until launch."""
+        out = []
+        for s in batch:
+            toks = s.request.tokens(s.start, s.start + s.num_tokens)
+            if toks and toks[-1] == Scheduler.PENDING:
+                toks = toks[:-1] + [0]
+            out.append(StepEntry(s.request.request_id, toks,
+                                 [s.num_tokens - 1] if s.sample else []))
+        return out
+
+    def _launch(self, batch, prepared, entries) -> "_Flight":
+        """Launch a prepared step with the requests' tokens as they are now, and the choice of
+        the next tokens behind it; nothing waits for the device."""
+        token_ids = np.fromiter((t for s in batch
+                                 for t in s.request.tokens(s.start, s.start + s.num_tokens)),
+                                dtype=np.int64)
+        logits = self.runner.launch(prepared, entries, token_ids)
+        picks = [s for s in batch if s.sample]
+        pending = self.sampler.sample_async(
+            logits, [s.request.params.temperature for s in picks],
+            [s.request.seed for s in picks],
+            [s.start + s.num_tokens - len(s.request.prompt) for s in picks])
+        return _Flight(batch, pending)
+
+    def is_idle(self) -> bool:
+        return self._flight is None and self.scheduler.is_finished()
+
     def step(self) -> list[Request]:
-        """Schedule, run, sample, post-process; returns the requests that finished."""
+        """Complete one step: schedule and launch it unless the previous call already did, and
+        (``pipeline``) schedule and prepare the following step on the host while the device still
+        runs this one; then read the sampled tokens, post-process, and launch the following step.
+        Returns the requests that finished.  A request that ends on an EOS token while it is
+        already part of the following step is returned one call later (its extra token is
+        dropped); its output is the same either way."""
         t0 = time.perf_counter()
-        batch, dropped = self.scheduler.schedule()
-        finished = list(dropped)
-        if batch:
-            entries = [StepEntry(s.request.request_id,
-                                 s.request.tokens(s.start, s.start + s.num_tokens),
-                                 [s.num_tokens - 1] if s.sample else []) for s in batch]
-            logits = self.runner.step(entries)
-            picks = [s for s in batch if s.sample]
-            tokens = self.sampler.sample(
-                logits, [s.request.params.temperature for s in picks],
-                [s.request.seed for s in picks], [len(s.request.output) for s in picks])
-            gemm_bf16.check_errors(self.cfg.device)
-            finished += self.scheduler.postprocess(batch, tokens)
-            dt = time.perf_counter() - t0
-            if any(s.num_tokens > 1 for s in batch):
-                self.stats.prefill_tokens += sum(s.num_tokens for s in batch)
-                self.stats.prefill_seconds += dt
-            else:
-                self.stats.decode_tokens += len(batch)
-                self.stats.decode_seconds += dt
-            self.stats.steps += 1
+        finished: list[Request] = []
+        if self._flight is None:
+            batch, dropped = self.scheduler.schedule()
+            finished += dropped
+            if not batch:
+                return finished
+            entries = self._entries(batch)
+            self._flight = self._launch(batch, self.runner.prepare(entries), entries)
+        cur = self._flight
+        finished += self.scheduler.advance(cur.batch)
+        nxt = None
+        if self.pipeline:
+            batch, dropped = self.scheduler.schedule()
+            finished += dropped
+            if batch:
+                entries = self._entries(batch)
+                nxt = (batch, self.runner.prepare(entries), entries)
+        tokens = cur.pending.result()                   # the device catches up here
+        gemm_bf16.check_errors(self.cfg.device)
+        in_next = {s.request.request_id for s in nxt[0]} if nxt else ()
+        finished += self.scheduler.resolve(cur.batch, tokens, in_next)
+        self._flight = self._launch(*nxt) if nxt else None
+        dt = time.perf_counter() - t0
+        if any(s.num_tokens > 1 for s in cur.batch):
+            self.stats.prefill_tokens += sum(s.num_tokens for s in cur.batch)
+            self.stats.prefill_seconds += dt
+        else:
+            self.stats.decode_tokens += len(cur.batch)
+            self.stats.decode_seconds += dt
+        self.stats.steps += 1
         self.stats.preemptions = self.scheduler.num_preemptions
         return finished
 
@@ -129,7 +183,7 @@ class Engine:
         if len(sampling_params) != len(prompts):
             raise ValueError("one SamplingParams per prompt is needed")
         ids = [self.add_request(p, sp) for p, sp in zip(prompts, sampling_params)]
-        while not self.scheduler.is_finished():
+        while not self.is_idle():
             self.step()
         out = [self.requests[i].output for i in ids]
         self.last_requests = [self.requests.pop(i) for i in ids]

@@ -25,6 +25,7 @@ class Request:
     state: RequestState = RequestState.WAITING
     num_computed: int = 0            # tokens whose keys are in the cache
     finish_reason: str | None = None  # "eos" | "max_tokens" | "max_seq_len" | "out_of_pages"
+    finish_pending: str | None = None  # ended, but still part of a step that is under way
     num_preemptions: int = 0
     arrival_time: float = 0.0
     first_token_time: float | None = None

@@ -150,8 +150,6 @@ class ModelRunner:
 
         tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64).reshape(-1)
                                  for e in entries])
-        if tokens.min() < 0 or tokens.max() >= self.vocab_size:
-            raise ValueError(f"token ids must lie in [0, {self.vocab_size})")
         cu = np.zeros(B + 1, dtype=np.int64)
         np.cumsum(q_lens, out=cu[1:])
         seq_of_token = np.repeat(np.arange(B), q_lens)
@@ -269,11 +267,19 @@ class ModelRunner:
         return _DecodeGraph(graph, ints, {}, logits, ops.launch_count() - before)
 
     @torch.no_grad()
-    def step(self, entries: list[StepEntry]) -> torch.Tensor:
-        """Run the entries' tokens as one batch; returns fp32 logits ``[wanted, vocab]`` on the
-        device, in the order of the entries and of each entry's ``want``.  The tensor is valid
-        until the next call of ``step``."""
-        arrays, facts = self.prepare(entries)
+    def launch(self, prepared, entries: list[StepEntry], token_ids=None) -> torch.Tensor:
+        """Second half of a step: copy the integers and run.  ``token_ids`` (all tokens of the
+        step, packed) replaces the values the entries held when the step was prepared, for a
+        caller that prepares a step before its last tokens are known."""
+        arrays, facts = prepared
+        if token_ids is not None:
+            token_ids = np.asarray(token_ids, dtype=np.int64).reshape(-1)
+            if token_ids.size != facts["T"]:
+                raise ValueError(f"{token_ids.size} token ids for a step of {facts['T']} tokens")
+            arrays["token_ids"] = token_ids
+        tokens = arrays["token_ids"]
+        if tokens.min() < 0 or tokens.max() >= self.vocab_size:
+            raise ValueError(f"token ids must lie in [0, {self.vocab_size})")
         with torch.cuda.device(self.device):
             key = self._graph_key(entries, facts)
             if key is not None:
@@ -292,3 +298,9 @@ class ModelRunner:
             self.cache.commit(e.request_id, int(n))
         self.steps_run += 1
         return logits
+
+    def step(self, entries: list[StepEntry]) -> torch.Tensor:
+        """Run the entries' tokens as one batch; returns fp32 logits ``[wanted, vocab]`` on the
+        device, in the order of the entries and of each entry's ``want``.  The tensor is valid
+        until the next call of ``step``."""
+        return self.launch(self.prepare(entries), entries)

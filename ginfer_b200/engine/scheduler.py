@@ -39,6 +39,7 @@ class Scheduled:
     start: int            # position of the first token of the portion
     num_tokens: int
     sample: bool          # the portion ends at the request's last token: a token is sampled
+    dropped: bool = False  # the request had ended already when this step was advanced
 
 
 class Scheduler:
@@ -195,24 +196,61 @@ class Scheduler:
     def postprocess(self, batch: list[Scheduled], sampled: list[int]) -> list[Request]:
         """``sampled``: one token for every entry of ``batch`` with ``sample`` set, in order.
         Appends tokens, finishes requests, returns the finished ones."""
+        finished = self.advance(batch)
+        finished += self.resolve(batch, sampled)
+        return finished
+
+    # The two halves of post-processing, for a host that prepares the next step while the
+    # device still runs this one.  ``advance`` needs no token values: it moves the requests
+    # forward, appends a placeholder for each token being sampled, and finishes what is finished
+    # by count.  ``resolve`` fills the placeholders in once the tokens are known and applies the
+    # EOS rule; a request that is already part of a step in preparation (``in_next``) is only
+    # marked and finishes when that step is advanced (its extra token is dropped).
+    PENDING = -1
+
+    def advance(self, batch: list[Scheduled]) -> list[Request]:
         finished = []
-        it = iter(sampled)
-        now = time.perf_counter()
         for s in batch:
             req = s.request
+            if req.finish_pending is not None:        # hit EOS one step ago: this step is dropped
+                reason, req.finish_pending = req.finish_pending, None
+                s.dropped = True
+                self._finish(req, reason)
+                finished.append(req)
+                continue
             req.num_computed = s.start + s.num_tokens
             if not s.sample:
                 continue
-            tok = int(next(it))
-            req.output.append(tok)
-            if req.first_token_time is None:
-                req.first_token_time = now
-            if not req.params.ignore_eos and tok in self.eos:
-                self._finish(req, "eos")
-            elif len(req.output) >= req.params.max_tokens:
+            req.output.append(self.PENDING)
+            if len(req.output) >= req.params.max_tokens:
                 self._finish(req, "max_tokens")
             elif req.num_tokens >= self.max_seq_len:
                 self._finish(req, "max_seq_len")
             if req.state is RequestState.FINISHED:
                 finished.append(req)
+        return finished
+
+    def resolve(self, batch: list[Scheduled], sampled: list[int], in_next=()) -> list[Request]:
+        finished = []
+        it = iter(sampled)
+        now = time.perf_counter()
+        for s in batch:
+            if not s.sample:
+                continue
+            tok = int(next(it))
+            if s.dropped:
+                continue
+            req = s.request
+            idx = s.start + s.num_tokens - len(req.prompt)       # the output index of this token
+            req.output[idx] = tok
+            if req.first_token_time is None:
+                req.first_token_time = now
+            if not req.params.ignore_eos and tok in self.eos:
+                if req.state is RequestState.FINISHED:
+                    req.finish_reason = "eos"                     # by count as well: EOS names it
+                elif req.request_id in in_next:
+                    req.finish_pending = "eos"
+                else:
+                    self._finish(req, "eos")
+                    finished.append(req)
         return finished

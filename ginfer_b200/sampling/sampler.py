@@ -28,26 +28,56 @@ def uniform(seed: int, index: int) -> float:
     return (h >> 40) / float(1 << 24)
 
 
+class Pending:
+    """Tokens on their way to the host; ``result()`` waits for them."""
+
+    def __init__(self, host: torch.Tensor, n: int, event):
+        self._host, self._n, self._event = host, n, event
+
+    def result(self) -> list[int]:
+        if self._event is not None:
+            self._event.synchronize()
+        return self._host[:self._n].tolist()
+
+
 class Sampler:
     def __init__(self, device):
         self.device = torch.device(device)
-        self._host = torch.empty((2, 1024), dtype=torch.float32, pin_memory=True) \
-            if self.device.type == "cuda" else None
+        cuda = self.device.type == "cuda"
+        self._host = torch.empty((2, 1024), dtype=torch.float32, pin_memory=True) if cuda else None
+        # two result buffers: a step's tokens may be read while the next step's are on their way
+        self._out = [torch.empty(1024, dtype=torch.int32, pin_memory=True) for _ in range(2)] \
+            if cuda else None
+        self._turn = 0
+
+    def sample_async(self, logits: torch.Tensor, temperatures: list[float], seeds: list[int],
+                     indices: list[int]) -> Pending:
+        """Launch the choice of a token per row of ``logits [R, V]`` (fp32, on the device) and
+        its copy to pinned host memory; row ``r`` belongs to a request with ``temperatures[r]``,
+        ``seeds[r]``, generating its token number ``indices[r]``."""
+        R = logits.shape[0]
+        if R == 0:
+            return Pending(torch.empty(0, dtype=torch.int32), 0, None)
+        if all(t <= 0 for t in temperatures):
+            picks = ops.argmax(logits)
+        else:
+            if R > self._host.shape[1]:
+                self._host = torch.empty((2, 2 * R), dtype=torch.float32, pin_memory=True)
+            h = self._host.numpy()
+            h[0, :R] = np.asarray(temperatures, dtype=np.float32)
+            h[1, :R] = np.asarray([uniform(s, i) for s, i in zip(seeds, indices)],
+                                  dtype=np.float32)
+            d = self._host[:, :R].to(self.device, non_blocking=True)
+            picks = ops.sample(logits, d[0].contiguous(), d[1].contiguous())
+        self._turn ^= 1
+        if R > self._out[self._turn].numel():
+            self._out[self._turn] = torch.empty(2 * R, dtype=torch.int32, pin_memory=True)
+        out = self._out[self._turn]
+        out[:R].copy_(picks, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        return Pending(out, R, ev)
 
     def sample(self, logits: torch.Tensor, temperatures: list[float], seeds: list[int],
                indices: list[int]) -> list[int]:
-        """``logits [R, V]`` fp32 on the device; row ``r`` belongs to a request with
-        ``temperatures[r]``, ``seeds[r]``, generating its token number ``indices[r]``."""
-        R = logits.shape[0]
-        if R == 0:
-            return []
-        if all(t <= 0 for t in temperatures):
-            return ops.argmax(logits).tolist()
-        if R > self._host.shape[1]:
-            self._host = torch.empty((2, 2 * R), dtype=torch.float32, pin_memory=True)
-        h = self._host.numpy()
-        h[0, :R] = np.asarray(temperatures, dtype=np.float32)
-        h[1, :R] = np.asarray([uniform(s, i) for s, i in zip(seeds, indices)], dtype=np.float32)
-        d = self._host[:, :R].to(self.device, non_blocking=True)
-        out = ops.sample(logits, d[0].contiguous(), d[1].contiguous()).tolist()
-        return out
+        return self.sample_async(logits, temperatures, seeds, indices).result()

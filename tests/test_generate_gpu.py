@@ -45,6 +45,8 @@ def test_greedy_generation_equals_plain(folders, name, lengths, new):
     # so few pages that requests are preempted and computed again: same tokens
     few = _engine(d, num_kvcache_blocks=9, max_num_batched_tokens=64)
     assert few.generate(prompts, sp) == want
+    # without preparing steps ahead: same tokens
+    assert _engine(d, pipeline=False, max_num_batched_tokens=13).generate(prompts, sp) == want
     if name == "B":
         assert few.stats.preemptions >= 1
 
@@ -62,9 +64,12 @@ def test_eos_stops_generation(folders):
     json.dump(cfg2, open(os.path.join(d2, "config.json"), "w"))
     if not os.path.exists(os.path.join(d2, "model.safetensors")):
         os.link(os.path.join(d, "model.safetensors"), os.path.join(d2, "model.safetensors"))
-    eng = _engine(d2)
-    assert eng.generate([p], SamplingParams(max_tokens=6)) == [free[:free.index(free[2]) + 1]]
-    assert eng.last_requests[0].finish_reason == "eos"
+    for pipeline in (True, False):
+        eng = _engine(d2, pipeline=pipeline)
+        assert eng.generate([p], SamplingParams(max_tokens=6)) == \
+            [free[:free.index(free[2]) + 1]]
+        assert eng.last_requests[0].finish_reason == "eos"
+        assert eng.runner.cache.free_pages() == [40] and not eng.runner.cache.requests
     assert eng.generate([p], SamplingParams(max_tokens=6, ignore_eos=True)) == [free]
 
 
