@@ -73,6 +73,40 @@ def prefill(qkv, pages, block_table, cu_seqlens_q, kv_lens, B, max_q_len, nh, nk
     return out
 
 
+def tc_supports(hd: int, page_size: int) -> bool:
+    return hd in (64, 128) and page_size % 8 == 0 and 128 % page_size == 0
+
+
+def prefill_tc(qkv, pages, block_table, cu_seqlens_q, kv_lens, B, max_q_len, nh, nkv, hd, scale,
+               window, page_size, trace=None):
+    """Prefill attention on tcgen05 (``csrc/attention_tc.cu``); ``None`` if it cannot serve the
+    shapes.  ``trace``: an int64 tensor of 512 slots that receives clock stamps of the first
+    CTA's phases (for tuning)."""
+    from ctypes import c_float, c_int, c_void_p
+
+    from . import _fn, _ok, _p, _stream
+    from .gemm_bf16 import _dev_state
+    if not tc_supports(hd, page_size) or qkv.stride(0) % 8:
+        return None
+    T = qkv.shape[0]
+    out = torch.empty((T, nh * hd), dtype=torch.bfloat16, device=qkv.device)
+    f = _fn("attention_tc", "gf_attn_prefill_tc",
+            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
+             c_void_p, c_void_p], (f"GF_HEAD_DIM={hd}",))
+    rc = f(_p(qkv), qkv.stride(0), _p(pages[0]), _p(pages[1]), pages.shape[1], _p(block_table),
+           block_table.stride(0), _p(cu_seqlens_q), _p(kv_lens), _p(out), T, B, int(max_q_len),
+           nh, nkv, page_size, int(window), float(scale), _p(_dev_state(qkv.device)["err"]),
+           _p(trace), _stream())
+    if rc == -6:
+        return None
+    _ok(rc, "attn_prefill_tc")
+    return out
+
+
+TC_MIN_QUERY_ROWS = 64      # below this a portion is too short to fill 128-row tiles
+
+
 def try_run(qkv, pages, block_table, ctx, nh, nkv, hd, scale, window, page_size):
     """Run a bf16 kernel if one takes this head size; ``None`` hands the work to the plain
     fp32-arithmetic kernel."""
@@ -83,5 +117,10 @@ def try_run(qkv, pages, block_table, ctx, nh, nkv, hd, scale, window, page_size)
         splits = ctx.extras.get("decode_splits") or decode_splits(ctx.num_seqs, nh, nkv, keys)
         return decode(qkv, pages, block_table, ctx.cu_seqlens_q, ctx.positions, ctx.num_seqs, nh,
                       nkv, hd, scale, window, page_size, splits)
+    if ctx.max_q_len >= TC_MIN_QUERY_ROWS:
+        out = prefill_tc(qkv, pages, block_table, ctx.cu_seqlens_q, ctx.kv_lens, ctx.num_seqs,
+                         ctx.max_q_len, nh, nkv, hd, scale, window, page_size)
+        if out is not None:
+            return out
     return prefill(qkv, pages, block_table, ctx.cu_seqlens_q, ctx.kv_lens, ctx.num_seqs,
                    ctx.max_q_len, nh, nkv, hd, scale, window, page_size)

@@ -245,6 +245,30 @@ def test_attention_bf16_prefill(case):
     torch.testing.assert_close(out.double().cpu(), want, atol=1e-2, rtol=2e-2)
 
 
+TC_CASES = [
+    # kv lens, q lens, nh, nkv, hd, page, window
+    ([515, 260], [2, 260], 12, 2, 128, 16, 0),
+    ([700, 90], [65, 90], 6, 3, 64, 16, 100),
+    ([1100], [1100], 14, 2, 64, 32, 0),
+    ([300, 129, 77, 1000], [300, 1, 77, 129], 4, 4, 128, 8, 0),
+    ([640, 400], [128, 400], 2, 1, 128, 16, 200),
+    ([2048], [2048], 4, 2, 128, 16, 0),
+]
+
+
+@pytest.mark.parametrize("case", TC_CASES)
+def test_attention_tcgen05_prefill(case):
+    from ginfer_b200.ops import attention_bf16, gemm_bf16
+    lens, qls, nh, nkv, hd, P, window = case
+    dev, want, scale = _paged_case(lens, qls, nh, nkv, hd, P, window, torch.bfloat16)
+    out = attention_bf16.prefill_tc(_qkv(dev, nh, nkv, hd), dev["pages"], dev["table"], dev["cu"],
+                                    dev["kv_lens"], len(lens), max(qls), nh, nkv, hd, scale,
+                                    window, P)
+    assert out is not None
+    gemm_bf16.check_errors()
+    torch.testing.assert_close(out.double().cpu(), want, atol=1e-2, rtol=2e-2)
+
+
 DEC_CASES = [
     ([70, 5, 130, 1], 4, 2, 16, 16, 0),
     ([200, 64, 1, 63, 65], 3, 1, 32, 8, 0),
