@@ -15,8 +15,8 @@
 // [token slots, kv_heads * HD]; a page is a box of page_size rows; pages past the request's end are
 // loaded from out-of-range coordinates, which TMA fills with zeros.
 //
-// Warps: 0 = TMA loader (every lane issues one box), 1 = tensor-memory allocation and MMA issue
-// (one thread), 2..9 = softmax and epilogue (two threads per query row).  The reference's prefill kernel is a 64x64 mma.sync
+// Warps: 0..3 = TMA loaders (K: 0-1, V: 2-3; every lane issues one box), 4 = tensor-memory
+// allocation and MMA issue (one thread), 5..12 = softmax and epilogue (two threads per query row).  The reference's prefill kernel is a 64x64 mma.sync
 // flash loop with S, P and the row maximum held in bf16
 // (ginfer/core/op/kernels/cuda/page_attn_kernel/flash_gqa_varlen_kernel.cu:420-512).
 //
@@ -41,7 +41,7 @@ constexpr int KT = 128;                    // keys per tile
 constexpr int HALVES = HD / 64;            // 64-channel swizzle atoms per row
 constexpr int K_STAGES = HD == 128 ? 3 : 4;   // K_j is free as soon as S_j is computed
 constexpr int V_STAGES = HD == 128 ? 2 : 3;   // V_j is free once O += P_j V_j is complete
-constexpr int NTHREADS = 320;              // loader warp, MMA warp, eight softmax warps
+constexpr int NTHREADS = 416;              // four loader warps, MMA warp, eight softmax warps
 constexpr uint32_t ATOM_BYTES = 128 * 64 * 2;            // a [128][64] bf16 tile: 16 KB
 constexpr uint32_t Q_BYTES = HALVES * ATOM_BYTES;
 constexpr uint32_t K_BYTES = HALVES * ATOM_BYTES;        // [128 keys][HD]
@@ -214,7 +214,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
   // optional time stamps of the first CTA's phases (dbg: 16 slots per tile per role)
   const bool trace = dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
 #define GF_STAMP(role, i, slot) \
-  if (trace && (i) < 32) dbg[((role) * 32 + (i)) * 8 + (slot)] = clock64()
+  if (trace && (i) < 32) dbg[((role) * 32 + (i)) * 8 + (slot)] = clock64()  /* dbg: 3 * 32 * 8 */
   pdl_trigger();
   pdl_wait();
   const int q_begin = cu_seqlens_q[b], q_len = cu_seqlens_q[b + 1] - q_begin;
@@ -237,11 +237,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
     for (int s = 0; s < K_STAGES; ++s) {
-      mbar_init(&bars->k_full[s], 1);
+      mbar_init(&bars->k_full[s], 2);          // one arrival (with its byte count) per loader warp
       mbar_init(&bars->k_empty[s], 1);
     }
     for (int s = 0; s < V_STAGES; ++s) {
-      mbar_init(&bars->v_full[s], 1);
+      mbar_init(&bars->v_full[s], 2);
       mbar_init(&bars->v_empty[s], 1);
     }
     mbar_init(&bars->s_full[0], 1);
@@ -255,7 +255,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_k) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_v) : "memory");
   }
-  if (warp == 1) {
+  if (warp == 4) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                  ::"r"(smem_u32(&bars->tmem_base)), "r"(TMEM_COLS)
                  : "memory");
@@ -267,25 +267,38 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
   const uint32_t tmem = bars->tmem_base;
   const uint32_t tmem_s = tmem, tmem_o = tmem + 256;          // S buffer b at tmem_s + 128 * b
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ loader
-    if (lane == 0) {
+  if (warp < 4) {
+    // ------------------------------------------------------------------ loaders
+    // Four warps: warps 0-1 bring K tiles, warps 2-3 V tiles, each every other box of its
+    // operand (a box = one page x 64 channels; issuing a TMA copy costs its thread ~80 cycles and
+    // the lanes of a warp issue one after the other, so one warp alone could not keep up with
+    // 16-token pages).  The block-table look-ups of tile i + 1 are made while tile i's boxes are
+    // under way.
+    const bool is_v = warp >= 2;
+    const int part = warp & 1;
+    if (warp == 0 && lane == 0) {
       mbar_expect_tx(&bars->q_full, Q_BYTES);
       for (int h = 0; h < HALVES; ++h)
         tma_load_2d(q_s + h * ATOM_BYTES, &tmap_q, &bars->q_full, head * HD + h * 64,
                     q_begin + r0);
     }
-    // Per tile and operand: one box per (page, 64-channel half); lane l issues boxes l, l + 32, ...
-    // The block-table look-ups of tile i + 1 are made while tile i's boxes are under way.
     const int pages_per_tile = KT / page_size;
-    const int ops = pages_per_tile * HALVES;
-    constexpr int MAX_OPS = (KT / 8) * HALVES / 32 + 1;        // page sizes down to 8
+    const int ops = pages_per_tile * HALVES;                   // boxes per tile of one operand
+    const int my_ops = (ops - part + 1) / 2;                   // boxes part, part + 2, ...
+    constexpr int MAX_OPS = ((KT / 8) * HALVES / 2 + 31) / 32; // page sizes down to 8
+    const int nstages = is_v ? V_STAGES : K_STAGES;
+    const uint32_t tile_bytes = is_v ? V_BYTES : K_BYTES;
+    unsigned char* ring = is_v ? v_s : k_s;
+    uint64_t* full = is_v ? bars->v_full : bars->k_full;
+    uint64_t* empty = is_v ? bars->v_empty : bars->k_empty;
+    const CUtensorMap* map = is_v ? &tmap_v : &tmap_k;
+    const uint32_t my_bytes = (uint32_t)my_ops * (uint32_t)page_size * 128u;
     int rows_next[MAX_OPS];
     auto lookup = [&](int i) {
       const int key0 = (j0 + i) * KT;
 #pragma unroll
       for (int u = 0; u < MAX_OPS; ++u) {
-        const int op = lane + 32 * u;
+        const int op = part + 2 * (lane + 32 * u);
         rows_next[u] = oob_row;
         if (op < ops && i < ntiles) {
           const int c = key0 + (op / HALVES) * page_size;      // first key of this page
@@ -303,41 +316,31 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
       int rows_now[MAX_OPS];
 #pragma unroll
       for (int u = 0; u < MAX_OPS; ++u) rows_now[u] = rows_next[u];
-      const int ks = i % K_STAGES, vs = i % V_STAGES;
+      const int st = i % nstages;
       int ok = 1;
       if (lane == 0) {
-        ok = mbar_wait(&bars->k_empty[ks], ((i / K_STAGES) & 1) ^ 1, abort_flag, err, 1);
-        if (ok) mbar_expect_tx(&bars->k_full[ks], K_BYTES);
+        if (warp == 0) { GF_STAMP(2, i, 0); }
+        ok = mbar_wait(&empty[st], ((i / nstages) & 1) ^ 1, abort_flag, err, 1);
+        if (ok && my_bytes) mbar_expect_tx(&full[st], my_bytes);
+        else if (ok) mbar_arrive(&full[st]);
+        if (warp == 0) { GF_STAMP(2, i, 1); }
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
 #pragma unroll
       for (int u = 0; u < MAX_OPS; ++u) {
-        const int op = lane + 32 * u;
+        const int op = part + 2 * (lane + 32 * u);
         if (op < ops) {
           const int pg = op / HALVES, h = op - pg * HALVES;
-          tma_load_2d(k_s + ks * K_BYTES + h * ATOM_BYTES + (size_t)pg * page_size * 128, &tmap_k,
-                      &bars->k_full[ks], kvh * HD + h * 64, rows_now[u]);
+          tma_load_2d(ring + (size_t)st * tile_bytes + h * ATOM_BYTES +
+                          (size_t)pg * page_size * 128,
+                      map, &full[st], kvh * HD + h * 64, rows_now[u]);
         }
       }
-      lookup(i + 1);                                            // overlaps the wait below
-      if (lane == 0) {
-        ok = mbar_wait(&bars->v_empty[vs], ((i / V_STAGES) & 1) ^ 1, abort_flag, err, 8);
-        if (ok) mbar_expect_tx(&bars->v_full[vs], V_BYTES);
-      }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) break;
-#pragma unroll
-      for (int u = 0; u < MAX_OPS; ++u) {
-        const int op = lane + 32 * u;
-        if (op < ops) {
-          const int pg = op / HALVES, h = op - pg * HALVES;
-          tma_load_2d(v_s + vs * V_BYTES + h * ATOM_BYTES + (size_t)pg * page_size * 128, &tmap_v,
-                      &bars->v_full[vs], kvh * HD + h * 64, rows_now[u]);
-        }
-      }
+      if (warp == 0 && lane == 0) { GF_STAMP(2, i, 2); }
+      lookup(i + 1);                                            // overlaps the next wait
     }
-  } else if (warp == 1) {
+  } else if (warp == 4) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t id_qk = idesc(KT, false), id_pv = idesc(HD, true);
@@ -395,7 +398,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
     // a row agree on the row maximum through shared memory and an mbarrier (a bounded wait; a
     // named barrier could not be left if the other thread gave up).
     const int qd = warp & 3;                                   // TMEM lane quarter of this warp
-    const int half = (warp - 2) >> 2;                          // which 64 keys / which channels
+    const int half = (warp - 5) >> 2;                          // which 64 keys / which channels
     const int r = qd * 32 + lane;                              // query row of this thread
     const int p = pos0 + r0 + r;                               // its position
     const bool live = r < rows;
@@ -541,7 +544,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 4) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem),
                  "r"(TMEM_COLS)
                  : "memory");
