@@ -223,6 +223,70 @@ def prefill_timed(eng, tokens: int, reps: int, warmup: int, seed: int):
     return times[len(times) // 2]
 
 
+# ----------------------------------------------------------------------------- small workloads
+MICRO = ("gemm_gateup_m8", "gemm_down_m8", "gemm_lmhead_m8", "attn_decode_b8", "attn_decode_b64",
+         "prefill_2layers")
+
+
+def run_micro(name: str) -> int:
+    """A few launches of one kernel at the benchmark's sizes, small enough to profile (the
+    commands in ``profiles/`` run these).  Weights are rotated over copies that together exceed
+    the L2 cache."""
+    import math
+
+    import torch
+
+    from ginfer_b200.ops import attention_bf16, gemm_bf16
+    c = QWEN2_1P5B
+    H, I, V = c["hidden_size"], c["intermediate_size"], c["vocab_size"]
+    nh, nkv, hd = c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"]
+    dev = "cuda:0"
+    if name.startswith("gemm_"):
+        M, N, K, epi, out = {"gemm_gateup_m8": (8, 2 * I, H, 2, torch.bfloat16),
+                             "gemm_down_m8": (8, H, I, 0, torch.bfloat16),
+                             "gemm_lmhead_m8": (8, V, H, 0, torch.float32)}[name]
+        copies = max(2, min(8, (300 << 20) // (N * K * 2)))
+        x = torch.randn(M, K, device=dev).to(torch.bfloat16)
+        ws = [(torch.randn(N, K, device=dev) * 0.05).to(torch.bfloat16) for _ in range(copies)]
+        for i in range(8):
+            y = gemm_bf16.gemm(x, ws[i % copies], None, out, epi=epi)
+        torch.cuda.synchronize()
+        gemm_bf16.check_errors()
+        print(json.dumps({"micro": name, "out": list(y.shape)}))
+        return 0
+    if name.startswith("attn_decode"):
+        B = 8 if name.endswith("b8") else 64
+        ctx = PROMPT + 64
+        pages_n = B * (ctx // PAGE + 2)
+        pages = torch.randn(2, pages_n, PAGE, nkv, hd, device=dev).to(torch.bfloat16)
+        table = torch.randperm(pages_n, device=dev).to(torch.int32).reshape(B, -1).contiguous()
+        qkv = torch.randn(B, (nh + 2 * nkv) * hd, device=dev).to(torch.bfloat16)
+        cu = torch.arange(B + 1, dtype=torch.int32, device=dev)
+        pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
+        splits = attention_bf16.decode_splits(B, nh, nkv, ctx)
+        for _ in range(6):
+            y = attention_bf16.decode(qkv, pages, table, cu, pos, B, nh, nkv, hd,
+                                      1 / math.sqrt(hd), 0, PAGE, splits)
+        torch.cuda.synchronize()
+        print(json.dumps({"micro": name, "splits": splits, "out": list(y.shape)}))
+        return 0
+    if name == "prefill_2layers":
+        from ginfer_b200.engine import StepEntry
+        from ginfer_b200.engine.llm import Engine
+        cfg = dict(c)
+        cfg["num_hidden_layers"] = 2
+        eng = Engine(config=cfg, dtype="bfloat16", max_num_seqs=4, max_seq_len=CONTEXT,
+                     num_kvcache_blocks=PREFILL_TOKENS // PAGE + 64, enforce_eager=True)
+        prompt = torch.randint(0, V, (PREFILL_TOKENS,)).tolist()
+        for _ in range(3):
+            eng.runner.step([StepEntry("p", prompt, [PREFILL_TOKENS - 1])])
+            eng.runner.end("p")
+        torch.cuda.synchronize()
+        print(json.dumps({"micro": name, "tokens": PREFILL_TOKENS}))
+        return 0
+    raise SystemExit(f"unknown workload {name!r}; known: {MICRO}")
+
+
 # ----------------------------------------------------------------------------- main
 def main() -> int:
     ap = argparse.ArgumentParser()
@@ -235,7 +299,11 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--enforce-eager", action="store_true")
+    ap.add_argument("--micro", choices=MICRO, default=None,
+                    help="run one small kernel workload (for profiling) instead of the benchmark")
     args = ap.parse_args()
+    if args.micro:
+        return run_micro(args.micro)
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
