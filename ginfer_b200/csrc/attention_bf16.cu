@@ -237,6 +237,19 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[HD 
   }
 }
 
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_dsmem(const float* local, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)),
+               "r"(rank));
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
 // ================================================================================== decode
 // grid (splits, nkv * head_chunks, B); 4 warps, warp w owns keys [16w, 16w + 16) of every tile.
 // Partials: po [B, nh, splits, HD] fp32 unnormalised, pml [B, nh, splits, 2] = (max in log2 units,
@@ -267,7 +280,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   pdl_trigger();
   pdl_wait();
-  const int row = cu_seqlens_q[b];
+  const int row = cu_seqlens_q ? cu_seqlens_q[b] : b;         // null: request b is row b
   const int p = positions[row];
   const int lo = window > 0 ? max(0, p - window + 1) : 0;
   const int nkeys = p - lo + 1;
@@ -353,6 +366,9 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
   float* so = reinterpret_cast<float*>(smem_raw);               // [4][16][HD]
   float* sm = so + 4 * 16 * HD;                                 // [4][16]
   float* sl = sm + 4 * 16;                                      // [4][16]
+  float* cpart = sl + 4 * 16;                                   // [16][HD]: the CTA's partial
+  float* cpart_m = cpart + 16 * HD;                             // [16]
+  float* cpart_l = cpart_m + 16;                                // [16]
 #pragma unroll
   for (int n = 0; n < HD / 8; ++n) {
     float* base = so + (warp * 16) * HD + n * 8 + 2 * t;
@@ -383,6 +399,12 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
     const int head = h0 + r;
     if (splits == 1) {
       out[((size_t)row * nh + head) * HD + d] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+    } else if (fused_merge == 2) {
+      cpart[i] = acc;                                   // this CTA's partial stays in shared memory
+      if (d == 0) {
+        cpart_m[r] = mm;
+        cpart_l[r] = lsum;
+      }
     } else {
       const size_t pi = ((size_t)b * nh + head) * splits + split;
       po[pi * HD + d] = acc;
@@ -391,6 +413,38 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
         pml[pi * 2 + 1] = lsum;
       }
     }
+  }
+  if (fused_merge == 2 && splits > 1) {
+    // The splits of a (request, kv head) form a thread-block cluster: after a cluster barrier every
+    // CTA combines a share of the output channels over all peers' partials, read through
+    // distributed shared memory in split order.  No scratch in global memory, no atomics.
+    cluster_sync_all();
+    float* cw = cpart_l + 16;                           // [16 rows][16 splits] weights
+    float* cinv = cw + 256;                             // [16]
+    if (threadIdx.x < nrows) {
+      const int r = threadIdx.x;
+      float mm = -INFINITY;
+      for (int p = 0; p < splits; ++p) mm = fmaxf(mm, ld_dsmem(cpart_m + r, p));
+      float lsum = 0.f;
+      for (int p = 0; p < splits; ++p) {
+        const float mp = ld_dsmem(cpart_m + r, p);
+        const float wgt = mp == -INFINITY ? 0.f : exp2f(mp - mm);
+        cw[r * 16 + p] = wgt;
+        lsum += wgt * ld_dsmem(cpart_l + r, p);
+      }
+      cinv[r] = lsum > 0.f ? 1.f / lsum : 0.f;
+    }
+    __syncthreads();
+    const int total = nrows * HD, share = (total + splits - 1) / splits;
+    const int i0 = split * share, i1 = min(total, i0 + share);
+    for (int i = i0 + threadIdx.x; i < i1; i += NTHREADS) {
+      const int r = i / HD, d = i - r * HD;
+      float acc = 0.f;
+      for (int p = 0; p < splits; ++p) acc += cw[r * 16 + p] * ld_dsmem(cpart + i, p);
+      out[((size_t)row * nh + h0 + r) * HD + d] = __float2bfloat16_rn(acc * cinv[r]);
+    }
+    cluster_sync_all();                                 // nobody leaves while a peer reads it
+    return;
   }
   if (splits == 1 || !fused_merge) return;
   // the CTA that finishes this (request, kv head, chunk) last merges the splits' partial results
@@ -663,8 +717,10 @@ GF_EXPORT long long gf_attn_decode_scratch_bytes(int B, int nh, int splits) {
   return splits <= 1 ? 0 : (long long)B * nh * splits * (HD + 2) * (long long)sizeof(float);
 }
 
-// One query token per request (row cu_seqlens_q[b] of q / out).  scratch: fp32, at least
-// gf_attn_decode_scratch_bytes; may be null when splits == 1.
+// One query token per request (row cu_seqlens_q[b] of q / out; row b if cu_seqlens_q is null).
+// splits > 1 with scratch (fp32, at least gf_attn_decode_scratch_bytes): partial results go through
+// it; without scratch the splits (2, 4, 8 or 16) form a thread-block cluster and merge through
+// distributed shared memory.
 GF_EXPORT int gf_attn_decode(const void* q, int q_row_stride, const void* kpages,
                              const void* vpages, const int* block_table, int table_stride,
                              const int* cu_seqlens_q, const int* positions, void* out,
@@ -672,11 +728,10 @@ GF_EXPORT int gf_attn_decode(const void* q, int q_row_stride, const void* kpages
                              float scale, int splits, void* stream) {
   if (B <= 0) return 0;
   if (nh % nkv || splits < 1) return -3;
-  if (splits > 1 && !scratch) return -4;
   auto st = (cudaStream_t)stream;
   const int G = nh / nkv, chunks = (G + 15) / 16;
   const size_t tiles = (size_t)2 * DEC_STAGES * KT * ROW * sizeof(bf16);
-  const size_t merge = (size_t)(4 * 16 * HD + 2 * 4 * 16) * sizeof(float);
+  const size_t merge = (size_t)(5 * 16 * HD + 2 * 4 * 16 + 32 + 256 + 16) * sizeof(float);
   const size_t work = ((tiles > merge ? tiles : merge) + 15) / 16 * 16;
   const int tbl_cap = table_stride < kMaxTableCopy ? table_stride : kMaxTableCopy;
   const size_t smem = work + (size_t)tbl_cap * sizeof(int);
@@ -691,6 +746,23 @@ GF_EXPORT int gf_attn_decode(const void* q, int q_row_stride, const void* kpages
   float* po = (float*)scratch;
   float* pml = po ? po + (size_t)B * nh * splits * HD : nullptr;
   dim3 grid(splits, nkv * chunks, B);
+  if (splits > 1 && !scratch) {
+    // cluster mode: the splits of a group merge through distributed shared memory
+    if (splits != 2 && splits != 4 && splits != 8 && splits != 16) return -4;
+    static bool np_done = false;
+    if (!np_done) {
+      cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel,
+                                           cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+      if (e != cudaSuccess) return (int)e;
+      np_done = true;
+    }
+    return launch_kernel_cluster_dims(attn_decode_kernel, grid, dim3(NTHREADS), smem, st, splits,
+                                      true, (const bf16*)q, q_row_stride, (const bf16*)kpages,
+                                      (const bf16*)vpages, block_table, table_stride,
+                                      cu_seqlens_q, positions, (bf16*)out, (float*)nullptr,
+                                      (float*)nullptr, nh, nkv, page_size, window, scale * LOG2E,
+                                      splits, 2, (int)work, tbl_cap);
+  }
   const int fused = (size_t)B * nkv * chunks <= (size_t)kMaxDecodeGroups ? 1 : 0;
   int rc = launch_kernel(attn_decode_kernel, grid, dim3(NTHREADS), smem, st, (const bf16*)q,
                          q_row_stride, (const bf16*)kpages, (const bf16*)vpages, block_table,

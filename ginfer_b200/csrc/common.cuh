@@ -67,10 +67,11 @@ inline int& pdl_flag() {
   return enabled;
 }
 
-// cluster_z > 1 launches thread-block clusters of (1, 1, cluster_z).
+// cluster > 1 launches thread-block clusters of (1, 1, cluster), or (cluster, 1, 1) with along_x.
 template <typename... KArgs, typename... Args>
-inline int launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                                 cudaStream_t stream, int cluster_z, Args... args) {
+inline int launch_kernel_cluster_dims(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                      cudaStream_t stream, int cluster_z, bool along_x,
+                                      Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -85,9 +86,9 @@ inline int launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block
   }
   if (cluster_z > 1) {
     attr[n].id = cudaLaunchAttributeClusterDimension;
-    attr[n].val.clusterDim.x = 1;
+    attr[n].val.clusterDim.x = along_x ? (unsigned)cluster_z : 1;
     attr[n].val.clusterDim.y = 1;
-    attr[n].val.clusterDim.z = (unsigned)cluster_z;
+    attr[n].val.clusterDim.z = along_x ? 1 : (unsigned)cluster_z;
     ++n;
   }
   cfg.attrs = attr;
@@ -96,9 +97,15 @@ inline int launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block
 }
 
 template <typename... KArgs, typename... Args>
+inline int launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, int cluster_z, Args... args) {
+  return launch_kernel_cluster_dims(kernel, grid, block, smem, stream, cluster_z, false, args...);
+}
+
+template <typename... KArgs, typename... Args>
 inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                          cudaStream_t stream, Args... args) {
-  return launch_kernel_cluster(kernel, grid, block, smem, stream, 1, args...);
+  return launch_kernel_cluster_dims(kernel, grid, block, smem, stream, 1, false, args...);
 }
 
 }  // namespace gf

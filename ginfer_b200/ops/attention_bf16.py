@@ -18,12 +18,17 @@ def supports(hd: int, nh: int, nkv: int) -> bool:
 
 
 def decode_splits(batch: int, nh: int, nkv: int, max_keys: int) -> int:
-    """How many ways to split each request's keys so that the grid fills the GPU."""
+    """How many ways to split each request's keys so that the grid fills the GPU: a power of two
+    up to 8, so that the splits of a request can form a thread-block cluster."""
     chunks = (nh // nkv + 15) // 16
     base = max(1, batch * nkv * chunks)
-    by_gpu = max(1, TARGET_CTAS // base)
-    by_len = max(1, -(-max_keys // KEY_TILE))
-    return int(min(by_gpu, by_len, MAX_SPLITS))
+    want = min(max(1, TARGET_CTAS // base), max(1, -(-max_keys // KEY_TILE)))
+    splits = 1
+    while splits * 2 <= min(want, 8):                 # clusters of 16 schedule badly: 8 at most
+        splits *= 2
+    if splits < 8 and splits < want and splits * 2 - want <= want - splits:
+        splits *= 2                                   # round to the nearer power of two
+    return splits
 
 
 def _scratch_for(nbytes: int, device) -> torch.Tensor:
@@ -36,12 +41,14 @@ def _scratch_for(nbytes: int, device) -> torch.Tensor:
 
 
 def decode(qkv, pages, block_table, cu_seqlens_q, positions, B, nh, nkv, hd, scale, window,
-           page_size, splits, out=None, scratch=None):
+           page_size, splits, out=None, scratch=None, through_scratch=False):
+    """Split-KV decode attention.  ``splits`` of 2, 4, 8 or 16 merge inside a thread-block cluster
+    (no scratch memory) unless ``through_scratch``; any other number goes through scratch."""
     from . import _fn, _ok, _p, _stream
     defines = (f"GF_HEAD_DIM={hd}",)
     if out is None:
         out = torch.empty((qkv.shape[0], nh * hd), dtype=torch.bfloat16, device=qkv.device)
-    if splits > 1 and scratch is None:
+    if splits > 1 and scratch is None and (through_scratch or splits not in (2, 4, 8, 16)):
         nbytes = B * nh * splits * (hd + 2) * 4
         if torch.cuda.is_current_stream_capturing():
             # a graph keeps its own scratch (from the graph's memory pool): the shared buffer

@@ -280,15 +280,16 @@ DEC_CASES = [
 
 
 @pytest.mark.parametrize("case", DEC_CASES)
-@pytest.mark.parametrize("splits", [1, 2, 5, 16])
+@pytest.mark.parametrize("splits", [1, 2, 5, 8, 16, -4])
 def test_attention_bf16_decode(case, splits):
     from ginfer_b200.ops import attention_bf16
     lens, nh, nkv, hd, P, window = case
     qls = [1] * len(lens)
     dev, want, scale = _paged_case(lens, qls, nh, nkv, hd, P, window, torch.bfloat16)
+    # 2, 4, 8, 16 merge inside a cluster; other counts (and negative ones here) through scratch
     out = attention_bf16.decode(_qkv(dev, nh, nkv, hd), dev["pages"], dev["table"], dev["cu"],
                                 dev["positions"], len(lens), nh, nkv, hd, scale, window, P,
-                                splits)
+                                abs(splits), through_scratch=splits < 0)
     torch.testing.assert_close(out.double().cpu(), want, atol=1e-2, rtol=2e-2)
 
 
