@@ -103,3 +103,81 @@ def try_linear(x, weight, bias_f32, out_dtype):
     if x.shape[0] > MAX_TOKENS:
         return None
     return gemm(x, weight, bias_f32, out_dtype, epi=0)
+
+
+# ----------------------------------------------------------------------------- fused with the norm
+FUSED_MAX_TOKENS = 32          # the fused kernels take token tiles of 16 and 32
+SS_LD = 32                     # tokens per row of the partial sums of squares
+
+
+def _cluster_split(N: int, K: int, k_share_max: int | None = None) -> int:
+    """2, 4 or 8 K-splits (a thread-block cluster) for products whose row tiles alone would leave
+    most SMs idle; ``k_share_max`` bounds the K range of one split (elements)."""
+    tiles = -(-N // 128)
+    nkb = -(-K // 64)
+    split = 1
+    while split < 8 and tiles * split * 2 <= NUM_SMS + NUM_SMS // 4 and nkb // (split * 2) >= 2:
+        split *= 2
+    while k_share_max is not None and split < 8 and -(-nkb // split) * 64 > k_share_max:
+        split *= 2
+    return split
+
+
+def gemm_resid(x, weight, bias_f32, resid):
+    """``s = resid + x @ weight^T (+ bias)`` in fp32 with, per token, the partial sums of
+    ``s^2`` (``csrc/gemm_fused_norm.cu``).  Returns ``(s [M, N] fp32, sumsq [parts, 32] fp32)``
+    or ``None`` if the kernel cannot serve the shapes."""
+    from . import _fn, _ok, _p, _stream
+    M, K = x.shape
+    N = weight.shape[0]
+    if M > FUSED_MAX_TOKENS or not supports(x, weight) or resid.dtype != torch.float32:
+        return None
+    if resid.shape != (M, N) or not resid.is_contiguous():
+        return None
+    split = _cluster_split(N, K)
+    parts = -(-N // 128) * split
+    out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    sumsq = torch.empty((parts, SS_LD), dtype=torch.float32, device=x.device)
+    f = _fn("gemm_fused_norm", "gf_gemm_resid",
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+             c_int, c_int, c_int, c_void_p, c_void_p])
+    rc = f(_p(x), x.stride(0), _p(weight), _p(bias_f32), _p(resid), _p(out), _p(sumsq), SS_LD, M,
+           N, K, split, _p(_dev_state(x.device)["err"]), _stream())
+    if rc == -6:
+        return None
+    _ok(rc, "gemm_resid")
+    return out, sumsq
+
+
+def gemm_normed(resid, sumsq, gamma, eps, weight, bias_f32=None, out_dtype=torch.bfloat16,
+                gated: bool = False):
+    """``norm(resid) @ weight^T (+ bias)`` (or ``silu(gate) * up`` over row-interleaved weights)
+    where ``norm`` is the RMS normalisation with ``gamma`` and the statistics a
+    :func:`gemm_resid` left in ``sumsq``.  ``None`` if the kernel cannot serve the shapes."""
+    from ctypes import c_float
+
+    from . import _fn, _ok, _p, _stream
+    M, K = resid.shape
+    N = weight.shape[0]
+    if M > FUSED_MAX_TOKENS or K % 8 or resid.dtype != torch.float32 or not resid.is_contiguous():
+        return None
+    if weight.data_ptr() % 16 or gamma.data_ptr() % 16 or gamma.numel() != K:
+        return None
+    bn = 16 if M <= 16 else 32
+    # the CTA's share of the normalised operand stays in shared memory: at most 64 KB of it
+    split = _cluster_split(N, K, k_share_max=(64 << 10) // (bn * 2))
+    if -(-(-(-K // 64)) // split) * 64 * bn * 2 > (64 << 10):
+        return None
+    cols = N // 2 if gated else N
+    out = torch.empty((M, cols), dtype=out_dtype, device=resid.device)
+    f = _fn("gemm_fused_norm", "gf_gemm_normed",
+            [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_float, c_void_p, c_void_p,
+             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    rc = f(_p(resid), _p(sumsq), sumsq.shape[0], sumsq.stride(0), _p(gamma),
+           1 if gamma.dtype == torch.float32 else 0, float(eps), _p(weight), _p(bias_f32), _p(out),
+           cols, M, N, K, 1 if gated else 0, 1 if out_dtype == torch.float32 else 0, split,
+           _p(_dev_state(resid.device)["err"]), _stream())
+    if rc == -6:
+        return None
+    _ok(rc, "gemm_normed")
+    return out
