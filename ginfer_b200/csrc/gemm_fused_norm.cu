@@ -24,7 +24,7 @@
 namespace gf {
 
 constexpr int NTHREADS = 192;
-constexpr int STAGES = 5;
+constexpr int MAX_STAGES = 10;      // the launcher takes as many as fit beside the operand tiles
 constexpr int EPI_STORE = 0, EPI_SILU = 2, EPI_RESID = 3;
 constexpr int kMaxParts = 1024;
 
@@ -57,15 +57,15 @@ __global__ void __launch_bounds__(NTHREADS)
 gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_w,
                   const __grid_constant__ CUtensorMap tmap_x, const float* __restrict__ bias,
                   OUT* __restrict__ out, int ldo, int M, int N, int K, int split_k,
-                  const FuseArgs fa, int* __restrict__ err) {
+                  const int STAGES, const FuseArgs fa, int* __restrict__ err) {
   static_assert(BN == 16 || BN == 32, "token tiles of 16 or 32");
   constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
   constexpr uint32_t STAGE_BYTES = A_BYTES + (NORMB ? 0 : B_BYTES);
   constexpr uint32_t TMEM_COLS = 32;
   constexpr uint32_t RED_BYTES = BM * (BN + 4) * 4;          // parked partial tile
   constexpr uint32_t SQ_BYTES = BM * BN * 4;                  // squares for the row sums
-  constexpr uint32_t REGION0 = STAGES * STAGE_BYTES > RED_BYTES + SQ_BYTES
-                                   ? STAGES * STAGE_BYTES : RED_BYTES + SQ_BYTES;
+  const uint32_t REGION0 = STAGES * STAGE_BYTES > RED_BYTES + SQ_BYTES
+                               ? STAGES * STAGE_BYTES : RED_BYTES + SQ_BYTES;
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* tiles = (unsigned char*)(((uintptr_t)smem + 1023) & ~(uintptr_t)1023);
 
@@ -155,48 +155,81 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_w,
     const int e = threadIdx.x - 64;                           // 0 .. 127
     pdl_wait();
     if (NORMB) {
-      // 1. rms of every token from the producer's partial sums (added in part order)
-      for (int m = e; m < BN; m += 128) {
+      // 1. rms of every token from the producer's partial sums: 128 / BN threads a token, each
+      //    over every (128 / BN)-th part, then a fixed shuffle tree (the order of the additions
+      //    depends on nothing but the number of parts)
+      {
+        constexpr int TPT = 128 / BN;                          // threads per token: 8 or 4
+        const int m = e / TPT, sub = e % TPT;
         float ss = 0.f;
         if (m < M)
-          for (int p = 0; p < fa.b_parts; ++p) ss += __ldg(fa.b_sumsq + (size_t)p * fa.ss_ld + m);
-        rms_s[m] = sqrtf(ss / (float)K + fa.eps);
+          for (int p = sub; p < fa.b_parts; p += TPT)
+            ss += __ldg(fa.b_sumsq + (size_t)p * fa.ss_ld + m);
+#pragma unroll
+        for (int o = TPT / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (sub == 0) rms_s[m] = sqrtf(ss / (float)K + fa.eps);
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");          // the four epilogue warps only
-      // 2. this CTA's K range of the operand: bf16(s * gamma / rms), 8 channels (16 bytes) a time
-      const int chunks = nkb * BN * 8;
-      for (int idx = e; idx < chunks; idx += 128) {
-        const int ch = idx & 7, m = (idx >> 3) % BN, kbl = idx / (8 * BN);
-        const int k = (kb0 + kbl) * BK + ch * 8;
-        uint4 w = make_uint4(0u, 0u, 0u, 0u);
-        if (m < M && k < K) {                                  // K is a multiple of 8
-          const float4 s0 = *reinterpret_cast<const float4*>(fa.b_resid + (size_t)m * K + k);
-          const float4 s1 = *reinterpret_cast<const float4*>(fa.b_resid + (size_t)m * K + k + 4);
-          float g[8];
+      // 2. this CTA's K range of the operand: bf16(s * gamma / rms), 8 channels (16 bytes) a time.
+      //    The loads of four chunks are issued together and without branches (addresses are
+      //    clamped, results of clamped loads dropped); rows past the last token are zero.
+      //    Thread e owns channel group e & 7 of the rows e >> 3, + 16, + 32, ... of the list of
+      //    (k block, token) pairs; the pair is advanced without divisions.
+      const int ch = e & 7;
+      const int pairs = nkb * M;
+      const int step_k = 16 / M, step_m = 16 % M;
+      int j = e >> 3, kbl = j / M, m = j % M;
+      const int k_last = K - 8;                                 // K is a multiple of 8
+      while (j < pairs) {
+        float4 s0[4], s1[4], g0[4], g1[4];
+        int kbl_u[4], m_u[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          kbl_u[u] = kbl, m_u[u] = m;
+          const int kc = min(kbl, nkb - 1);
+          const int k = min((kb0 + kc) * BK + ch * 8, k_last);
+          const float4* sp = reinterpret_cast<const float4*>(fa.b_resid + (size_t)m * K + k);
+          s0[u] = __ldg(sp);
+          s1[u] = __ldg(sp + 1);
           if (fa.gamma_f32) {
-            const float4 g0 = __ldg(reinterpret_cast<const float4*>((const float*)fa.gamma + k));
-            const float4 g1 = __ldg(reinterpret_cast<const float4*>((const float*)fa.gamma + k + 4));
-            g[0] = g0.x, g[1] = g0.y, g[2] = g0.z, g[3] = g0.w;
-            g[4] = g1.x, g[5] = g1.y, g[6] = g1.z, g[7] = g1.w;
+            g0[u] = __ldg(reinterpret_cast<const float4*>((const float*)fa.gamma + k));
+            g1[u] = __ldg(reinterpret_cast<const float4*>((const float*)fa.gamma + k + 4));
           } else {
             const uint4 gr = __ldg(reinterpret_cast<const uint4*>((const bf16*)fa.gamma + k));
-            const bf16* gp = reinterpret_cast<const bf16*>(&gr);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) g[j] = __bfloat162float(gp[j]);
+            const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gr);
+            const float2 a0 = __bfloat1622float2(gp[0]), a1 = __bfloat1622float2(gp[1]);
+            const float2 a2 = __bfloat1622float2(gp[2]), a3 = __bfloat1622float2(gp[3]);
+            g0[u] = make_float4(a0.x, a0.y, a1.x, a1.y);
+            g1[u] = make_float4(a2.x, a2.y, a3.x, a3.y);
           }
-          const float r = rms_s[m];
-          const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-          uint32_t pk[4];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            __nv_bfloat162 t = __floats2bfloat162_rn(sv[2 * j] * g[2 * j] / r,
-                                                     sv[2 * j + 1] * g[2 * j + 1] / r);
-            pk[j] = *reinterpret_cast<uint32_t*>(&t);
-          }
-          w = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          kbl += step_k, m += step_m;
+          if (m >= M) m -= M, ++kbl;
         }
-        *reinterpret_cast<uint4*>(bres + (size_t)kbl * B_BYTES + m * 128 + ((ch ^ (m & 7)) << 4)) = w;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (j + 16 * u < pairs) {
+            const int mm = m_u[u];
+            const int k = (kb0 + kbl_u[u]) * BK + ch * 8;
+            uint4 w = make_uint4(0u, 0u, 0u, 0u);
+            if (k < K) {
+              const float r = rms_s[mm];
+              __nv_bfloat162 t0 = __floats2bfloat162_rn(s0[u].x * g0[u].x / r, s0[u].y * g0[u].y / r);
+              __nv_bfloat162 t1 = __floats2bfloat162_rn(s0[u].z * g0[u].z / r, s0[u].w * g0[u].w / r);
+              __nv_bfloat162 t2 = __floats2bfloat162_rn(s1[u].x * g1[u].x / r, s1[u].y * g1[u].y / r);
+              __nv_bfloat162 t3 = __floats2bfloat162_rn(s1[u].z * g1[u].z / r, s1[u].w * g1[u].w / r);
+              w = make_uint4(*reinterpret_cast<uint32_t*>(&t0), *reinterpret_cast<uint32_t*>(&t1),
+                             *reinterpret_cast<uint32_t*>(&t2), *reinterpret_cast<uint32_t*>(&t3));
+            }
+            *reinterpret_cast<uint4*>(bres + (size_t)kbl_u[u] * B_BYTES + mm * 128 +
+                                      ((ch ^ (mm & 7)) << 4)) = w;
+          }
+        }
+        j += 64;
       }
+      for (int kb = e >> 3; kb < nkb; kb += 16)
+        for (int mm = M; mm < BN; ++mm)
+          *reinterpret_cast<uint4*>(bres + (size_t)kb * B_BYTES + mm * 128 +
+                                    ((ch ^ (mm & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(b_ready);
     }
@@ -345,9 +378,17 @@ static int launch_fused(const CUtensorMap& mw, const CUtensorMap& mx, const floa
   constexpr size_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
   constexpr size_t STAGE = A_BYTES + (NORMB ? 0 : B_BYTES);
   constexpr size_t RED = BM * (BN + 4) * 4 + BM * BN * 4;
-  const size_t region0 = STAGES * STAGE > RED ? STAGES * STAGE : RED;
   const size_t bres = NORMB ? (size_t)per * B_BYTES : 0;
-  const size_t smem = 1024 + region0 + bres + (2 * STAGES + 2) * sizeof(uint64_t) + 8 + BN * 4 + 16;
+  const size_t fixed = 1024 + bres + (2 * MAX_STAGES + 2) * sizeof(uint64_t) + 8 + BN * 4 + 16;
+  int stages = per < MAX_STAGES ? per : MAX_STAGES;
+  if (stages < 2) stages = 2;
+  // one wave: the deepest ring that fits (weights stream in while the operand is normalised);
+  // several waves: two CTAs to an SM, so that one streams while the other starts up
+  const size_t ctas = (size_t)((N + BM - 1) / BM) * split_k;
+  const size_t room = ctas > 148 ? 112 * 1024 : 200 * 1024;
+  while (stages > 2 && fixed + stages * STAGE > room) --stages;
+  const size_t region0 = stages * STAGE > RED ? stages * STAGE : RED;
+  const size_t smem = fixed + region0;
   if (smem > 200 * 1024) return -6;
   auto k = gemm_fused_kernel<BN, EPI, OUT, NORMB>;
   static size_t attr = 0;
@@ -358,7 +399,7 @@ static int launch_fused(const CUtensorMap& mw, const CUtensorMap& mx, const floa
   }
   dim3 grid((N + BM - 1) / BM, 1, split_k);
   return launch_kernel_cluster(k, grid, dim3(NTHREADS), smem, st, split_k, mw, mx, bias, (OUT*)out,
-                               ldo, M, N, K, split_k, fa, err);
+                               ldo, M, N, K, split_k, stages, fa, err);
 }
 
 template <int BN>

@@ -179,7 +179,9 @@ class ModelRunner:
         for g in range(cache.num_groups):
             arrays[f"slot_mapping{g}"] = slot_maps[g]
             arrays[f"block_table{g}"] = tables[g]
+        all_rows = len(rows) == T and all(int(r) == i for i, r in enumerate(rows))
         facts = dict(T=T, B=B, q_lens=q_lens, q_starts=q_starts, slot_ids=slot_ids, width=width,
+                     all_rows=all_rows,
                      max_q_len=int(q_lens.max()), max_kv_len=int(kv_lens.max()))
         return arrays, facts
 
@@ -223,7 +225,7 @@ class ModelRunner:
             q_starts_host=[int(x) for x in facts["q_starts"]],
             slot_ids_host=[int(x) for x in facts["slot_ids"]],
             max_q_len=facts["max_q_len"], max_kv_len=facts["max_kv_len"],
-            decode_only=facts["max_q_len"] == 1)
+            decode_only=facts["max_q_len"] == 1, all_rows_wanted=facts["all_rows"])
 
     def binder(self, dev: dict[str, torch.Tensor]):
         def bind(entry):

@@ -89,15 +89,15 @@ def embedding(token_ids: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
 
 # ----------------------------------------------------------------------------- add + rmsnorm
 def add_rmsnorm(x: torch.Tensor, delta, gamma: torch.Tensor, eps: float, rows=None,
-                want_sum: bool = True):
+                want_sum: bool = True, out_dtype=None):
     """``s = x + delta`` in fp32; returns ``(s or None, s * gamma / rms(s))``.  ``x`` is the fp32
     residual stream or an activation; ``delta`` and the normed output have the activation dtype
-    (that of ``delta``, else of ``x``).  Without ``delta`` and ``rows`` the returned ``s`` is
-    ``x`` itself."""
+    (``out_dtype``, else that of ``delta``, else of ``x``).  Without ``delta`` and ``rows`` the
+    returned ``s`` is ``x`` itself."""
     _cuda(x, delta, gamma, rows)
     assert x.dim() == 2 and x.is_contiguous()
     H = x.shape[1]
-    act = x.dtype if delta is None else delta.dtype
+    act = out_dtype or (x.dtype if delta is None else delta.dtype)
     if delta is not None:
         assert delta.shape == x.shape and delta.is_contiguous()
     assert gamma.numel() == H and gamma.is_contiguous()
@@ -230,4 +230,4 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, u: torch.Tensor) -> 
     return out
 
 
-from .linear import GatedLinear, Linear  # noqa: E402,F401
+from .linear import GatedLinear, Linear, add_to  # noqa: E402,F401

@@ -53,7 +53,15 @@ class Linear:
         else:
             raise TypeError(f"Linear takes float32 or bfloat16 weights, not {self.dtype}")
 
-    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+    def __call__(self, x) -> torch.Tensor:
+        if hasattr(x, "materialize"):                 # a normalisation not computed yet
+            if self.dtype == torch.bfloat16:
+                from . import gemm_bf16
+                y = gemm_bf16.gemm_normed(x.summed.tensor, x.summed.sumsq, x.gamma, x.eps,
+                                          self.weight, self._bias_f32, self.out_dtype)
+                if y is not None:
+                    return y
+            x = x.materialize()
         if x.dtype != self.dtype:
             raise TypeError(f"Linear holds {self.dtype} weights but got {x.dtype} input")
         if self.dtype == torch.float32:
@@ -72,6 +80,15 @@ class Linear:
         return torch.mm(x, self.weight.t())
 
 
+def add_to(linear: "Linear", x: torch.Tensor, residual: torch.Tensor):
+    """``(residual + linear(x), partial sums of its squares)`` from one kernel, or ``None`` if the
+    fused kernel does not serve this case (then the caller adds in the next norm)."""
+    if linear.dtype != torch.bfloat16 or residual.dtype != torch.float32:
+        return None
+    from . import gemm_bf16
+    return gemm_bf16.gemm_resid(x, linear.weight, linear._bias_f32, residual)
+
+
 class GatedLinear:
     """``silu(x W_g^T) * (x W_u^T)``.  The two matrices are joined row by row (gate_0, up_0,
     gate_1, up_1, ...) so that ``x`` is read once and a gate meets its up value in neighbouring
@@ -84,7 +101,15 @@ class GatedLinear:
         self.intermediate, k = gate.shape
         self.proj = Linear(torch.stack([gate, up], dim=1).reshape(2 * self.intermediate, k))
 
-    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+    def __call__(self, x) -> torch.Tensor:
+        if hasattr(x, "materialize"):                 # a normalisation not computed yet
+            if self.proj.dtype == torch.bfloat16:
+                from . import gemm_bf16
+                z = gemm_bf16.gemm_normed(x.summed.tensor, x.summed.sumsq, x.gamma, x.eps,
+                                          self.proj.weight, None, torch.bfloat16, gated=True)
+                if z is not None:
+                    return z
+            x = x.materialize()
         if x.dtype == torch.bfloat16:
             from . import gemm_bf16
             if x.shape[0] <= gemm_bf16.MAX_TOKENS:

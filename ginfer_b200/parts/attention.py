@@ -19,11 +19,14 @@ import math
 import torch
 
 from .. import ops
-from .base import Mixer, PagedKVSpec, TensorSpec, make_part, register_mixer
+from .base import Mixer, PagedKVSpec, Summed, TensorSpec, make_part, register_mixer
 from .plan import PartSpec
 
 
 class Attention(Mixer):
+    takes_lazy_norm = True        # the joined q/k/v product normalises its own operand
+    adds_residual = True          # the output product adds the residual and leaves statistics
+
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: PartSpec, window: int = 0, qkv_bias: bool = True,
                  out_bias: bool = False, prefix: str = "self_attn", scale: float | None = None):
@@ -77,7 +80,7 @@ class Attention(Mixer):
     def cache_spec(self):
         return PagedKVSpec(self.num_kv_heads, self.head_dim, self.window)
 
-    def forward(self, x, ctx, cache):
+    def forward(self, x, ctx, cache, residual=None):
         nh, nkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
         qkv = self.qkv(x)                                         # [T, (nh + 2 nkv) hd]
         fused = self.position.rotary_table()
@@ -93,6 +96,10 @@ class Attention(Mixer):
                           cache.pages, nh, nkv, hd)
         o = ops.paged_attention(qkv, cache.pages, cache.block_table, ctx, nh, nkv, hd,
                                 self.scale, cache.window, cache.page_size)
+        if residual is not None:
+            s = ops.add_to(self.out, o, residual)
+            if s is not None:
+                return Summed(*s)
         return self.out(o)
 
 

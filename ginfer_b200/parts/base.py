@@ -90,8 +90,34 @@ class StepContext:
     max_q_len: int = 0
     max_kv_len: int = 0
     decode_only: bool = False
+    all_rows_wanted: bool = False  # logit_rows is every row of the step, in order
     capturing: bool = False       # inside CUDA-graph capture: no host syncs, no allocation tricks
     extras: dict[str, Any] = field(default_factory=dict)
+
+
+# ----------------------------------------------------------------------------- folded norms
+@dataclass
+class Summed:
+    """A hidden state whose last residual addition is done: ``tensor [T, H]`` in fp32, with the
+    partial sums of squares of its rows that the product which formed it left behind
+    (``sumsq [parts, tokens]``), so that a following RMS normalisation needs no pass of its own."""
+    tensor: torch.Tensor
+    sumsq: torch.Tensor
+
+
+@dataclass
+class LazyNorm:
+    """The RMS normalisation of a :class:`Summed` state, not computed yet.  A product that can
+    normalise its own operand takes it as it is; anything else calls :meth:`materialize`."""
+    summed: Summed
+    gamma: torch.Tensor
+    eps: float
+    dtype: torch.dtype
+
+    def materialize(self) -> torch.Tensor:
+        from .. import ops
+        return ops.add_rmsnorm(self.summed.tensor, None, self.gamma, self.eps, want_sum=False,
+                               out_dtype=self.dtype)[1]
 
 
 # ----------------------------------------------------------------------------- part interfaces
@@ -108,12 +134,18 @@ class Part:
 
 class Norm(Part):
     def forward(self, x: torch.Tensor, delta: torch.Tensor | None = None,
-                rows: torch.Tensor | None = None, want_sum: bool = True
+                rows: torch.Tensor | None = None, want_sum: bool = True, out_dtype=None
                 ) -> tuple[torch.Tensor | None, torch.Tensor]:
         """Return ``(s, norm(s))`` with ``s = x + delta`` (``s = x`` if ``delta`` is None), the
         sum formed in 32-bit.  ``rows`` (int32) selects rows of ``x``/``delta`` first.  ``s`` is
-        None when ``want_sum`` is false."""
+        None when ``want_sum`` is false.  ``out_dtype``: the activation dtype of ``norm(s)`` when
+        it cannot be read off ``delta`` or ``x``."""
         raise NotImplementedError
+
+    def lazy(self, summed: Summed, dtype: torch.dtype) -> LazyNorm | None:
+        """The normalisation of ``summed`` as a :class:`LazyNorm`, if this norm can be folded
+        into the product that consumes it; ``None`` otherwise."""
+        return None
 
 
 class PositionEncoding(Part):
@@ -132,6 +164,11 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # A mixer (or feed-forward) that sets these takes a LazyNorm as input, and a ``residual``
+    # keyword: given one it may return ``Summed(residual + output)`` instead of its output.
+    takes_lazy_norm = False
+    adds_residual = False
+
     def cache_spec(self) -> PagedKVSpec | StateSpec | None:
         return None
 
@@ -140,6 +177,9 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    takes_lazy_norm = False
+    adds_residual = False
+
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
 

@@ -7,7 +7,15 @@ block's first norm or the final norm), which fuses it with its normalisation.
 """
 from __future__ import annotations
 
-from .base import Block, make_part, register_block
+import torch
+
+from .base import Block, Summed, make_part, register_block
+
+# Steps of at most this many tokens fold the additions and normalisations into the neighbouring
+# products (the kernels take up to 32).  Measured on a B200 at the 1.5B shape the folded layer is
+# slower than the separate norm kernels (each of the 140 gate/up CTAs normalises the whole operand
+# for itself before its first product), so it is off unless a caller raises it.
+FOLD_MAX_TOKENS = 0
 
 
 class PreNormBlock(Block):
@@ -32,11 +40,44 @@ class PreNormBlock(Block):
             p.load(tensors, dtype, device)
 
     def forward(self, x, delta, ctx, cache):
-        h, n = self.mixer_norm.forward(x, delta)            # h = x + delta
-        a = self.mixer.forward(n, ctx, cache)
-        r, n2 = self.feed_forward_norm.forward(h, a)        # r = h + a
-        m = self.feed_forward.forward(n2, ctx)
-        return r, m                                         # meaning r + m
+        """``x`` is a tensor (with ``delta`` still to be added) or a :class:`Summed` state.  For
+        short bf16 steps the additions and normalisations are folded into the neighbouring
+        products where the parts can do that: the mixer's and the feed-forward's last product
+        add the residual and leave the statistics of the sum (``Summed``), and their first
+        product normalises its own operand (``LazyNorm``)."""
+        fold = ctx.dtype == torch.bfloat16 and ctx.num_tokens <= FOLD_MAX_TOKENS
+        # the state before the mixer, and its normalisation
+        n = None
+        if isinstance(x, Summed):
+            h = x.tensor
+            if fold and self.mixer.takes_lazy_norm:
+                n = self.mixer_norm.lazy(x, ctx.dtype)
+            if n is None:
+                _, n = self.mixer_norm.forward(h, None, out_dtype=ctx.dtype)
+        else:
+            h, n = self.mixer_norm.forward(x, delta)            # h = x + delta
+        if fold and self.mixer.adds_residual:
+            a = self.mixer.forward(n, ctx, cache, residual=h if h.dtype == torch.float32
+                                   else h.float())
+        else:
+            a = self.mixer.forward(n, ctx, cache)
+        # the state before the feed-forward, and its normalisation
+        n2 = None
+        if isinstance(a, Summed):
+            r = a.tensor
+            if fold and self.feed_forward.takes_lazy_norm:
+                n2 = self.feed_forward_norm.lazy(a, ctx.dtype)
+            if n2 is None:
+                _, n2 = self.feed_forward_norm.forward(r, None, out_dtype=ctx.dtype)
+        else:
+            r, n2 = self.feed_forward_norm.forward(h, a)        # r = h + a
+        if fold and self.feed_forward.adds_residual and r.dtype == torch.float32:
+            m = self.feed_forward.forward(n2, ctx, residual=r)
+        else:
+            m = self.feed_forward.forward(n2, ctx)
+        if isinstance(m, Summed):
+            return m, None
+        return r, m                                             # meaning r + m
 
 
 register_block("prenorm", PreNormBlock)

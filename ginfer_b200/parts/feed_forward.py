@@ -10,10 +10,13 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from .base import FeedForward, TensorSpec, register_feed_forward
+from .base import FeedForward, Summed, TensorSpec, register_feed_forward
 
 
 class SwiGLU(FeedForward):
+    takes_lazy_norm = True
+    adds_residual = True
+
     def __init__(self, hidden_size: int, intermediate_size: int, prefix: str = "mlp",
                  gate_name: str = "gate_proj", up_name: str = "up_proj",
                  down_name: str = "down_proj"):
@@ -35,8 +38,12 @@ class SwiGLU(FeedForward):
         self.gate_up = ops.GatedLinear(tensors[self.gate_key], tensors[self.up_key])
         self.down = ops.Linear(tensors[self.down_key])
 
-    def forward(self, x, ctx):
+    def forward(self, x, ctx, residual=None):
         z = self.gate_up(x)            # silu(gate) * up, [T, intermediate]
+        if residual is not None:
+            s = ops.add_to(self.down, z, residual)
+            if s is not None:
+                return Summed(*s)
         return self.down(z)
 
 

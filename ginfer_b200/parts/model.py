@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import StepContext, TensorSpec, make_part
+from .base import StepContext, Summed, TensorSpec, make_part
 from .plan import ModelPlan
 
 
@@ -76,5 +76,13 @@ class DecoderModel:
             x, delta = self.blocks[e.layer].forward(x, delta, ctx, bind_cache(e))
         if ctx.logit_rows.numel() == 0:
             return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=ctx.device)
-        _, n = self.final_norm.forward(x, delta, rows=ctx.logit_rows, want_sum=False)
+        n = None
+        if isinstance(x, Summed):
+            if ctx.all_rows_wanted:
+                n = self.final_norm.lazy(x, ctx.dtype)          # folded into the head's product
+            if n is None:
+                _, n = self.final_norm.forward(x.tensor, None, rows=ctx.logit_rows,
+                                               want_sum=False, out_dtype=ctx.dtype)
+        else:
+            _, n = self.final_norm.forward(x, delta, rows=ctx.logit_rows, want_sum=False)
         return self.head.forward(n, ctx)

@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from .base import Norm, TensorSpec, register_norm
+from .base import LazyNorm, Norm, TensorSpec, register_norm
 
 
 class RMSNorm(Norm):
@@ -27,8 +27,12 @@ class RMSNorm(Norm):
     def load(self, tensors, dtype, device):
         self.weight = tensors[self.weight_name]
 
-    def forward(self, x, delta=None, rows=None, want_sum=True):
-        return ops.add_rmsnorm(x, delta, self.weight, self.eps, rows=rows, want_sum=want_sum)
+    def forward(self, x, delta=None, rows=None, want_sum=True, out_dtype=None):
+        return ops.add_rmsnorm(x, delta, self.weight, self.eps, rows=rows, want_sum=want_sum,
+                               out_dtype=out_dtype)
+
+    def lazy(self, summed, dtype):
+        return LazyNorm(summed, self.weight, self.eps, dtype)
 
 
 register_norm("rmsnorm", RMSNorm)

@@ -120,3 +120,18 @@ def test_trace_program_mixed(folders, tmp_path, dtype):
     steps, peak = replay.cut_mixed(reqs, seed=3)
     rows = replay.run_trace_program(model_dir, dtype, steps, peak, str(tmp_path / "out"))
     replay.compare(rows, replay.plain_logits(model_dir, reqs, dtype), dtype, reqs)
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("cut", ["tail", "mixed"])
+def test_cuts_agree_with_plain_when_norms_are_folded_into_products(folders, name, cut, monkeypatch):
+    """Short bfloat16 steps with the residual additions and the normalisations folded into the
+    neighbouring products (off by default) give the logits of the plain implementation too."""
+    from ginfer_b200.parts import block
+    monkeypatch.setattr(block, "FOLD_MAX_TOKENS", 32)
+    model_dir = folders[(name, "bfloat16")]
+    reqs = _requests(name)
+    steps = replay.cut_tail_decode(reqs) if cut == "tail" else replay.cut_mixed(reqs, seed=7)[0]
+    runner = _runner(model_dir, "bfloat16", PAGE[name], replay.peak_tokens(steps))
+    rows = replay.run_in_process(runner, steps)
+    replay.compare(rows, replay.plain_logits(model_dir, reqs, "bfloat16"), "bfloat16", reqs)
