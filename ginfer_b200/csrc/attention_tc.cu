@@ -33,7 +33,6 @@
 
 namespace gf {
 
-using bf16 = __nv_bfloat16;
 constexpr int HD = GF_HEAD_DIM;
 static_assert(HD == 64 || HD == 128, "the tcgen05 attention kernel takes head sizes 64 and 128");
 constexpr int QT = 128;                    // query rows per CTA = TMEM lanes
@@ -52,9 +51,6 @@ constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float kRescaleStep = 8.f;        // log2 units a maximum may grow before O is rescaled
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }

@@ -7,16 +7,11 @@
 
 namespace gf {
 
-using bf16 = __nv_bfloat16;
-
 constexpr int BM = 128;            // W rows per CTA = TMEM lanes
 constexpr int BK = 64;             // K elements per stage: one 128-byte swizzle row of bf16
 constexpr int UMMA_K = 16;
 constexpr uint32_t kSpinLimit = 1u << 22;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
