@@ -54,6 +54,89 @@ __global__ void add_rmsnorm_kernel(const XT* __restrict__ x, const T* __restrict
     normed[dst + j] = from_f32<T>(row[j] * gam[j] / rms);
 }
 
+
+// The same with 8 channels (an octet) per access and the row kept in registers: OPT octets a
+// thread, one block per row.  Needs H to be a multiple of 8 and 16-byte aligned rows; the launcher
+// checks.  Per row this moves what the definition needs and nothing else: x (and delta) in, the
+// sum and the normalised row out.
+template <typename T> struct Oct;                       // 8 values of T <-> 8 floats
+template <> struct Oct<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+};
+template <> struct Oct<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h[i]);
+      v[2 * i] = f.x, v[2 * i + 1] = f.y;
+    }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = raw;
+  }
+};
+
+template <typename XT, typename T, typename G, int OPT>
+__global__ void add_rmsnorm_vec_kernel(const XT* __restrict__ x, const T* __restrict__ delta,
+                                       const G* __restrict__ gamma, const int* __restrict__ rows,
+                                       float* __restrict__ sum_out, T* __restrict__ normed, int H,
+                                       float eps) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x, noct = H >> 3;
+  pdl_trigger();
+  float gam[OPT][8], s[OPT][8];
+#pragma unroll
+  for (int u = 0; u < OPT; ++u) {                       // weights: before the wait
+    const int o = threadIdx.x + u * blockDim.x;
+    if (o < noct) Oct<G>::load(gamma + o * 8, gam[u]);
+  }
+  pdl_wait();
+  const size_t src = (size_t)(rows ? rows[r] : r) * H;
+  const size_t dst = (size_t)r * H;
+  float ss = 0.f;
+#pragma unroll
+  for (int u = 0; u < OPT; ++u) {
+    const int o = threadIdx.x + u * blockDim.x;
+    if (o < noct) {
+      Oct<XT>::load(x + src + o * 8, s[u]);
+      if (delta) {
+        float d[8];
+        Oct<T>::load(delta + src + o * 8, d);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s[u][i] += d[i];
+      }
+      if (sum_out) Oct<float>::store(sum_out + dst + o * 8, s[u]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += s[u][i] * s[u][i];
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float rms = sqrtf(ss / (float)H + eps);
+#pragma unroll
+  for (int u = 0; u < OPT; ++u) {
+    const int o = threadIdx.x + u * blockDim.x;
+    if (o < noct) {
+      float v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = s[u][i] * gam[u][i] / rms;
+      Oct<T>::store(normed + dst + o * 8, v);
+    }
+  }
+}
+
 // ----------------------------------------------------------------------------- rope + KV write
 // qkv[t] = [q heads | k heads | v heads], each head hd wide.  The first `rot` channels of every q
 // and k head are rotated in pairs (j, j + rot/2) by the angle of positions[t]; table row p holds
@@ -171,23 +254,24 @@ template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, size_t total) {
   pdl_trigger();
   pdl_wait();
-  // 16 bytes of (gate, up) pairs per load: 4 pairs of bf16, 2 pairs of fp32
-  constexpr int PAIRS = 16 / (2 * (int)sizeof(T));
+  // two 16-byte loads of (gate, up) pairs and one 16-byte store a thread and pass: 8 pairs of
+  // bf16, 4 pairs of fp32
+  constexpr int PAIRS = 32 / (2 * (int)sizeof(T));
   const size_t nvec = total / PAIRS;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
        i += (size_t)gridDim.x * blockDim.x) {
-    const uint4 raw = reinterpret_cast<const uint4*>(gu)[i];
-    const T* p = reinterpret_cast<const T*>(&raw);
+    const uint4 raw0 = reinterpret_cast<const uint4*>(gu)[2 * i];
+    const uint4 raw1 = reinterpret_cast<const uint4*>(gu)[2 * i + 1];
+    T in[2 * PAIRS];
+    *reinterpret_cast<uint4*>(in) = raw0;
+    *reinterpret_cast<uint4*>(in + PAIRS) = raw1;
     T res[PAIRS];
 #pragma unroll
     for (int k = 0; k < PAIRS; ++k) {
-      const float g = to_f32(p[2 * k]), u = to_f32(p[2 * k + 1]);
+      const float g = to_f32(in[2 * k]), u = to_f32(in[2 * k + 1]);
       res[k] = from_f32<T>(g * (1.0f / (1.0f + expf(-g))) * u);
     }
-    if (sizeof(T) == 2)
-      reinterpret_cast<uint2*>(out)[i] = *reinterpret_cast<const uint2*>(res);
-    else
-      reinterpret_cast<uint2*>(out)[i] = *reinterpret_cast<const uint2*>(res);
+    reinterpret_cast<uint4*>(out)[i] = *reinterpret_cast<const uint4*>(res);
   }
   for (size_t i = nvec * PAIRS + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (size_t)gridDim.x * blockDim.x) {
@@ -199,6 +283,23 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, s
 template <typename XT, typename T, typename G>
 int launch_add_rmsnorm(const void* x, const void* delta, const void* gamma, const int* rows,
                        void* sum_out, void* normed, int R, int H, float eps, cudaStream_t st) {
+  // rows of whole octets at 16-byte aligned addresses: the register-resident kernel
+  const bool aligned = H % 8 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)delta % 16 == 0) &&
+                       ((uintptr_t)gamma % 16 == 0) && ((uintptr_t)sum_out % 16 == 0) &&
+                       ((uintptr_t)normed % 16 == 0);
+  if (aligned && H <= 8 * 4 * 256) {
+    const int noct = H / 8;
+    const int opt = noct <= 256 ? 1 : noct <= 512 ? 2 : 4;
+    const int threads = ((noct + opt - 1) / opt + 31) / 32 * 32;
+#define GF_VEC(OPT)                                                                              \
+  return launch_kernel(add_rmsnorm_vec_kernel<XT, T, G, OPT>, dim3(R), dim3(threads), 0, st,      \
+                       (const XT*)x, (const T*)delta, (const G*)gamma, rows, (float*)sum_out,     \
+                       (T*)normed, H, eps)
+    if (opt == 1) GF_VEC(1);
+    if (opt == 2) GF_VEC(2);
+    GF_VEC(4);
+#undef GF_VEC
+  }
   const size_t smem = (size_t)2 * H * sizeof(float);
   auto k = add_rmsnorm_kernel<XT, T, G>;
   if (smem > 48 * 1024) {
@@ -296,7 +397,7 @@ GF_EXPORT int gf_silu_mul(const void* gu, void* out, int T, int I, int dtype, vo
   const size_t total = (size_t)T * I;
   if (total == 0) return 0;
   auto st = (cudaStream_t)stream;
-  const size_t want = (total / 2 + 255) / 256 + 1;
+  const size_t want = (total / 4 + 255) / 256 + 1;
   const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
   if (dtype == GF_F32)
     return launch_kernel(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, st, (const float*)gu,
