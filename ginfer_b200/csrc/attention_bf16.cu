@@ -34,6 +34,52 @@ __device__ __forceinline__ float ld_dsmem(const float* local, uint32_t rank) {
   return v;
 }
 
+// The cluster's CTAs combine their partial results: every CTA a share of the output channels,
+// over all peers' partials, read through distributed shared memory in split order.
+template <int MAXC>
+__device__ __forceinline__ void cluster_merge(float* cpart, float* cpart_m, float* cpart_l,
+                                              float* cw, float* cinv, bf16* __restrict__ out,
+                                              int nrows, int splits, int split, int row, int nh,
+                                              int h0) {
+  // Loads from the peers are issued eight at a time without branches (the peer index is
+  // clamped, a clamped load's weight is zero); the additions stay in split order.
+  if (threadIdx.x < nrows) {
+    const int r = threadIdx.x;
+    float mp[MAXC], lp[MAXC];
+#pragma unroll
+    for (int p = 0; p < MAXC; ++p) {
+      const uint32_t peer = (uint32_t)min(p, splits - 1);
+      mp[p] = ld_dsmem(cpart_m + r, peer);
+      lp[p] = ld_dsmem(cpart_l + r, peer);
+    }
+    float mm = -INFINITY;
+#pragma unroll
+    for (int p = 0; p < MAXC; ++p)
+      if (p < splits) mm = fmaxf(mm, mp[p]);
+    float lsum = 0.f;
+#pragma unroll
+    for (int p = 0; p < MAXC; ++p) {
+      const float wgt = (p < splits && mp[p] != -INFINITY) ? exp2f(mp[p] - mm) : 0.f;
+      cw[r * 16 + p] = wgt;
+      lsum += wgt * lp[p];
+    }
+    cinv[r] = lsum > 0.f ? 1.f / lsum : 0.f;
+  }
+  __syncthreads();
+  const int total = nrows * HD, share = (total + splits - 1) / splits;
+  const int i0 = split * share, i1 = min(total, i0 + share);
+  for (int i = i0 + threadIdx.x; i < i1; i += NTHREADS) {
+    const int r = i / HD, d = i - r * HD;
+    float v[MAXC];
+#pragma unroll
+    for (int p = 0; p < MAXC; ++p) v[p] = ld_dsmem(cpart + i, (uint32_t)min(p, splits - 1));
+    float acc = 0.f;
+#pragma unroll
+    for (int p = 0; p < MAXC; ++p) acc += p < splits ? cw[r * 16 + p] * v[p] : 0.f;
+    out[((size_t)row * nh + h0 + r) * HD + d] = __float2bfloat16_rn(acc * cinv[r]);
+  }
+}
+
 // ================================================================================== decode
 // grid (splits, nkv * head_chunks, B); 4 warps, warp w owns keys [16w, 16w + 16) of every tile.
 // Partials: po [B, nh, splits, HD] fp32 unnormalised, pml [B, nh, splits, 2] = (max in log2 units,
@@ -205,28 +251,10 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
     cluster_sync_all();
     float* cw = cpart_l + 16;                           // [16 rows][16 splits] weights
     float* cinv = cw + 256;                             // [16]
-    if (threadIdx.x < nrows) {
-      const int r = threadIdx.x;
-      float mm = -INFINITY;
-      for (int p = 0; p < splits; ++p) mm = fmaxf(mm, ld_dsmem(cpart_m + r, p));
-      float lsum = 0.f;
-      for (int p = 0; p < splits; ++p) {
-        const float mp = ld_dsmem(cpart_m + r, p);
-        const float wgt = mp == -INFINITY ? 0.f : exp2f(mp - mm);
-        cw[r * 16 + p] = wgt;
-        lsum += wgt * ld_dsmem(cpart_l + r, p);
-      }
-      cinv[r] = lsum > 0.f ? 1.f / lsum : 0.f;
-    }
-    __syncthreads();
-    const int total = nrows * HD, share = (total + splits - 1) / splits;
-    const int i0 = split * share, i1 = min(total, i0 + share);
-    for (int i = i0 + threadIdx.x; i < i1; i += NTHREADS) {
-      const int r = i / HD, d = i - r * HD;
-      float acc = 0.f;
-      for (int p = 0; p < splits; ++p) acc += cw[r * 16 + p] * ld_dsmem(cpart + i, p);
-      out[((size_t)row * nh + h0 + r) * HD + d] = __float2bfloat16_rn(acc * cinv[r]);
-    }
+    if (splits <= 8)
+      cluster_merge<8>(cpart, cpart_m, cpart_l, cw, cinv, out, nrows, splits, split, row, nh, h0);
+    else
+      cluster_merge<16>(cpart, cpart_m, cpart_l, cw, cinv, out, nrows, splits, split, row, nh, h0);
     cluster_sync_all();                                 // nobody leaves while a peer reads it
     return;
   }

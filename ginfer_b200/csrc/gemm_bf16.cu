@@ -249,11 +249,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         const int row = rank * band + u % band, c = (u / band) * 4;
         const int n = n0 + row;
         if (m0 + c >= M || n >= N) continue;
+        // the peers' loads are issued together, without branches (a clamped peer index; what a
+        // clamped load brings is not added); the additions stay in rank order
+        float4 t[8];
+#pragma unroll
+        for (int p = 0; p < 8; ++p)
+          t[p] = ld_dsmem_f4(red + (uint32_t)((row * (BN + 4) + c) * 4), min(p, split_k - 1));
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 8
-        for (int p = 0; p < split_k; ++p) {
-          const float4 t = ld_dsmem_f4(red + (uint32_t)((row * (BN + 4) + c) * 4), p);
-          v.x += t.x, v.y += t.y, v.z += t.z, v.w += t.w;
+#pragma unroll
+        for (int p = 0; p < 8; ++p) {
+          const bool on = p < split_k;
+          v.x += on ? t[p].x : 0.f, v.y += on ? t[p].y : 0.f;
+          v.z += on ? t[p].z : 0.f, v.w += on ? t[p].w : 0.f;
         }
         const float b = bias ? bias[n] : 0.f;
         const float vv[4] = {v.x + b, v.y + b, v.z + b, v.w + b};
@@ -267,13 +274,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         const int row = rank * band + 2 * (u % pairs), c = (u / pairs) * 4;
         const int pair = (n0 + row) >> 1;
         if (m0 + c >= M || n0 + row + 1 >= N) continue;
+        float4 ta[8], tb[8];
+#pragma unroll
+        for (int p = 0; p < 8; ++p) {
+          const int peer = min(p, split_k - 1);
+          ta[p] = ld_dsmem_f4(red + (uint32_t)((row * (BN + 4) + c) * 4), peer);
+          tb[p] = ld_dsmem_f4(red + (uint32_t)(((row + 1) * (BN + 4) + c) * 4), peer);
+        }
         float4 g = make_float4(0.f, 0.f, 0.f, 0.f), up = g;
-#pragma unroll 8
-        for (int p = 0; p < split_k; ++p) {
-          const float4 a = ld_dsmem_f4(red + (uint32_t)((row * (BN + 4) + c) * 4), p);
-          const float4 b = ld_dsmem_f4(red + (uint32_t)(((row + 1) * (BN + 4) + c) * 4), p);
-          g.x += a.x, g.y += a.y, g.z += a.z, g.w += a.w;
-          up.x += b.x, up.y += b.y, up.z += b.z, up.w += b.w;
+#pragma unroll
+        for (int p = 0; p < 8; ++p) {
+          const bool on = p < split_k;
+          g.x += on ? ta[p].x : 0.f, g.y += on ? ta[p].y : 0.f;
+          g.z += on ? ta[p].z : 0.f, g.w += on ? ta[p].w : 0.f;
+          up.x += on ? tb[p].x : 0.f, up.y += on ? tb[p].y : 0.f;
+          up.z += on ? tb[p].z : 0.f, up.w += on ? tb[p].w : 0.f;
         }
         const float gv[4] = {g.x, g.y, g.z, g.w}, uv[4] = {up.x, up.y, up.z, up.w};
 #pragma unroll
