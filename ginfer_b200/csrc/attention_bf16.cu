@@ -85,6 +85,16 @@ __device__ __forceinline__ void cluster_merge(float* cpart, float* cpart_m, floa
 // Partials: po [B, nh, splits, HD] fp32 unnormalised, pml [B, nh, splits, 2] = (max in log2 units,
 // sum).  With one split the normalised bf16 result goes straight to `out`.
 constexpr int DEC_STAGES = 3;
+// With `fused` set, q and the new token's k arrive unrotated in the q/k/v row: the kernel rotates
+// q by the angles of the token's position (table row: cos | sin, `rot` channels wide) and the
+// split that holds the token's position rotates k, and writes k and v to their cache slot, before
+// it reads that range of keys.  One launch less than rotating and writing in a kernel before.
+struct RopeArgs {
+  const float* table;          // [positions][rot] or null (nothing is rotated)
+  int rot;
+  int fused;                   // 0: q is rotated and the cache written already
+  int write_kv;                // 0: the cache is another layer's to write
+};
 constexpr int kMaxTableCopy = 4096;   // block-table entries a CTA copies to shared memory at most
 constexpr int kMaxDecodeGroups = 1 << 16;     // (request, kv head, head chunk) triples with a counter
 __device__ unsigned int g_decode_done[kMaxDecodeGroups];
@@ -96,7 +106,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
                    const int* __restrict__ positions, bf16* __restrict__ out,
                    float* __restrict__ po, float* __restrict__ pml, int nh, int nkv,
                    int page_size, int window, float scale_log2, int splits, int fused_merge,
-                   int tbl_off, int tbl_cap) {
+                   int tbl_off, int tbl_cap, const RopeArgs rope) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ bool last_split;
   bf16* ks = reinterpret_cast<bf16*>(smem_raw);                 // [STAGES][KT][ROW]
@@ -122,15 +132,70 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
   const size_t tok_stride = (size_t)nkv * HD;
   const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
 
-  // query fragments straight from global memory: rows are the heads h0 + g and h0 + g + 8
+  // query fragments: rows are the heads h0 + g and h0 + g + 8; straight from global memory, or
+  // (fused rotation) rotated into shared memory first
   uint32_t qf[KCH][4];
+  const bf16* qrow = q + (size_t)row * q_row_stride + (size_t)h0 * HD;
+  const int q_ld = HD;
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw + tbl_off + (size_t)tbl_cap * sizeof(int));
+  bf16* knew = qs + 16 * HD;   // [HD], then v [HD]
+  bf16* vnew = knew + HD;
+  bool patch = false;          // the last tile of this CTA gets the new token's k and v from here
+  if (rope.fused && begin < end) {
+    const bf16* base = q + (size_t)row * q_row_stride;
+    const int half = rope.rot >> 1, tail = HD - rope.rot;
+    const float* cs = rope.table ? rope.table + (size_t)p * rope.rot : nullptr;
+    for (int i = threadIdx.x; i < nrows * half; i += NTHREADS) {
+      const int r = i / half, j = i - r * half;
+      const float a = __bfloat162float(qrow[r * HD + j]);
+      const float bb = __bfloat162float(qrow[r * HD + j + half]);
+      const float c = cs[j], sn = cs[half + j];
+      qs[r * HD + j] = __float2bfloat16_rn(a * c - bb * sn);
+      qs[r * HD + j + half] = __float2bfloat16_rn(a * sn + bb * c);
+    }
+    for (int i = threadIdx.x; i < nrows * tail; i += NTHREADS) {
+      const int r = i / tail, j = rope.rot + (i - r * tail);
+      qs[r * HD + j] = qrow[r * HD + j];
+    }
+    if (rope.write_kv && p >= begin && p < end) {
+      // This split holds the new token.  Its k (rotated) and v are kept in shared memory and put
+      // into the tile of keys once that has landed, so that no CTA depends on when another one's
+      // write reaches memory; the CTA of the first head chunk also writes them to the cache slot.
+      patch = true;
+      const int lp = p / page_size;
+      const size_t slot = (size_t)block_table[(size_t)b * table_stride + lp] * page_size +
+                          (size_t)(p - lp * page_size);
+      bf16* kd = const_cast<bf16*>(kpages) + slot * ((size_t)nkv * HD) + (size_t)kvh * HD;
+      bf16* vd = const_cast<bf16*>(vpages) + slot * ((size_t)nkv * HD) + (size_t)kvh * HD;
+      const bf16* kn = base + (size_t)(nh + kvh) * HD;
+      const bf16* vn = base + (size_t)(nh + nkv + kvh) * HD;
+      const bool store = chunk == 0;
+      for (int j = threadIdx.x; j < half; j += NTHREADS) {
+        const float a = __bfloat162float(kn[j]), bb = __bfloat162float(kn[j + half]);
+        const float c = cs[j], sn = cs[half + j];
+        const bf16 lo_v = __float2bfloat16_rn(a * c - bb * sn);
+        const bf16 hi_v = __float2bfloat16_rn(a * sn + bb * c);
+        knew[j] = lo_v, knew[j + half] = hi_v;
+        if (store) kd[j] = lo_v, kd[j + half] = hi_v;
+      }
+      for (int j = rope.rot + threadIdx.x; j < HD; j += NTHREADS) {
+        knew[j] = kn[j];
+        if (store) kd[j] = kn[j];
+      }
+      for (int j = threadIdx.x; j < HD; j += NTHREADS) {
+        vnew[j] = vn[j];
+        if (store) vd[j] = vn[j];
+      }
+    }
+    __syncthreads();             // q, and the new k and v, are in shared memory
+    qrow = qs;
+  }
   {
-    const bf16* qrow = q + (size_t)row * q_row_stride + (size_t)h0 * HD;
 #pragma unroll
     for (int kc = 0; kc < KCH; ++kc) {
       const int d = kc * 16 + 2 * t;
-      const uint32_t* r0 = reinterpret_cast<const uint32_t*>(qrow + (size_t)g * HD + d);
-      const uint32_t* r1 = reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * HD + d);
+      const uint32_t* r0 = reinterpret_cast<const uint32_t*>(qrow + (size_t)g * q_ld + d);
+      const uint32_t* r1 = reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * q_ld + d);
       qf[kc][0] = g < nrows ? r0[0] : 0u;
       qf[kc][1] = g + 8 < nrows ? r1[0] : 0u;
       qf[kc][2] = g < nrows ? r0[4] : 0u;
@@ -165,6 +230,14 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
   for (int it = 0; it < ntiles; ++it) {
     cp_async_wait<DEC_STAGES - 2>();
     __syncthreads();
+    if (patch && it == ntiles - 1) {
+      const int st = it % DEC_STAGES, rp = p - (begin + it * KT);
+      for (int j = threadIdx.x; j < HD; j += NTHREADS) {
+        ks[(st * KT + rp) * ROW + j] = knew[j];
+        vs[(st * KT + rp) * ROW + j] = vnew[j];
+      }
+      __syncthreads();
+    }
     const int nxt = it + DEC_STAGES - 1;
     if (nxt < ntiles) {
       const int st = nxt % DEC_STAGES;
@@ -533,11 +606,11 @@ GF_EXPORT long long gf_attn_decode_scratch_bytes(int B, int nh, int splits) {
 // splits > 1 with scratch (fp32, at least gf_attn_decode_scratch_bytes): partial results go through
 // it; without scratch the splits (2, 4, 8 or 16) form a thread-block cluster and merge through
 // distributed shared memory.
-GF_EXPORT int gf_attn_decode(const void* q, int q_row_stride, const void* kpages,
-                             const void* vpages, const int* block_table, int table_stride,
-                             const int* cu_seqlens_q, const int* positions, void* out,
-                             void* scratch, int B, int nh, int nkv, int page_size, int window,
-                             float scale, int splits, void* stream) {
+static int attn_decode_impl(const void* q, int q_row_stride, const void* kpages,
+                            const void* vpages, const int* block_table, int table_stride,
+                            const int* cu_seqlens_q, const int* positions, void* out,
+                            void* scratch, int B, int nh, int nkv, int page_size, int window,
+                            float scale, int splits, const RopeArgs& rope, void* stream) {
   if (B <= 0) return 0;
   if (nh % nkv || splits < 1) return -3;
   auto st = (cudaStream_t)stream;
@@ -546,12 +619,13 @@ GF_EXPORT int gf_attn_decode(const void* q, int q_row_stride, const void* kpages
   const size_t merge = (size_t)(5 * 16 * HD + 2 * 4 * 16 + 32 + 256 + 16) * sizeof(float);
   const size_t work = ((tiles > merge ? tiles : merge) + 15) / 16 * 16;
   const int tbl_cap = table_stride < kMaxTableCopy ? table_stride : kMaxTableCopy;
-  const size_t smem = work + (size_t)tbl_cap * sizeof(int);
+  const size_t q_tile = (size_t)18 * HD * sizeof(bf16);        // fused mode: rotated q, new k and v
+  const size_t smem = work + (size_t)tbl_cap * sizeof(int) + q_tile;
   static bool attr_done = false;
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)(work + kMaxTableCopy * sizeof(int)));
+                                         (int)(work + kMaxTableCopy * sizeof(int) + q_tile));
     if (e != cudaSuccess) return (int)e;
     attr_done = true;
   }
@@ -573,16 +647,41 @@ GF_EXPORT int gf_attn_decode(const void* q, int q_row_stride, const void* kpages
                                       (const bf16*)vpages, block_table, table_stride,
                                       cu_seqlens_q, positions, (bf16*)out, (float*)nullptr,
                                       (float*)nullptr, nh, nkv, page_size, window, scale * LOG2E,
-                                      splits, 2, (int)work, tbl_cap);
+                                      splits, 2, (int)work, tbl_cap, rope);
   }
   const int fused = (size_t)B * nkv * chunks <= (size_t)kMaxDecodeGroups ? 1 : 0;
   int rc = launch_kernel(attn_decode_kernel, grid, dim3(NTHREADS), smem, st, (const bf16*)q,
                          q_row_stride, (const bf16*)kpages, (const bf16*)vpages, block_table,
                          table_stride, cu_seqlens_q, positions, (bf16*)out, po, pml, nh, nkv,
-                         page_size, window, scale * LOG2E, splits, fused, (int)work, tbl_cap);
+                         page_size, window, scale * LOG2E, splits, fused, (int)work, tbl_cap, rope);
   if (rc || splits == 1 || fused) return rc;
   return launch_kernel(attn_decode_merge_kernel, dim3(nh, B), dim3(HD), 0, st, (const float*)po,
                        (const float*)pml, cu_seqlens_q, (bf16*)out, nh, splits);
+}
+
+GF_EXPORT int gf_attn_decode(const void* q, int q_row_stride, const void* kpages,
+                             const void* vpages, const int* block_table, int table_stride,
+                             const int* cu_seqlens_q, const int* positions, void* out,
+                             void* scratch, int B, int nh, int nkv, int page_size, int window,
+                             float scale, int splits, void* stream) {
+  return attn_decode_impl(q, q_row_stride, kpages, vpages, block_table, table_stride,
+                          cu_seqlens_q, positions, out, scratch, B, nh, nkv, page_size, window,
+                          scale, splits, RopeArgs{nullptr, 0, 0, 0}, stream);
+}
+
+// The same with the rotation of q and k and the write of the new k and v to the cache done by the
+// attention kernel itself: `q` points at rows [q | k | v] as the q/k/v product left them;
+// `rope_table` row p holds cos | sin of position p over `rot` channels (null: no rotation).
+GF_EXPORT int gf_attn_decode_rope(const void* q, int q_row_stride, void* kpages, void* vpages,
+                                  const int* block_table, int table_stride,
+                                  const int* cu_seqlens_q, const int* positions, void* out,
+                                  void* scratch, int B, int nh, int nkv, int page_size,
+                                  int window, float scale, int splits, const float* rope_table,
+                                  int rot, int write_kv, void* stream) {
+  if (rot < 0 || rot > HD || rot % 2 || (!rope_table && rot)) return -3;
+  return attn_decode_impl(q, q_row_stride, kpages, vpages, block_table, table_stride,
+                          cu_seqlens_q, positions, out, scratch, B, nh, nkv, page_size, window,
+                          scale, splits, RopeArgs{rope_table, rot, 1, write_kv ? 1 : 0}, stream);
 }
 
 GF_EXPORT int gf_attn_prefill(const void* q, int q_row_stride, const void* kpages,

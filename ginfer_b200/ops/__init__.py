@@ -175,17 +175,27 @@ def paged_attention_simt(qkv, pages, block_table, seq_of_token, positions, nh, n
     return out
 
 
+def attention_fuses_rope(qkv: torch.Tensor, ctx, nh: int, nkv: int, hd: int) -> bool:
+    """True if :func:`paged_attention` can rotate q and k and write the new k and v itself for
+    this step (pass ``rope=`` then, and skip :func:`rope_kv_write`)."""
+    from . import attention_bf16
+    return attention_bf16.fuses_rope(qkv, ctx, hd, nh, nkv)
+
+
 def paged_attention(qkv: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor, ctx,
-                    nh: int, nkv: int, hd: int, scale: float, window: int, page_size: int
-                    ) -> torch.Tensor:
+                    nh: int, nkv: int, hd: int, scale: float, window: int, page_size: int,
+                    rope=None) -> torch.Tensor:
     """Attention of the step's queries (first ``nh * hd`` columns of ``qkv``) over the paged
-    cache; returns ``[T, nh * hd]``.  Picks the kernel by dtype, head size and batch shape."""
+    cache; returns ``[T, nh * hd]``.  Picks the kernel by dtype, head size and batch shape.
+    ``rope = (table or None, rotary_dim, write)`` where :func:`attention_fuses_rope`: q and k are
+    still unrotated and the new k and v not yet in the cache."""
     from . import attention_bf16
     if qkv.dtype == torch.bfloat16:
         out = attention_bf16.try_run(qkv, pages, block_table, ctx, nh, nkv, hd, scale, window,
-                                     page_size)
+                                     page_size, rope=rope)
         if out is not None:
             return out
+    assert rope is None
     return paged_attention_simt(qkv, pages, block_table, ctx.seq_of_token, ctx.positions, nh, nkv,
                                 hd, scale, window, page_size)
 

@@ -41,9 +41,11 @@ def _scratch_for(nbytes: int, device) -> torch.Tensor:
 
 
 def decode(qkv, pages, block_table, cu_seqlens_q, positions, B, nh, nkv, hd, scale, window,
-           page_size, splits, out=None, scratch=None, through_scratch=False):
+           page_size, splits, out=None, scratch=None, through_scratch=False, rope=None):
     """Split-KV decode attention.  ``splits`` of 2, 4, 8 or 16 merge inside a thread-block cluster
-    (no scratch memory) unless ``through_scratch``; any other number goes through scratch."""
+    (no scratch memory) unless ``through_scratch``; any other number goes through scratch.
+    ``rope = (table or None, rotary_dim, write)``: q and k arrive unrotated and the kernel
+    rotates them itself and (``write``) puts the new k and v into their cache slot."""
     from . import _fn, _ok, _p, _stream
     defines = (f"GF_HEAD_DIM={hd}",)
     if out is None:
@@ -56,6 +58,18 @@ def decode(qkv, pages, block_table, cu_seqlens_q, positions, B, nh, nkv, hd, sca
             scratch = torch.empty(nbytes // 4, dtype=torch.float32, device=qkv.device)
         else:
             scratch = _scratch_for(nbytes, qkv.device)
+    if rope is not None:
+        table, rot, write = rope
+        f = _fn("attention_bf16", "gf_attn_decode_rope",
+                [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
+                 c_int, c_int, c_void_p], defines, kernels=1)
+        _ok(f(_p(qkv), qkv.stride(0), _p(pages[0]), _p(pages[1]), _p(block_table),
+              block_table.stride(0), _p(cu_seqlens_q), _p(positions), _p(out), _p(scratch), B, nh,
+              nkv, page_size, int(window), float(scale), int(splits), _p(table),
+              int(rot) if table is not None else 0, int(bool(write)), _stream()),
+            "attn_decode_rope")
+        return out
     f = _fn("attention_bf16", "gf_attn_decode",
             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
              c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p], defines,
@@ -114,16 +128,23 @@ def prefill_tc(qkv, pages, block_table, cu_seqlens_q, kv_lens, B, max_q_len, nh,
 TC_MIN_QUERY_ROWS = 64      # below this a portion is too short to fill 128-row tiles
 
 
-def try_run(qkv, pages, block_table, ctx, nh, nkv, hd, scale, window, page_size):
+def fuses_rope(qkv, ctx, hd: int, nh: int, nkv: int) -> bool:
+    """Whether attention over this step rotates q and k and writes the cache by itself (bf16
+    decode steps), so that the caller skips the kernel that would do it before."""
+    return qkv.dtype == torch.bfloat16 and ctx.decode_only and supports(hd, nh, nkv)
+
+
+def try_run(qkv, pages, block_table, ctx, nh, nkv, hd, scale, window, page_size, rope=None):
     """Run a bf16 kernel if one takes this head size; ``None`` hands the work to the plain
-    fp32-arithmetic kernel."""
+    fp32-arithmetic kernel.  ``rope``: see :func:`decode` (only where :func:`fuses_rope`)."""
     if not supports(hd, nh, nkv):
         return None
     if ctx.decode_only:
         keys = ctx.max_kv_len if window <= 0 else min(window, ctx.max_kv_len)
         splits = ctx.extras.get("decode_splits") or decode_splits(ctx.num_seqs, nh, nkv, keys)
         return decode(qkv, pages, block_table, ctx.cu_seqlens_q, ctx.positions, ctx.num_seqs, nh,
-                      nkv, hd, scale, window, page_size, splits)
+                      nkv, hd, scale, window, page_size, splits, rope=rope)
+    assert rope is None, "only decode steps rotate inside the attention kernel"
     if ctx.max_q_len >= TC_MIN_QUERY_ROWS:
         out = prefill_tc(qkv, pages, block_table, ctx.cu_seqlens_q, ctx.kv_lens, ctx.num_seqs,
                          ctx.max_q_len, nh, nkv, hd, scale, window, page_size)

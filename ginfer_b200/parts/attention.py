@@ -91,11 +91,17 @@ class Attention(Mixer):
             table, rot = None, 0
         else:
             table, rot = fused
-        ops.rope_kv_write(qkv, table, rot, ctx.positions,
-                          cache.slot_mapping if cache.write else None,
-                          cache.pages, nh, nkv, hd)
-        o = ops.paged_attention(qkv, cache.pages, cache.block_table, ctx, nh, nkv, hd,
-                                self.scale, cache.window, cache.page_size)
+        if fused is not None and ops.attention_fuses_rope(qkv, ctx, nh, nkv, hd):
+            # decode steps: the attention kernel rotates q and k and writes the cache itself
+            o = ops.paged_attention(qkv, cache.pages, cache.block_table, ctx, nh, nkv, hd,
+                                    self.scale, cache.window, cache.page_size,
+                                    rope=(table, rot, cache.write))
+        else:
+            ops.rope_kv_write(qkv, table, rot, ctx.positions,
+                              cache.slot_mapping if cache.write else None,
+                              cache.pages, nh, nkv, hd)
+            o = ops.paged_attention(qkv, cache.pages, cache.block_table, ctx, nh, nkv, hd,
+                                    self.scale, cache.window, cache.page_size)
         if residual is not None:
             s = ops.add_to(self.out, o, residual)
             if s is not None:

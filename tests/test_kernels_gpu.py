@@ -293,6 +293,47 @@ def test_attention_bf16_decode(case, splits):
     torch.testing.assert_close(out.double().cpu(), want, atol=1e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("case", DEC_CASES)
+@pytest.mark.parametrize("splits", [1, 4, 8, -3])
+@pytest.mark.parametrize("rot_frac", [1.0, 0.5])
+def test_attention_bf16_decode_rotates_and_writes_the_cache_itself(case, splits, rot_frac):
+    """The decode kernel given unrotated q and k equals the rotation-and-write kernel followed by
+    the decode kernel, bit for bit in the cache and in the output."""
+    from ginfer_b200 import ops
+    from ginfer_b200.ops import attention_bf16
+    lens, nh, nkv, hd, P, window = case
+    B = len(lens)
+    dev, _, scale = _paged_case(lens, [1] * B, nh, nkv, hd, P, window, torch.bfloat16, spike=False)
+    g = torch.Generator().manual_seed(5)
+    qkv = torch.randn(B, (nh + 2 * nkv) * hd, generator=g).to(torch.bfloat16).cuda()
+    rot = int(hd * rot_frac) // 2 * 2
+    ang = torch.rand(max(lens) + 1, rot // 2, generator=g) * 6.28
+    table = torch.cat([ang.cos(), ang.sin()], dim=1).float().cuda().contiguous()
+    slots = torch.tensor([int(dev["table"][b, (n - 1) // P]) * P + (n - 1) % P
+                          for b, n in enumerate(lens)], dtype=torch.int32).cuda()
+    # separately: rotate q in place, write k and v, then attend
+    qkv_a, pages_a = qkv.clone(), dev["pages"].clone()
+    ops.rope_kv_write(qkv_a, table, rot, dev["positions"], slots, pages_a, nh, nkv, hd)
+    want = attention_bf16.decode(qkv_a, pages_a, dev["table"], dev["cu"], dev["positions"], B, nh,
+                                 nkv, hd, scale, window, P, abs(splits),
+                                 through_scratch=splits < 0)
+    # in one kernel
+    pages_b = dev["pages"].clone()
+    got = attention_bf16.decode(qkv.clone(), pages_b, dev["table"], dev["cu"], dev["positions"],
+                                B, nh, nkv, hd, scale, window, P, abs(splits),
+                                through_scratch=splits < 0, rope=(table, rot, True))
+    torch.cuda.synchronize()
+    assert torch.equal(pages_b, pages_a), "the cache differs"
+    assert torch.equal(got, want)
+    # without the write, the cache stays as it was
+    pages_c = dev["pages"].clone()
+    attention_bf16.decode(qkv.clone(), pages_c, dev["table"], dev["cu"], dev["positions"], B, nh,
+                          nkv, hd, scale, window, P, abs(splits), through_scratch=splits < 0,
+                          rope=(table, rot, False))
+    torch.cuda.synchronize()
+    assert torch.equal(pages_c, dev["pages"])
+
+
 def test_attention_refuses_head_sizes_it_cannot_take():
     from ginfer_b200 import ops
     from ginfer_b200.ops import attention_bf16
