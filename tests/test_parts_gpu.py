@@ -278,6 +278,129 @@ def test_a_toy_mixer_with_state_of_its_own_registers_builds_and_steps(tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_register_and_step(tmp_path, dtype):
+    """Two more parts defined here, not in the framework.  A feed-forward with routing: a router
+    scores three small experts in 32-bit, each token goes through its best expert, scaled by the
+    router's softmax weight.  A position encoding with code of its own: q and k are scaled, channel
+    by channel, by a cosine of the position.  One layer uses both, the other the framework's own
+    parts; the layers of the model therefore differ in mixer options and in feed-forward.  Whole
+    prompts, portions and decoding one by one agree; moving a token changes later logits."""
+    from ginfer_b200 import ops
+    from ginfer_b200.config import register_architecture
+    from ginfer_b200.engine import ModelRunner, StepEntry
+    from ginfer_b200.engine.loading import load_model
+    from ginfer_b200.parts import (FeedForward, LayerSpec, ModelPlan, PartSpec, PositionEncoding,
+                                   TensorSpec, register_feed_forward, register_position,
+                                   sequential_run)
+    from ginfer_b200.weights import write_random_model
+
+    class RoutedFF(FeedForward):
+        def __init__(self, hidden_size, expert_size, num_experts, prefix="moe"):
+            self.h, self.e, self.n, self.prefix = hidden_size, expert_size, num_experts, prefix
+
+        def tensor_specs(self):
+            out = [TensorSpec(f"{self.prefix}.router.weight", (self.n, self.h))]
+            for i in range(self.n):
+                out += [TensorSpec(f"{self.prefix}.experts.{i}.up.weight", (self.e, self.h)),
+                        TensorSpec(f"{self.prefix}.experts.{i}.down.weight", (self.h, self.e))]
+            return out
+
+        def load(self, tensors, dtype, device):
+            self.router = tensors[f"{self.prefix}.router.weight"].float()
+            self.up = [ops.Linear(tensors[f"{self.prefix}.experts.{i}.up.weight"])
+                       for i in range(self.n)]
+            self.down = [ops.Linear(tensors[f"{self.prefix}.experts.{i}.down.weight"])
+                         for i in range(self.n)]
+
+        def forward(self, x, ctx):
+            scores = torch.softmax(x.float() @ self.router.t(), dim=-1)   # router in 32-bit
+            weight, choice = scores.max(dim=-1)
+            out = torch.zeros_like(x)
+            for i in range(self.n):                                       # plain torch: a toy
+                rows = torch.nonzero(choice == i).flatten()
+                if rows.numel():
+                    y = self.down[i](torch.relu(self.up[i](x[rows].contiguous())))
+                    out[rows] = (y.float() * weight[rows, None]).to(x.dtype)
+            return out
+
+    class CosineScale(PositionEncoding):
+        def __init__(self, head_dim, period):
+            self.freq = torch.arange(1, head_dim + 1, dtype=torch.float32) / (head_dim * period)
+
+        def load(self, tensors, dtype, device):
+            self.freq = self.freq.to(device)
+
+        def apply(self, q, k, ctx):                    # rotary_table() stays None: code of its own
+            f = torch.cos(ctx.positions.float()[:, None] * self.freq)[:, None, :]
+            q.copy_((q.float() * f).to(q.dtype))
+            k.copy_((k.float() * f).to(k.dtype))
+
+    register_feed_forward("toy_routed", RoutedFF)
+    register_position("toy_cosine_scale", CosineScale)
+
+    class ToyConfig:
+        torch_dtype = "float32"
+
+        def __init__(self, d):
+            self.d = dict(d)
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d)
+
+        def to_dict(self):
+            return dict(self.d)
+
+    def toy_plan(cfg):
+        H, V = cfg.d["hidden_size"], cfg.d["vocab_size"]
+        norm = lambda name: PartSpec("rmsnorm", dict(size=H, eps=2e-5, weight_name=name))
+        attn = lambda pos, heads, kv: PartSpec("attention", dict(
+            hidden_size=H, num_heads=heads, num_kv_heads=kv, head_dim=16, position=pos))
+        rotary = PartSpec("rotary", dict(head_dim=16, theta=1e4, max_positions=256))
+        layers = (
+            LayerSpec("l0", attn(PartSpec("toy_cosine_scale", dict(head_dim=16, period=7.0)), 4, 4),
+                      PartSpec("toy_routed", dict(hidden_size=H, expert_size=40, num_experts=3)),
+                      norm("n1"), norm("n2")),
+            LayerSpec("l1", attn(rotary, 6, 2),
+                      PartSpec("swiglu", dict(hidden_size=H, intermediate_size=104)),
+                      norm("n1"), norm("n2")),
+        )
+        return ModelPlan(hidden_size=H, vocab_size=V, max_positions=256,
+                         embedding=PartSpec("token", dict(vocab_size=V, hidden_size=H, name="emb")),
+                         layers=layers, run=sequential_run(2), final_norm=norm("final"),
+                         head=PartSpec("linear", dict(vocab_size=V, hidden_size=H, name="head")))
+
+    register_architecture("ToyRoutedLM", ToyConfig, toy_plan)
+    cfg = {"architectures": ["ToyRoutedLM"], "hidden_size": 48, "vocab_size": 90}
+    d = str(tmp_path / "toy_routed")
+    write_random_model(d, cfg, seed=4, storage_dtype=dtype)
+    model, _ = load_model(d, dtype)
+
+    def runner():
+        return ModelRunner(model, page_size=8, max_num_seqs=2, max_seq_len=128, num_pages=20)
+
+    toks = prompt(60, 90, 9)
+    r = runner()
+    whole = r.step([StepEntry("a", toks, list(range(60)))]).cpu()
+    r = runner()
+    parts, at = [], 0
+    for n in (17, 2, 30, 1, 1, 1, 8):                  # portions, then tokens one by one
+        parts.append(r.step([StepEntry("a", toks[at:at + n], list(range(n)))]).cpu())
+        at += n
+    got = torch.cat(parts)
+    if dtype == "float32":
+        torch.testing.assert_close(got, whole, atol=2e-5, rtol=1e-4)
+    else:
+        # bfloat16: a token near a tie between experts may flip; compare where routing is stable
+        close = (got - whole).abs().amax(dim=-1) <= 2.0 ** -6 * whole.abs().max()
+        assert close.float().mean() >= 0.9, f"only {int(close.sum())} of 60 positions agree"
+    other = list(toks)
+    other[3] = (other[3] + 1) % 90
+    changed = runner().step([StepEntry("a", other, [59])]).cpu()
+    assert not torch.allclose(changed[0], whole[59], atol=1e-4)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_run_list_names_a_layer_twice_and_shares_a_cache(tmp_path, dtype):
     """A Qwen2 folder run under another plan: layer 0 runs twice (second time with a cache of its
     own) and the last run of layer 1 reads the cache layer 1 wrote; compared with plain."""
