@@ -119,7 +119,11 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
   const int nrows = min(16, G - chunk * 16);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   pdl_trigger();
-  pdl_wait();
+  // When this kernel itself writes the new token's k and v, the keys it reads from the cache are
+  // all from earlier steps (the new token's come through shared memory): the first tiles are
+  // fetched before the wait for the kernel in front (the q/k/v product), whose tail they overlap.
+  const bool late_wait = rope.fused && rope.write_kv;
+  if (!late_wait) pdl_wait();
   const int row = cu_seqlens_q ? cu_seqlens_q[b] : b;         // null: request b is row b
   const int p = positions[row];
   const int lo = window > 0 ? max(0, p - window + 1) : 0;
@@ -132,6 +136,32 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
   const size_t tok_stride = (size_t)nkv * HD;
   const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
 
+  float o[HD / 8][4];
+#pragma unroll
+  for (int n = 0; n < HD / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  const int lo2[2] = {begin, begin}, hi2[2] = {end - 1, end - 1};
+
+  const int ntiles = begin < end ? (end - begin + KT - 1) / KT : 0;
+  // this split's block-table entries -> shared memory
+  int lp_base = 0;
+  if (ntiles > 0) {
+    const int lp0 = begin / page_size, nlp = (end - 1) / page_size - lp0 + 1;
+    if (nlp <= tbl_cap) {
+      int* stbl = reinterpret_cast<int*>(smem_raw + tbl_off);
+      for (int i = threadIdx.x; i < nlp; i += NTHREADS) stbl[i] = tbl[lp0 + i];
+      __syncthreads();
+      tbl = stbl;
+      lp_base = lp0;
+    }
+  }
+  for (int s = 0; s < DEC_STAGES - 1; ++s) {
+    if (s < ntiles)
+      load_kv_tiles(ks + s * KT * ROW, vs + s * KT * ROW, kpages, vpages, tbl, lp_base,
+                    begin + s * KT, begin, end, page_size, page_shift, tok_stride, kvh, threadIdx.x);
+    cp_async_commit();
+  }
+  if (late_wait) pdl_wait();     // everything above read only what earlier steps and the host wrote
   // query fragments: rows are the heads h0 + g and h0 + g + 8; straight from global memory, or
   // (fused rotation) rotated into shared memory first
   uint32_t qf[KCH][4];
@@ -201,31 +231,6 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
       qf[kc][2] = g < nrows ? r0[4] : 0u;
       qf[kc][3] = g + 8 < nrows ? r1[4] : 0u;
     }
-  }
-  float o[HD / 8][4];
-#pragma unroll
-  for (int n = 0; n < HD / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-  const int lo2[2] = {begin, begin}, hi2[2] = {end - 1, end - 1};
-
-  const int ntiles = begin < end ? (end - begin + KT - 1) / KT : 0;
-  // this split's block-table entries -> shared memory
-  int lp_base = 0;
-  if (ntiles > 0) {
-    const int lp0 = begin / page_size, nlp = (end - 1) / page_size - lp0 + 1;
-    if (nlp <= tbl_cap) {
-      int* stbl = reinterpret_cast<int*>(smem_raw + tbl_off);
-      for (int i = threadIdx.x; i < nlp; i += NTHREADS) stbl[i] = tbl[lp0 + i];
-      __syncthreads();
-      tbl = stbl;
-      lp_base = lp0;
-    }
-  }
-  for (int s = 0; s < DEC_STAGES - 1; ++s) {
-    if (s < ntiles)
-      load_kv_tiles(ks + s * KT * ROW, vs + s * KT * ROW, kpages, vpages, tbl, lp_base,
-                    begin + s * KT, begin, end, page_size, page_shift, tok_stride, kvh, threadIdx.x);
-    cp_async_commit();
   }
   for (int it = 0; it < ntiles; ++it) {
     cp_async_wait<DEC_STAGES - 2>();
