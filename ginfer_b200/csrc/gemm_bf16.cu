@@ -79,6 +79,65 @@ __device__ __forceinline__ void epilogue16(float (&v)[16], OUT* __restrict__ out
   }
 }
 
+// Cluster split-K: every CTA of the cluster sums a band of the tile's rows over all SPLIT peers'
+// parked partial tiles, read through distributed shared memory.  The peers' loads are issued
+// together and the additions stay in rank order.
+template <int BN, int EPI, typename OUT, int SPLIT>
+__device__ __forceinline__ void cluster_reduce(uint32_t red, const float* __restrict__ bias,
+                                               OUT* __restrict__ out, int ldo, int M, int N,
+                                               int n0, int m0) {
+  const int rank = (int)cluster_rank();
+  constexpr int band = BM / SPLIT;
+  constexpr int QUADS = BN / 4;                       // a unit of work: one row (pair), 4 tokens
+  if (EPI == EPI_STORE) {
+    for (int u = threadIdx.x; u < band * QUADS; u += NTHREADS) {
+      const int row = rank * band + u % band, c = (u / band) * 4;
+      const int n = n0 + row;
+      if (m0 + c >= M || n >= N) continue;
+      float4 t[SPLIT];
+#pragma unroll
+      for (int p = 0; p < SPLIT; ++p)
+        t[p] = ld_dsmem_f4(red + (uint32_t)((row * (BN + 4) + c) * 4), p);
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int p = 0; p < SPLIT; ++p) v.x += t[p].x, v.y += t[p].y, v.z += t[p].z, v.w += t[p].w;
+      const float b = bias ? bias[n] : 0.f;
+      const float vv[4] = {v.x + b, v.y + b, v.z + b, v.w + b};
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (m0 + c + j < M) store_out<OUT>(out + (size_t)(m0 + c + j) * ldo + n, vv[j]);
+    }
+  } else {
+    constexpr int pairs = band / 2;
+    for (int u = threadIdx.x; u < pairs * QUADS; u += NTHREADS) {
+      const int row = rank * band + 2 * (u % pairs), c = (u / pairs) * 4;
+      const int pair = (n0 + row) >> 1;
+      if (m0 + c >= M || n0 + row + 1 >= N) continue;
+      float4 ta[SPLIT], tb[SPLIT];
+#pragma unroll
+      for (int p = 0; p < SPLIT; ++p) {
+        ta[p] = ld_dsmem_f4(red + (uint32_t)((row * (BN + 4) + c) * 4), p);
+        tb[p] = ld_dsmem_f4(red + (uint32_t)(((row + 1) * (BN + 4) + c) * 4), p);
+      }
+      float4 g = make_float4(0.f, 0.f, 0.f, 0.f), up = g;
+#pragma unroll
+      for (int p = 0; p < SPLIT; ++p) {
+        g.x += ta[p].x, g.y += ta[p].y, g.z += ta[p].z, g.w += ta[p].w;
+        up.x += tb[p].x, up.y += tb[p].y, up.z += tb[p].z, up.w += tb[p].w;
+      }
+      const float gv[4] = {g.x, g.y, g.z, g.w}, uv[4] = {up.x, up.y, up.z, up.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float gg = __bfloat162float(__float2bfloat16_rn(gv[j]));
+        const float uu = __bfloat162float(__float2bfloat16_rn(uv[j]));
+        if (m0 + c + j < M)
+          store_out<OUT>(out + (size_t)(m0 + c + j) * ldo + pair,
+                         gg * (1.0f / (1.0f + expf(-gg))) * uu);
+      }
+    }
+  }
+}
+
 template <int BN, int EPI, typename OUT, bool CLUSTER>
 __global__ void __launch_bounds__(NTHREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
@@ -240,67 +299,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     // every CTA of the cluster sums a band of rows over all peers, in rank order
     pdl_wait();
     cluster_sync();
-    const int rank = (int)cluster_rank();
-    const int band = BM / split_k;                    // split_k is 2, 4 or 8
-    constexpr int QUADS = BN / 4;                     // a unit of work: one row (pair), 4 tokens
     const uint32_t red = smem_u32(tiles);
-    if (EPI == EPI_STORE) {
-      for (int u = threadIdx.x; u < band * QUADS; u += NTHREADS) {
-        const int row = rank * band + u % band, c = (u / band) * 4;
-        const int n = n0 + row;
-        if (m0 + c >= M || n >= N) continue;
-        // the peers' loads are issued together, without branches (a clamped peer index; what a
-        // clamped load brings is not added); the additions stay in rank order
-        float4 t[8];
-#pragma unroll
-        for (int p = 0; p < 8; ++p)
-          t[p] = ld_dsmem_f4(red + (uint32_t)((row * (BN + 4) + c) * 4), min(p, split_k - 1));
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int p = 0; p < 8; ++p) {
-          const bool on = p < split_k;
-          v.x += on ? t[p].x : 0.f, v.y += on ? t[p].y : 0.f;
-          v.z += on ? t[p].z : 0.f, v.w += on ? t[p].w : 0.f;
-        }
-        const float b = bias ? bias[n] : 0.f;
-        const float vv[4] = {v.x + b, v.y + b, v.z + b, v.w + b};
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (m0 + c + j < M) store_out<OUT>(out + (size_t)(m0 + c + j) * ldo + n, vv[j]);
-      }
-    } else {
-      const int pairs = band / 2;
-      for (int u = threadIdx.x; u < pairs * QUADS; u += NTHREADS) {
-        const int row = rank * band + 2 * (u % pairs), c = (u / pairs) * 4;
-        const int pair = (n0 + row) >> 1;
-        if (m0 + c >= M || n0 + row + 1 >= N) continue;
-        float4 ta[8], tb[8];
-#pragma unroll
-        for (int p = 0; p < 8; ++p) {
-          const int peer = min(p, split_k - 1);
-          ta[p] = ld_dsmem_f4(red + (uint32_t)((row * (BN + 4) + c) * 4), peer);
-          tb[p] = ld_dsmem_f4(red + (uint32_t)(((row + 1) * (BN + 4) + c) * 4), peer);
-        }
-        float4 g = make_float4(0.f, 0.f, 0.f, 0.f), up = g;
-#pragma unroll
-        for (int p = 0; p < 8; ++p) {
-          const bool on = p < split_k;
-          g.x += on ? ta[p].x : 0.f, g.y += on ? ta[p].y : 0.f;
-          g.z += on ? ta[p].z : 0.f, g.w += on ? ta[p].w : 0.f;
-          up.x += on ? tb[p].x : 0.f, up.y += on ? tb[p].y : 0.f;
-          up.z += on ? tb[p].z : 0.f, up.w += on ? tb[p].w : 0.f;
-        }
-        const float gv[4] = {g.x, g.y, g.z, g.w}, uv[4] = {up.x, up.y, up.z, up.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float gg = __bfloat162float(__float2bfloat16_rn(gv[j]));
-          const float uu = __bfloat162float(__float2bfloat16_rn(uv[j]));
-          if (m0 + c + j < M)
-            store_out<OUT>(out + (size_t)(m0 + c + j) * ldo + pair,
-                           gg * (1.0f / (1.0f + expf(-gg))) * uu);
-        }
-      }
-    }
+    if (split_k == 2)
+      cluster_reduce<BN, EPI, OUT, 2>(red, bias, out, ldo, M, N, n0, m0);
+    else if (split_k == 4)
+      cluster_reduce<BN, EPI, OUT, 4>(red, bias, out, ldo, M, N, n0, m0);
+    else
+      cluster_reduce<BN, EPI, OUT, 8>(red, bias, out, ldo, M, N, n0, m0);
     cluster_sync();                                   // nobody leaves while a peer still reads it
     return;
   }
