@@ -167,6 +167,23 @@ using namespace gf;
 GF_DEFINE_PDL_SWITCH
 
 // scratch: room for 2 * R * ceil(V / 4096) 32-bit words (parked pairs); may be null when V <= 4096.
+// dst[dst_idx[i]] = src[src_idx[i]]: tokens chosen in the step before are fed to the next step
+// on the device, before the host has seen them.
+__global__ void scatter_tokens_kernel(int* __restrict__ dst, const int* __restrict__ dst_idx,
+                                      const int* __restrict__ src, const int* __restrict__ src_idx,
+                                      int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[dst_idx[i]] = src[src_idx[i]];
+}
+
+GF_EXPORT int gf_scatter_tokens(int* dst, const int* dst_idx, const int* src, const int* src_idx,
+                                int n, void* stream) {
+  if (n <= 0) return 0;
+  scatter_tokens_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(dst, dst_idx, src,
+                                                                            src_idx, n);
+  return (int)cudaGetLastError();
+}
+
 GF_EXPORT int gf_argmax(const float* logits, int* out, int R, int V, void* scratch, void* stream) {
   if (R <= 0) return 0;
   if (R > kMaxRows) return -5;

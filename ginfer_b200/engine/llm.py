@@ -50,6 +50,8 @@ class _Flight:
     """A step that has been launched: its batch and the sampled tokens on their way."""
     batch: list
     pending: object
+    err_host: object = None        # pinned int: the kernels' error word, copied behind the tokens
+    err_event: object = None
 
 
 class Engine:
@@ -84,6 +86,8 @@ class Engine:
         self.seed = int(seed)
         self.pipeline = bool(pipeline)
         self._flight = None
+        self._err_host = [torch.zeros(1, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._err_turn = 0
         self.stats = EngineStats()
         self._next_id = 0
         self.requests: dict[int, Request] = {}
@@ -116,19 +120,39 @@ class Engine:
                                  [s.num_tokens - 1] if s.sample else []))
         return out
 
-    def _launch(self, batch, prepared, entries) -> "_Flight":
+    def _launch(self, batch, prepared, entries, before: "_Flight | None" = None) -> "_Flight":
         """Launch a prepared step with the requests' tokens as they are now, and the choice of
-        the next tokens behind it; nothing waits for the device."""
+        the next tokens behind it; nothing waits for the device.  A token that the step
+        ``before`` is still choosing is taken from that step's result on the device."""
         token_ids = np.fromiter((t for s in batch
                                  for t in s.request.tokens(s.start, s.start + s.num_tokens)),
                                 dtype=np.int64)
-        logits = self.runner.launch(prepared, entries, token_ids)
+        feedback = None
+        unknown = np.nonzero(token_ids == Scheduler.PENDING)[0]
+        if unknown.size:
+            if before is None or before.pending.device_tokens is None:
+                raise RuntimeError("a step has tokens that no earlier step is choosing")
+            pick_of = {s.request.request_id: i
+                       for i, s in enumerate(x for x in before.batch if x.sample)}
+            ends = np.cumsum([s.num_tokens for s in batch]) - 1
+            row_owner = {int(r): s.request.request_id for r, s in zip(ends, batch)}
+            feedback = (before.pending.device_tokens, [int(r) for r in unknown],
+                        [pick_of[row_owner[int(r)]] for r in unknown])
+            token_ids[unknown] = 0
+        logits = self.runner.launch(prepared, entries, token_ids, feedback)
         picks = [s for s in batch if s.sample]
         pending = self.sampler.sample_async(
             logits, [s.request.params.temperature for s in picks],
             [s.request.seed for s in picks],
             [s.start + s.num_tokens - len(s.request.prompt) for s in picks])
-        return _Flight(batch, pending)
+        # the kernels' error word travels behind the tokens, so that checking it waits for this
+        # step only and not for the one launched after it
+        self._err_turn ^= 1
+        err_host = self._err_host[self._err_turn]
+        err_host.copy_(gemm_bf16.error_word(self.cfg.device), non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        return _Flight(batch, pending, err_host, ev)
 
     def is_idle(self) -> bool:
         return self._flight is None and self.scheduler.is_finished()
@@ -158,11 +182,15 @@ class Engine:
             if batch:
                 entries = self._entries(batch)
                 nxt = (batch, self.runner.prepare(entries), entries)
+        # the following step goes to the device before this one's tokens are read: where it
+        # needs them it takes them from this step's result on the device
+        following = self._launch(*nxt, before=cur) if nxt else None
         tokens = cur.pending.result()                   # the device catches up here
-        gemm_bf16.check_errors(self.cfg.device)
+        cur.err_event.synchronize()
+        gemm_bf16.raise_for(int(cur.err_host[0]), self.cfg.device)
         in_next = {s.request.request_id for s in nxt[0]} if nxt else ()
         finished += self.scheduler.resolve(cur.batch, tokens, in_next)
-        self._flight = self._launch(*nxt) if nxt else None
+        self._flight = following
         dt = time.perf_counter() - t0
         if any(s.num_tokens > 1 for s in cur.batch):
             self.stats.prefill_tokens += sum(s.num_tokens for s in cur.batch)

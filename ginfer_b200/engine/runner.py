@@ -250,7 +250,7 @@ class ModelRunner:
 
     def _capture(self, key, arrays, facts) -> _DecodeGraph:
         from .. import ops
-        total = sum(_align4(a.size) for a in arrays.values())
+        total = sum(_align4(a.size) for a in arrays.values()) + 2 * _align4(facts["B"])
         ints = torch.empty(total, dtype=torch.int32, device=self.device)
         dev = self.upload(arrays, into=ints)
         ctx = self.make_context(dev, facts)
@@ -269,11 +269,20 @@ class ModelRunner:
         return _DecodeGraph(graph, ints, {}, logits, ops.launch_count() - before)
 
     @torch.no_grad()
-    def launch(self, prepared, entries: list[StepEntry], token_ids=None) -> torch.Tensor:
+    def launch(self, prepared, entries: list[StepEntry], token_ids=None, feedback=None
+               ) -> torch.Tensor:
         """Second half of a step: copy the integers and run.  ``token_ids`` (all tokens of the
         step, packed) replaces the values the entries held when the step was prepared, for a
-        caller that prepares a step before its last tokens are known."""
+        caller that prepares a step before its last tokens are known.  ``feedback = (src, rows,
+        picks)``: token ``rows[i]`` of this step is ``src[picks[i]]``, an int32 tensor on the
+        device (the tokens the step before chose), put in place by a kernel: the host need not
+        have seen those tokens."""
         arrays, facts = prepared
+        arrays = dict(arrays)
+        arrays.pop("fb_rows", None), arrays.pop("fb_picks", None)
+        if feedback is not None and len(feedback[1]):
+            arrays["fb_rows"] = np.asarray(feedback[1], dtype=np.int64)      # packed last
+            arrays["fb_picks"] = np.asarray(feedback[2], dtype=np.int64)
         if token_ids is not None:
             token_ids = np.asarray(token_ids, dtype=np.int64).reshape(-1)
             if token_ids.size != facts["T"]:
@@ -288,18 +297,26 @@ class ModelRunner:
                 g = self._graphs.get(key)
                 if g is None:
                     g = self._graphs[key] = self._capture(key, arrays, facts)
-                self.upload(arrays, into=g.ints)
+                dev = self.upload(arrays, into=g.ints)
+                self._feed_back(dev, feedback)
                 g.graph.replay()
                 self.graph_launches += g.launches
                 logits = g.logits
             else:
                 dev = self.upload(arrays)
+                self._feed_back(dev, feedback)
                 ctx = self.make_context(dev, facts)
                 logits = self.model.forward(ctx, self.binder(dev))
         for e, n in zip(entries, facts["q_lens"]):
             self.cache.commit(e.request_id, int(n))
         self.steps_run += 1
         return logits
+
+    @staticmethod
+    def _feed_back(dev, feedback) -> None:
+        if feedback is not None and "fb_rows" in dev:
+            from .. import ops
+            ops.scatter_tokens(dev["token_ids"], dev["fb_rows"], feedback[0], dev["fb_picks"])
 
     def step(self, entries: list[StepEntry]) -> torch.Tensor:
         """Run the entries' tokens as one batch; returns fp32 logits ``[wanted, vocab]`` on the

@@ -240,4 +240,16 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, u: torch.Tensor) -> 
     return out
 
 
+def scatter_tokens(dst: torch.Tensor, dst_idx: torch.Tensor, src: torch.Tensor,
+                   src_idx: torch.Tensor) -> None:
+    """``dst[dst_idx[i]] = src[src_idx[i]]`` (all int32, on the device)."""
+    _cuda(dst, dst_idx, src, src_idx)
+    assert all(t.dtype == torch.int32 for t in (dst, dst_idx, src, src_idx))
+    n = dst_idx.numel()
+    assert src_idx.numel() == n
+    f = _fn("sampling", "gf_scatter_tokens",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+    _ok(f(_p(dst), _p(dst_idx), _p(src), _p(src_idx), n, _stream()), "scatter_tokens")
+
+
 from .linear import GatedLinear, Linear, add_to  # noqa: E402,F401

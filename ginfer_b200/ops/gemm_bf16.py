@@ -31,6 +31,19 @@ def check_errors(device="cuda:0") -> None:
                            "1 = TMA producer, 2 = MMA issuer, 3 = epilogue)")
 
 
+def error_word(device="cuda:0") -> torch.Tensor:
+    """The device int that kernels set when a bounded wait runs out (for a caller that reads it
+    back together with other results instead of calling :func:`check_errors`)."""
+    return _dev_state(torch.device(device))["err"]
+
+
+def raise_for(code: int, device="cuda:0") -> None:
+    if code:
+        _dev_state(torch.device(device))["err"].zero_()
+        raise RuntimeError(f"gemm_bf16: a wait inside the tcgen05 kernel ran out (role {code}: "
+                           "1 = TMA producer, 2 = MMA issuer, 3 = epilogue)")
+
+
 def token_tile(M: int) -> int:
     return 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
 

@@ -31,8 +31,9 @@ def uniform(seed: int, index: int) -> float:
 class Pending:
     """Tokens on their way to the host; ``result()`` waits for them."""
 
-    def __init__(self, host: torch.Tensor, n: int, event):
+    def __init__(self, host: torch.Tensor, n: int, event, device_tokens=None):
         self._host, self._n, self._event = host, n, event
+        self.device_tokens = device_tokens      # int32 [n] on the device, for the step behind
 
     def result(self) -> list[int]:
         if self._event is not None:
@@ -76,7 +77,7 @@ class Sampler:
         out[:R].copy_(picks, non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
-        return Pending(out, R, ev)
+        return Pending(out, R, ev, picks)
 
     def sample(self, logits: torch.Tensor, temperatures: list[float], seeds: list[int],
                indices: list[int]) -> list[int]:
