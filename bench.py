@@ -198,7 +198,7 @@ def decode_end_to_end(eng, batch: int, steps: int, warmup: int, seed: int):
     while not eng.is_idle():
         eng.step()
     eng.requests.clear()
-    return 1e3 * dt / steps, int(h2d), 4 * batch
+    return 1e3 * dt / steps, int(h2d), 4 * batch + 4      # the tokens and the kernels' error word
 
 
 def prefill_timed(eng, tokens: int, reps: int, warmup: int, seed: int):
