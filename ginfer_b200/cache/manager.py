@@ -104,9 +104,9 @@ class CacheManager:
         """Pages per group that :meth:`reserve` would take for ``n_new`` more tokens."""
         rc = self.requests.get(request_id)
         if rc is None:
-            return [self._new_pages(0, 0, n_new) for _ in self.pools]
-        have = rc.num_tokens + rc.reserved
-        return [self._new_pages(rc.next_page[g], have, n_new) for g in range(self.num_groups)]
+            return [-(-n_new // self.page_size)] * len(self.pools)
+        end_page = -(-(rc.num_tokens + rc.reserved + n_new) // self.page_size)
+        return [end_page - p if end_page > p else 0 for p in rc.next_page]
 
     def free_pages(self) -> list[int]:
         return [p.num_free for p in self.pools]
@@ -114,6 +114,8 @@ class CacheManager:
     def can_reserve(self, request_id, n_new: int, already: list[int] | None = None) -> bool:
         """``already``: pages per group that the caller has promised to others in this step."""
         need = self.pages_needed(request_id, n_new)
+        if not any(need):
+            return True
         free = self.free_pages()
         if already is not None:
             free = [f - a for f, a in zip(free, already)]

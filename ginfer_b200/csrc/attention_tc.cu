@@ -206,7 +206,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.z, head = blockIdx.y;
+  const int b = blockIdx.z, head = blockIdx.x;
   // optional time stamps of the first CTA's phases (dbg: 16 slots per tile per role)
   const bool trace = dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
 #define GF_STAMP(role, i, slot) \
@@ -214,7 +214,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
   pdl_trigger();
   pdl_wait();
   const int q_begin = cu_seqlens_q[b], q_len = cu_seqlens_q[b + 1] - q_begin;
-  const int r0 = (int)(gridDim.x - 1 - blockIdx.x) * QT;       // heavy tiles first
+  // CTAs start in the order of their index with x running fastest: the heads are on x and the
+  // query tiles on y, last (heaviest: most keys under the causal mask) first, so that every
+  // head's heavy tiles are in the first wave and the light ones fill the SMs that finish early
+  const int r0 = (int)(gridDim.y - 1 - blockIdx.y) * QT;
   if (r0 >= q_len) return;
   if (smem_u32(smem_raw) & 1023u) {
     if (threadIdx.x == 0 && err) atomicExch(err, 12);
@@ -616,7 +619,7 @@ GF_EXPORT int gf_attn_prefill_tc(const void* q, int q_row_stride, const void* kp
     if (e != cudaSuccess) return (int)e;
     attr_done = true;
   }
-  dim3 grid((max_q_len + QT - 1) / QT, nh, B);
+  dim3 grid(nh, (max_q_len + QT - 1) / QT, B);
   return launch_kernel(attn_prefill_tc_kernel, grid, dim3(NTHREADS), smem, (cudaStream_t)stream,
                        mq, mk, mv, block_table, table_stride, cu_seqlens_q, kv_lens, (bf16*)out,
                        nh, nkv, page_size, window, scale * LOG2E, (int)slots, err,
