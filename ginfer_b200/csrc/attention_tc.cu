@@ -211,6 +211,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
   const bool trace = dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
 #define GF_STAMP(role, i, slot) \
   if (trace && (i) < 32) dbg[((role) * 32 + (i)) * 8 + (slot)] = clock64()  /* dbg: 3 * 32 * 8 */
+  // with dbg: every CTA also leaves (start ns, end ns, SM) behind the first CTA's stamps
+  const int cta_lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  if (dbg && threadIdx.x == 0) {
+    unsigned long long t;
+    unsigned int sm;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+    dbg[768 + cta_lin * 4] = (long long)t;
+    dbg[768 + cta_lin * 4 + 2] = sm;
+  }
   pdl_trigger();
   pdl_wait();
   const int q_begin = cu_seqlens_q[b], q_len = cu_seqlens_q[b + 1] - q_begin;
@@ -543,6 +553,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (dbg && threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t) : : "memory");   // stays behind the barrier
+    dbg[768 + cta_lin * 4 + 1] = (long long)t;
+  }
   if (warp == 4) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem),
                  "r"(TMEM_COLS)

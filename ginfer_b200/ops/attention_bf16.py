@@ -101,8 +101,8 @@ def tc_supports(hd: int, page_size: int) -> bool:
 def prefill_tc(qkv, pages, block_table, cu_seqlens_q, kv_lens, B, max_q_len, nh, nkv, hd, scale,
                window, page_size, trace=None):
     """Prefill attention on tcgen05 (``csrc/attention_tc.cu``); ``None`` if it cannot serve the
-    shapes.  ``trace``: an int64 tensor of 512 slots that receives clock stamps of the first
-    CTA's phases (for tuning)."""
+    shapes.  ``trace``: an int64 tensor of ``768 + 4 * CTAs`` slots that receives clock stamps of
+    the first CTA's phases and, behind them, every CTA's (start ns, end ns, SM) (for tuning)."""
     from ctypes import c_float, c_int, c_void_p
 
     from . import _fn, _ok, _p, _stream
