@@ -15,7 +15,7 @@ from dataclasses import dataclass, field
 import numpy as np
 import torch
 
-from ..cache import CacheManager, CacheStorage, OutOfPages, plan_groups
+from ..cache import CacheStorage, NativeCacheManager, OutOfPages, plan_groups
 from ..parts.base import PagedKVBinding, StateBinding, StepContext
 from ..parts.model import DecoderModel
 
@@ -64,8 +64,8 @@ class ModelRunner:
         if num_pages is None:
             num_pages = self._pages_from_memory(gpu_memory_utilization, itemsize)
         counts = [int(num_pages)] * len(self.groups)
-        self.cache = CacheManager([g.window for g in self.groups], counts, self.page_size,
-                                  self.max_num_seqs, self.max_seq_len)
+        self.cache = NativeCacheManager([g.window for g in self.groups], counts, self.page_size,
+                                        self.max_num_seqs, self.max_seq_len)
         self.storage = CacheStorage(specs, self.groups, counts, self.page_size,
                                     self.max_num_seqs, self.dtype, self.device)
         self.vocab_size = model.plan.vocab_size
@@ -120,18 +120,16 @@ class ModelRunner:
         if (q_lens <= 0).any():
             raise ValueError("an entry brings no tokens")
         T = int(q_lens.sum())
-        # pages: check the whole step before taking any
-        need = [0] * cache.num_groups
-        new = []
-        for e, n in zip(entries, q_lens):
-            if not cache.has(e.request_id):
-                new.append(e.request_id)
+        # pages: check the whole step before taking any (one call into the native manager)
+        slots = np.fromiter((cache.requests[i].slot if i in cache.requests else -1 for i in ids),
+                            dtype=np.int32, count=B)
+        need, over = cache.step_need(slots, q_lens)
+        if over >= 0:
+            e = entries[over]
             have = cache.get(e.request_id).num_tokens if cache.has(e.request_id) else 0
-            if have + int(n) > self.max_seq_len:
-                raise ValueError(f"request {e.request_id!r} would reach {have + int(n)} tokens; "
-                                 f"the limit is {self.max_seq_len}")
-            for g, k in enumerate(cache.pages_needed(e.request_id, int(n))):
-                need[g] += k
+            raise ValueError(f"request {e.request_id!r} would reach {have + int(q_lens[over])} "
+                             f"tokens; the limit is {self.max_seq_len}")
+        new = [e.request_id for e, sl in zip(entries, slots) if sl < 0]
         if len(new) > cache.slots.num_free:
             raise RuntimeError(f"{len(new)} new requests but {cache.slots.num_free} free slots")
         for g, (k, f) in enumerate(zip(need, cache.free_pages())):
@@ -139,14 +137,14 @@ class ModelRunner:
                 raise OutOfPages(f"the step needs {k} pages of group {g}; {f} are free")
         for rid in new:
             cache.admit(rid)
-        rcs = [cache.get(e.request_id) for e in entries]
-        q_starts = np.fromiter((rc.num_tokens for rc in rcs), dtype=np.int64, count=B)
+        if new:
+            slots = np.fromiter((cache.requests[i].slot for i in ids), dtype=np.int32, count=B)
+        q_starts = cache.lengths(slots).astype(np.int64)
         if self.storage.state:
-            for rc in rcs:
-                if rc.num_tokens == 0:       # a sequence starts (again): its state starts at zero
-                    self.storage.reset_slot(rc.slot)
-        for e, n in zip(entries, q_lens):
-            cache.reserve(e.request_id, int(n))
+            for sl, n0 in zip(slots, q_starts):
+                if n0 == 0:                  # a sequence starts (again): its state starts at zero
+                    self.storage.reset_slot(int(sl))
+        cache.reserve_step(slots, q_lens)
 
         tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64).reshape(-1)
                                  for e in entries])
@@ -155,7 +153,7 @@ class ModelRunner:
         seq_of_token = np.repeat(np.arange(B), q_lens)
         positions = np.arange(T) - np.repeat(cu[:-1] - q_starts, q_lens)
         kv_lens = q_starts + q_lens
-        slot_ids = np.fromiter((rc.slot for rc in rcs), dtype=np.int64, count=B)
+        slot_ids = slots.astype(np.int64)
         rows = []
         for b, e in enumerate(entries):
             for w in e.want:
@@ -307,8 +305,7 @@ class ModelRunner:
                 self._feed_back(dev, feedback)
                 ctx = self.make_context(dev, facts)
                 logits = self.model.forward(ctx, self.binder(dev))
-        for e, n in zip(entries, facts["q_lens"]):
-            self.cache.commit(e.request_id, int(n))
+        self.cache.commit_step(facts["slot_ids"], facts["q_lens"])
         self.steps_run += 1
         return logits
 

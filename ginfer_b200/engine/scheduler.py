@@ -29,7 +29,7 @@ import time
 from collections import deque
 from dataclasses import dataclass
 
-from ..cache.manager import CacheManager
+from ..cache import NativeCacheManager as CacheManager
 from .request import Request, RequestState
 
 

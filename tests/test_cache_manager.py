@@ -5,9 +5,17 @@ import random
 import numpy as np
 import pytest
 
-from ginfer_b200.cache.manager import CacheManager
+from ginfer_b200.cache.manager import CacheManager as PyCacheManager
+from ginfer_b200.cache.native import NativeCacheManager
 from ginfer_b200.cache.page_pool import OutOfPages, PagePool, PagePoolError
 from ginfer_b200.cache.slots import NoFreeSlot, SlotPool
+
+
+@pytest.fixture(params=["python", "native"])
+def CacheManager(request):
+    """Both managers: the one in Python that states the rules and the one in C++ that the engine
+    runs (host code; it compiles and runs without a GPU)."""
+    return PyCacheManager if request.param == "python" else NativeCacheManager
 
 
 def test_pool_refuses_double_return_and_foreign_return():
@@ -39,7 +47,7 @@ def test_slots():
     assert s.take("z") == a and s.holder_of(a) == "z"
 
 
-def test_reserve_commit_tables_and_slot_mapping():
+def test_reserve_commit_tables_and_slot_mapping(CacheManager):
     m = CacheManager([0], num_pages=6, page_size=4, max_num_seqs=2, max_seq_len=24)
     rc = m.admit("a")
     assert m.pages_needed("a", 5) == [2] and m.pages_needed("new", 9) == [3]
@@ -64,7 +72,7 @@ def test_reserve_commit_tables_and_slot_mapping():
     m.check()
 
 
-def test_reserve_is_all_or_nothing_across_groups():
+def test_reserve_is_all_or_nothing_across_groups(CacheManager):
     m = CacheManager([0, 8], num_pages=[2, 8], page_size=4, max_num_seqs=2, max_seq_len=64)
     m.admit("a")
     with pytest.raises(OutOfPages):
@@ -73,7 +81,7 @@ def test_reserve_is_all_or_nothing_across_groups():
     m.check()
 
 
-def test_window_gives_pages_back_and_never_one_that_is_visible():
+def test_window_gives_pages_back_and_never_one_that_is_visible(CacheManager):
     P, W = 4, 10
     m = CacheManager([0, W], num_pages=40, page_size=P, max_num_seqs=1, max_seq_len=160)
     rc = m.admit("a")
@@ -99,7 +107,7 @@ def test_window_gives_pages_back_and_never_one_that_is_visible():
 
 
 @pytest.mark.parametrize("seed", range(8))
-def test_random_orders_keep_every_page_accounted_for(seed):
+def test_random_orders_keep_every_page_accounted_for(CacheManager, seed):
     rng = random.Random(seed)
     P = rng.choice([1, 4, 16])
     windows = rng.choice([[0], [0, 24], [0, 7, 40]])
@@ -154,3 +162,78 @@ def test_random_orders_keep_every_page_accounted_for(seed):
     m.check()
     assert m.free_pages() == [pages] * len(windows) and m.slots.num_free == 4
     assert reused, "the scenario never used a page again"
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_native_manager_does_what_the_python_manager_does(seed):
+    """The same random sequence of operations on both managers: same answers, same tables, same
+    free counts, same refusals, step by step; and the calls for a whole step agree with the calls
+    per request."""
+    rng = random.Random(100 + seed)
+    P = rng.choice([1, 4, 16])
+    windows = rng.choice([[0], [0, 24], [0, 7, 40]])
+    pages = rng.choice([12, 30])
+    a = PyCacheManager(windows, pages, P, 4, pages * P)
+    b = NativeCacheManager(windows, pages, P, 4, pages * P)
+    live: list[str] = []
+    issued = 0
+
+    def both(fn):
+        out = []
+        for m in (a, b):
+            try:
+                out.append(("ok", fn(m)))
+            except (OutOfPages, ValueError, NoFreeSlot, KeyError) as e:
+                out.append((type(e).__name__, None))
+        assert out[0] == out[1], out
+        return out[0]
+
+    for _ in range(500):
+        act = rng.random()
+        if act < 0.15:
+            rid = f"r{issued}"
+            issued += 1
+            if both(lambda m: m.admit(rid).slot)[0] == "ok":
+                live.append(rid)
+        elif act < 0.7 and live:
+            rid, n = rng.choice(live), rng.choice([1, 1, 2, 5, 17, 40])
+            both(lambda m: m.pages_needed(rid, n))
+            both(lambda m: m.can_reserve(rid, n))
+            if both(lambda m: m.reserve(rid, n))[0] == "ok":
+                k = rng.randint(0, n)
+                both(lambda m: m.commit(rid, k))
+                both(lambda m: m.commit(rid, n - k))
+        elif act < 0.8 and live:
+            rid = rng.choice(live)
+            both(lambda m: m.release(rid, keep_slot=True))
+        elif act < 0.9 and live:
+            rid = live.pop(rng.randrange(len(live)))
+            both(lambda m: m.release(rid))
+        elif live:
+            # a whole step: need, then reserve, then commit, against the calls per request
+            ids = rng.sample(live, rng.randint(1, len(live)))
+            ns = [rng.choice([1, 1, 3, 9]) for _ in ids]
+            slots = np.array([b.get(i).slot for i in ids])
+            need, over = b.step_need(slots, np.array(ns))
+            want = [sum(a.pages_needed(i, n)[g] for i, n in zip(ids, ns))
+                    for g in range(len(windows))]
+            assert need == want
+            fits = all(a.get(i).num_tokens + a.get(i).reserved + n <= a.max_seq_len
+                       for i, n in zip(ids, ns))
+            assert (over < 0) == fits
+            if fits and all(k <= f for k, f in zip(need, a.free_pages())):
+                for i, n in zip(ids, ns):
+                    a.reserve(i, n)
+                b.reserve_step(slots, np.array(ns))
+                assert list(b.lengths(slots)) == [a.get(i).num_tokens for i in ids]
+                for i, n in zip(ids, ns):
+                    a.commit(i, n)
+                b.commit_step(slots, np.array(ns))
+        a.check(), b.check()
+        assert a.free_pages() == b.free_pages() and a.slots.num_free == b.slots.num_free
+        for rid in live:
+            ra, rb = a.get(rid), b.get(rid)
+            assert (ra.slot, ra.num_tokens, ra.reserved, ra.first_page, ra.next_page) == \
+                (rb.slot, rb.num_tokens, rb.reserved, rb.first_page, rb.next_page)
+        for ta, tb in zip(a.tables, b.tables):
+            assert (ta == tb).all()

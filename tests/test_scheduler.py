@@ -3,14 +3,25 @@ import random
 
 import pytest
 
-from ginfer_b200.cache.manager import CacheManager
+from ginfer_b200.cache.manager import CacheManager as PyCacheManager
+from ginfer_b200.cache.native import NativeCacheManager
 from ginfer_b200.engine.request import Request, RequestState
 from ginfer_b200.engine.scheduler import Scheduler
 from ginfer_b200.sampling import SamplingParams, uniform
 
 
+_MANAGER = [NativeCacheManager]
+
+
+@pytest.fixture(autouse=True, params=["native", "python"])
+def _both_managers(request):
+    """Every test here runs over the C++ cache manager (what the engine uses) and the Python one."""
+    _MANAGER[0] = NativeCacheManager if request.param == "native" else PyCacheManager
+    yield
+
+
 def _sched(pages=16, page=4, seqs=4, budget=16, max_len=64, eos=(), windows=(0,)):
-    cache = CacheManager(list(windows), pages, page, seqs, max_len)
+    cache = _MANAGER[0](list(windows), pages, page, seqs, max_len)
     return Scheduler(cache, seqs, budget, max_len, eos), cache
 
 
