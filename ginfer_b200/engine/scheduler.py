@@ -94,6 +94,12 @@ class Scheduler:
             n -= 1
         return n
 
+    def _need_fits(self, need: list[int], promised: list[int]) -> bool:
+        """Whether ``need`` pages per group are free beyond what is ``promised`` to others."""
+        if not any(need):
+            return True
+        return all(k <= f - p for k, f, p in zip(need, self.cache.free_pages(), promised))
+
     def _promise(self, req: Request, n: int, promised: list[int]) -> None:
         for g, k in enumerate(self.cache.pages_needed(req.request_id, n)):
             promised[g] += k
@@ -129,7 +135,8 @@ class Scheduler:
                 continue
             if budget <= 0:
                 break
-            while not self.cache.can_reserve(req.request_id, 1, promised):
+            need = self.cache.pages_needed(req.request_id, 1)    # preempting others leaves it as is
+            while not self._need_fits(need, promised):
                 victims = [r for r in self.running if r is not req
                            and all(s.request is not r for s in batch)]
                 if victims:
@@ -140,10 +147,10 @@ class Scheduler:
                     self._finish(req, "out_of_pages")
                     dropped.append(req)
                     break
-            if req.state is not RequestState.RUNNING or \
-                    not self.cache.can_reserve(req.request_id, 1, promised):
+            if req.state is not RequestState.RUNNING or not self._need_fits(need, promised):
                 continue
-            self._promise(req, 1, promised)
+            for g, k in enumerate(need):
+                promised[g] += k
             batch.append(Scheduled(req, req.num_computed, 1, True))
             budget -= 1
 
