@@ -41,6 +41,18 @@ QWEN2_1P5B = {
     "tie_word_embeddings": False, "sliding_window": 4096, "use_sliding_window": False,
     "torch_dtype": "bfloat16",
 }
+# the other shapes the baseline names (layer sizes only; run them with --layers where the whole
+# model would not be needed): Qwen2.5-7B and Qwen2.5-32B
+SHAPES = {
+    "1.5b": QWEN2_1P5B,
+    "7b": dict(QWEN2_1P5B, num_hidden_layers=28, hidden_size=3584, num_attention_heads=28,
+               num_key_value_heads=4, intermediate_size=18944, vocab_size=152064,
+               rope_theta=1e6, max_position_embeddings=8192),
+    "32b": dict(QWEN2_1P5B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=40,
+                num_key_value_heads=8, intermediate_size=27648, vocab_size=152064,
+                rope_theta=1e6, max_position_embeddings=16384),
+}
+SHAPE_NAMES = {"1.5b": "Qwen2-1.5B shape", "7b": "Qwen2.5-7B shape", "32b": "Qwen2.5-32B shape"}
 CONTEXT = 4096
 PROMPT = 512
 PREFILL_TOKENS = 2048
@@ -338,6 +350,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None,
                     help="run fewer layers than the configuration has (both numbers are reported)")
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--shape", choices=sorted(SHAPES), default="1.5b",
+                    help="layer sizes: the benchmark's own (default) or the larger ones the "
+                         "baseline names")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--enforce-eager", action="store_true")
     ap.add_argument("--micro", choices=MICRO, default=None,
@@ -362,7 +377,7 @@ def main() -> int:
     import torch
 
     from ginfer_b200.engine.llm import Engine
-    cfg = dict(QWEN2_1P5B)
+    cfg = dict(SHAPES[args.shape])
     full_layers = cfg["num_hidden_layers"]
     layers = args.layers or full_layers
     cfg["num_hidden_layers"] = layers
@@ -391,20 +406,21 @@ def main() -> int:
     flops = prefill_flops(cfg, layers, PREFILL_TOKENS)
     value = B / (ms * 1e-3)
     line = {
-        "metric": "decode tok/s at batch 8 (one B200), Qwen2-1.5B shape",
+        "metric": f"decode tok/s at batch {B} (one B200), {SHAPE_NAMES[args.shape]}",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random token ids, random-init weights N(0, 0.02)",
         "impl": "ours",
         "config": {
-            "model": "Qwen2-1.5B shape", "layers_run": layers, "layers_config": full_layers,
+            "model": SHAPE_NAMES[args.shape], "layers_run": layers, "layers_config": full_layers,
             "hidden_size": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
             "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
             "intermediate_size": cfg["intermediate_size"], "vocab_size": cfg["vocab_size"],
             "global_batch": B, "seq_len": CONTEXT, "prompt_len": PROMPT,
             "kv_block": PAGE, "parallelism": "single GPU",
-            "l2": "inputs larger than L2 (3.1 GB of weights read per step)",
+            "l2": f"inputs larger than L2 ({weight_bytes(cfg, layers) / 1e9:.1f} GB of weights read "
+                  "per step)",
             "cuda_graphs": not args.enforce_eager, "peaks": peak_src,
         },
         "e2e": {"value": round(B / (e2e_ms * 1e-3), 1), "unit": "tok/s",
