@@ -4,10 +4,10 @@
 //   producer  (o_proj, down_proj):   s = residual + x W^T (+ b)            -> fp32, the new residual
 //                                    sumsq[part][token] = sum over the part's rows of s^2
 //   consumer  (qkv, gate/up, head):  y = norm(s) W^T (+ b)   or   silu(gate) * up
-//             where norm(s)[token, k] = bf16(s * gamma[k] / rms[token]),
-//             rms = sqrtf(sum_parts sumsq / K + eps): the same formula and the same rounding as the
-//             stand-alone norm kernel (csrc/elementwise.cu), so the result does not depend on
-//             which path ran beyond the order in which the squares are added.
+//             where norm(s)[token, k] = bf16(s * gamma[k] * (1 / rms[token])),
+//             rms = sqrtf(sum_parts sumsq / K + eps): the formula of the stand-alone norm kernel
+//             (csrc/elementwise.cu), which divides by rms where this one multiplies by 1 / rms
+//             (one fp32 ulp before the rounding to bf16) and adds the squares in another order.
 //
 // The consumer does not load its activation operand by TMA: the four epilogue warps read the fp32
 // residual rows, normalise them and write the bf16 operand tiles for the CTA's K range into shared
@@ -167,7 +167,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_w,
             ss += __ldg(fa.b_sumsq + (size_t)p * fa.ss_ld + m);
 #pragma unroll
         for (int o = TPT / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (sub == 0) rms_s[m] = sqrtf(ss / (float)K + fa.eps);
+        if (sub == 0) rms_s[m] = 1.0f / sqrtf(ss / (float)K + fa.eps);   // one division a token
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");          // the four epilogue warps only
       // 2. this CTA's K range of the operand: bf16(s * gamma / rms), 8 channels (16 bytes) a time.
@@ -212,11 +212,14 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_w,
             const int k = (kb0 + kbl_u[u]) * BK + ch * 8;
             uint4 w = make_uint4(0u, 0u, 0u, 0u);
             if (k < K) {
+              // multiplied by 1/rms: at four warps a CTA the eight IEEE divisions a chunk that
+              // the stand-alone norm kernel makes cost microseconds here (the result differs
+              // from that kernel's by at most one fp32 ulp before the rounding to bf16)
               const float r = rms_s[mm];
-              __nv_bfloat162 t0 = __floats2bfloat162_rn(s0[u].x * g0[u].x / r, s0[u].y * g0[u].y / r);
-              __nv_bfloat162 t1 = __floats2bfloat162_rn(s0[u].z * g0[u].z / r, s0[u].w * g0[u].w / r);
-              __nv_bfloat162 t2 = __floats2bfloat162_rn(s1[u].x * g1[u].x / r, s1[u].y * g1[u].y / r);
-              __nv_bfloat162 t3 = __floats2bfloat162_rn(s1[u].z * g1[u].z / r, s1[u].w * g1[u].w / r);
+              __nv_bfloat162 t0 = __floats2bfloat162_rn(s0[u].x * g0[u].x * r, s0[u].y * g0[u].y * r);
+              __nv_bfloat162 t1 = __floats2bfloat162_rn(s0[u].z * g0[u].z * r, s0[u].w * g0[u].w * r);
+              __nv_bfloat162 t2 = __floats2bfloat162_rn(s1[u].x * g1[u].x * r, s1[u].y * g1[u].y * r);
+              __nv_bfloat162 t3 = __floats2bfloat162_rn(s1[u].z * g1[u].z * r, s1[u].w * g1[u].w * r);
               w = make_uint4(*reinterpret_cast<uint32_t*>(&t0), *reinterpret_cast<uint32_t*>(&t1),
                              *reinterpret_cast<uint32_t*>(&t2), *reinterpret_cast<uint32_t*>(&t3));
             }
