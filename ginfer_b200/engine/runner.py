@@ -31,11 +31,17 @@ def _align4(n: int) -> int:
     return (n + 3) & ~3
 
 
-GRAPH_WIDTH_STEP = 64        # block-table widths of graph-replayed decode steps, in pages
+GRAPH_WIDTH_STEP = 64        # block-table widths of graph-replayed steps, in pages
+# Steps with prompt portions are replayed from a graph when the same shape (portion lengths, table
+# width, wanted rows) comes a second time: whole-budget portions of long prompts do.  Only steps
+# of at most this many requests and at least this many tokens, and this many graphs at most.
+PORTION_GRAPH_MAX_SEQS = 4
+PORTION_GRAPH_MIN_TOKENS = 256
+PORTION_GRAPH_LIMIT = 16
 
 
 @dataclass
-class _DecodeGraph:
+class _StepGraph:
     graph: object
     ints: torch.Tensor            # static device buffer the graph's kernels read
     spans: dict
@@ -72,6 +78,7 @@ class ModelRunner:
         self._host = None            # pinned staging for the step's integers
         self._host_cap = 0
         self._graphs: dict = {}
+        self._portion_seen: dict = {}     # shapes of steps with prompt portions -> times seen
         self._graph_pool = None
         self._copied = torch.cuda.Event()     # the last copy out of the staging buffer
         self._copy_pending = False
@@ -164,9 +171,10 @@ class ModelRunner:
         logit_rows = np.asarray(rows, dtype=np.int64)
         width = int(-(-int(kv_lens.max()) // P))
         decode_only = int(q_lens.max()) == 1
-        if decode_only and not self.enforce_eager:
-            # decode steps are replayed from CUDA graphs, one per (batch size, table width):
-            # widths come in steps of GRAPH_WIDTH_STEP pages so that few graphs are needed
+        graphable = decode_only or (B <= PORTION_GRAPH_MAX_SEQS and T >= PORTION_GRAPH_MIN_TOKENS)
+        if graphable and not self.enforce_eager:
+            # such steps are replayed from CUDA graphs, one per (shape, table width): widths come
+            # in steps of GRAPH_WIDTH_STEP pages so that few graphs are needed
             width = min(cache.table_width, -(-width // GRAPH_WIDTH_STEP) * GRAPH_WIDTH_STEP)
         slots_of_token = slot_ids[seq_of_token]
         slot_maps = [cache.slot_mapping(g, slots_of_token, positions)
@@ -239,14 +247,28 @@ class ModelRunner:
         return bind
 
     def _graph_key(self, entries, facts):
-        """Decode steps in which every request wants its token's logits replay a CUDA graph."""
-        if self.enforce_eager or facts["max_q_len"] != 1 or self.storage.state:
+        """Decode steps in which every request wants its token's logits replay a CUDA graph; so
+        do steps with prompt portions whose shape has come before (see PORTION_GRAPH_*)."""
+        if self.enforce_eager or self.storage.state:
             return None
-        if any(len(e.want) != 1 for e in entries):
+        if facts["max_q_len"] == 1:
+            if any(len(e.want) != 1 for e in entries):
+                return None
+            return (facts["B"], facts["width"])
+        if facts["B"] > PORTION_GRAPH_MAX_SEQS or facts["T"] < PORTION_GRAPH_MIN_TOKENS:
             return None
-        return (facts["B"], facts["width"])
+        key = ("portions", tuple(int(n) for n in facts["q_lens"]), facts["width"],
+               tuple(tuple(int(w) for w in e.want) for e in entries))
+        if key in self._graphs:
+            return key
+        seen = self._portion_seen.get(key, 0) + 1
+        if len(self._portion_seen) > 4096:
+            self._portion_seen.clear()
+        self._portion_seen[key] = seen
+        graphs = sum(1 for k in self._graphs if isinstance(k[0], str))
+        return key if seen >= 2 and graphs < PORTION_GRAPH_LIMIT else None
 
-    def _capture(self, key, arrays, facts) -> _DecodeGraph:
+    def _capture(self, key, arrays, facts) -> _StepGraph:
         from .. import ops
         total = sum(_align4(a.size) for a in arrays.values()) + 2 * _align4(facts["B"])
         ints = torch.empty(total, dtype=torch.int32, device=self.device)
@@ -264,7 +286,7 @@ class ModelRunner:
         before = ops.launch_count()
         with torch.cuda.graph(graph, pool=self._graph_pool):
             logits = self.model.forward(ctx, bind)
-        return _DecodeGraph(graph, ints, {}, logits, ops.launch_count() - before)
+        return _StepGraph(graph, ints, {}, logits, ops.launch_count() - before)
 
     @torch.no_grad()
     def launch(self, prepared, entries: list[StepEntry], token_ids=None, feedback=None

@@ -135,3 +135,25 @@ def test_cuts_agree_with_plain_when_norms_are_folded_into_products(folders, name
     runner = _runner(model_dir, "bfloat16", PAGE[name], replay.peak_tokens(steps))
     rows = replay.run_in_process(runner, steps)
     replay.compare(rows, replay.plain_logits(model_dir, reqs, "bfloat16"), "bfloat16", reqs)
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_prompt_portions_of_a_shape_that_comes_again_are_replayed_from_graphs(folders, name):
+    """Steps with prompt portions whose shape (portion lengths, wanted rows, table width) has come
+    before are replayed from a CUDA graph: four requests of 300 tokens, fed as 260 + 40, one after
+    the other; from the third on the 260-token step is a replay.  All agree with plain."""
+    model_dir = folders[(name, "bfloat16")]
+    v = CONFIGS[name]["vocab_size"]
+    reqs = {f"q{i}": prompt(300, v, seed=50 + i) for i in range(4)}
+    steps = []
+    for rid, toks in reqs.items():
+        steps.append({"step": len(steps), "end": [], "entries": [
+            {"id": rid, "tokens": toks[:260], "want": list(range(260))}]})
+        steps.append({"step": len(steps), "end": [rid], "entries": [
+            {"id": rid, "tokens": toks[260:], "want": list(range(40))}]})
+    runner = _runner(model_dir, "bfloat16", PAGE[name], 320, eager=False)
+    before = runner.graph_launches
+    rows = replay.run_in_process(runner, steps)
+    replay.compare(rows, replay.plain_logits(model_dir, reqs, "bfloat16"), "bfloat16", reqs)
+    assert runner.graph_launches > before, "no step was replayed from a graph"
+    assert any(isinstance(k[0], str) for k in runner._graphs)
