@@ -47,6 +47,7 @@ def _lib():
         lib.gf_cm_commit_many.argtypes = [c_void_p, ip, ip, c_int]
         lib.gf_cm_release.argtypes = [c_void_p, c_int, c_int]
         lib.gf_cm_check.argtypes = [c_void_p]
+        lib.gf_sched_decide.argtypes = [c_void_p, c_int, c_int, c_int, c_int] + [ip] * 9
         lib._gf_typed = True
     return lib
 
@@ -275,6 +276,47 @@ class NativeCacheManager:
                                          int(slots.size))
         if rc:
             self._raise(rc)
+
+    # ------------------------------------------------------------------ the scheduler's decision
+    def decide(self, budget: int, max_num_seqs: int, running: list, waiting: list):
+        """One scheduling decision in native code (``gf_sched_decide`` in ``csrc/cache_core.cu``;
+        the rules are those of ``engine/scheduler.py``).  ``running`` and ``waiting``: lists of
+        ``(request_id, tokens, computed)`` in order.  Pages of preempted requests are released and
+        admitted requests get their slots here.  Returns ``(batch, running_order, waiting_order,
+        preempts, dropped)``: ``batch`` = ``(entry, start, n, sample)`` tuples with entries
+        numbered through ``running + waiting``; the orders are entry numbers; ``preempts[e]`` says
+        how often entry ``e`` was preempted, ``dropped[e]`` whether it was given up."""
+        reqs = list(running) + list(waiting)
+        n, nr = len(reqs), len(running)
+        slot = np.fromiter((self.requests[r[0]].slot if r[0] in self.requests else -1
+                            for r in reqs), dtype=np.int32, count=n)
+        slot_in = slot.copy()
+        tokens = np.fromiter((r[1] for r in reqs), dtype=np.int32, count=n)
+        computed = np.fromiter((r[2] for r in reqs), dtype=np.int32, count=n)
+        preempts = np.zeros(n, dtype=np.int32)
+        dropped = np.zeros(n, dtype=np.int32)
+        batch = np.zeros(4 * max(n, 1), dtype=np.int32)
+        order = np.zeros(max(n, 1), dtype=np.int32)
+        n_batch, n_running = c_int(0), c_int(0)
+        ip = POINTER(c_int)
+        rc = self._lib.gf_sched_decide(
+            self._h, int(budget), int(max_num_seqs), nr, n - nr, slot.ctypes.data_as(ip),
+            tokens.ctypes.data_as(ip), computed.ctypes.data_as(ip), preempts.ctypes.data_as(ip),
+            dropped.ctypes.data_as(ip), batch.ctypes.data_as(ip), ctypes.byref(n_batch),
+            order.ctypes.data_as(ip), ctypes.byref(n_running))
+        if rc:
+            self._raise(rc)
+        for e in range(n):                         # slots taken and given back on the native side
+            rid = reqs[e][0]
+            if slot_in[e] < 0 <= slot[e]:
+                self.requests[rid] = _Request(self, rid, int(slot[e]))
+            elif slot_in[e] >= 0 > slot[e]:
+                del self.requests[rid]
+        acts = [tuple(int(v) for v in batch[4 * i:4 * i + 4]) for i in range(n_batch.value)]
+        k = n_running.value
+        live = n - int(dropped.sum())
+        return (acts, [int(e) for e in order[:k]], [int(e) for e in order[k:live]],
+                preempts.tolist(), dropped.tolist())
 
     # ------------------------------------------------------------------ what the step needs
     def slot_mapping(self, group: int, slots_of_token: np.ndarray, positions: np.ndarray

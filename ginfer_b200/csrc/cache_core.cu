@@ -374,3 +374,211 @@ GF_EXPORT int gf_cm_check(void* h) {
     if (!seen[s] && !m->reqs[s].live) return m->fail(CHECK_FAILED, "a slot is lost");
   return OK;
 }
+
+// ----------------------------------------------------------------------------- one scheduling decision
+// The order of work of ginfer_b200/engine/scheduler.py (which stays as the statement of the rules
+// and runs when the manager is the Python one): (1) one token for every running request that is
+// decoding, oldest first; a request that needs a page takes it from the most recently admitted
+// other running request that is not yet in the batch, which is preempted (pages back, slot kept,
+// front of the waiting queue, computed again from its first token); (2) portions for running
+// requests still in their prompt; (3) admission, oldest first, no overtaking, while a slot, budget
+// and pages for a first portion are there; (4) if nothing could move, the youngest running request
+// is preempted and the decision is taken again, or a request that is alone is given up.
+//
+// Requests come as entries 0 .. nr - 1 (running, in order of admission) and nr .. nr + nw - 1
+// (waiting, in queue order): slot (-1: none yet), tokens (prompt + output), computed.  The function
+// releases and admits through the manager itself.  Results: the batch (entry, start, n, sample),
+// the new running and waiting orders, per entry the slot, how often it was preempted and whether
+// it was given up (out of pages).
+namespace {
+
+struct Sched {
+  Manager* m;
+  std::vector<int> slot, tokens, computed, preempts, dropped;
+  std::vector<int> running, waiting;          // entry indices
+  std::vector<int> promised;
+  std::vector<int> batch;                     // 4 ints an action
+  std::vector<char> in_batch;
+  int budget = 0;
+
+  void pages_needed(int e, int n, std::vector<int>& need) const {
+    need.resize(m->G);
+    if (slot[e] < 0) {
+      for (int g = 0; g < m->G; ++g) need[g] = (n + m->page_size - 1) / m->page_size;
+      return;
+    }
+    const Req& r = m->reqs[slot[e]];
+    for (int g = 0; g < m->G; ++g)
+      need[g] = m->new_pages(r.next_page[g], r.num_tokens + r.reserved, n);
+  }
+  bool fits(const std::vector<int>& need) const {
+    for (int g = 0; g < m->G; ++g)
+      if (need[g] > (int)m->pools[g].free_.size() - promised[g]) return false;
+    return true;
+  }
+  bool can_reserve(int e, int n) const {
+    std::vector<int> need;
+    pages_needed(e, n, need);
+    return fits(need);
+  }
+  int fit(int e, int want) const {
+    if (want <= 0) return 0;
+    if (can_reserve(e, want)) return want;
+    int free_pages = 1 << 30;
+    for (int g = 0; g < m->G; ++g)
+      free_pages = std::min(free_pages, (int)m->pools[g].free_.size() - promised[g]);
+    if (free_pages < 0) return 0;
+    int held_end = 0;
+    if (slot[e] >= 0) {
+      const Req& r = m->reqs[slot[e]];
+      held_end = *std::min_element(r.next_page.begin(), r.next_page.end()) * m->page_size;
+    }
+    const int room = std::max(0, held_end - computed[e]) + free_pages * m->page_size;
+    int n = std::min(want, room);
+    while (n > 0 && !can_reserve(e, n)) --n;
+    return n;
+  }
+  void promise(int e, int n) {
+    std::vector<int> need;
+    pages_needed(e, n, need);
+    for (int g = 0; g < m->G; ++g) promised[g] += need[g];
+  }
+  void take(int e, int start, int n, bool sample) {
+    batch.push_back(e), batch.push_back(start), batch.push_back(n), batch.push_back(sample);
+    in_batch[e] = 1;
+    budget -= n;
+  }
+  int preempt(int e) {
+    if (int rc = gf_cm_release(m, slot[e], 1)) return rc;
+    computed[e] = 0;
+    ++preempts[e];
+    running.erase(std::find(running.begin(), running.end(), e));
+    waiting.insert(waiting.begin(), e);
+    return OK;
+  }
+  int give_up(int e) {
+    dropped[e] = 1;
+    auto it = std::find(running.begin(), running.end(), e);
+    if (it != running.end()) running.erase(it);
+    if (slot[e] >= 0) {
+      if (int rc = gf_cm_release(m, slot[e], 0)) return rc;
+      slot[e] = -1;
+    }
+    return OK;
+  }
+  bool is_running(int e) const {
+    return std::find(running.begin(), running.end(), e) != running.end();
+  }
+
+  int decide(int max_num_seqs, int full_budget) {
+    for (;;) {
+      budget = full_budget;
+      std::fill(promised.begin(), promised.end(), 0);
+      batch.clear();
+      std::fill(in_batch.begin(), in_batch.end(), 0);
+      bool any_dropped = false;
+      // 1. decoding requests, oldest first
+      const std::vector<int> snapshot = running;
+      std::vector<int> need;
+      for (int e : snapshot) {
+        if (!is_running(e) || tokens[e] - computed[e] != 1) continue;
+        if (budget <= 0) break;
+        pages_needed(e, 1, need);
+        while (!fits(need)) {
+          int victim = -1;
+          for (int r : running)
+            if (r != e && !in_batch[r]) victim = r;          // the last one: most recently admitted
+          if (victim >= 0) {
+            if (int rc = preempt(victim)) return rc;
+          } else if (running.size() > 1 || !batch.empty()) {
+            break;                                           // others hold this step's pages: wait
+          } else {
+            if (int rc = give_up(e)) return rc;
+            any_dropped = true;
+            break;
+          }
+        }
+        if (!is_running(e) || !fits(need)) continue;
+        for (int g = 0; g < m->G; ++g) promised[g] += need[g];
+        take(e, computed[e], 1, true);
+      }
+      // 2. running requests still feeding their prompt
+      const std::vector<int> snapshot2 = running;
+      for (int e : snapshot2) {
+        const int left = tokens[e] - computed[e];
+        if (!is_running(e) || left <= 1 || budget <= 0) continue;
+        const int n = fit(e, std::min(left, budget));
+        if (n <= 0) continue;
+        promise(e, n);
+        take(e, computed[e], n, n == left);
+      }
+      // 3. admission, oldest first, no overtaking
+      while (!waiting.empty() && budget > 0 && (int)running.size() < max_num_seqs) {
+        const int e = waiting.front();
+        if (slot[e] < 0 && m->free_slots.empty()) break;
+        const int left = tokens[e];
+        const int n = fit(e, std::min(left, budget));
+        if (n <= 0) break;
+        waiting.erase(waiting.begin());
+        if (slot[e] < 0) {
+          int s = -1;
+          if (int rc = gf_cm_admit(m, &s)) return rc;
+          slot[e] = s;
+        }
+        running.push_back(e);
+        promise(e, n);
+        take(e, 0, n, n == left);
+      }
+      // 4. nothing could move although requests are live
+      if (batch.empty() && !any_dropped && (!running.empty() || !waiting.empty())) {
+        if (running.size() > 1) {
+          if (int rc = preempt(running.back())) return rc;
+          continue;                                          // decide again
+        }
+        if (!running.empty()) {
+          if (int rc = give_up(running[0])) return rc;
+        } else {
+          const int e = waiting.front();
+          waiting.erase(waiting.begin());
+          if (int rc = give_up(e)) return rc;
+        }
+      }
+      return OK;
+    }
+  }
+};
+
+}  // namespace
+
+// in: nr, nw, slot/tokens/computed [nr + nw].  out: slot [nr + nw] (updated in place), preempts
+// [nr + nw], dropped [nr + nw], batch [4 * (nr + nw)] with *n_batch actions, order [nr + nw] =
+// the new running order then the new waiting order, with *n_running.
+GF_EXPORT int gf_sched_decide(void* h, int budget, int max_num_seqs, int nr, int nw, int* slot,
+                              const int* tokens, const int* computed, int* preempts, int* dropped,
+                              int* batch, int* n_batch, int* order, int* n_running) {
+  auto* m = (Manager*)h;
+  const int n = nr + nw;
+  Sched s;
+  s.m = m;
+  s.slot.assign(slot, slot + n);
+  s.tokens.assign(tokens, tokens + n);
+  s.computed.assign(computed, computed + n);
+  s.preempts.assign(n, 0);
+  s.dropped.assign(n, 0);
+  s.in_batch.assign(n, 0);
+  s.promised.assign(m->G, 0);
+  for (int i = 0; i < nr; ++i) s.running.push_back(i);
+  for (int i = nr; i < n; ++i) s.waiting.push_back(i);
+  const int rc = s.decide(max_num_seqs, budget);
+  if (rc) return rc;
+  std::copy(s.slot.begin(), s.slot.end(), slot);
+  std::copy(s.preempts.begin(), s.preempts.end(), preempts);
+  std::copy(s.dropped.begin(), s.dropped.end(), dropped);
+  *n_batch = (int)s.batch.size() / 4;
+  std::copy(s.batch.begin(), s.batch.end(), batch);
+  *n_running = (int)s.running.size();
+  int k = 0;
+  for (int e : s.running) order[k++] = e;
+  for (int e : s.waiting) order[k++] = e;
+  return OK;
+}

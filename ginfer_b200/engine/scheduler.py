@@ -123,7 +123,39 @@ class Scheduler:
             self.cache.release(req.request_id)
 
     def schedule(self) -> tuple[list[Scheduled], list[Request]]:
-        """Returns the step's batch and the requests finished without a step (out of pages)."""
+        """Returns the step's batch and the requests finished without a step (out of pages).
+        With the native cache manager the decision is taken in C++ (same rules, one call)."""
+        if hasattr(self.cache, "decide"):
+            return self._schedule_native()
+        return self._schedule_python()
+
+    def _schedule_native(self) -> tuple[list[Scheduled], list[Request]]:
+        reqs = list(self.running) + list(self.waiting)
+        nr = len(self.running)
+        acts, running, waiting, preempts, dropped = self.cache.decide(
+            self.max_num_batched_tokens, self.max_num_seqs,
+            [(r.request_id, r.num_tokens, r.num_computed) for r in reqs[:nr]],
+            [(r.request_id, r.num_tokens, r.num_computed) for r in reqs[nr:]])
+        out: list[Request] = []
+        for e, req in enumerate(reqs):
+            if preempts[e]:
+                req.num_computed = 0
+                req.num_preemptions += preempts[e]
+                self.num_preemptions += preempts[e]
+            if dropped[e]:
+                req.state = RequestState.FINISHED
+                req.finish_reason = "out_of_pages"
+                req.finish_time = time.perf_counter()
+                out.append(req)
+        self.running = [reqs[e] for e in running]
+        self.waiting = deque(reqs[e] for e in waiting)
+        for r in self.running:
+            r.state = RequestState.RUNNING
+        for r in self.waiting:
+            r.state = RequestState.WAITING
+        return [Scheduled(reqs[e], start, n, bool(sample)) for e, start, n, sample in acts], out
+
+    def _schedule_python(self) -> tuple[list[Scheduled], list[Request]]:
         budget = self.max_num_batched_tokens
         promised = [0] * self.cache.num_groups
         batch: list[Scheduled] = []
@@ -189,7 +221,7 @@ class Scheduler:
         if not batch and not dropped and (self.running or self.waiting):
             if len(self.running) > 1:
                 self._preempt(self.running[-1])
-                return self.schedule()
+                return self._schedule_python()
             if self.running:
                 req = self.running[0]
                 self._finish(req, "out_of_pages")

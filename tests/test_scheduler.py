@@ -217,3 +217,40 @@ def test_sampling_numbers_depend_on_seed_and_index_only():
     assert all(0.0 <= x < 1.0 for x in xs) and len(set(xs)) > 1990
     assert abs(sum(xs) / len(xs) - 0.5) < 0.03
     assert uniform(1, 7) != uniform(2, 7)
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_native_decisions_are_the_python_decisions(seed):
+    """The same arrivals on a scheduler over the C++ manager (decisions taken in C++) and on one
+    over the Python manager (decisions taken in Python), pools so small that requests are
+    preempted and given up: the same batch at every step, the same preemptions, the same ends."""
+    rng = random.Random(500 + seed)
+    page = rng.choice([1, 4, 8])
+    pages = rng.choice([5, 9, 14])
+    windows = rng.choice([(0,), (0, 6), (0, 5, 13)])
+    budget = rng.choice([3, 8, 16])
+    max_len = pages * page
+    plan = [(i, rng.randint(1, min(30, (pages - 1) * page)), rng.randint(1, 12), rng.randint(0, 3))
+            for i in range(rng.randint(3, 10))]
+    logs = []
+    for manager in (PyCacheManager, NativeCacheManager):
+        cache = manager(list(windows), pages, page, 3, max_len)
+        sched = Scheduler(cache, 3, budget, max_len, ())
+        assert hasattr(cache, "decide") == (manager is NativeCacheManager)
+        reqs = [_req(i, n, max_tokens=mt) for i, n, mt, _ in plan]
+        pending = list(zip(reqs, (gap for *_, gap in plan)))
+        log, steps = [], 0
+        while pending or not sched.is_finished():
+            while pending and pending[0][1] <= 0:
+                sched.add(pending.pop(0)[0])
+            if pending:
+                pending[0] = (pending[0][0], pending[0][1] - 1)
+            _, done = _run_step(sched, cache, log)
+            log.append(sorted((r.request_id, r.finish_reason) for r in done))
+            log.append([r.request_id for r in sched.running] + ["|"] +
+                       [r.request_id for r in sched.waiting])
+            steps += 1
+            assert steps < 3000
+        logs.append((log, sched.num_preemptions,
+                     [(r.output, r.finish_reason, r.num_preemptions) for r in reqs]))
+    assert logs[0] == logs[1]
