@@ -87,13 +87,13 @@ __device__ __forceinline__ void cluster_reduce(uint32_t red, const float* __rest
                                                OUT* __restrict__ out, int ldo, int M, int N,
                                                int n0, int m0) {
   const int rank = (int)cluster_rank();
-  constexpr int band = BM / SPLIT;
+  constexpr int band = ((BM + SPLIT - 1) / SPLIT + 1) & ~1;   // rows a CTA adds up (even: row pairs)
   constexpr int QUADS = BN / 4;                       // a unit of work: one row (pair), 4 tokens
   if (EPI == EPI_STORE) {
     for (int u = threadIdx.x; u < band * QUADS; u += NTHREADS) {
       const int row = rank * band + u % band, c = (u / band) * 4;
       const int n = n0 + row;
-      if (m0 + c >= M || n >= N) continue;
+      if (row >= BM || m0 + c >= M || n >= N) continue;
       float4 t[SPLIT];
 #pragma unroll
       for (int p = 0; p < SPLIT; ++p)
@@ -112,7 +112,7 @@ __device__ __forceinline__ void cluster_reduce(uint32_t red, const float* __rest
     for (int u = threadIdx.x; u < pairs * QUADS; u += NTHREADS) {
       const int row = rank * band + 2 * (u % pairs), c = (u / pairs) * 4;
       const int pair = (n0 + row) >> 1;
-      if (m0 + c >= M || n0 + row + 1 >= N) continue;
+      if (row >= BM || m0 + c >= M || n0 + row + 1 >= N) continue;
       float4 ta[SPLIT], tb[SPLIT];
 #pragma unroll
       for (int p = 0; p < SPLIT; ++p) {
@@ -304,8 +304,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       cluster_reduce<BN, EPI, OUT, 2>(red, bias, out, ldo, M, N, n0, m0);
     else if (split_k == 4)
       cluster_reduce<BN, EPI, OUT, 4>(red, bias, out, ldo, M, N, n0, m0);
-    else
+    else if (split_k == 8)
       cluster_reduce<BN, EPI, OUT, 8>(red, bias, out, ldo, M, N, n0, m0);
+    else
+      cluster_reduce<BN, EPI, OUT, 12>(red, bias, out, ldo, M, N, n0, m0);
     cluster_sync();                                   // nobody leaves while a peer still reads it
     return;
   }
@@ -360,6 +362,14 @@ static int launch_mode(const CUtensorMap& mw, const CUtensorMap& mx, const float
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     done = true;
+  }
+  if (CLUSTER && split_k > 8) {                       // clusters of more than 8 CTAs are opt-in
+    static bool np_done = false;
+    if (!np_done) {
+      cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+      if (e != cudaSuccess) return (int)e;
+      np_done = true;
+    }
   }
   dim3 grid((N + BM - 1) / BM, (M + BN - 1) / BN, split_k);
   return launch_kernel_cluster(k, grid, dim3(NTHREADS), smem, st, CLUSTER ? split_k : 1, mw, mx,
@@ -425,7 +435,8 @@ GF_EXPORT int gf_gemm_bf16_tc(const void* x, int ldx, const void* w, const float
   if (split_k < 1) split_k = 1;
   const long long tiles = (long long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
   // split_k > 1 without a workspace asks for cluster mode
-  if (split_k > 1 && !workspace && split_k != 2 && split_k != 4 && split_k != 8) return -6;
+  if (split_k > 1 && !workspace && split_k != 2 && split_k != 4 && split_k != 8 && split_k != 12)
+    return -6;
   if (split_k > 1 && workspace && tiles > kMaxTiles) return -6;
   CUtensorMap mw, mx;
   if (!make_map(&mw, w, N, K, K, BM) || !make_map(&mx, x, M, K, ldx, bn)) return -6;

@@ -26,7 +26,8 @@ def test_product_and_bias(M, N, K, bias):
     w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
     b = torch.randn(N, generator=g).to(DEV) if bias else None
     want = _ref(x, w, b)
-    for split_k, ws in ((None, False), (1, False), (2, False), (4, False), (8, False), (3, True)):
+    for split_k, ws in ((None, False), (1, False), (2, False), (4, False), (8, False), (12, False),
+                        (3, True)):
         got = gemm_bf16.gemm(x, w, b, torch.bfloat16, split_k=split_k, through_workspace=ws)
         assert got is not None, (split_k, ws)
         torch.testing.assert_close(got.double(), want, atol=2e-2, rtol=1e-2)
