@@ -271,19 +271,20 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
     l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
     l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
   }
-  float* so = reinterpret_cast<float*>(smem_raw);               // [4][16][HD]
-  float* sm = so + 4 * 16 * HD;                                 // [4][16]
+  // (rows 8 floats apart in banks: the 8-byte stores of a half-warp then hit every bank once)
+  constexpr int SOP = HD + 8;
+  float* so = reinterpret_cast<float*>(smem_raw);               // [4][16][SOP]
+  float* sm = so + 4 * 16 * SOP;                                // [4][16]
   float* sl = sm + 4 * 16;                                      // [4][16]
   float* cpart = sl + 4 * 16;                                   // [16][HD]: the CTA's partial
   float* cpart_m = cpart + 16 * HD;                             // [16]
   float* cpart_l = cpart_m + 16;                                // [16]
+  float* ww = cpart_l + 16;                                     // [4][16]: a warp's weight in a row
 #pragma unroll
   for (int n = 0; n < HD / 8; ++n) {
-    float* base = so + (warp * 16) * HD + n * 8 + 2 * t;
-    base[g * HD] = o[n][0];
-    base[g * HD + 1] = o[n][1];
-    base[(g + 8) * HD] = o[n][2];
-    base[(g + 8) * HD + 1] = o[n][3];
+    float* base = so + (warp * 16) * SOP + n * 8 + 2 * t;
+    *reinterpret_cast<float2*>(base + g * SOP) = make_float2(o[n][0], o[n][1]);
+    *reinterpret_cast<float2*>(base + (g + 8) * SOP) = make_float2(o[n][2], o[n][3]);
   }
   if (t == 0) {
     sm[warp * 16 + g] = m[0];
@@ -292,17 +293,24 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
     sl[warp * 16 + g + 8] = l[1];
   }
   __syncthreads();
+  if (threadIdx.x < 64) {
+    const int r = threadIdx.x & 15;
+    const float mm = fmaxf(fmaxf(sm[r], sm[16 + r]), fmaxf(sm[32 + r], sm[48 + r]));
+    ww[threadIdx.x] = mm == -INFINITY ? 0.f : exp2f(sm[threadIdx.x] - mm);
+  }
+  __syncthreads();
   for (int i = threadIdx.x; i < nrows * HD; i += NTHREADS) {
     const int r = i / HD, d = i - r * HD;
-    float mm = -INFINITY;
+    float acc = 0.f;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, sm[w * 16 + r]);
-    float acc = 0.f, lsum = 0.f;
+    for (int w = 0; w < 4; ++w) acc += ww[w * 16 + r] * so[(w * 16 + r) * SOP + d];
+    float mm = -INFINITY, lsum = 0.f;
+    if (d == 0 || splits == 1) {
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float wgt = mm == -INFINITY ? 0.f : exp2f(sm[w * 16 + r] - mm);
-      acc += wgt * so[(w * 16 + r) * HD + d];
-      lsum += wgt * sl[w * 16 + r];
+      for (int w = 0; w < 4; ++w) {
+        mm = fmaxf(mm, sm[w * 16 + r]);
+        lsum += ww[w * 16 + r] * sl[w * 16 + r];
+      }
     }
     const int head = h0 + r;
     if (splits == 1) {
@@ -621,7 +629,7 @@ static int attn_decode_impl(const void* q, int q_row_stride, const void* kpages,
   auto st = (cudaStream_t)stream;
   const int G = nh / nkv, chunks = (G + 15) / 16;
   const size_t tiles = (size_t)2 * DEC_STAGES * KT * ROW * sizeof(bf16);
-  const size_t merge = (size_t)(5 * 16 * HD + 2 * 4 * 16 + 32 + 256 + 16) * sizeof(float);
+  const size_t merge = (size_t)(4 * 16 * (HD + 8) + 16 * HD + 2 * 4 * 16 + 32 + 256 + 16) * sizeof(float);
   const size_t work = ((tiles > merge ? tiles : merge) + 15) / 16 * 16;
   const int tbl_cap = table_stride < kMaxTableCopy ? table_stride : kMaxTableCopy;
   const size_t q_tile = (size_t)18 * HD * sizeof(bf16);        // fused mode: rotated q, new k and v
