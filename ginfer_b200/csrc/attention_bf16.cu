@@ -18,6 +18,7 @@
 // flash_gqa_varlen_kernel.cu:169-172,220-257); P is rounded to bf16 for the P*V product.
 // Visibility: the query at position p sees key c iff c <= p and (window == 0 or p - c < window).
 #include "attention_mma.cuh"
+#include "tc_common.cuh"
 
 namespace gf {
 
@@ -40,9 +41,10 @@ template <int MAXC>
 __device__ __forceinline__ void cluster_merge(float* cpart, float* cpart_m, float* cpart_l,
                                               float* cw, float* cinv, bf16* __restrict__ out,
                                               int nrows, int splits, int split, int row, int nh,
-                                              int h0) {
+                                              int h0, bool active = true) {
   // Loads from the peers are issued eight at a time without branches (the peer index is
   // clamped, a clamped load's weight is zero); the additions stay in split order.
+  // (`active` false: a thread beyond the NTHREADS that work here; it only joins the barrier)
   if (threadIdx.x < nrows) {
     const int r = threadIdx.x;
     float mp[MAXC], lp[MAXC];
@@ -68,7 +70,7 @@ __device__ __forceinline__ void cluster_merge(float* cpart, float* cpart_m, floa
   __syncthreads();
   const int total = nrows * HD, share = (total + splits - 1) / splits;
   const int i0 = split * share, i1 = min(total, i0 + share);
-  for (int i = i0 + threadIdx.x; i < i1; i += NTHREADS) {
+  for (int i = i0 + threadIdx.x; i < i1 && active; i += NTHREADS) {
     const int r = i / HD, d = i - r * HD;
     float v[MAXC];
 #pragma unroll
@@ -394,6 +396,385 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __r
   }
 }
 
+#if GF_HEAD_DIM % 64 == 0
+// ================================================================== decode, tiles by TMA
+// The same split-KV decode for head sizes that are a multiple of 64 and page sizes that divide (or
+// are a multiple of) the 64-key tile, built for bandwidth: at many requests or long contexts the
+// kernel above spends its time on instructions (about 750 per warp and 16 keys: 16-byte copies
+// with their page look-ups, and tensor-core tiles that are 16 query heads wide although a group
+// has at most 8).  Here
+//  * K and V tiles come by TMA, one box per page and 64-channel half, issued by the lanes of
+//    a fifth warp that does nothing else (issuing a tile's 16 boxes takes longer than the
+//    arithmetic on the tile), into 128-byte-swizzled rows (no padding: 32 KB a stage at head
+//    size 128); a page past the request's keys is loaded from a row outside the tensor, which
+//    TMA fills with zeros;
+//  * the roles in the tensor-core tiles are swapped: keys (or channels) are the 16 rows and the
+//    group's query heads the 8 columns.  S^T = K Q^T takes HD/16 instructions per 16 keys and
+//    O^T += V^T P^T another HD/16 (half of what 16-row head tiles take), P^T reaches its operand
+//    layout by two movmatrix transposes, and the accumulator is HD/4 registers instead of HD/2.
+// Groups of more than 8 query heads take several CTAs (chunks of 8).  The splits merge inside a
+// thread-block cluster as above.  Arithmetic is the same (fp32 scores, maxima, sums, accumulator).
+constexpr int HALVES = HD / 64;
+constexpr int TMAX_STAGES = 6;                         // ring depth: 2 .. 6, chosen per launch
+constexpr uint32_t HALF_BYTES = KT * 128;                // [64 keys][64 channels] of bf16
+constexpr uint32_t TILE_BYTES = HALVES * HALF_BYTES;     // K (or V) of a stage
+constexpr uint32_t STAGE_BYTES = 2 * TILE_BYTES;
+constexpr int kMaxTableCopyTma = 2048;
+
+__device__ __forceinline__ uint32_t movmatrix_t(uint32_t v) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(v));
+  return d;
+}
+// byte offset, inside a K or V tile, of the 8 channels from `ch` (a multiple of 8) of key row `key`
+__device__ __forceinline__ uint32_t swz(int key, int ch) {
+  return (uint32_t)(ch >> 6) * HALF_BYTES + (uint32_t)key * 128u +
+         (uint32_t)((((ch >> 3) & 7) ^ (key & 7)) << 4);
+}
+
+constexpr int TMA_THREADS = NTHREADS + 32;               // four consumer warps and the loader
+__device__ __forceinline__ void consumer_sync() {        // the four consumer warps only
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+
+__global__ void __launch_bounds__(TMA_THREADS)
+attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap,
+                       const __grid_constant__ CUtensorMap vmap, const bf16* __restrict__ q,
+                       int q_row_stride, bf16* __restrict__ kpages, bf16* __restrict__ vpages,
+                       const int* __restrict__ block_table, int table_stride,
+                       const int* __restrict__ cu_seqlens_q, const int* __restrict__ positions,
+                       bf16* __restrict__ out, int nh, int nkv, int page_size, int window,
+                       float scale_log2, int splits, int oob_row, int tbl_cap, int nst,
+                       int* err, const RopeArgs rope) {
+  // No static shared memory in this kernel: the dynamic part then starts at the aligned base,
+  // which the swizzled tiles need (checked below: a misaligned base ends the CTA with code 5).
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* ring = smem_raw;                               // [nst][K tile | V tile]
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw + (size_t)nst * STAGE_BYTES);
+  uint64_t* empty = full + TMAX_STAGES;
+  int* stbl = reinterpret_cast<int*>(full + 2 * TMAX_STAGES);
+  bf16* qs = reinterpret_cast<bf16*>(stbl + tbl_cap);           // [8][HD] rotated q, then new k, v
+  bf16* knew = qs + 8 * HD;
+  bf16* vnew = knew + HD;
+  const int split = blockIdx.x, b = blockIdx.z;
+  const int G = nh / nkv;
+  const int chunks = (G + 7) / 8;
+  const int kvh = blockIdx.y / chunks, chunk = blockIdx.y - kvh * chunks;
+  const int h0 = kvh * G + chunk * 8;                           // first query head of this CTA
+  const int nrows = min(8, G - chunk * 8);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const bool consumer = warp < 4;
+  pdl_trigger();
+  if (smem_u32(smem_raw) & 1023u) {                             // the same in every CTA
+    if (threadIdx.x == 0 && err) atomicExch(err, 5);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < nst; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 4);                                  // one arrival per consumer warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&kmap) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&vmap) : "memory");
+  }
+  const bool late_wait = rope.fused && rope.write_kv;           // see the kernel above
+  if (!late_wait) pdl_wait();
+  const int row = cu_seqlens_q ? cu_seqlens_q[b] : b;
+  const int p = positions[row];
+  const int lo = window > 0 ? max(0, p - window + 1) : 0;
+  const int lo_al = lo / KT * KT;                               // tiles start on tile boundaries
+  const int nkeys = p - lo_al + 1;
+  int per = (nkeys + splits - 1) / splits;
+  per = (per + KT - 1) / KT * KT;
+  const int begin = lo_al + split * per;
+  const int end = min(p + 1, begin + per);
+  const int first = max(begin, lo);                             // first visible key of this split
+  const int ntiles = first < end ? (end - begin + KT - 1) / KT : 0;
+  const int* tbl = block_table + (size_t)b * table_stride;
+  int lp_base = 0;
+  if (ntiles > 0) {
+    const int lp0 = begin / page_size, nlp = (end - 1) / page_size - lp0 + 1;
+    if (nlp <= tbl_cap) {
+      for (int i = threadIdx.x; i < nlp; i += TMA_THREADS) stbl[i] = tbl[lp0 + i];
+      tbl = stbl;
+      lp_base = lp0;
+    }
+  }
+  __syncthreads();                                              // barriers and table are set up
+
+  float o[HD / 16][4];           // O^T: channels 16 mt + g (and + 8) of heads 2t, 2t + 1
+#pragma unroll
+  for (int mt = 0; mt < HD / 16; ++mt) o[mt][0] = o[mt][1] = o[mt][2] = o[mt][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};      // of heads 2t and 2t + 1
+
+  if (!consumer) {
+    // ---------------------------------------------------------------- the loader warp
+    // A tile is 2 (K, V) x HALVES x boxes TMA boxes of box_rows keys; a lane keeps its boxes over
+    // the tiles (two a lane where there are more than 32).  Tiles past the ring wait until the
+    // four consumer warps have let go of their stage.  It reads only what earlier steps wrote
+    // to the cache, so it does not wait for the kernel in front.
+    const int box_rows = min(page_size, KT), boxes = KT / box_rows;
+    const int ops = 2 * HALVES * boxes;
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
+    int key_off[2];                                             // first key of the box in its tile
+    uint32_t dst_off[2];
+    int x_coord[2];
+    bool is_v[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int op = min(lane + 32 * u, ops - 1);
+      const int v = op / (HALVES * boxes), rem = op - v * HALVES * boxes;
+      const int h = rem / boxes, bx = rem - h * boxes;
+      is_v[u] = v != 0;
+      key_off[u] = bx * box_rows;
+      dst_off[u] = (uint32_t)v * TILE_BYTES + (uint32_t)h * HALF_BYTES +
+                   (uint32_t)bx * (uint32_t)box_rows * 128u;
+      x_coord[u] = kvh * HD + h * 64;
+    }
+    int st = 0;
+    uint32_t ph = 0;                                            // of the ring's current round
+    for (int it = 0; it < ntiles; ++it) {
+      const int key0 = begin + it * KT;
+      // (the wait for the round before the first one returns at once on a fresh barrier)
+      if (!mbar_wait(&empty[st], ph ^ 1u, err, 6)) break;
+      if (lane == 0) mbar_expect_tx(&full[st], STAGE_BYTES);
+      __syncwarp();
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        if (lane + 32 * u < ops) {
+          const int c = key0 + key_off[u];
+          int src_row = oob_row;                                // past the tensor: zeros
+          if (c < end && c + box_rows > first) {
+            const int lp = page_shift >= 0 ? c >> page_shift : c / page_size;
+            const int page = tbl[lp - lp_base];
+            if (page >= 0) src_row = page * page_size + (c - lp * page_size);
+          }
+          tma_load_2d(ring + (size_t)st * STAGE_BYTES + dst_off[u], is_v[u] ? &vmap : &kmap,
+                      &full[st], x_coord[u], src_row);
+        }
+      }
+      if (++st == nst) st = 0, ph ^= 1u;
+    }
+  } else {
+    // ---------------------------------------------------------------- the consumer warps
+    if (late_wait) pdl_wait();   // q (and the new k and v) come from the kernel in front
+    // q as the 8-column operand: thread (g, t) holds channels 16 kc + 2t, +1 and + 8, + 9 of head g
+    uint32_t qf[KCH][2];
+    const bf16* qrow = q + (size_t)row * q_row_stride + (size_t)h0 * HD;
+    bool patch = false;          // the last tile of this CTA gets the new token's k and v from here
+    if (rope.fused && ntiles > 0) {
+      const bf16* base = q + (size_t)row * q_row_stride;
+      const int half = rope.rot >> 1, tail = HD - rope.rot;
+      const float* cs = rope.table ? rope.table + (size_t)p * rope.rot : nullptr;
+      for (int i = threadIdx.x; i < nrows * half; i += NTHREADS) {
+        const int r = i / half, j = i - r * half;
+        const float a = __bfloat162float(qrow[r * HD + j]);
+        const float bb = __bfloat162float(qrow[r * HD + j + half]);
+        const float c = cs[j], sn = cs[half + j];
+        qs[r * HD + j] = __float2bfloat16_rn(a * c - bb * sn);
+        qs[r * HD + j + half] = __float2bfloat16_rn(a * sn + bb * c);
+      }
+      for (int i = threadIdx.x; i < nrows * tail; i += NTHREADS) {
+        const int r = i / tail, j = rope.rot + (i - r * tail);
+        qs[r * HD + j] = qrow[r * HD + j];
+      }
+      if (rope.write_kv && p >= begin && p < end) {
+        // this split holds the new token: its k (rotated) and v go into the tile of keys through
+        // shared memory; the CTA of the first head chunk also writes them to the cache slot
+        patch = true;
+        const int lp = p / page_size;
+        const size_t slot = (size_t)block_table[(size_t)b * table_stride + lp] * page_size +
+                            (size_t)(p - lp * page_size);
+        bf16* kd = kpages + slot * ((size_t)nkv * HD) + (size_t)kvh * HD;
+        bf16* vd = vpages + slot * ((size_t)nkv * HD) + (size_t)kvh * HD;
+        const bf16* kn = base + (size_t)(nh + kvh) * HD;
+        const bf16* vn = base + (size_t)(nh + nkv + kvh) * HD;
+        const bool store = chunk == 0;
+        for (int j = threadIdx.x; j < half; j += NTHREADS) {
+          const float a = __bfloat162float(kn[j]), bb = __bfloat162float(kn[j + half]);
+          const float c = cs[j], sn = cs[half + j];
+          const bf16 lo_v = __float2bfloat16_rn(a * c - bb * sn);
+          const bf16 hi_v = __float2bfloat16_rn(a * sn + bb * c);
+          knew[j] = lo_v, knew[j + half] = hi_v;
+          if (store) kd[j] = lo_v, kd[j + half] = hi_v;
+        }
+        for (int j = rope.rot + threadIdx.x; j < HD; j += NTHREADS) {
+          knew[j] = kn[j];
+          if (store) kd[j] = kn[j];
+        }
+        for (int j = threadIdx.x; j < HD; j += NTHREADS) {
+          vnew[j] = vn[j];
+          if (store) vd[j] = vn[j];
+        }
+      }
+      consumer_sync();           // q, and the new k and v, are in shared memory
+      qrow = qs;
+    }
+#pragma unroll
+    for (int kc = 0; kc < KCH; ++kc) {
+      const uint32_t* r0 = reinterpret_cast<const uint32_t*>(
+          qrow + (size_t)min(g, nrows - 1) * HD + kc * 16 + 2 * t);
+      qf[kc][0] = g < nrows ? r0[0] : 0u;
+      qf[kc][1] = g < nrows ? r0[4] : 0u;
+    }
+    const int mi = lane >> 3;
+    int st = 0;
+    uint32_t ph = 0;
+    for (int it = 0; it < ntiles; ++it) {
+      if (!mbar_wait(&full[st], ph, err, 4)) break;
+      unsigned char* kt = ring + (size_t)st * STAGE_BYTES;
+      unsigned char* vt = kt + TILE_BYTES;
+      if (patch && it == ntiles - 1) {
+        const int rp = p - (begin + it * KT);
+        for (int j = threadIdx.x; j < HD; j += NTHREADS) {
+          const uint32_t off = swz(rp, j & ~7) + (uint32_t)(j & 7) * 2u;
+          *reinterpret_cast<bf16*>(kt + off) = knew[j];
+          *reinterpret_cast<bf16*>(vt + off) = vnew[j];
+        }
+        consumer_sync();
+      }
+      const int col0 = begin + it * KT + warp * 16;
+      if (col0 < end && col0 + 16 > first) {
+        float s[4] = {0.f, 0.f, 0.f, 0.f};   // S^T: keys col0 + g (and + 8) of heads 2t, 2t + 1
+        {
+          const int key = warp * 16 + (lane & 15), chsel = (lane >> 4) * 8;
+#pragma unroll
+          for (int kc = 0; kc < KCH; ++kc) {
+            uint32_t a[4];
+            ldsm_x4(a, kt + swz(key, kc * 16 + chsel));
+            mma16816(s, a, qf[kc][0], qf[kc][1]);
+          }
+        }
+        const int ka = col0 + g, kb = ka + 8;
+        const bool va = ka >= first && ka < end, vb = kb >= first && kb < end;
+        s[0] = va ? s[0] * scale_log2 : -INFINITY;
+        s[1] = va ? s[1] * scale_log2 : -INFINITY;
+        s[2] = vb ? s[2] * scale_log2 : -INFINITY;
+        s[3] = vb ? s[3] * scale_log2 : -INFINITY;
+        float mx[2] = {fmaxf(s[0], s[2]), fmaxf(s[1], s[3])};
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 4));
+          mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 8));
+          mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 16));
+        }
+        float corr[2], msub[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const float mnew = fmaxf(m[i], mx[i]);
+          msub[i] = mnew == -INFINITY ? 0.f : mnew;
+          corr[i] = fast_exp2(m[i] - msub[i]);
+          m[i] = mnew;
+        }
+        const float p0 = fast_exp2(s[0] - msub[0]), p1 = fast_exp2(s[1] - msub[1]);
+        const float p2 = fast_exp2(s[2] - msub[0]), p3 = fast_exp2(s[3] - msub[1]);
+        l[0] = l[0] * corr[0] + (p0 + p2);
+        l[1] = l[1] * corr[1] + (p1 + p3);
+        if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
+#pragma unroll
+          for (int mt = 0; mt < HD / 16; ++mt) {
+            o[mt][0] *= corr[0];
+            o[mt][1] *= corr[1];
+            o[mt][2] *= corr[0];
+            o[mt][3] *= corr[1];
+          }
+        }
+        // P^T as the 8-column operand: (keys 2t, 2t + 1 | + 8, + 9) of head g
+        const uint32_t b0 = movmatrix_t(pack_bf16(p0, p1));
+        const uint32_t b1 = movmatrix_t(pack_bf16(p2, p3));
+        const int key = warp * 16 + (mi >> 1) * 8 + (lane & 7), chsel = (mi & 1) * 8;
+#pragma unroll
+        for (int mt = 0; mt < HD / 16; ++mt) {
+          uint32_t a[4];
+          ldsm_x4_t(a, vt + swz(key, mt * 16 + chsel));
+          mma16816(o[mt], a, b0, b1);
+        }
+      }
+      // this warp lets go of the stage
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[st]);
+      if (++st == nst) st = 0, ph ^= 1u;
+    }
+  }
+  __syncthreads();               // the ring is free: the merge buffers lie over it
+
+  // a thread's sums cover its keys only: add up over the lanes that share its heads
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 4);
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 8);
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 16);
+  }
+  constexpr int SOP = HD + 4;    // head rows 4 banks apart: the scalar stores below do not collide
+  float* so = reinterpret_cast<float*>(smem_raw);               // [4][8][SOP]
+  float* sm = so + 4 * 8 * SOP;                                 // [4][8]
+  float* sl = sm + 4 * 8;                                       // [4][8]
+  float* cpart = sl + 4 * 8;                                    // [8][HD]: the CTA's partial
+  float* cpart_m = cpart + 8 * HD;                              // [16]
+  float* cpart_l = cpart_m + 16;                                // [16]
+  float* cw = cpart_l + 16;                                     // [16][16], first [4][8] here
+  float* cinv = cw + 256;                                       // [16]
+  if (consumer) {
+#pragma unroll
+    for (int mt = 0; mt < HD / 16; ++mt) {
+      float* base = so + (warp * 8 + 2 * t) * SOP + mt * 16 + g;
+      base[0] = o[mt][0];
+      base[SOP] = o[mt][1];
+      base[8] = o[mt][2];
+      base[SOP + 8] = o[mt][3];
+    }
+    if (g == 0) {
+      sm[warp * 8 + 2 * t] = m[0];
+      sm[warp * 8 + 2 * t + 1] = m[1];
+      sl[warp * 8 + 2 * t] = l[0];
+      sl[warp * 8 + 2 * t + 1] = l[1];
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int r = threadIdx.x & 7;
+    const float mm = fmaxf(fmaxf(sm[r], sm[8 + r]), fmaxf(sm[16 + r], sm[24 + r]));
+    cw[threadIdx.x] = mm == -INFINITY ? 0.f : exp2f(sm[threadIdx.x] - mm);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < nrows * HD && consumer; i += NTHREADS) {
+    const int r = i / HD, d = i - r * HD;
+    float acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) acc += cw[w * 8 + r] * so[(w * 8 + r) * SOP + d];
+    float mm = -INFINITY, lsum = 0.f;
+    if (d == 0 || splits == 1) {
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        mm = fmaxf(mm, sm[w * 8 + r]);
+        lsum += cw[w * 8 + r] * sl[w * 8 + r];
+      }
+    }
+    if (splits == 1) {
+      out[((size_t)row * nh + h0 + r) * HD + d] =
+          __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+    } else {
+      cpart[i] = acc;
+      if (d == 0) {
+        cpart_m[r] = mm;
+        cpart_l[r] = lsum;
+      }
+    }
+  }
+  if (splits > 1) {
+    cluster_sync_all();          // also orders the weights above before they are overwritten
+    if (splits <= 8)
+      cluster_merge<8>(cpart, cpart_m, cpart_l, cw, cinv, out, nrows, splits, split, row, nh, h0,
+                       consumer);
+    else
+      cluster_merge<16>(cpart, cpart_m, cpart_l, cw, cinv, out, nrows, splits, split, row, nh, h0,
+                        consumer);
+    cluster_sync_all();          // nobody leaves while a peer reads it
+  }
+}
+#endif  // GF_HEAD_DIM % 64 == 0
+
 // grid (nh, B), HD threads... one thread per output channel (HD <= 256).
 __global__ void attn_decode_merge_kernel(const float* __restrict__ po,
                                          const float* __restrict__ pml,
@@ -670,6 +1051,64 @@ static int attn_decode_impl(const void* q, int q_row_stride, const void* kpages,
   if (rc || splits == 1 || fused) return rc;
   return launch_kernel(attn_decode_merge_kernel, dim3(nh, B), dim3(HD), 0, st, (const float*)po,
                        (const float*)pml, cu_seqlens_q, (bf16*)out, nh, splits);
+}
+
+// The TMA kernel where it serves the case: head sizes that are a multiple of 64, page sizes that
+// are a multiple of 8 and divide (or are a multiple of) the 64-key tile, 1 split or a cluster of
+// 2, 4, 8 or 16.  -6: not served (the caller takes gf_attn_decode / gf_attn_decode_rope).
+// `stages`: depth of the ring of tiles (2 .. 6, cut to what shared memory holds; 3 lets two CTAs
+// share an SM).  `err` receives 4 or 6 if a wait for a tile or for a free stage ran out.
+GF_EXPORT int gf_attn_decode_tma(const void* q, int q_row_stride, void* kpages, void* vpages,
+                                 int num_pages, const int* block_table, int table_stride,
+                                 const int* cu_seqlens_q, const int* positions, void* out, int B,
+                                 int nh, int nkv, int page_size, int window, float scale,
+                                 int splits, int stages, const float* rope_table, int rot,
+                                 int fused, int write_kv, int* err, void* stream) {
+#if GF_HEAD_DIM % 64 == 0
+  if (B <= 0) return 0;
+  if (nh % nkv || splits < 1) return -3;
+  if (fused && (rot < 0 || rot > HD || rot % 2 || (!rope_table && rot))) return -3;
+  if (splits != 1 && splits != 2 && splits != 4 && splits != 8 && splits != 16) return -6;
+  if (page_size % 8 || (KT % page_size && page_size % KT) || num_pages <= 0) return -6;
+  if (((uintptr_t)q & 3) || q_row_stride % 2 || ((uintptr_t)kpages & 15) ||
+      ((uintptr_t)vpages & 15))
+    return -6;
+  const long long slots = (long long)num_pages * page_size;
+  if (slots >= (1ll << 31) - KT) return -6;
+  const int box_rows = page_size < KT ? page_size : KT;
+  CUtensorMap mk, mv;
+  if (!make_map(&mk, kpages, (int)slots, nkv * HD, nkv * HD, box_rows)) return -6;
+  if (!make_map(&mv, vpages, (int)slots, nkv * HD, nkv * HD, box_rows)) return -6;
+  auto st = (cudaStream_t)stream;
+  const int G = nh / nkv, chunks = (G + 7) / 8;
+  const int tbl_cap = table_stride < kMaxTableCopyTma ? table_stride : kMaxTableCopyTma;
+  const size_t small = 2 * TMAX_STAGES * sizeof(uint64_t) + (size_t)10 * HD * sizeof(bf16);
+  const size_t room = (size_t)227 * 1024 - small - kMaxTableCopyTma * sizeof(int);
+  const int most = (int)(room / STAGE_BYTES) < TMAX_STAGES ? (int)(room / STAGE_BYTES) : TMAX_STAGES;
+  const int nst = stages < 2 ? 2 : stages > most ? most : stages;
+  const size_t smem = (size_t)nst * STAGE_BYTES + small + (size_t)tbl_cap * sizeof(int);
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(
+        attn_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        (int)((size_t)most * STAGE_BYTES + small + kMaxTableCopyTma * sizeof(int)));
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_decode_tma_kernel,
+                               cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) return (int)e;
+    attr_done = true;
+  }
+  const RopeArgs rope{fused ? rope_table : nullptr, fused ? rot : 0, fused ? 1 : 0,
+                      fused && write_kv ? 1 : 0};
+  dim3 grid(splits, nkv * chunks, B);
+  return launch_kernel_cluster_dims(attn_decode_tma_kernel, grid, dim3(TMA_THREADS), smem, st, splits,
+                                    true, mk, mv, (const bf16*)q, q_row_stride, (bf16*)kpages,
+                                    (bf16*)vpages, block_table, table_stride, cu_seqlens_q,
+                                    positions, (bf16*)out, nh, nkv, page_size, window,
+                                    scale * LOG2E, splits, (int)slots, tbl_cap, nst, err, rope);
+#else
+  return -6;
+#endif
 }
 
 GF_EXPORT int gf_attn_decode(const void* q, int q_row_stride, const void* kpages,

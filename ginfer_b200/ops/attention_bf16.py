@@ -31,6 +31,12 @@ def decode_splits(batch: int, nh: int, nkv: int, max_keys: int) -> int:
     return splits
 
 
+def tma_serves(hd: int, page_size: int, splits: int) -> bool:
+    """Whether decode attention takes the kernel that loads its tiles by TMA."""
+    return (hd % 64 == 0 and page_size % 8 == 0 and splits in (1, 2, 4, 8, 16)
+            and (KEY_TILE % page_size == 0 or page_size % KEY_TILE == 0))
+
+
 def _scratch_for(nbytes: int, device) -> torch.Tensor:
     key = (device.index if device.index is not None else torch.cuda.current_device())
     buf = _scratch.get(key)
@@ -41,11 +47,16 @@ def _scratch_for(nbytes: int, device) -> torch.Tensor:
 
 
 def decode(qkv, pages, block_table, cu_seqlens_q, positions, B, nh, nkv, hd, scale, window,
-           page_size, splits, out=None, scratch=None, through_scratch=False, rope=None):
+           page_size, splits, out=None, scratch=None, through_scratch=False, rope=None,
+           use_tma=True, stages=3):
     """Split-KV decode attention.  ``splits`` of 2, 4, 8 or 16 merge inside a thread-block cluster
     (no scratch memory) unless ``through_scratch``; any other number goes through scratch.
     ``rope = (table or None, rotary_dim, write)``: q and k arrive unrotated and the kernel
-    rotates them itself and (``write``) puts the new k and v into their cache slot."""
+    rotates them itself and (``write``) puts the new k and v into their cache slot.
+    ``use_tma``: take the kernel that loads its tiles by TMA where it serves the case (head sizes
+    64, 128, 192 and 256, page sizes 8, 16, 32, 64 and multiples of 64, cluster merge), with a
+    ring of ``stages`` tiles (2 .. 6; three let two CTAs share an SM, and with clusters of 8 only
+    that fits a grid of 128 CTAs in one wave: four and six stages measured half as fast)."""
     from . import _fn, _ok, _p, _stream
     defines = (f"GF_HEAD_DIM={hd}",)
     if out is None:
@@ -58,6 +69,22 @@ def decode(qkv, pages, block_table, cu_seqlens_q, positions, B, nh, nkv, hd, sca
             scratch = torch.empty(nbytes // 4, dtype=torch.float32, device=qkv.device)
         else:
             scratch = _scratch_for(nbytes, qkv.device)
+    if use_tma and hd % 64 == 0 and scratch is None and not through_scratch:
+        from .gemm_bf16 import error_word
+        table, rot, write = rope if rope is not None else (None, 0, False)
+        f = _fn("attention_bf16", "gf_attn_decode_tma",
+                [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
+                 c_int, c_int, c_int, c_void_p, c_void_p], defines, kernels=1)
+        rc = f(_p(qkv), qkv.stride(0), _p(pages[0]), _p(pages[1]), pages.shape[1],
+               _p(block_table), block_table.stride(0), _p(cu_seqlens_q), _p(positions), _p(out), B,
+               nh, nkv, page_size, int(window), float(scale), int(splits),
+               int(stages), _p(table),
+               int(rot) if table is not None else 0, 1 if rope is not None else 0,
+               int(bool(write)), _p(error_word(qkv.device)), _stream())
+        if rc != -6:
+            _ok(rc, "attn_decode_tma")
+            return out
     if rope is not None:
         table, rot, write = rope
         f = _fn("attention_bf16", "gf_attn_decode_rope",

@@ -293,6 +293,34 @@ def test_attention_bf16_decode(case, splits):
     torch.testing.assert_close(out.double().cpu(), want, atol=1e-2, rtol=2e-2)
 
 
+DEC_TMA_CASES = [   # what the kernel that loads by TMA serves: page sizes and head sizes
+    ([300, 64, 1, 65, 129], 8, 1, 128, 8, 0),
+    ([1000, 130, 63], 14, 2, 64, 32, 0),
+    ([700, 257, 64], 16, 2, 128, 64, 300),
+    ([900, 5], 4, 4, 256, 128, 0),
+    ([1500, 700], 6, 3, 128, 16, 130),           # a window that starts inside a tile
+    ([4100], 18, 2, 64, 16, 0),                   # 9 query heads per kv head: two chunks of 8
+]
+
+
+@pytest.mark.parametrize("case", DEC_TMA_CASES)
+@pytest.mark.parametrize("splits", [1, 2, 4, 8, 16])
+def test_attention_bf16_decode_with_tiles_by_tma(case, splits):
+    """The decode kernel that loads by TMA against the oracle and against the kernel that gathers
+    with 16-byte copies (the same arithmetic in another tile layout: equal within rounding)."""
+    from ginfer_b200.ops import attention_bf16, gemm_bf16
+    lens, nh, nkv, hd, P, window = case
+    dev, want, scale = _paged_case(lens, [1] * len(lens), nh, nkv, hd, P, window, torch.bfloat16)
+    args = (_qkv(dev, nh, nkv, hd), dev["pages"], dev["table"], dev["cu"], dev["positions"],
+            len(lens), nh, nkv, hd, scale, window, P, splits)
+    assert attention_bf16.tma_serves(hd, P, splits)
+    out = attention_bf16.decode(*args)
+    gemm_bf16.check_errors()
+    torch.testing.assert_close(out.double().cpu(), want, atol=1e-2, rtol=2e-2)
+    other = attention_bf16.decode(*args, use_tma=False)
+    torch.testing.assert_close(out.float(), other.float(), atol=1e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("case", DEC_CASES)
 @pytest.mark.parametrize("splits", [1, 4, 8, -3])
 @pytest.mark.parametrize("rot_frac", [1.0, 0.5])
