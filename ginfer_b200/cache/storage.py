@@ -45,8 +45,10 @@ class CacheStorage:
         self.groups = groups
         self.page_size = page_size
         self.num_pages = list(num_pages)
-        self.kv = [torch.zeros((len(g.cache_ids), 2, n, page_size, g.num_kv_heads, g.head_dim),
-                               dtype=dtype, device=device)
+        # one page more than the manager hands out: page `n` of a group belongs to no request; the
+        # rows that pad a step up to a CUDA graph's batch size write and read there
+        self.kv = [torch.zeros((len(g.cache_ids), 2, n + 1, page_size, g.num_kv_heads,
+                                g.head_dim), dtype=dtype, device=device)
                    for g, n in zip(groups, num_pages)]
         self._where = {cid: (gi, i) for gi, g in enumerate(groups)
                        for i, cid in enumerate(g.cache_ids)}

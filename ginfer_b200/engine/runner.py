@@ -246,6 +246,45 @@ class ModelRunner:
             return None
         return bind
 
+    @staticmethod
+    def graph_batch(B: int) -> int:
+        """The batch size of the CUDA graph that serves a decode step of ``B`` requests: exact up
+        to 8, then the next multiple of 8 (of 16 above 64).  The rows in between are padding."""
+        if B <= 8:
+            return B
+        step = 8 if B <= 64 else 16
+        return -(-B // step) * step
+
+    def _pad_decode(self, arrays, facts, Bp: int):
+        """A decode step of B requests as one of ``Bp``: the added rows are requests of one token
+        at position 0 whose page is the scratch page of each group (no request owns it)."""
+        B = facts["B"]
+        extra = Bp - B
+        a = dict(arrays)
+
+        def app(key, values):
+            a[key] = np.concatenate([arrays[key], np.asarray(values, dtype=arrays[key].dtype)])
+        app("token_ids", [0] * extra)
+        app("positions", [0] * extra)
+        app("seq_of_token", range(B, Bp))
+        app("cu_seqlens_q", range(B + 1, Bp + 1))
+        app("kv_lens", [1] * extra)
+        app("slot_ids", [0] * extra)
+        app("logit_rows", range(B, Bp))
+        for g in range(self.cache.num_groups):
+            scratch = self.storage.num_pages[g]
+            app(f"slot_mapping{g}", [scratch * self.page_size] * extra)
+            t = arrays[f"block_table{g}"]
+            a[f"block_table{g}"] = np.concatenate(
+                [t, np.full((extra, t.shape[1]), scratch, dtype=t.dtype)])
+        if "fb_rows" in a:                             # stays last
+            a["fb_rows"], a["fb_picks"] = a.pop("fb_rows"), a.pop("fb_picks")
+        f = dict(facts, B=Bp, T=Bp,
+                 q_lens=np.concatenate([facts["q_lens"], np.ones(extra, dtype=np.int64)]),
+                 q_starts=np.concatenate([facts["q_starts"], np.zeros(extra, dtype=np.int64)]),
+                 slot_ids=np.concatenate([facts["slot_ids"], np.zeros(extra, dtype=np.int64)]))
+        return a, f
+
     def _graph_key(self, entries, facts):
         """Decode steps in which every request wants its token's logits replay a CUDA graph; so
         do steps with prompt portions whose shape has come before (see PORTION_GRAPH_*)."""
@@ -254,7 +293,7 @@ class ModelRunner:
         if facts["max_q_len"] == 1:
             if any(len(e.want) != 1 for e in entries):
                 return None
-            return (facts["B"], facts["width"])
+            return (self.graph_batch(facts["B"]), facts["width"])
         if facts["B"] > PORTION_GRAPH_MAX_SEQS or facts["T"] < PORTION_GRAPH_MIN_TOKENS:
             return None
         key = ("portions", tuple(int(n) for n in facts["q_lens"]), facts["width"],
@@ -314,14 +353,17 @@ class ModelRunner:
         with torch.cuda.device(self.device):
             key = self._graph_key(entries, facts)
             if key is not None:
+                padded, pfacts = arrays, facts
+                if facts["max_q_len"] == 1 and key[0] != facts["B"]:
+                    padded, pfacts = self._pad_decode(arrays, facts, key[0])
                 g = self._graphs.get(key)
                 if g is None:
-                    g = self._graphs[key] = self._capture(key, arrays, facts)
-                dev = self.upload(arrays, into=g.ints)
+                    g = self._graphs[key] = self._capture(key, padded, pfacts)
+                dev = self.upload(padded, into=g.ints)
                 self._feed_back(dev, feedback)
                 g.graph.replay()
                 self.graph_launches += g.launches
-                logits = g.logits
+                logits = g.logits[:len(facts["slot_ids"])] if padded is not arrays else g.logits
             else:
                 dev = self.upload(arrays)
                 self._feed_back(dev, feedback)

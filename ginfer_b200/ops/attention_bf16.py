@@ -108,9 +108,10 @@ def decode(qkv, pages, block_table, cu_seqlens_q, positions, B, nh, nkv, hd, sca
 
 
 def prefill(qkv, pages, block_table, cu_seqlens_q, kv_lens, B, max_q_len, nh, nkv, hd, scale,
-            window, page_size):
+            window, page_size, out=None):
     from . import _fn, _ok, _p, _stream
-    out = torch.empty((qkv.shape[0], nh * hd), dtype=torch.bfloat16, device=qkv.device)
+    if out is None:
+        out = torch.empty((qkv.shape[0], nh * hd), dtype=torch.bfloat16, device=qkv.device)
     f = _fn("attention_bf16", "gf_attn_prefill",
             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
@@ -126,7 +127,7 @@ def tc_supports(hd: int, page_size: int) -> bool:
 
 
 def prefill_tc(qkv, pages, block_table, cu_seqlens_q, kv_lens, B, max_q_len, nh, nkv, hd, scale,
-               window, page_size, trace=None):
+               window, page_size, trace=None, out=None):
     """Prefill attention on tcgen05 (``csrc/attention_tc.cu``); ``None`` if it cannot serve the
     shapes.  ``trace``: an int64 tensor of ``768 + 4 * CTAs`` slots that receives clock stamps of
     the first CTA's phases and, behind them, every CTA's (start ns, end ns, SM) (for tuning)."""
@@ -137,7 +138,8 @@ def prefill_tc(qkv, pages, block_table, cu_seqlens_q, kv_lens, B, max_q_len, nh,
     if not tc_supports(hd, page_size) or qkv.stride(0) % 8:
         return None
     T = qkv.shape[0]
-    out = torch.empty((T, nh * hd), dtype=torch.bfloat16, device=qkv.device)
+    if out is None:
+        out = torch.empty((T, nh * hd), dtype=torch.bfloat16, device=qkv.device)
     f = _fn("attention_tc", "gf_attn_prefill_tc",
             [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
@@ -172,10 +174,25 @@ def try_run(qkv, pages, block_table, ctx, nh, nkv, hd, scale, window, page_size,
         return decode(qkv, pages, block_table, ctx.cu_seqlens_q, ctx.positions, ctx.num_seqs, nh,
                       nkv, hd, scale, window, page_size, splits, rope=rope)
     assert rope is None, "only decode steps rotate inside the attention kernel"
-    if ctx.max_q_len >= TC_MIN_QUERY_ROWS:
-        out = prefill_tc(qkv, pages, block_table, ctx.cu_seqlens_q, ctx.kv_lens, ctx.num_seqs,
-                         ctx.max_q_len, nh, nkv, hd, scale, window, page_size)
-        if out is not None:
-            return out
-    return prefill(qkv, pages, block_table, ctx.cu_seqlens_q, ctx.kv_lens, ctx.num_seqs,
-                   ctx.max_q_len, nh, nkv, hd, scale, window, page_size)
+    # A mixed step whose single tokens come first (as the scheduler orders them): those requests
+    # go to the decode kernel, the portions behind them to a prefill kernel.  (A single token as a
+    # portion of its own costs a whole tile of query rows per head.)
+    B, nd = ctx.num_seqs, 0
+    q_lens = ctx.q_lens_host
+    while nd < B and nd < len(q_lens) and q_lens[nd] == 1:
+        nd += 1
+    out, cu, kv_lens, table, max_q = None, ctx.cu_seqlens_q, ctx.kv_lens, block_table, ctx.max_q_len
+    if 0 < nd < B and len(q_lens) == B:
+        keys = ctx.max_kv_len if window <= 0 else min(window, ctx.max_kv_len)
+        out = torch.empty((qkv.shape[0], nh * hd), dtype=torch.bfloat16, device=qkv.device)
+        decode(qkv, pages, block_table[:nd], None, ctx.positions, nd, nh, nkv, hd, scale, window,
+               page_size, decode_splits(nd, nh, nkv, keys), out=out)
+        cu, kv_lens, table, B = cu[nd:], kv_lens[nd:], block_table[nd:], B - nd
+        max_q = max(q_lens[nd:])
+    if max_q >= TC_MIN_QUERY_ROWS:
+        res = prefill_tc(qkv, pages, table, cu, kv_lens, B, max_q, nh, nkv, hd, scale, window,
+                         page_size, out=out)
+        if res is not None:
+            return res
+    return prefill(qkv, pages, table, cu, kv_lens, B, max_q, nh, nkv, hd, scale, window, page_size,
+                   out=out)

@@ -58,9 +58,11 @@ def cut_portions(requests, sizes=(7, 2, 13, 3, 16, 2, 5, 31, 2, 1, 17)):
     return steps
 
 
-def cut_mixed(requests, max_live: int = 4, seed: int = 0, decode_tail: int = 12):
+def cut_mixed(requests, max_live: int = 4, seed: int = 0, decode_tail: int = 12,
+              singles_first: bool = False):
     """Up to ``max_live`` live requests; each step holds portions of some beside single tokens of
-    others; a request is sometimes left out of a step.  Returns ``(steps, max_tokens)`` where
+    others; a request is sometimes left out of a step.  ``singles_first``: a step's single tokens
+    come before its portions (the order in which a scheduler that decodes first sends them).  Returns ``(steps, max_tokens)`` where
     ``max_tokens`` is the most the live requests hold at any time, each rounded up to 64."""
     rng = random.Random(seed)
     waiting = list(requests.items())
@@ -89,6 +91,8 @@ def cut_mixed(requests, max_live: int = 4, seed: int = 0, decode_tail: int = 12)
             if live[rid] == len(requests[rid]):
                 ended.append(rid)
                 del live[rid]
+        if singles_first:
+            entries.sort(key=lambda e: len(e["tokens"]) != 1)
         if entries:
             steps.append({"step": len(steps), "entries": entries, "end": ended})
     return steps, peak

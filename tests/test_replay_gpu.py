@@ -42,7 +42,7 @@ def _runner(model_dir, dtype, page, max_tokens, eager=True):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B", "C"])
-@pytest.mark.parametrize("cut", ["whole", "tail", "portions", "mixed"])
+@pytest.mark.parametrize("cut", ["whole", "tail", "portions", "mixed", "mixed_singles_first"])
 def test_cuts_agree_with_plain(folders, name, dtype, cut):
     model_dir = folders[(name, _storage(dtype))]
     reqs = _requests(name)
@@ -53,7 +53,7 @@ def test_cuts_agree_with_plain(folders, name, dtype, cut):
     elif cut == "portions":
         steps = replay.cut_portions(reqs)
     else:
-        steps, _ = replay.cut_mixed(reqs, seed=7)
+        steps, _ = replay.cut_mixed(reqs, seed=7, singles_first=cut.endswith("first"))
     max_tokens = replay.peak_tokens(steps)          # so few pages that they are used again
     runner = _runner(model_dir, dtype, PAGE[name], max_tokens)
     rows = replay.run_in_process(runner, steps)
@@ -157,3 +157,48 @@ def test_prompt_portions_of_a_shape_that_comes_again_are_replayed_from_graphs(fo
     replay.compare(rows, replay.plain_logits(model_dir, reqs, "bfloat16"), "bfloat16", reqs)
     assert runner.graph_launches > before, "no step was replayed from a graph"
     assert any(isinstance(k[0], str) for k in runner._graphs)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_decode_batches_are_padded_to_the_batch_size_of_a_graph(folders, name, dtype):
+    """Eleven requests decode side by side (the graph is one of 16: five rows of padding that
+    write and read the scratch page), then ten and nine as requests end, with so few pages that
+    freed ones are taken again by the request that joins late.  All agree with plain."""
+    from ginfer_b200.engine import ModelRunner
+    from ginfer_b200.engine.loading import load_model
+    model_dir = folders[(name, _storage(dtype))]
+    v = CONFIGS[name]["vocab_size"]
+    lens = [30, 41, 52, 33, 44, 55, 36, 47, 58, 39, 50, 45]
+    reqs = {f"p{i}": prompt(n, v, seed=70 + i) for i, n in enumerate(lens)}
+    ids = list(reqs)
+    first, late = ids[:11], ids[11]
+    steps = [{"step": 0, "end": [], "entries": [
+        {"id": r, "tokens": reqs[r][:20], "want": list(range(20))} for r in first]}]
+    at = {r: 20 for r in first}
+    live = list(first)
+    while live:
+        ent = [{"id": r, "tokens": [reqs[r][at[r]]], "want": [0]} for r in live]
+        for r in live:
+            at[r] += 1
+        done = [r for r in live if at[r] == len(reqs[r])]
+        steps.append({"step": len(steps), "entries": ent, "end": done})
+        live = [r for r in live if r not in done]
+        if done and late not in at and len(live) <= 9:
+            at[late] = 0                               # joins with its whole prompt but the last
+            n = len(reqs[late]) - 10
+            steps.append({"step": len(steps), "end": [], "entries": [
+                {"id": late, "tokens": reqs[late][:n], "want": list(range(n))}]})
+            at[late] = n
+            live.append(late)
+    page = PAGE[name]
+    model, _ = load_model(model_dir, dtype)
+    pages = sum(-(-n // page) for n in lens[:11]) + 1
+    runner = ModelRunner(model, page_size=page, max_num_seqs=12, max_seq_len=64,
+                         num_pages=pages, max_num_batched_tokens=256, enforce_eager=False)
+    assert runner.graph_batch(11) == 16 and runner.graph_batch(8) == 8
+    rows = replay.run_in_process(runner, steps)
+    assert any(k[0] == 16 for k in runner._graphs) and runner.graph_launches > 0
+    replay.compare(rows, replay.plain_logits(model_dir, reqs, dtype), dtype, reqs)
+    assert not runner.cache.requests and all(
+        f == p.num_pages for f, p in zip(runner.cache.free_pages(), runner.cache.pools))

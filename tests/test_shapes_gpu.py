@@ -30,15 +30,19 @@ def test_bfloat16_path_agrees_with_the_32_bit_path_at_large_layer_sizes(name):
            "use_sliding_window": False, "torch_dtype": "bfloat16"}
     cfg.update(SHAPES[name])
     toks = {"a": prompt(70, 643, 1), "b": prompt(33, 643, 2)}
+    late = prompt(92, 643, 3)      # joins while the others decode: portions beside single tokens
     out = {}
     for dtype in ("float32", "bfloat16"):
         model, _ = random_model(cfg, 11, dtype)
-        r = ModelRunner(model, page_size=16, max_num_seqs=2, max_seq_len=256, num_pages=32,
+        r = ModelRunner(model, page_size=16, max_num_seqs=3, max_seq_len=256, num_pages=32,
                         enforce_eager=(dtype == "float32"))
         rows = [r.step([StepEntry(k, t[:-4], [len(t) - 5]) for k, t in toks.items()]).clone()]
+        cuts = {4: late[:80], 3: late[80:90], 2: late[90:91], 1: late[91:]}
         for i in range(4, 0, -1):                       # then token by token (graphs in bf16)
             # (a step's logits are valid until the next step: keep a copy)
-            rows.append(r.step([StepEntry(k, [t[-i]], [0]) for k, t in toks.items()]).clone())
+            ent = [StepEntry(k, [t[-i]], [0]) for k, t in toks.items()]
+            ent.append(StepEntry("late", cuts[i], [len(cuts[i]) - 1]))
+            rows.append(r.step(ent).clone())
         out[dtype] = torch.cat(rows).float().cpu()
         del r, model
         torch.cuda.empty_cache()
