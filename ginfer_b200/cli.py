@@ -45,6 +45,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--kvcache-block-size", type=int, default=16)
     ap.add_argument("--num-kvcache-blocks", type=int, default=None)
     ap.add_argument("--enforce-eager", action="store_true")
+    ap.add_argument("--capture-graphs", action="store_true",
+                    help="capture the decode steps' CUDA graphs at start-up, not on first use")
     ap.add_argument("--device", default="cuda:0")
     return ap
 
@@ -88,6 +90,7 @@ def main(argv=None) -> int:
                  gpu_memory_utilization=args.gpu_memory_utilization,
                  kvcache_block_size=args.kvcache_block_size,
                  num_kvcache_blocks=args.num_kvcache_blocks, enforce_eager=args.enforce_eager,
+                 capture_graphs=args.capture_graphs,
                  device=args.device, seed=args.seed)
     sp = SamplingParams(max_tokens=args.max_tokens, ignore_eos=args.ignore_eos,
                         temperature=args.temperature)

@@ -61,10 +61,12 @@ class Engine:
                  max_seq_len: int = 4096, gpu_memory_utilization: float = 0.8,
                  kvcache_block_size: int = 16, num_kvcache_blocks: int | None = None,
                  enforce_eager: bool = False, device: str = "cuda:0", seed: int = 0,
-                 pipeline: bool = True):
+                 pipeline: bool = True, warmup: bool = True, capture_graphs: bool = False):
         """``model_path``: a folder with ``config.json`` and ``model.safetensors``; or give
         ``config`` (a ``config.json`` as a dict) and ``weights_seed`` for random weights.
-        ``pipeline``: prepare each step on the host while the device runs the one before."""
+        ``pipeline``: prepare each step on the host while the device runs the one before.
+        ``warmup``: run one token through the model before the first request;
+        ``capture_graphs``: also capture the decode steps' CUDA graphs then, not on first use."""
         self.cfg = EngineConfig(model_path or "<random>", dtype, max_num_batched_tokens,
                                 max_num_seqs, max_seq_len, gpu_memory_utilization,
                                 kvcache_block_size, num_kvcache_blocks, enforce_eager, device)
@@ -80,6 +82,8 @@ class Engine:
             max_seq_len=max_seq_len, num_pages=num_kvcache_blocks,
             gpu_memory_utilization=gpu_memory_utilization,
             max_num_batched_tokens=max_num_batched_tokens, enforce_eager=enforce_eager)
+        if warmup:
+            self.runner.warmup(capture_graphs=capture_graphs)
         self.scheduler = Scheduler(self.runner.cache, max_num_seqs, max_num_batched_tokens,
                                    self.runner.max_seq_len, self.model.plan.eos_token_ids)
         self.sampler = Sampler(device)

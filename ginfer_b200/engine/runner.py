@@ -285,6 +285,51 @@ class ModelRunner:
                  slot_ids=np.concatenate([facts["slot_ids"], np.zeros(extra, dtype=np.int64)]))
         return a, f
 
+    def _padding_step(self, Bp: int, width: int):
+        """The arrays and facts of a decode step that consists of ``Bp`` padding rows only."""
+        def z(*shape):
+            return np.zeros(shape, dtype=np.int64)
+        arrays = dict(token_ids=z(0), positions=z(0), seq_of_token=z(0), cu_seqlens_q=z(1),
+                      kv_lens=z(0), slot_ids=z(0), logit_rows=z(0))
+        for g in range(self.cache.num_groups):
+            arrays[f"slot_mapping{g}"] = z(0)
+            arrays[f"block_table{g}"] = z(0, width)
+        facts = dict(T=0, B=0, q_lens=z(0), q_starts=z(0), slot_ids=z(0), width=width,
+                     all_rows=True, max_q_len=1, max_kv_len=1)
+        return self._pad_decode(arrays, facts, Bp)
+
+    @torch.no_grad()
+    def warmup(self, capture_graphs: bool = False, max_width: int | None = None) -> int:
+        """One token at position 0 through the model, on the scratch page, so that every library
+        the model needs is built and loaded before the first request (the reference warms its
+        model up the same way: ``engine/model_runner.cc:34-50``).  ``capture_graphs``: also
+        capture the CUDA graphs of decode steps now, for every batch-size bucket up to
+        ``max_num_seqs`` and every table width up to ``max_width`` pages (default: four width
+        steps), instead of when a step first needs one.  Returns how many graphs were captured.
+        Models with per-request state are left alone (the padding row would write slot 0)."""
+        if self.storage.state:
+            return 0
+        with torch.cuda.device(self.device):
+            arrays, facts = self._padding_step(1, 1)
+            dev = self.upload(arrays)
+            self.model.forward(self.make_context(dev, facts), self.binder(dev))
+            torch.cuda.synchronize(self.device)
+            if not capture_graphs or self.enforce_eager:
+                return 0
+            top = self.cache.table_width
+            max_width = min(top, max_width or 4 * GRAPH_WIDTH_STEP)
+            widths = sorted({min(top, w) for w in
+                             range(GRAPH_WIDTH_STEP, max_width + GRAPH_WIDTH_STEP, GRAPH_WIDTH_STEP)})
+            sizes = sorted({self.graph_batch(b) for b in range(1, self.max_num_seqs + 1)})
+            made = 0
+            for width in widths:
+                for Bp in sizes:
+                    if (Bp, width) not in self._graphs and Bp <= self.max_num_seqs + 15:
+                        a, f = self._padding_step(Bp, width)
+                        self._graphs[(Bp, width)] = self._capture((Bp, width), a, f)
+                        made += 1
+            return made
+
     def _graph_key(self, entries, facts):
         """Decode steps in which every request wants its token's logits replay a CUDA graph; so
         do steps with prompt portions whose shape has come before (see PORTION_GRAPH_*)."""

@@ -139,3 +139,22 @@ def test_no_cpu_path():
     from ginfer_b200.engine.loading import require_cuda
     with pytest.raises(RuntimeError, match="no CPU path"):
         require_cuda("cpu")
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_graphs_captured_at_start_up_give_the_same_tokens(folders, name):
+    """With ``capture_graphs`` the decode steps' CUDA graphs exist before the first request (one
+    per batch-size bucket and table width), no further one is captured while generating, and the
+    tokens are those of the plain implementation."""
+    from ginfer_b200.sampling import SamplingParams
+    d = folders[name]
+    cfg, w = plain.read_model_folder(d)
+    prompts = [prompt(n, cfg["vocab_size"], seed=n) for n in (7, 21, 40, 3, 12, 30, 9, 16, 25, 11)]
+    want = [plain.greedy_generate(w, cfg, p, 6) for p in prompts]
+    eng = _engine(d, capture_graphs=True, max_num_seqs=12, num_kvcache_blocks=60,
+                  max_num_batched_tokens=64)
+    before = set(eng.runner._graphs)
+    assert {k[0] for k in before} == {1, 2, 3, 4, 5, 6, 7, 8, 16}
+    assert eng.generate(prompts, SamplingParams(max_tokens=6, ignore_eos=True)) == want
+    assert set(eng.runner._graphs) == before and eng.runner.graph_launches > 0
+    assert eng.runner.cache.free_pages() == [60] * eng.runner.cache.num_groups
