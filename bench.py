@@ -16,6 +16,10 @@ of the sampled ids), timed with the wall clock around synchronised steps.  ``pre
 once, and the cache of the live requests) over its time, against the measured copy bandwidth.
 ``points``: decoding at batch 1 and 64.
 
+``--scenario serve64|chunked [--shape 7b|32b] [--layers L]`` runs one of the serving workloads
+instead (continuous batching of 64 requests; 8,192-token prompts in portions beside decoding
+requests) and prints its own line.
+
 Only one GPU is used; ``--gpus N`` with N > 1 prints a line that says so and exits with 2.
 ``--impl reference`` reports why the reference cannot run here.
 """
@@ -340,6 +344,61 @@ def run_micro(name: str) -> int:
     raise SystemExit(f"unknown workload {name!r}; known: {MICRO}")
 
 
+# ----------------------------------------------------------------------------- scenarios
+SCENARIOS = ("serve64", "chunked")
+
+
+def run_scenario(name: str, shape: str, layers: int | None) -> int:
+    """The serving workloads the baseline names beside the headline, through the Python entry
+    point (scheduler, chunked prompts, decode graphs), wall clock, second pass reported (the first
+    one captures graphs).  ``serve64``: continuous batching of 64 requests, prompts of 128..2048
+    tokens, 64..256 generated each.  ``chunked``: 8 prompts of 8,192 tokens fed in 2,048-token
+    portions beside 32 requests that generate 256 tokens each.  One JSON line."""
+    import random
+    import time
+
+    import torch
+
+    from ginfer_b200.engine.llm import Engine
+    from ginfer_b200.sampling import SamplingParams
+    cfg = dict(SHAPES[shape])
+    full_layers = cfg["num_hidden_layers"]
+    cfg["num_hidden_layers"] = layers or full_layers
+    rng = random.Random(0)
+    V = cfg["vocab_size"]
+    if name == "serve64":
+        prompts = [[rng.randrange(V) for _ in range(rng.randint(128, 2048))] for _ in range(64)]
+        params = [SamplingParams(max_tokens=rng.randint(64, 256), ignore_eos=True)
+                  for _ in range(64)]
+        eng = Engine(config=cfg, dtype="bfloat16", max_num_seqs=64, max_seq_len=8192,
+                     max_num_batched_tokens=2048, kvcache_block_size=PAGE,
+                     num_kvcache_blocks=64 * (2304 // PAGE + 2))
+    else:
+        prompts = ([[rng.randrange(V) for _ in range(32)] for _ in range(32)] +
+                   [[rng.randrange(V) for _ in range(8192)] for _ in range(8)])
+        params = ([SamplingParams(max_tokens=256, ignore_eos=True)] * 32 +
+                  [SamplingParams(max_tokens=8, ignore_eos=True)] * 8)
+        eng = Engine(config=cfg, dtype="bfloat16", max_num_seqs=40, max_seq_len=16384,
+                     max_num_batched_tokens=2048 + 32, kvcache_block_size=PAGE,
+                     num_kvcache_blocks=8 * (8200 // PAGE + 2) + 32 * (288 // PAGE + 2))
+    result = None
+    for _ in range(2):
+        torch.cuda.synchronize()
+        t0, s0 = time.perf_counter(), eng.runner.steps_run
+        outs = eng.generate(prompts, params)
+        torch.cuda.synchronize()
+        dt, steps = time.perf_counter() - t0, eng.runner.steps_run - s0
+        tin, tout = sum(map(len, prompts)), sum(map(len, outs))
+        result = {"scenario": name, "model": SHAPE_NAMES[shape], "layers_run": cfg["num_hidden_layers"],
+                  "layers_config": full_layers, "requests": len(prompts), "prompt_tokens": tin,
+                  "generated_tokens": tout, "seconds": round(dt, 4), "steps": steps,
+                  "ms_per_step": round(1e3 * dt / steps, 3),
+                  "total_tok_s": round((tin + tout) / dt, 1),
+                  "generated_tok_s": round(tout / dt, 1), "preemptions": eng.stats.preemptions}
+    print(json.dumps(result))
+    return 0
+
+
 # ----------------------------------------------------------------------------- main
 def main() -> int:
     ap = argparse.ArgumentParser()
@@ -357,9 +416,16 @@ def main() -> int:
     ap.add_argument("--enforce-eager", action="store_true")
     ap.add_argument("--micro", choices=MICRO, default=None,
                     help="run one small kernel workload (for profiling) instead of the benchmark")
+    ap.add_argument("--scenario", choices=SCENARIOS, default=None,
+                    help="run a serving workload through the entry point instead of the benchmark")
     args = ap.parse_args()
     if args.micro:
         return run_micro(args.micro)
+    if args.scenario:
+        if args.gpus != 1:
+            print(json.dumps({"error": "this engine runs on one GPU", "n_gpus": args.gpus}))
+            return 2
+        return run_scenario(args.scenario, args.shape, args.layers)
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
