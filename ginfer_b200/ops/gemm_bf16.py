@@ -58,6 +58,8 @@ def split_k_for(M: int, N: int, K: int) -> int:
         split *= 2
     if split == 8 and tiles * 12 <= NUM_SMS and nkb // 12 >= 8:
         split = 12      # a long reduction on few tiles (the down product): 144 CTAs instead of 96
+    if split == 1 and M <= 16 and NUM_SMS // 2 < tiles <= NUM_SMS and nkb >= 16:
+        split = 2       # about one tile an SM (gate/up): pairs of CTAs have more under way
     return split
 
 
@@ -109,23 +111,30 @@ def gemm(x, weight, bias_f32=None, out_dtype=torch.bfloat16, epi: int = 0, split
     return out
 
 
-MAX_TOKENS = 128    # the largest token count this kernel is used for (the gated product: 28.7 us
-                    # against 36.6 for cuBLAS + SiLU*mul at 128 tokens, 38.4 against 24.6 at 192)
+# The largest token count the gated product runs here for.  In a CUDA graph, 1.5B shapes, weights
+# from HBM: 8 tokens 11.5 us (two K splits) against 12.6 for cuBLAS + SiLU*mul, 16 tokens 11.8
+# against 12.6, 32 tokens 13.3 against 12.7, 64 tokens 14.8 against 13.7: every CTA streams the whole
+# activation matrix beside its weights, which costs as much as the weights from 32 tokens on.
+MAX_TOKENS = 16
 
 
 def try_linear(x, weight, bias_f32, out_dtype):
     """Run the tcgen05 kernel where it is the faster one (the small batches of decode steps and
     short prompt portions); ``None`` hands the product to cuBLAS."""
-    if x.shape[0] > PLAIN_MAX_TOKENS:
+    limit = PLAIN_MAX_TOKENS_LONG_K if weight.shape[1] >= LONG_K else PLAIN_MAX_TOKENS
+    if x.shape[0] > limit:
         return None
     return gemm(x, weight, bias_f32, out_dtype, epi=0)
 
 
-# Plain products leave for cuBLAS above this many tokens (measured at 64 tokens on a B200, 1.5B
-# shapes: q/k/v 8.6 us here against 4.8, output 9.8 against 5.1, down 14.7 against 13.8; the step at
-# batch 64 is 15 % faster); the gated product stays here up to MAX_TOKENS, where its fused
-# SiLU*mul epilogue saves a kernel and the round trip of gate and up through memory.
-PLAIN_MAX_TOKENS = 32
+# Plain products leave for cuBLAS above this many tokens.  In a CUDA graph on a B200, 1.5B shapes,
+# weights from HBM (us, here / cuBLAS): q/k/v 8 tokens 4.2 / 5.6, 16 tokens 4.6 / 4.6, 32 tokens
+# 6.3 / 4.6; output 4.3 / 5.0, 4.7 / 4.6, 6.5 / 4.5; down (a reduction of 8,960) 8 tokens 8.6 / 16.9,
+# 32 tokens 10.5 / 13.2, 48 tokens 12.6 / 13.2, 64 tokens 14.1 / 13.3.  With these limits the decode
+# step at batch 32 and 64 is 8 % faster than with 32 tokens for all.
+PLAIN_MAX_TOKENS = 16
+PLAIN_MAX_TOKENS_LONG_K = 48   # for reductions of at least LONG_K
+LONG_K = 4096
 
 
 # ----------------------------------------------------------------------------- fused with the norm

@@ -254,3 +254,13 @@ def test_native_decisions_are_the_python_decisions(seed):
         logs.append((log, sched.num_preemptions,
                      [(r.output, r.finish_reason, r.num_preemptions) for r in reqs]))
     assert logs[0] == logs[1]
+
+
+def test_batch_sizes_of_decode_graphs():
+    """Decode steps are replayed from a graph of their own batch size up to 8 requests, of the
+    next multiple of 8 up to 64 and of 16 above (the rows in between are padding)."""
+    from ginfer_b200.engine.runner import ModelRunner
+    sizes = [ModelRunner.graph_batch(b) for b in range(1, 100)]
+    assert sizes[:8] == list(range(1, 9))
+    assert all(s >= b and s - b < (8 if b <= 64 else 16) for b, s in zip(range(1, 100), sizes))
+    assert sorted(set(sizes)) == list(range(1, 9)) + [16, 24, 32, 40, 48, 56, 64, 80, 96, 112]
