@@ -1,0 +1,264 @@
+// y[M, N] = x[M, K] @ W[N, K]^T for many tokens (prompt portions): a persistent tcgen05 kernel.
+//
+// Tiles of 128 tokens x 256 weight rows: the tokens are the 128 rows of the MMA (= TMEM lanes),
+// the weight rows its 256 columns, so that a thread of the epilogue owns one token and writes
+// runs of neighbouring output channels with 16-byte stores, and a gate finds its up value in the
+// next column (weights interleaved gate_0, up_0, gate_1, ...: SiLU*mul is fused, and only the
+// product is written: the round trip of gate and up through memory, 110 MB a layer at 2,048
+// tokens of the 1.5B shape, goes away).
+//
+// One CTA an SM walks over tiles (tile = blockIdx.x + i * gridDim.x; the tiles of one block of
+// weight rows are neighbours, so that block is read from HBM once and from L2 after that).  Roles:
+//   warp 0      TMA producer: x tile (16 KB) and W tile (32 KB) per 64-wide K block into a ring of
+//               four stages (full / empty mbarriers)
+//   warp 1      allocates all 512 TMEM columns (two accumulators of 256), issues tcgen05.mma
+//               (128 x 256 x 16, four per stage), commits stages and accumulators
+//   warps 2-9   epilogue: two warps per quarter of the TMEM lanes, each half of the columns:
+//               tcgen05.ld, bias or SiLU*mul in fp32, bf16 / fp32 stores.  The epilogue of a tile
+//               runs while the next tile's products go into the other accumulator.
+// Every wait is bounded; a wait that runs out sets *err (1 producer, 2 MMA issuer, 3 epilogue)
+// and the roles leave their loops, after which the CTA frees its tensor memory and returns.
+#include "tc_common.cuh"
+
+namespace gf {
+
+constexpr int PM = 128;                       // tokens per tile
+constexpr int PN = 256;                       // weight rows per tile
+constexpr int PSTAGES = 4;
+constexpr uint32_t PA_BYTES = PM * BK * 2;    // x tile of a stage
+constexpr uint32_t PB_BYTES = PN * BK * 2;    // W tile of a stage
+constexpr int EPI_WARPS = 8;
+constexpr int P_THREADS = (2 + EPI_WARPS) * 32;
+constexpr uint32_t P_TMEM_COLS = 512;
+
+constexpr int PEPI_STORE = 0;                 // out[m, n] = acc (+ bias[n])
+constexpr int PEPI_GATED = 2;                 // out[m, n / 2] = silu(acc[m, n]) * acc[m, n + 1], n even
+
+template <int EPI, typename OUT>
+__global__ void __launch_bounds__(P_THREADS)
+gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
+                    const __grid_constant__ CUtensorMap tmap_w, const float* __restrict__ bias,
+                    OUT* __restrict__ out, int ldo, int M, int N, int K, int* __restrict__ err) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  unsigned char* tiles = (unsigned char*)(((uintptr_t)smem + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(tiles + PSTAGES * (PA_BYTES + PB_BYTES));
+  uint64_t* empty = full + PSTAGES;
+  uint64_t* acc_full = empty + PSTAGES;       // [2]
+  uint64_t* acc_empty = acc_full + 2;         // [2]
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (M + PM - 1) / PM, n_tiles = (N + PN - 1) / PN;
+  const int ntiles = m_tiles * n_tiles;
+  const int nkb = (K + BK - 1) / BK;
+
+  pdl_trigger();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PSTAGES; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full + b, 1);
+      mbar_init(acc_empty + b, EPI_WARPS * 32);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_x) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_w) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(tmem_slot)), "r"(P_TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      pdl_wait();                                      // x comes from the kernel in front
+      int it = 0;                                      // K blocks issued so far, over all tiles
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        const int n0 = (tile / m_tiles) * PN, m0 = (tile % m_tiles) * PM;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % PSTAGES;
+          if (!mbar_wait(empty + s, ((it / PSTAGES) & 1) ^ 1, err, 1)) { ok = false; break; }
+          mbar_expect_tx(full + s, PA_BYTES + PB_BYTES);
+          unsigned char* a = tiles + s * (PA_BYTES + PB_BYTES);
+          tma_load_2d(a, &tmap_x, full + s, kb * BK, m0);
+          tma_load_2d(a + PA_BYTES, &tmap_w, full + s, kb * BK, n0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(PN);
+      int it = 0, t = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++t) {
+        const int buf = t & 1, use = t >> 1;
+        // the epilogue must have read this accumulator's last tile (passes at once the first time)
+        if (!mbar_wait(acc_empty + buf, (uint32_t)(use & 1) ^ 1u, err, 2)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t acc = tmem + (uint32_t)(buf * PN);
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % PSTAGES;
+          if (!mbar_wait(full + s, (it / PSTAGES) & 1, err, 2)) { ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a = smem_u32(tiles + s * (PA_BYTES + PB_BYTES));
+          const uint64_t ad = umma_desc(a), bd = umma_desc(a + PA_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma(acc, ad + (uint64_t)(k * UMMA_K * 2 >> 4), bd + (uint64_t)(k * UMMA_K * 2 >> 4),
+                 idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit(empty + s);                      // the stage is free once these have read it
+        }
+        if (ok) umma_commit(acc_full + buf);           // the tile's accumulator is complete
+      }
+    }
+  } else {
+    // epilogue: TMEM lanes (warp % 4) * 32 .. + 31 = tokens, columns half * 128 .. + 127
+    const int e = warp - 2, q = warp & 3, half = e >> 2;
+    pdl_wait();                                        // nothing is written before the kernel ahead is done
+    int t = 0;
+    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++t) {
+      const int buf = t & 1, use = t >> 1;
+      const int n0 = (tile / m_tiles) * PN + half * 128, m = (tile % m_tiles) * PM + q * 32 + lane;
+      if (!mbar_wait(acc_full + buf, (uint32_t)(use & 1), err, 3)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * PN + half * 128);
+#pragma unroll 1
+      for (int c = 0; c < 128; c += 32) {
+        float v[32];
+        __syncwarp();                                  // the loads below want the whole warp
+        if (nkb > 0) {
+          tmem_ld16(taddr + c, *reinterpret_cast<float(*)[16]>(v));
+          tmem_ld16(taddr + c + 16, *reinterpret_cast<float(*)[16]>(v + 16));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+        }
+        if (c == 96) {                                 // the last read of this accumulator
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          mbar_arrive(acc_empty + buf);
+        }
+        const int n = n0 + c;
+        if (m >= M || n >= N) continue;
+        if (EPI == PEPI_STORE) {
+          if (bias) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += (n + j < N) ? bias[n + j] : 0.f;
+          }
+          OUT* dst = out + (size_t)m * ldo + n;
+          if (sizeof(OUT) == 2) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (n + j >= N) break;                   // N is a multiple of 8
+              __nv_bfloat162 p[4];
+#pragma unroll
+              for (int u = 0; u < 4; ++u) p[u] = __floats2bfloat162_rn(v[j + 2 * u], v[j + 2 * u + 1]);
+              *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<const uint4*>(p);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              if (n + j >= N) break;
+              *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            }
+          }
+        } else {
+          // (gate, up) in neighbouring columns, both rounded to bf16 first as a product's output
+          // would be; 16 results
+          OUT* dst = out + (size_t)m * ldo + (n >> 1);
+#pragma unroll
+          for (int j = 0; j < 32; j += 16) {
+            if (n + j >= N) break;                     // N is a multiple of 16 here
+            __nv_bfloat162 p[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              float z[2];
+#pragma unroll
+              for (int w = 0; w < 2; ++w) {
+                const float g = __bfloat162float(__float2bfloat16_rn(v[j + 4 * u + 2 * w]));
+                const float up = __bfloat162float(__float2bfloat16_rn(v[j + 4 * u + 2 * w + 1]));
+                z[w] = g * (1.0f / (1.0f + expf(-g))) * up;
+              }
+              p[u] = __floats2bfloat162_rn(z[0], z[1]);
+            }
+            *reinterpret_cast<uint4*>(dst + (j >> 1)) = *reinterpret_cast<const uint4*>(p);
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem),
+                 "r"(P_TMEM_COLS)
+                 : "memory");
+  }
+}
+
+template <int EPI, typename OUT>
+static int launch_prefill(const CUtensorMap& mx, const CUtensorMap& mw, const float* bias, void* out,
+                          int ldo, int M, int N, int K, int* err, int ctas, cudaStream_t st) {
+  const size_t smem = 1024 + (size_t)PSTAGES * (PA_BYTES + PB_BYTES) +
+                      (2 * PSTAGES + 4) * sizeof(uint64_t) + 16;
+  auto k = gemm_prefill_kernel<EPI, OUT>;
+  static bool done = false;
+  if (!done) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    done = true;
+  }
+  return launch_kernel(k, dim3(ctas), dim3(P_THREADS), smem, st, mx, mw, bias, (OUT*)out, ldo, M,
+                       N, K, err);
+}
+
+}  // namespace gf
+
+using namespace gf;
+
+GF_DEFINE_PDL_SWITCH
+
+// x [M, K] bf16 (row stride ldx), w [N, K] bf16 contiguous, bias fp32 [N] or null.
+// epi 0: out [M, N] (row stride ldo) bf16 or fp32 = x w^T (+ bias); epi 2: w rows interleaved
+// (gate_i, up_i), out [M, N / 2] bf16 = silu(gate) * up.  `ctas`: CTAs to launch (0: one an SM).
+// -6: a shape or alignment this kernel does not take (the caller uses another product).
+GF_EXPORT int gf_gemm_prefill(const void* x, int ldx, const void* w, const void* bias, void* out,
+                              int ldo, int M, int N, int K, int epi, int out_f32, int ctas,
+                              int* err, void* stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K < 8 || K % 8 || ldx % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) ||
+      ((uintptr_t)out & 15))
+    return -6;
+  if (epi == PEPI_GATED ? (N % 16 || ldo % 8 || out_f32) : (epi != PEPI_STORE || N % 8 ||
+                                                            ldo % (out_f32 ? 4 : 8)))
+    return -6;
+  CUtensorMap mx, mw;
+  if (!make_map(&mx, x, M, K, ldx, PM)) return -6;
+  if (!make_map(&mw, w, N, K, K, PN)) return -6;
+  const int ntiles = ((M + PM - 1) / PM) * ((N + PN - 1) / PN);
+  int sms = 148;
+  {
+    int dev = 0, v = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0)
+      sms = v;
+  }
+  if (ctas <= 0 || ctas > sms) ctas = sms;
+  if (ctas > ntiles) ctas = ntiles;
+  auto st = (cudaStream_t)stream;
+  if (epi == PEPI_GATED)
+    return launch_prefill<PEPI_GATED, bf16>(mx, mw, nullptr, out, ldo, M, N, K, err, ctas, st);
+  if (out_f32)
+    return launch_prefill<PEPI_STORE, float>(mx, mw, (const float*)bias, out, ldo, M, N, K, err,
+                                             ctas, st);
+  return launch_prefill<PEPI_STORE, bf16>(mx, mw, (const float*)bias, out, ldo, M, N, K, err, ctas,
+                                          st);
+}

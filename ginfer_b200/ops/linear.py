@@ -3,8 +3,9 @@ reference reads the same memory as a column-major ``[in, out]`` view:
 ``ginfer/core/layer/linear.cc:13-16``).
 
 float32: the hand-written FMA kernel of ``csrc/gemm_f32.cu`` (no reduced-precision mode).
-bfloat16: the tcgen05 kernel of ``csrc/gemm_bf16.cu`` where it takes the shape, else cuBLAS
-through ``torch`` (fp32 accumulation), which is what the reference uses for every product.
+bfloat16: the tcgen05 kernels of ``csrc/gemm_bf16.cu`` (few tokens) and ``csrc/gemm_prefill.cu``
+(the gated product of many tokens) where they are the faster ones, else cuBLAS through ``torch``
+(fp32 accumulation), which is what the reference uses for every product.
 """
 from __future__ import annotations
 
@@ -89,6 +90,13 @@ def add_to(linear: "Linear", x: torch.Tensor, residual: torch.Tensor):
     return gemm_bf16.gemm_resid(x, linear.weight, linear._bias_f32, residual)
 
 
+# From this many tokens on the gated product runs on the persistent tcgen05 kernel of
+# csrc/gemm_prefill.cu (SiLU*mul in its epilogue).  On a B200 at the 1.5B shape (17920 x 1536):
+# 2,048 tokens 87.7 us against 96.0 for cuBLAS + SiLU*mul, 8,192 tokens 336 against 386, 512 tokens
+# 27.4 against 27.1; at the 7B shape (37888 x 3584) 383 against 392.
+PREFILL_GATED_MIN_TOKENS = 1024
+
+
 class GatedLinear:
     """``silu(x W_g^T) * (x W_u^T)``.  The two matrices are joined row by row (gate_0, up_0,
     gate_1, up_1, ...) so that ``x`` is read once and a gate meets its up value in neighbouring
@@ -111,9 +119,13 @@ class GatedLinear:
                     return z
             x = x.materialize()
         if x.dtype == torch.bfloat16:
-            from . import gemm_bf16
+            from . import gemm_bf16, gemm_prefill
             if x.shape[0] <= gemm_bf16.MAX_TOKENS:
                 z = gemm_bf16.gemm(x, self.proj.weight, None, torch.bfloat16, epi=2)
+                if z is not None:
+                    return z
+            elif x.shape[0] >= PREFILL_GATED_MIN_TOKENS:
+                z = gemm_prefill.gemm(x, self.proj.weight, None, torch.bfloat16, epi=2)
                 if z is not None:
                     return z
         return silu_mul(self.proj(x))
