@@ -240,8 +240,8 @@ def prefill_timed(eng, tokens: int, reps: int, warmup: int, seed: int):
 
 
 # ----------------------------------------------------------------------------- small workloads
-MICRO = ("gemm_gateup_m8", "gemm_down_m8", "gemm_lmhead_m8", "attn_decode_b8", "attn_decode_b64",
-         "prefill_2layers", "decode_layers_phases")
+MICRO = ("gemm_gateup_m8", "gemm_down_m8", "gemm_lmhead_m8", "gemm_gateup_m2048", "attn_decode_b8",
+         "attn_decode_b64", "prefill_2layers", "decode_layers_phases")
 
 
 def run_micro(name: str) -> int:
@@ -257,6 +257,17 @@ def run_micro(name: str) -> int:
     H, I, V = c["hidden_size"], c["intermediate_size"], c["vocab_size"]
     nh, nkv, hd = c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"]
     dev = "cuda:0"
+    if name == "gemm_gateup_m2048":
+        # the gated product of a 2,048-token prompt on the persistent tcgen05 kernel
+        from ginfer_b200.ops import gemm_prefill
+        x = torch.randn(PREFILL_TOKENS, H, device=dev).to(torch.bfloat16)
+        ws = [(torch.randn(2 * I, H, device=dev) * 0.05).to(torch.bfloat16) for _ in range(3)]
+        for i in range(6):
+            y = gemm_prefill.gemm(x, ws[i % 3], None, torch.bfloat16, epi=2)
+        torch.cuda.synchronize()
+        gemm_bf16.check_errors()
+        print(json.dumps({"micro": name, "out": list(y.shape)}))
+        return 0
     if name.startswith("gemm_"):
         M, N, K, epi, out = {"gemm_gateup_m8": (8, 2 * I, H, 2, torch.bfloat16),
                              "gemm_down_m8": (8, H, I, 0, torch.bfloat16),
