@@ -1,8 +1,11 @@
 // bf16 grouped-query attention over the paged cache for the serving path, compiled for one head
 // size (-DGF_HEAD_DIM=<multiple of 16, at most 256>).
 //
-//  * gf_attn_decode: one query token per request.  One CTA per (request, kv head, split of the
-//    keys, chunk of 16 query heads): the query heads of a group share every K/V byte that is
+//  * gf_attn_decode_tma: one query token per request, for head sizes that are a multiple of 64 and
+//    page sizes that fit the 64-key tile: tiles by TMA through a loader warp, query heads as the 8
+//    columns of the tensor-core tiles (described where the kernel stands, further down).
+//  * gf_attn_decode: the same for every head size and page size.  One CTA per (request, kv head,
+//    split of the keys, chunk of 16 query heads): the query heads of a group share every K/V byte that is
 //    loaded (the reference's decode kernel reads K/V once per query head:
 //    ginfer/core/op/kernels/cuda/page_attn_kernel/flash_gqa_varlen_decode_kvcache.cu:272-335).
 //    Splits write fp32 partial results (running maximum, sum, unnormalised output) to scratch
