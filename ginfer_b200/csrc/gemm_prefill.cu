@@ -13,8 +13,8 @@
 //               four stages (full / empty mbarriers)
 //   warp 1      allocates all 512 TMEM columns (two accumulators of 256), issues tcgen05.mma
 //               (128 x 256 x 16, four per stage), commits stages and accumulators
-//   warps 2-9   epilogue: two warps per quarter of the TMEM lanes, each half of the columns:
-//               tcgen05.ld, bias or SiLU*mul in fp32, bf16 / fp32 stores.  The epilogue of a tile
+//   warps 2-9   epilogue: two warps per quarter of the TMEM lanes, each half of the columns, 16
+//               at a time: tcgen05.ld, bias or SiLU*mul in fp32, bf16 / fp32 stores.  The epilogue of a tile
 //               runs while the next tile's products go into the other accumulator.
 // Every wait is bounded; a wait that runs out sets *err (1 producer, 2 MMA issuer, 3 epilogue)
 // and the roles leave their loops, after which the CTA frees its tensor memory and returns.
@@ -22,11 +22,16 @@
 
 namespace gf {
 
+#ifndef GF_PN
+#define GF_PN 256
+#endif
 constexpr int PM = 128;                       // tokens per tile
-constexpr int PN = 256;                       // weight rows per tile
-constexpr int PSTAGES = 4;
+constexpr int PN = GF_PN;                     // weight rows per tile (a multiple of 32, <= 256)
+// as many stages as shared memory holds: 4 at 256 rows (5 at 224 rows measured no faster)
+constexpr int PSTAGES = (225 * 1024) / (PM * BK * 2 + PN * BK * 2);
 constexpr uint32_t PA_BYTES = PM * BK * 2;    // x tile of a stage
 constexpr uint32_t PB_BYTES = PN * BK * 2;    // W tile of a stage
+static_assert(PN % 32 == 0 && PN <= 256 && PSTAGES >= 2, "tile width");
 constexpr int EPI_WARPS = 8;
 constexpr int P_THREADS = (2 + EPI_WARPS) * 32;
 constexpr uint32_t P_TMEM_COLS = 512;
@@ -104,7 +109,7 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
         // the epilogue must have read this accumulator's last tile (passes at once the first time)
         if (!mbar_wait(acc_empty + buf, (uint32_t)(use & 1) ^ 1u, err, 2)) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t acc = tmem + (uint32_t)(buf * PN);
+        const uint32_t acc = tmem + (uint32_t)(buf * 256);
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it % PSTAGES;
           if (!mbar_wait(full + s, (it / PSTAGES) & 1, err, 2)) { ok = false; break; }
@@ -127,22 +132,21 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
     int t = 0;
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++t) {
       const int buf = t & 1, use = t >> 1;
-      const int n0 = (tile / m_tiles) * PN + half * 128, m = (tile % m_tiles) * PM + q * 32 + lane;
+      const int n0 = (tile / m_tiles) * PN + half * (PN / 2), m = (tile % m_tiles) * PM + q * 32 + lane;
       if (!mbar_wait(acc_full + buf, (uint32_t)(use & 1), err, 3)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * PN + half * 128);
+      const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 256 + half * (PN / 2));
 #pragma unroll 1
-      for (int c = 0; c < 128; c += 32) {
-        float v[32];
-        __syncwarp();                                  // the loads below want the whole warp
+      for (int c = 0; c < PN / 2; c += 16) {
+        float v[16];
+        __syncwarp();                                  // the load below wants the whole warp
         if (nkb > 0) {
-          tmem_ld16(taddr + c, *reinterpret_cast<float(*)[16]>(v));
-          tmem_ld16(taddr + c + 16, *reinterpret_cast<float(*)[16]>(v + 16));
+          tmem_ld16(taddr + c, v);
         } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+          for (int j = 0; j < 16; ++j) v[j] = 0.f;
         }
-        if (c == 96) {                                 // the last read of this accumulator
+        if (c == PN / 2 - 16) {                        // the last read of this accumulator
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
           mbar_arrive(acc_empty + buf);
         }
@@ -151,12 +155,12 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
         if (EPI == PEPI_STORE) {
           if (bias) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] += (n + j < N) ? bias[n + j] : 0.f;
+            for (int j = 0; j < 16; ++j) v[j] += (n + j < N) ? bias[n + j] : 0.f;
           }
           OUT* dst = out + (size_t)m * ldo + n;
           if (sizeof(OUT) == 2) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
+            for (int j = 0; j < 16; j += 8) {
               if (n + j >= N) break;                   // N is a multiple of 8
               __nv_bfloat162 p[4];
 #pragma unroll
@@ -165,32 +169,28 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
             }
           } else {
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
+            for (int j = 0; j < 16; j += 4) {
               if (n + j >= N) break;
               *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
             }
           }
         } else {
           // (gate, up) in neighbouring columns, both rounded to bf16 first as a product's output
-          // would be; 16 results
-          OUT* dst = out + (size_t)m * ldo + (n >> 1);
+          // would be; 8 results (N is a multiple of 16 here)
+          __nv_bfloat162 p[4];
 #pragma unroll
-          for (int j = 0; j < 32; j += 16) {
-            if (n + j >= N) break;                     // N is a multiple of 16 here
-            __nv_bfloat162 p[4];
+          for (int u = 0; u < 4; ++u) {
+            float z[2];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              float z[2];
-#pragma unroll
-              for (int w = 0; w < 2; ++w) {
-                const float g = __bfloat162float(__float2bfloat16_rn(v[j + 4 * u + 2 * w]));
-                const float up = __bfloat162float(__float2bfloat16_rn(v[j + 4 * u + 2 * w + 1]));
-                z[w] = g * (1.0f / (1.0f + expf(-g))) * up;
-              }
-              p[u] = __floats2bfloat162_rn(z[0], z[1]);
+            for (int w = 0; w < 2; ++w) {
+              const float g = __bfloat162float(__float2bfloat16_rn(v[4 * u + 2 * w]));
+              const float up = __bfloat162float(__float2bfloat16_rn(v[4 * u + 2 * w + 1]));
+              z[w] = g * (1.0f / (1.0f + expf(-g))) * up;
             }
-            *reinterpret_cast<uint4*>(dst + (j >> 1)) = *reinterpret_cast<const uint4*>(p);
+            p[u] = __floats2bfloat162_rn(z[0], z[1]);
           }
+          *reinterpret_cast<uint4*>(out + (size_t)m * ldo + (n >> 1)) =
+              *reinterpret_cast<const uint4*>(p);
         }
       }
     }
