@@ -164,6 +164,10 @@ def set_pdl(enabled: bool) -> None:
                 lib.gf_set_pdl(ctypes.c_int(1 if _pdl_enabled else 0))
 
 
+# sources that are compiled per head size but take only some head sizes
+HEAD_DIMS_OF = {"attention_tc": (64, 128)}
+
+
 # every library the framework can ask for: (source name, defines)
 def all_libraries(head_dims=(64, 128)) -> list[tuple[str, tuple[str, ...]]]:
     libs: list[tuple[str, tuple[str, ...]]] = []
@@ -174,7 +178,9 @@ def all_libraries(head_dims=(64, 128)) -> list[tuple[str, tuple[str, ...]]]:
         with open(os.path.join(CSRC_DIR, f), "r", encoding="utf-8") as fh:
             per_head_dim = "GF_HEAD_DIM" in fh.read()
         if per_head_dim:
-            libs += [(name, (f"GF_HEAD_DIM={hd}",)) for hd in head_dims]
+            only = HEAD_DIMS_OF.get(name)
+            libs += [(name, (f"GF_HEAD_DIM={hd}",)) for hd in head_dims
+                     if only is None or hd in only]
         else:
             libs.append((name, ()))
     return libs
