@@ -253,6 +253,10 @@ TC_CASES = [
     ([300, 129, 77, 1000], [300, 1, 77, 129], 4, 4, 128, 8, 0),
     ([640, 400], [128, 400], 2, 1, 128, 16, 200),
     ([2048], [2048], 4, 2, 128, 16, 0),
+    # many key tiles per query tile: pairs of CTAs share them (also with a window, and where the
+    # second CTA's keys are all behind the window's start for the first rows)
+    ([1800, 900], [700, 900], 6, 2, 128, 16, 700),
+    ([3000], [130], 4, 1, 64, 8, 0),
 ]
 
 
