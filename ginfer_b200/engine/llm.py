@@ -71,6 +71,7 @@ class Engine:
                                 max_num_seqs, max_seq_len, gpu_memory_utilization,
                                 kvcache_block_size, num_kvcache_blocks, enforce_eager, device)
         self.cfg.validate()
+        self._weights_from = (model_path, int(weights_seed))
         if model_path is not None:
             self.model, self.model_config = load_model(model_path, dtype, device)
         elif config is not None:
@@ -95,6 +96,20 @@ class Engine:
         self.stats = EngineStats()
         self._next_id = 0
         self.requests: dict[int, Request] = {}
+
+    def weights(self) -> dict[str, torch.Tensor]:
+        """The model's tensors by their safetensors names, as stored (a folder's) or as drawn
+        (random weights: drawn again from the same seeds on the same device), for a caller that
+        wants to run its own implementation of the model beside this one."""
+        path, seed = self._weights_from
+        if path is not None:
+            from ..weights.safetensors_io import open_model_tensors
+            return {name: f.get(key) for name, (f, key) in open_model_tensors(path).items()}
+        from ..weights.loader import kept_dtype
+        from ..weights.random_init import draw_tensor
+        dt = self.runner.dtype
+        return {s.name: draw_tensor(s, seed, device=self.cfg.device).to(kept_dtype(s.role, dt, dt))
+                for s in self.model.tensor_specs()}
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_ids: list[int], params: SamplingParams | None = None) -> int:

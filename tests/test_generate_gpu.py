@@ -158,3 +158,16 @@ def test_graphs_captured_at_start_up_give_the_same_tokens(folders, name):
     assert eng.generate(prompts, SamplingParams(max_tokens=6, ignore_eos=True)) == want
     assert set(eng.runner._graphs) == before and eng.runner.graph_launches > 0
     assert eng.runner.cache.free_pages() == [60] * eng.runner.cache.num_groups
+
+
+def test_weights_of_an_engine_run_through_the_plain_implementation():
+    """``Engine.weights()`` gives the tensors by name, of a folder as stored and of a random model
+    as drawn: the plain implementation run on them generates the engine's tokens."""
+    from ginfer_b200.sampling import SamplingParams
+    from tiny import CONFIGS
+    cfg = dict(CONFIGS["A"])
+    eng = _engine(None, dtype="float32", config=cfg, weights_seed=9)
+    w = {k: v.double().cpu() for k, v in eng.weights().items()}
+    prompts = [prompt(n, cfg["vocab_size"], seed=n) for n in (6, 19)]
+    want = [plain.greedy_generate(w, cfg, p, 5) for p in prompts]
+    assert eng.generate(prompts, SamplingParams(max_tokens=5, ignore_eos=True)) == want
