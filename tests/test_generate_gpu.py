@@ -171,3 +171,26 @@ def test_weights_of_an_engine_run_through_the_plain_implementation():
     prompts = [prompt(n, cfg["vocab_size"], seed=n) for n in (6, 19)]
     want = [plain.greedy_generate(w, cfg, p, 5) for p in prompts]
     assert eng.generate(prompts, SamplingParams(max_tokens=5, ignore_eos=True)) == want
+
+
+@pytest.mark.parametrize("name,seed", [("A", 0), ("B", 1)])
+def test_many_requests_under_pressure_generate_the_plain_tokens(folders, name, seed):
+    """Fourteen requests of random lengths, a small token budget and so few pages that requests
+    are preempted: portions beside single tokens (which go to the decode kernel), decode batches
+    padded to a graph's size, pages used again.  Every request gets the plain implementation's
+    tokens."""
+    import random
+
+    from ginfer_b200.sampling import SamplingParams
+    d = folders[name]
+    cfg, w = plain.read_model_folder(d)
+    rng = random.Random(seed)
+    prompts = [prompt(rng.randint(3, 60), cfg["vocab_size"], seed=100 + i) for i in range(14)]
+    news = [rng.randint(1, 10) for _ in prompts]
+    want = [plain.greedy_generate(w, cfg, p, n) for p, n in zip(prompts, news)]
+    eng = _engine(d, max_num_seqs=12, max_num_batched_tokens=48, num_kvcache_blocks=22,
+                  kvcache_block_size=8 if name == "B" else 16)
+    got = eng.generate(prompts, [SamplingParams(max_tokens=n, ignore_eos=True) for n in news])
+    assert got == want
+    assert eng.runner.cache.free_pages() == [22] * eng.runner.cache.num_groups
+    assert eng.runner.graph_launches > 0
