@@ -173,6 +173,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 struct Barriers {
   uint64_t q_full;
+  uint64_t q_empty;       // the item's last S product has read Q
   uint64_t k_full[K_STAGES];
   uint64_t k_empty[K_STAGES];
   uint64_t v_full[V_STAGES];
@@ -181,9 +182,15 @@ struct Barriers {
   uint64_t p_ready;       // P_j is in shared memory and O is rescaled (256 arrivals)
   uint64_t max_ready;     // both halves of every row have posted their maximum (256 arrivals)
   uint64_t pv_done;       // O += P_j V_j is complete
+  uint64_t o_free;        // the softmax warps have read an item's O out (256 arrivals)
   uint32_t tmem_base;
   int abort_flag;
   float row_max[2][2][QT];   // [tile parity][half][row]
+};
+
+// One work item: 128 query rows of one head of one request, and the key tiles they see.
+struct Item {
+  int b, head, r0, rows, q_begin, pos0, key_lo, p_last, j0, ntiles, kvh;
 };
 
 __global__ void __launch_bounds__(NTHREADS)
@@ -193,8 +200,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
                        const int* __restrict__ block_table, int table_stride,
                        const int* __restrict__ cu_seqlens_q, const int* __restrict__ kv_lens,
                        bf16* __restrict__ out, int nh, int nkv, int page_size, int window,
-                       float scale_log2, int oob_row, int* __restrict__ err,
-                       long long* __restrict__ dbg) {
+                       float scale_log2, int oob_row, int q_tiles, int B,
+                       int* __restrict__ err, long long* __restrict__ dbg) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // the kernel has no static shared memory, so the dynamic part starts at the aligned base; the
   // swizzled tiles need that (checked below: a misaligned base ends the CTA with an error code)
@@ -206,13 +213,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.z, head = blockIdx.x;
-  // optional time stamps of the first CTA's phases (dbg: 16 slots per tile per role)
-  const bool trace = dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+  // optional time stamps of the first CTA's first item (dbg: 16 slots per tile per role)
+  bool trace = dbg != nullptr && blockIdx.x == 0;
 #define GF_STAMP(role, i, slot) \
   if (trace && (i) < 32) dbg[((role) * 32 + (i)) * 8 + (slot)] = clock64()  /* dbg: 3 * 32 * 8 */
   // with dbg: every CTA also leaves (start ns, end ns, SM) behind the first CTA's stamps
-  const int cta_lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  const int cta_lin = blockIdx.x;
   if (dbg && threadIdx.x == 0) {
     unsigned long long t;
     unsigned int sm;
@@ -223,28 +229,43 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
   }
   pdl_trigger();
   pdl_wait();
-  const int q_begin = cu_seqlens_q[b], q_len = cu_seqlens_q[b + 1] - q_begin;
-  // CTAs start in the order of their index with x running fastest: the heads are on x and the
-  // query tiles on y, last (heaviest: most keys under the causal mask) first, so that every
-  // head's heavy tiles are in the first wave and the light ones fill the SMs that finish early
-  const int r0 = (int)(gridDim.y - 1 - blockIdx.y) * QT;
-  if (r0 >= q_len) return;
   if (smem_u32(smem_raw) & 1023u) {
     if (threadIdx.x == 0 && err) atomicExch(err, 12);
     return;
   }
-  const int kv_len = kv_lens[b];
-  const int pos0 = kv_len - q_len;
-  const int kvh = head / (nh / nkv);
-  const int rows = min(QT, q_len - r0);
-  const int p_first = pos0 + r0, p_last = pos0 + r0 + rows - 1;
-  const int key_lo = window > 0 ? max(0, p_first - window + 1) : 0;
-  const int j0 = key_lo / KT, j1 = p_last / KT;                // key tiles j0 .. j1
-  const int ntiles = j1 - j0 + 1;
-  const int* tbl = block_table + (size_t)b * table_stride;
+  // The CTAs (one an SM) walk over the work items.  Items are numbered heads fastest, then query
+  // tiles from the last (heaviest: most keys under the causal mask) to the first, then requests;
+  // CTA c takes items c, 2G - 1 - c, 2G + c, ... (G CTAs): the CTAs that got the lightest items of
+  // one round get the heaviest of the next.  Barrier phases run on over the items (every role
+  // counts tiles and items for itself), so the loads and the first S product of the next item
+  // overlap the last P V, the read-out and the stores of this one.
+  const int items = nh * q_tiles * B;
+  auto item_of = [&](int n, Item& it) -> int {   // 0: no more items, 1: it, 2: an empty item
+    const int G = gridDim.x;
+    const int idx = n * G + ((n & 1) ? G - 1 - (int)blockIdx.x : (int)blockIdx.x);
+    if (idx >= items) return 0;
+    it.head = idx % nh;
+    const int rest = idx / nh;
+    it.b = rest / q_tiles;
+    it.r0 = (q_tiles - 1 - rest % q_tiles) * QT;
+    it.q_begin = cu_seqlens_q[it.b];
+    const int q_len = cu_seqlens_q[it.b + 1] - it.q_begin;
+    if (it.r0 >= q_len) return 2;
+    const int kv_len = kv_lens[it.b];
+    it.pos0 = kv_len - q_len;
+    it.kvh = it.head / (nh / nkv);
+    it.rows = min(QT, q_len - it.r0);
+    const int p_first = it.pos0 + it.r0;
+    it.p_last = it.pos0 + it.r0 + it.rows - 1;
+    it.key_lo = window > 0 ? max(0, p_first - window + 1) : 0;
+    it.j0 = it.key_lo / KT;
+    it.ntiles = it.p_last / KT - it.j0 + 1;
+    return 1;
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
+    mbar_init(&bars->q_empty, 1);
     for (int s = 0; s < K_STAGES; ++s) {
       mbar_init(&bars->k_full[s], 2);          // one arrival (with its byte count) per loader warp
       mbar_init(&bars->k_empty[s], 1);
@@ -258,6 +279,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
     mbar_init(&bars->p_ready, 256);
     mbar_init(&bars->max_ready, 256);
     mbar_init(&bars->pv_done, 1);
+    mbar_init(&bars->o_free, 256);
     bars->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_q) : "memory");
@@ -285,12 +307,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
     // under way.
     const bool is_v = warp >= 2;
     const int part = warp & 1;
-    if (warp == 0 && lane == 0) {
-      mbar_expect_tx(&bars->q_full, Q_BYTES);
-      for (int h = 0; h < HALVES; ++h)
-        tma_load_2d(q_s + h * ATOM_BYTES, &tmap_q, &bars->q_full, head * HD + h * 64,
-                    q_begin + r0);
-    }
     const int pages_per_tile = KT / page_size;
     const int ops = pages_per_tile * HALVES;                   // boxes per tile of one operand
     const int my_ops = (ops - part + 1) / 2;                   // boxes part, part + 2, ...
@@ -302,102 +318,137 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
     uint64_t* empty = is_v ? bars->v_empty : bars->k_empty;
     const CUtensorMap* map = is_v ? &tmap_v : &tmap_k;
     const uint32_t my_bytes = (uint32_t)my_ops * (uint32_t)page_size * 128u;
-    int rows_next[MAX_OPS];
-    auto lookup = [&](int i) {
-      const int key0 = (j0 + i) * KT;
+    int cnt = 0, seq = 0;                                      // tiles and items so far
+    bool go = true;
+    Item it;
+    for (int n = 0; go; ++n) {
+      const int kind = item_of(n, it);
+      if (kind == 0) break;
+      if (kind == 2) continue;
+      const int* tbl = block_table + (size_t)it.b * table_stride;
+      if (warp == 0 && lane == 0) {
+        // Q's buffer is free once the last S product of the item before has read it
+        if (!mbar_wait(&bars->q_empty, (uint32_t)(seq & 1) ^ 1u, abort_flag, err, 13)) break;
+        mbar_expect_tx(&bars->q_full, Q_BYTES);
+        for (int h = 0; h < HALVES; ++h)
+          tma_load_2d(q_s + h * ATOM_BYTES, &tmap_q, &bars->q_full, it.head * HD + h * 64,
+                      it.q_begin + it.r0);
+      }
+      int rows_next[MAX_OPS];
+      auto lookup = [&](int i) {
+        const int key0 = (it.j0 + i) * KT;
 #pragma unroll
-      for (int u = 0; u < MAX_OPS; ++u) {
-        const int op = part + 2 * (lane + 32 * u);
-        rows_next[u] = oob_row;
-        if (op < ops && i < ntiles) {
-          const int c = key0 + (op / HALVES) * page_size;      // first key of this page
-          // pages past the request's last key (or wholly before the window) come from an
-          // out-of-range row: TMA fills them with zeros
-          if (c <= p_last && c + page_size > key_lo) {
-            const int page = tbl[c / page_size];
-            if (page >= 0) rows_next[u] = page * page_size;
+        for (int u = 0; u < MAX_OPS; ++u) {
+          const int op = part + 2 * (lane + 32 * u);
+          rows_next[u] = oob_row;
+          if (op < ops && i < it.ntiles) {
+            const int c = key0 + (op / HALVES) * page_size;    // first key of this page
+            // pages past the request's last key (or wholly before the window) come from an
+            // out-of-range row: TMA fills them with zeros
+            if (c <= it.p_last && c + page_size > it.key_lo) {
+              const int page = tbl[c / page_size];
+              if (page >= 0) rows_next[u] = page * page_size;
+            }
           }
         }
-      }
-    };
-    lookup(0);
-    for (int i = 0; i < ntiles; ++i) {
-      int rows_now[MAX_OPS];
+      };
+      lookup(0);
+      for (int i = 0; i < it.ntiles; ++i, ++cnt) {
+        int rows_now[MAX_OPS];
 #pragma unroll
-      for (int u = 0; u < MAX_OPS; ++u) rows_now[u] = rows_next[u];
-      const int st = i % nstages;
-      int ok = 1;
-      if (lane == 0) {
-        if (warp == 0) { GF_STAMP(2, i, 0); }
-        ok = mbar_wait(&empty[st], ((i / nstages) & 1) ^ 1, abort_flag, err, 1);
-        if (ok && my_bytes) mbar_expect_tx(&full[st], my_bytes);
-        else if (ok) mbar_arrive(&full[st]);
-        if (warp == 0) { GF_STAMP(2, i, 1); }
-      }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) break;
-#pragma unroll
-      for (int u = 0; u < MAX_OPS; ++u) {
-        const int op = part + 2 * (lane + 32 * u);
-        if (op < ops) {
-          const int pg = op / HALVES, h = op - pg * HALVES;
-          tma_load_2d(ring + (size_t)st * tile_bytes + h * ATOM_BYTES +
-                          (size_t)pg * page_size * 128,
-                      map, &full[st], kvh * HD + h * 64, rows_now[u]);
+        for (int u = 0; u < MAX_OPS; ++u) rows_now[u] = rows_next[u];
+        const int st = cnt % nstages;
+        int ok = 1;
+        if (lane == 0) {
+          if (warp == 0) { GF_STAMP(2, i, 0); }
+          ok = mbar_wait(&empty[st], ((cnt / nstages) & 1) ^ 1, abort_flag, err, 1);
+          if (ok && my_bytes) mbar_expect_tx(&full[st], my_bytes);
+          else if (ok) mbar_arrive(&full[st]);
+          if (warp == 0) { GF_STAMP(2, i, 1); }
         }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) { go = false; break; }
+#pragma unroll
+        for (int u = 0; u < MAX_OPS; ++u) {
+          const int op = part + 2 * (lane + 32 * u);
+          if (op < ops) {
+            const int pg = op / HALVES, h = op - pg * HALVES;
+            tma_load_2d(ring + (size_t)st * tile_bytes + h * ATOM_BYTES +
+                            (size_t)pg * page_size * 128,
+                        map, &full[st], it.kvh * HD + h * 64, rows_now[u]);
+          }
+        }
+        if (warp == 0 && lane == 0) { GF_STAMP(2, i, 2); }
+        lookup(i + 1);                                          // overlaps the next wait
       }
-      if (warp == 0 && lane == 0) { GF_STAMP(2, i, 2); }
-      lookup(i + 1);                                            // overlaps the next wait
+      ++seq;
+      trace = false;
     }
   } else if (warp == 4) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t id_qk = idesc(KT, false), id_pv = idesc(HD, true);
-      bool ok = mbar_wait(&bars->q_full, 0, abort_flag, err, 2);
       const uint32_t qa = smem_u32(q_s), pa = smem_u32(p_s);
-      // S_i = Q K_i^T into S buffer i % 2: issued one tile ahead of P V, so that the tensor
-      // core works on tile i + 1 while the softmax warps work on tile i
-      auto issue_qk = [&](int i) -> bool {
-        const int s = i % K_STAGES;
-        if (!mbar_wait(&bars->k_full[s], (i / K_STAGES) & 1, abort_flag, err, 3)) return false;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t ka = smem_u32(k_s + s * K_BYTES);
+      int cnt = 0, seq = 0;                                    // tiles and items so far
+      bool ok = true;
+      Item it;
+      for (int n = 0; ok; ++n) {
+        const int kind = item_of(n, it);
+        if (kind == 0) break;
+        if (kind == 2) continue;
+        const int c0 = cnt;                                    // the item's first tile
+        ok = mbar_wait(&bars->q_full, (uint32_t)(seq & 1), abort_flag, err, 2);
+        // S_i = Q K_i^T into S buffer (c0 + i) % 2: issued one tile ahead of P V, so that the
+        // tensor core works on tile i + 1 while the softmax warps work on tile i
+        auto issue_qk = [&](int i) -> bool {
+          const int c = c0 + i, s = c % K_STAGES;
+          if (!mbar_wait(&bars->k_full[s], (c / K_STAGES) & 1, abort_flag, err, 3)) return false;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t ka = smem_u32(k_s + s * K_BYTES);
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) {
-          const uint32_t off = (k / 4) * ATOM_BYTES + (k % 4) * 32;   // 16 channels = 32 bytes
-          umma(tmem_s + 128 * (i & 1), desc_kmajor(qa + off), desc_kmajor(ka + off), id_qk,
-               k > 0 ? 1u : 0u);
-        }
-        umma_commit(&bars->k_empty[s]);         // K_i may be overwritten once S_i is computed
-        umma_commit(&bars->s_full[i & 1]);
-        return true;
-      };
-      if (ok) ok = issue_qk(0);
-      for (int i = 0; i < ntiles && ok; ++i) {
-        const int s = i % V_STAGES;
-        // S buffer (i + 1) % 2 held S_{i-1}: the softmax warps were done with it before they
-        // announced P_{i-1}, which this thread waited for in the last round
-        GF_STAMP(1, i, 0);
-        if (i + 1 < ntiles) ok = issue_qk(i + 1);
-        if (!ok) break;
-        GF_STAMP(1, i, 1);
-        ok = mbar_wait(&bars->v_full[s], (i / V_STAGES) & 1, abort_flag, err, 9);
-        GF_STAMP(1, i, 2);
-        if (ok) ok = mbar_wait(&bars->p_ready, i & 1, abort_flag, err, 4);
-        if (!ok) break;
-        GF_STAMP(1, i, 3);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t va = smem_u32(v_s + s * V_BYTES);
+          for (int k = 0; k < HD / 16; ++k) {
+            const uint32_t off = (k / 4) * ATOM_BYTES + (k % 4) * 32;   // 16 channels = 32 bytes
+            umma(tmem_s + 128 * (c & 1), desc_kmajor(qa + off), desc_kmajor(ka + off), id_qk,
+                 k > 0 ? 1u : 0u);
+          }
+          umma_commit(&bars->k_empty[s]);       // K_i may be overwritten once S_i is computed
+          umma_commit(&bars->s_full[c & 1]);
+          if (i == it.ntiles - 1) umma_commit(&bars->q_empty);   // Q has been read for the last time
+          return true;
+        };
+        if (ok) ok = issue_qk(0);
+        for (int i = 0; i < it.ntiles && ok; ++i) {
+          const int c = c0 + i, s = c % V_STAGES;
+          // S buffer (c + 1) % 2 held the tile before this one: the softmax warps were done with
+          // it before they announced its P, which this thread waited for in the last round
+          GF_STAMP(1, i, 0);
+          if (i + 1 < it.ntiles) ok = issue_qk(i + 1);
+          if (!ok) break;
+          GF_STAMP(1, i, 1);
+          ok = mbar_wait(&bars->v_full[s], (c / V_STAGES) & 1, abort_flag, err, 9);
+          GF_STAMP(1, i, 2);
+          if (ok) ok = mbar_wait(&bars->p_ready, c & 1, abort_flag, err, 4);
+          // the first P V of an item overwrites O: the item before must have been read out
+          if (ok && i == 0)
+            ok = mbar_wait(&bars->o_free, (uint32_t)(seq & 1) ^ 1u, abort_flag, err, 14);
+          if (!ok) break;
+          GF_STAMP(1, i, 3);
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t va = smem_u32(v_s + s * V_BYTES);
 #pragma unroll
-        for (int k = 0; k < KT / 16; ++k) {
-          const uint32_t poff = (k / 4) * ATOM_BYTES + (k % 4) * 32;  // 16 keys along P's rows
-          const uint32_t voff = k * 16 * 128;                         // 16 keys = 16 rows of V
-          umma(tmem_o, desc_kmajor(pa + poff), desc_mnmajor(va + voff), id_pv,
-               (i > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < KT / 16; ++k) {
+            const uint32_t poff = (k / 4) * ATOM_BYTES + (k % 4) * 32;  // 16 keys along P's rows
+            const uint32_t voff = k * 16 * 128;                         // 16 keys = 16 rows of V
+            umma(tmem_o, desc_kmajor(pa + poff), desc_mnmajor(va + voff), id_pv,
+                 (i > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&bars->v_empty[s]);         // V_i may be overwritten
+          umma_commit(&bars->pv_done);            // O holds tiles 0 .. i
+          GF_STAMP(1, i, 4);
         }
-        umma_commit(&bars->v_empty[s]);         // V_i may be overwritten
-        umma_commit(&bars->pv_done);            // O holds tiles 0 .. i
-        GF_STAMP(1, i, 4);
+        cnt = c0 + it.ntiles;
+        ++seq;
+        trace = false;
       }
     }
   } else {
@@ -409,146 +460,163 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const int qd = warp & 3;                                   // TMEM lane quarter of this warp
     const int half = (warp - 5) >> 2;                          // which 64 keys / which channels
     const int r = qd * 32 + lane;                              // query row of this thread
-    const int p = pos0 + r0 + r;                               // its position
-    const bool live = r < rows;
-    const int lo = window > 0 ? max(0, p - window + 1) : 0;
     const uint32_t lane_addr = (uint32_t)(qd * 32) << 16;
-    float m_used = -INFINITY;        // the maximum the accumulated P and l are scaled by
-    float l = 0.f;                   // this thread's half of the row sum
+    int cnt = 0, mr = 0;                                       // tiles, and uses of max_ready
     bool ok = true;
-    for (int i = 0; i < ntiles; ++i) {
-      const bool tr = r == 0 && half == 0;
-      if (tr) { GF_STAMP(0, i, 0); }
-      ok = mbar_wait(&bars->s_full[i & 1], (i >> 1) & 1, abort_flag, err, 5);
-      if (!ok) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (tr) { GF_STAMP(0, i, 1); }
-      const int col0 = (j0 + i) * KT + 64 * half;             // first key of this thread's half
-      // every row of this warp sees all of these keys: no comparisons
-      const int wp0 = pos0 + r0 + qd * 32;
-      const bool interior = col0 + 63 <= wp0 && qd * 32 + 32 <= rows &&
-                            (window <= 0 || col0 >= wp0 + 31 - window + 1);
-      float v[2][32];
-      const uint32_t srow = tmem_s + 128 * (i & 1) + 64 * half + lane_addr;
-      tmem_ld32(srow, v[0]);
-      tmem_ld32(srow + 32, v[1]);
-      tmem_ld_wait();
-      if (tr) { GF_STAMP(0, i, 2); }
-      // four running maxima (and four sums below) instead of one chain of dependent operations
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-      if (interior) {
+    Item it;
+    for (int n = 0; ok; ++n) {
+      const int kind = item_of(n, it);
+      if (kind == 0) break;
+      if (kind == 2) continue;
+      const int c0 = cnt;
+      const int p = it.pos0 + it.r0 + r;                       // this row's position
+      const bool live = r < it.rows;
+      const int lo = window > 0 ? max(0, p - window + 1) : 0;
+      float m_used = -INFINITY;        // the maximum the accumulated P and l are scaled by
+      float l = 0.f;                   // this thread's half of the row sum
+      for (int i = 0; i < it.ntiles; ++i) {
+        const int c = c0 + i;
+        const bool tr = r == 0 && half == 0;
+        if (tr) { GF_STAMP(0, i, 0); }
+        ok = mbar_wait(&bars->s_full[c & 1], (c >> 1) & 1, abort_flag, err, 5);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (tr) { GF_STAMP(0, i, 1); }
+        const int col0 = (it.j0 + i) * KT + 64 * half;         // first key of this thread's half
+        // every row of this warp sees all of these keys: no comparisons
+        const int wp0 = it.pos0 + it.r0 + qd * 32;
+        const bool interior = col0 + 63 <= wp0 && qd * 32 + 32 <= it.rows &&
+                              (window <= 0 || col0 >= wp0 + 31 - window + 1);
+        float v[2][32];
+        const uint32_t srow = tmem_s + 128 * (c & 1) + 64 * half + lane_addr;
+        tmem_ld32(srow, v[0]);
+        tmem_ld32(srow + 32, v[1]);
+        tmem_ld_wait();
+        if (tr) { GF_STAMP(0, i, 2); }
+        // four running maxima (and four sums below) instead of one chain of dependent operations
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (interior) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c)
+          for (int cc = 0; cc < 2; ++cc)
 #pragma unroll
-          for (int k = 0; k < 32; ++k) mx4[k & 3] = fmaxf(mx4[k & 3], v[c][k]);
-      } else {
+            for (int k = 0; k < 32; ++k) mx4[k & 3] = fmaxf(mx4[k & 3], v[cc][k]);
+        } else {
 #pragma unroll
-        for (int c = 0; c < 2; ++c)
+          for (int cc = 0; cc < 2; ++cc)
+#pragma unroll
+            for (int k = 0; k < 32; ++k) {
+              const int key = col0 + 32 * cc + k;
+              v[cc][k] = (live && key >= lo && key <= p) ? v[cc][k] : -INFINITY;
+              mx4[k & 3] = fmaxf(mx4[k & 3], v[cc][k]);
+            }
+        }
+        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        // the row's maximum over both halves
+        bars->row_max[mr & 1][half][r] = mx;
+        mbar_arrive(&bars->max_ready);
+        ok = mbar_wait(&bars->max_ready, mr & 1, abort_flag, err, 10);
+        if (!ok) break;
+        if (tr) { GF_STAMP(0, i, 3); }
+        mx = fmaxf(mx, bars->row_max[mr & 1][half ^ 1][r]) * scale_log2;   // scale > 0
+        ++mr;
+        // lazy rescale: keep the old reference maximum unless the row's maximum outgrew it
+        float m_new = m_used;
+        if (mx > m_used + kRescaleStep || m_used == -INFINITY) m_new = fmaxf(m_used, mx);
+        const float corr = (m_new == m_used) ? 1.f
+                           : (m_used == -INFINITY ? 0.f : fast_exp2(m_used - m_new));
+        const float msub = m_new == -INFINITY ? 0.f : m_new;
+        // probabilities (in place) and the row sum, while P V of the tile before may still run
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc)
 #pragma unroll
           for (int k = 0; k < 32; ++k) {
-            const int key = col0 + 32 * c + k;
-            v[c][k] = (live && key >= lo && key <= p) ? v[c][k] : -INFINITY;
-            mx4[k & 3] = fmaxf(mx4[k & 3], v[c][k]);
+            const float e = fast_exp2(fmaf(v[cc][k], scale_log2, -msub));
+            v[cc][k] = e;
+            sum4[k & 3] += e;
           }
-      }
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      // the row's maximum over both halves
-      bars->row_max[i & 1][half][r] = mx;
-      mbar_arrive(&bars->max_ready);
-      ok = mbar_wait(&bars->max_ready, i & 1, abort_flag, err, 10);
-      if (!ok) break;
-      if (tr) { GF_STAMP(0, i, 3); }
-      mx = fmaxf(mx, bars->row_max[i & 1][half ^ 1][r]) * scale_log2;   // scale > 0
-      // lazy rescale: keep the old reference maximum unless the row's maximum outgrew it
-      float m_new = m_used;
-      if (mx > m_used + kRescaleStep || m_used == -INFINITY) m_new = fmaxf(m_used, mx);
-      const float corr = (m_new == m_used) ? 1.f
-                         : (m_used == -INFINITY ? 0.f : fast_exp2(m_used - m_new));
-      const float msub = m_new == -INFINITY ? 0.f : m_new;
-      // probabilities (in place) and the row sum, while P V of the tile before may still run
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        if (tr) { GF_STAMP(0, i, 4); }
+        // O and the P buffer are free once P V of the tile before is complete (the item's first
+        // tile: the epilogue of the item before has waited for its last P V already)
+        if (i > 0) {
+          ok = mbar_wait(&bars->pv_done, (c - 1) & 1, abort_flag, err, 6);
+          if (!ok) break;
+          if (tr) { GF_STAMP(0, i, 5); }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          if (__any_sync(0xffffffffu, corr != 1.f)) {          // this thread's half of O's row
+#pragma unroll 1
+            for (int cc = 0; cc < HD / 2; cc += 32) {
+              float o[32];
+              tmem_ld32(tmem_o + lane_addr + half * (HD / 2) + cc, o);
+              tmem_ld_wait();
 #pragma unroll
-      for (int c = 0; c < 2; ++c)
-#pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          const float e = fast_exp2(fmaf(v[c][k], scale_log2, -msub));
-          v[c][k] = e;
-          sum4[k & 3] += e;
+              for (int k = 0; k < 32; ++k) o[k] *= corr;
+              tmem_st32(tmem_o + lane_addr + half * (HD / 2) + cc, o);
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          }
         }
-      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      if (tr) { GF_STAMP(0, i, 4); }
-      // O and the P buffer are free once P V of the tile before is complete
-      if (i > 0) {
-        ok = mbar_wait(&bars->pv_done, (i - 1) & 1, abort_flag, err, 6);
-        if (!ok) break;
-        if (tr) { GF_STAMP(0, i, 5); }
+        l = l * corr + sum;
+        m_used = m_new;
+        // P (bf16, K-major with 128-byte swizzle) -> shared memory: keys 64 * half .. + 63 are
+        // atom `half`, eight 16-byte chunks per row
+        unsigned char* prow = p_s + half * ATOM_BYTES + (size_t)r * 128;
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {                     // 8 keys = one 16-byte chunk
+            const int chunk = cc * 4 + ch;
+            uint4 w;
+            w.x = pack_bf16(v[cc][ch * 8 + 0], v[cc][ch * 8 + 1]);
+            w.y = pack_bf16(v[cc][ch * 8 + 2], v[cc][ch * 8 + 3]);
+            w.z = pack_bf16(v[cc][ch * 8 + 4], v[cc][ch * 8 + 5]);
+            w.w = pack_bf16(v[cc][ch * 8 + 6], v[cc][ch * 8 + 7]);
+            *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = w;
+          }
+        }
+        if (tr) { GF_STAMP(0, i, 6); }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is for the tensor core
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        mbar_arrive(&bars->p_ready);
+        if (tr) { GF_STAMP(0, i, 7); }
+      }
+      cnt = c0 + it.ntiles;
+      // epilogue: O / l -> out; the two halves of a row add up their sums first
+      if (ok) ok = mbar_wait(&bars->pv_done, (cnt - 1) & 1, abort_flag, err, 7);
+      if (ok) {
+        bars->row_max[mr & 1][half][r] = l;
+        mbar_arrive(&bars->max_ready);
+        ok = mbar_wait(&bars->max_ready, mr & 1, abort_flag, err, 11);
+      }
+      if (ok) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (__any_sync(0xffffffffu, corr != 1.f)) {            // this thread's half of O's row
-#pragma unroll 1
-          for (int c = 0; c < HD / 2; c += 32) {
-            float o[32];
-            tmem_ld32(tmem_o + lane_addr + half * (HD / 2) + c, o);
-            tmem_ld_wait();
+        l += bars->row_max[mr & 1][half ^ 1][r];
+        ++mr;
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        bf16* orow = out + ((size_t)(it.q_begin + it.r0 + r) * nh + it.head) * HD + half * (HD / 2);
+        float o[HD / 2];
 #pragma unroll
-            for (int k = 0; k < 32; ++k) o[k] *= corr;
-            tmem_st32(tmem_o + lane_addr + half * (HD / 2) + c, o);
-          }
-          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-        }
-      }
-      l = l * corr + sum;
-      m_used = m_new;
-      // P (bf16, K-major with 128-byte swizzle) -> shared memory: keys 64 * half .. + 63 are
-      // atom `half`, eight 16-byte chunks per row
-      unsigned char* prow = p_s + half * ATOM_BYTES + (size_t)r * 128;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {                       // 8 keys = one 16-byte chunk
-          const int chunk = c * 4 + ch;
-          uint4 w;
-          w.x = pack_bf16(v[c][ch * 8 + 0], v[c][ch * 8 + 1]);
-          w.y = pack_bf16(v[c][ch * 8 + 2], v[c][ch * 8 + 3]);
-          w.z = pack_bf16(v[c][ch * 8 + 4], v[c][ch * 8 + 5]);
-          w.w = pack_bf16(v[c][ch * 8 + 6], v[c][ch * 8 + 7]);
-          *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = w;
-        }
-      }
-      if (tr) { GF_STAMP(0, i, 6); }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is for the tensor core
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(&bars->p_ready);
-      if (tr) { GF_STAMP(0, i, 7); }
-    }
-    // epilogue: O / l -> out; the two halves of a row add up their sums first
-    if (ok) ok = mbar_wait(&bars->pv_done, (ntiles - 1) & 1, abort_flag, err, 7);
-    if (ok) {
-      bars->row_max[ntiles & 1][half][r] = l;
-      mbar_arrive(&bars->max_ready);
-      ok = mbar_wait(&bars->max_ready, ntiles & 1, abort_flag, err, 11);
-    }
-    if (ok) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      l += bars->row_max[ntiles & 1][half ^ 1][r];
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      bf16* orow = out + ((size_t)(q_begin + r0 + r) * nh + head) * HD + half * (HD / 2);
-#pragma unroll 1
-      for (int c = 0; c < HD / 2; c += 32) {
-        float v[32];
-        tmem_ld32(tmem_o + lane_addr + half * (HD / 2) + c, v);
+        for (int cc = 0; cc < HD / 2; cc += 32)
+          tmem_ld32(tmem_o + lane_addr + half * (HD / 2) + cc,
+                    *reinterpret_cast<float(*)[32]>(o + cc));
         tmem_ld_wait();
+        // O is read: the next item's first P V may overwrite it while this one is stored
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        mbar_arrive(&bars->o_free);
         if (live) {
 #pragma unroll
-          for (int k = 0; k < 32; k += 8) {
+          for (int k = 0; k < HD / 2; k += 8) {
             uint4 w;
-            w.x = pack_bf16(v[k] * inv, v[k + 1] * inv);
-            w.y = pack_bf16(v[k + 2] * inv, v[k + 3] * inv);
-            w.z = pack_bf16(v[k + 4] * inv, v[k + 5] * inv);
-            w.w = pack_bf16(v[k + 6] * inv, v[k + 7] * inv);
-            *reinterpret_cast<uint4*>(orow + c + k) = w;
+            w.x = pack_bf16(o[k] * inv, o[k + 1] * inv);
+            w.y = pack_bf16(o[k + 2] * inv, o[k + 3] * inv);
+            w.z = pack_bf16(o[k + 4] * inv, o[k + 5] * inv);
+            w.w = pack_bf16(o[k + 6] * inv, o[k + 7] * inv);
+            *reinterpret_cast<uint4*>(orow + k) = w;
           }
         }
       }
+      trace = false;
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -634,9 +702,16 @@ GF_EXPORT int gf_attn_prefill_tc(const void* q, int q_row_stride, const void* kp
     if (e != cudaSuccess) return (int)e;
     attr_done = true;
   }
-  dim3 grid(nh, (max_q_len + QT - 1) / QT, B);
+  const int q_tiles = (max_q_len + QT - 1) / QT;
+  const long long items = (long long)nh * q_tiles * B;
+  if (items >= (1ll << 30)) return -6;
+  int sms = 148, dev = 0, v = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess &&
+      cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0)
+    sms = v;
+  dim3 grid((unsigned)(items < sms ? items : sms));
   return launch_kernel(attn_prefill_tc_kernel, grid, dim3(NTHREADS), smem, (cudaStream_t)stream,
                        mq, mk, mv, block_table, table_stride, cu_seqlens_q, kv_lens, (bf16*)out,
-                       nh, nkv, page_size, window, scale * LOG2E, (int)slots, err,
+                       nh, nkv, page_size, window, scale * LOG2E, (int)slots, q_tiles, B, err,
                        (long long*)dbg);
 }
