@@ -304,6 +304,7 @@ DEC_TMA_CASES = [   # what the kernel that loads by TMA serves: page sizes and h
     ([900, 5], 4, 4, 256, 128, 0),
     ([1500, 700], 6, 3, 128, 16, 130),           # a window that starts inside a tile
     ([4100], 18, 2, 64, 16, 0),                   # 9 query heads per kv head: two chunks of 8
+    ([300, 70, 8], 4, 2, 256, 8, 0),              # 64 boxes a tile: two for each lane of the loader
 ]
 
 

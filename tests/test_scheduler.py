@@ -264,3 +264,25 @@ def test_batch_sizes_of_decode_graphs():
     assert sizes[:8] == list(range(1, 9))
     assert all(s >= b and s - b < (8 if b <= 64 else 16) for b, s in zip(range(1, 100), sizes))
     assert sorted(set(sizes)) == list(range(1, 9)) + [16, 24, 32, 40, 48, 56, 64, 80, 96, 112]
+
+
+def test_split_choices_of_the_kernels():
+    """How the decode attention splits a request's keys and the small products their reduction:
+    powers of two up to 8 (they form a thread-block cluster), more splits for fewer requests, none
+    where the grid fills the GPU anyway; 12 splits for a long reduction on few tiles."""
+    from ginfer_b200.ops import attention_bf16, gemm_bf16
+    assert attention_bf16.decode_splits(8, 12, 2, 576) == 8
+    assert attention_bf16.decode_splits(64, 12, 2, 576) == 2
+    assert attention_bf16.decode_splits(512, 12, 2, 576) == 1
+    assert attention_bf16.decode_splits(1, 12, 2, 40) == 1           # one tile of keys
+    for b in (1, 3, 8, 20, 64, 200):
+        for keys in (10, 600, 5000):
+            assert attention_bf16.decode_splits(b, 28, 4, keys) in (1, 2, 4, 8)
+    assert attention_bf16.tma_serves(128, 16, 8) and attention_bf16.tma_serves(64, 128, 1)
+    assert not attention_bf16.tma_serves(48, 16, 8) and not attention_bf16.tma_serves(128, 24, 2)
+    assert not attention_bf16.tma_serves(128, 16, 5)
+    assert gemm_bf16.split_k_for(8, 2048, 1536) == 8                 # q/k/v: 16 tiles
+    assert gemm_bf16.split_k_for(8, 1536, 8960) == 12                # down: 12 tiles, long K
+    assert gemm_bf16.split_k_for(8, 17920, 1536) == 2                # gate/up: about a tile an SM
+    assert gemm_bf16.split_k_for(8, 151936, 1536) == 1               # the head: tiles for all SMs
+    assert gemm_bf16.split_k_for(64, 17920, 1536) == 1
