@@ -5,7 +5,10 @@
 // runs of neighbouring output channels with 16-byte stores, and a gate finds its up value in the
 // next column (weights interleaved gate_0, up_0, gate_1, ...: SiLU*mul is fused, and only the
 // product is written: the round trip of gate and up through memory, 110 MB a layer at 2,048
-// tokens of the 1.5B shape, goes away).
+// tokens of the 1.5B shape, goes away).  A third epilogue serves the joined q/k/v product: a
+// thread holds whole heads of its token, so it adds the bias, rotates q and k by the token's
+// angles and writes k and v into the token's slot of the paged cache as well as into `out` (no
+// rotation kernel reads and rewrites q/k/v behind the product).
 //
 // One CTA an SM walks over tiles (tile = blockIdx.x + i * gridDim.x; the tiles of one block of
 // weight rows are neighbours, so that block is read from HBM once and from L2 after that).  Roles:
@@ -14,8 +17,9 @@
 //   warp 1      allocates all 512 TMEM columns (two accumulators of 256), issues tcgen05.mma
 //               (128 x 256 x 16, four per stage), commits stages and accumulators
 //   warps 2-9   epilogue: two warps per quarter of the TMEM lanes, each half of the columns, 16
-//               at a time: tcgen05.ld, bias or SiLU*mul in fp32, bf16 / fp32 stores.  The epilogue of a tile
-//               runs while the next tile's products go into the other accumulator.
+//               at a time: tcgen05.ld, bias, SiLU*mul or rotation in fp32, bf16 / fp32 stores.
+//               The epilogue of a tile runs while the next tile's products go into the other
+//               accumulator.
 // Every wait is bounded; a wait that runs out sets *err (1 producer, 2 MMA issuer, 3 epilogue)
 // and the roles leave their loops, after which the CTA frees its tensor memory and returns.
 #include "tc_common.cuh"
@@ -38,12 +42,41 @@ constexpr uint32_t P_TMEM_COLS = 512;
 
 constexpr int PEPI_STORE = 0;                 // out[m, n] = acc (+ bias[n])
 constexpr int PEPI_GATED = 2;                 // out[m, n / 2] = silu(acc[m, n]) * acc[m, n + 1], n even
+constexpr int PEPI_QKV = 3;                   // + bias, q and k heads rotated, k and v to the cache
+
+// What the q/k/v epilogue needs beside the product: rows [q heads | k heads | v heads] of `hd`
+// channels; q and k are rotated by the angles of the token's position (table row: cos | sin over
+// hd channels, half-rotation pairing j <-> j + hd / 2) after they have been rounded to bf16, as a
+// rotation kernel behind the product would find them; k (rotated) and v also go to the token's
+// slot of the paged cache ([slots][nkv][hd]; a negative slot is skipped).
+struct QkvArgs {
+  const float* rope;
+  const int* positions;
+  const int* slot_mapping;
+  bf16* kpages;
+  bf16* vpages;
+  int nh, nkv, hd;
+};
+
+__device__ __forceinline__ float round_bf16(float v) {
+  return __bfloat162float(__float2bfloat16_rn(v));
+}
+__device__ __forceinline__ void store16_bf16(bf16* dst, const float (&v)[16]) {
+#pragma unroll
+  for (int j = 0; j < 16; j += 8) {
+    __nv_bfloat162 p[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) p[u] = __floats2bfloat162_rn(v[j + 2 * u], v[j + 2 * u + 1]);
+    *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<const uint4*>(p);
+  }
+}
 
 template <int EPI, typename OUT>
 __global__ void __launch_bounds__(P_THREADS)
 gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
                     const __grid_constant__ CUtensorMap tmap_w, const float* __restrict__ bias,
-                    OUT* __restrict__ out, int ldo, int M, int N, int K, int* __restrict__ err) {
+                    OUT* __restrict__ out, int ldo, int M, int N, int K, const QkvArgs qkv,
+                    int* __restrict__ err) {
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* tiles = (unsigned char*)(((uintptr_t)smem + 1023) & ~(uintptr_t)1023);
   uint64_t* full = (uint64_t*)(tiles + PSTAGES * (PA_BYTES + PB_BYTES));
@@ -136,6 +169,71 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
       if (!mbar_wait(acc_full + buf, (uint32_t)(use & 1), err, 3)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 256 + half * (PN / 2));
+      if (EPI == PEPI_QKV) {
+        // whole heads of this thread's token: hd divides the half tile's 128 columns
+        const int hd = qkv.hd, hh = hd >> 1;
+        const bool row_ok = m < M;
+        const int mm = row_ok ? m : M - 1;
+        const float* cs = qkv.rope + (size_t)qkv.positions[mm] * hd;
+        const int slot_i = qkv.slot_mapping[mm];
+        const bool cache_ok = row_ok && slot_i >= 0;       // a negative slot: nothing is cached
+        const size_t slot = (size_t)(slot_i >= 0 ? slot_i : 0);
+#pragma unroll 1
+        for (int hb = 0; hb < PN / 2 && n0 + hb < N; hb += hd) {
+          const int head = (n0 + hb) / hd;
+          bf16* dst = reinterpret_cast<bf16*>(out) + (size_t)mm * ldo + n0 + hb;
+          if (head >= qkv.nh + qkv.nkv) {             // a v head: bias, to `out` and to the cache
+            bf16* page = qkv.vpages + (slot * qkv.nkv + (head - qkv.nh - qkv.nkv)) * hd;
+#pragma unroll 1
+            for (int j = 0; j < hd; j += 16) {
+              float v[16];
+              __syncwarp();
+              tmem_ld16(taddr + hb + j, v);
+              if (bias) {
+#pragma unroll
+                for (int u = 0; u < 16; ++u) v[u] += bias[n0 + hb + j + u];
+              }
+              if (row_ok) store16_bf16(dst + j, v);
+              if (cache_ok) store16_bf16(page + j, v);
+            }
+          } else {                                    // a q or k head: bias, round, rotate
+            bf16* page = head >= qkv.nh ? qkv.kpages + (slot * qkv.nkv + (head - qkv.nh)) * hd
+                                        : nullptr;
+#pragma unroll 1
+            for (int j = 0; j < hh; j += 16) {
+              float a[16], b[16];
+              __syncwarp();
+              tmem_ld16(taddr + hb + j, a);
+              tmem_ld16(taddr + hb + hh + j, b);
+              float cc[16], ss[16];                    // rows of the table are 16-byte aligned
+#pragma unroll
+              for (int u = 0; u < 16; u += 4) {
+                *reinterpret_cast<float4*>(cc + u) = *reinterpret_cast<const float4*>(cs + j + u);
+                *reinterpret_cast<float4*>(ss + u) =
+                    *reinterpret_cast<const float4*>(cs + hh + j + u);
+              }
+#pragma unroll
+              for (int u = 0; u < 16; ++u) {
+                const float x = round_bf16(a[u] + (bias ? bias[n0 + hb + j + u] : 0.f));
+                const float y = round_bf16(b[u] + (bias ? bias[n0 + hb + hh + j + u] : 0.f));
+                a[u] = x * cc[u] - y * ss[u];
+                b[u] = x * ss[u] + y * cc[u];
+              }
+              if (row_ok) {
+                store16_bf16(dst + j, a);
+                store16_bf16(dst + hh + j, b);
+                if (page && cache_ok) {
+                  store16_bf16(page + j, a);
+                  store16_bf16(page + hh + j, b);
+                }
+              }
+            }
+          }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        mbar_arrive(acc_empty + buf);
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < PN / 2; c += 16) {
         float v[16];
@@ -206,7 +304,8 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
 
 template <int EPI, typename OUT>
 static int launch_prefill(const CUtensorMap& mx, const CUtensorMap& mw, const float* bias, void* out,
-                          int ldo, int M, int N, int K, int* err, int ctas, cudaStream_t st) {
+                          int ldo, int M, int N, int K, int* err, int ctas, cudaStream_t st,
+                          const QkvArgs& qkv = QkvArgs{}) {
   const size_t smem = 1024 + (size_t)PSTAGES * (PA_BYTES + PB_BYTES) +
                       (2 * PSTAGES + 4) * sizeof(uint64_t) + 16;
   auto k = gemm_prefill_kernel<EPI, OUT>;
@@ -217,7 +316,7 @@ static int launch_prefill(const CUtensorMap& mx, const CUtensorMap& mw, const fl
     done = true;
   }
   return launch_kernel(k, dim3(ctas), dim3(P_THREADS), smem, st, mx, mw, bias, (OUT*)out, ldo, M,
-                       N, K, err);
+                       N, K, qkv, err);
 }
 
 }  // namespace gf
@@ -261,4 +360,36 @@ GF_EXPORT int gf_gemm_prefill(const void* x, int ldx, const void* w, const void*
                                              ctas, st);
   return launch_prefill<PEPI_STORE, bf16>(mx, mw, (const float*)bias, out, ldo, M, N, K, err, ctas,
                                           st);
+}
+
+// The q/k/v product of prompt portions with what follows it in its epilogue: x [M, K] bf16, w
+// [(nh + 2 nkv) * hd, K] bf16 (q heads, k heads, v heads), bias fp32 or null; out [M, N] bf16
+// receives q and k rotated and v; k (rotated) and v also go to slot slot_mapping[m] of the paged
+// cache.  rope: [positions][hd] fp32, cos | sin (the whole head is rotated).  Head sizes 64 and
+// 128.  -6: not served.
+GF_EXPORT int gf_gemm_prefill_qkv(const void* x, int ldx, const void* w, const void* bias,
+                                  void* out, int ldo, int M, int K, int nh, int nkv, int hd,
+                                  const float* rope, const int* positions,
+                                  const int* slot_mapping, void* kpages, void* vpages, int ctas,
+                                  int* err, void* stream) {
+  const int N = (nh + 2 * nkv) * hd;
+  if (M <= 0 || N <= 0) return 0;
+  if ((hd != 64 && hd != 128) || !rope || !positions || !slot_mapping || !kpages || !vpages)
+    return -6;
+  if (K < 8 || K % 8 || ldx % 8 || ldo % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) ||
+      ((uintptr_t)out & 15) || ((uintptr_t)kpages & 15) || ((uintptr_t)vpages & 15))
+    return -6;
+  CUtensorMap mx, mw;
+  if (!make_map(&mx, x, M, K, ldx, PM)) return -6;
+  if (!make_map(&mw, w, N, K, K, PN)) return -6;
+  const int ntiles = ((M + PM - 1) / PM) * ((N + PN - 1) / PN);
+  int sms = 148, dev = 0, v = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess &&
+      cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0)
+    sms = v;
+  if (ctas <= 0 || ctas > sms) ctas = sms;
+  if (ctas > ntiles) ctas = ntiles;
+  const QkvArgs args{rope, positions, slot_mapping, (bf16*)kpages, (bf16*)vpages, nh, nkv, hd};
+  return launch_prefill<PEPI_QKV, bf16>(mx, mw, (const float*)bias, out, ldo, M, N, K, err, ctas,
+                                        (cudaStream_t)stream, args);
 }

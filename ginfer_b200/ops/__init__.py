@@ -252,4 +252,16 @@ def scatter_tokens(dst: torch.Tensor, dst_idx: torch.Tensor, src: torch.Tensor,
     _ok(f(_p(dst), _p(dst_idx), _p(src), _p(src_idx), n, _stream()), "scatter_tokens")
 
 
+def qkv_rope_write(x, linear, table, rot, positions, slot_mapping, pages, nh, nkv, hd):
+    """``linear(x)`` with q and k rotated and k and v written to the cache by the product's own
+    epilogue, where that is served (bf16, many tokens; see ``gemm_prefill.qkv_rope_write``), else
+    ``None``."""
+    if (getattr(linear, "dtype", None) != torch.bfloat16 or x.dtype != torch.bfloat16
+            or linear.out_dtype != torch.bfloat16):
+        return None
+    from . import gemm_prefill
+    return gemm_prefill.qkv_rope_write(x, linear.weight, linear._bias_f32, table, rot, positions,
+                                       slot_mapping, pages, nh, nkv, hd)
+
+
 from .linear import GatedLinear, Linear, add_to  # noqa: E402,F401

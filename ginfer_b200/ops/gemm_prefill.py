@@ -1,8 +1,10 @@
 """bf16 matrix products for many tokens (``csrc/gemm_prefill.cu``): a persistent tcgen05 kernel
 with two accumulators in tensor memory, so that a tile's epilogue (bias, or SiLU*mul over
-interleaved gate/up rows) runs while the next tile is multiplied."""
+interleaved gate/up rows, or bias + rotation + cache write for the joined q/k/v product) runs
+while the next tile is multiplied."""
 from __future__ import annotations
 
+import os
 from ctypes import c_int, c_void_p
 
 import torch
@@ -36,4 +38,47 @@ def gemm(x, weight, bias_f32=None, out_dtype=torch.bfloat16, epi: int = 0, ctas:
     if rc == -6:
         return None
     _ok(rc, "gemm_prefill")
+    return out
+
+
+QKV_MIN_TOKENS = 1024     # below this cuBLAS and the rotation kernel behind it are the faster pair
+# GINFER_B200_QKV_EPILOGUE=0 keeps the plain product and the rotation kernel at every size
+QKV_EPILOGUE = os.environ.get("GINFER_B200_QKV_EPILOGUE", "1") != "0"
+
+
+def qkv_rope_write(x, weight, bias_f32, table, rot, positions, slot_mapping, pages, nh, nkv, hd,
+                   min_tokens: int | None = None, ctas: int = 0):
+    """The q/k/v product of a step of many tokens with bias, the rotation of q and k and the write
+    of k and v to the paged cache in its epilogue (what :func:`ginfer_b200.ops.rope_kv_write`
+    does behind a plain product).  ``pages [2, num_pages, page, nkv, hd]`` bf16.  Returns
+    ``[T, (nh + 2 nkv) hd]`` with q and k rotated, or ``None`` if the kernel does not serve the
+    case (head sizes 64 and 128, the whole head rotated, at least ``min_tokens`` tokens,
+    ``QKV_MIN_TOKENS`` unless given)."""
+    from . import _fn, _ok, _p, _stream
+    from .gemm_bf16 import error_word
+    M, K = x.shape
+    if min_tokens is None:
+        if not QKV_EPILOGUE:
+            return None
+        min_tokens = QKV_MIN_TOKENS
+    if (M < min_tokens or hd not in (64, 128) or table is None or rot != hd
+            or slot_mapping is None or x.dtype != torch.bfloat16 or not supports(x, weight)
+            or weight.shape[0] != (nh + 2 * nkv) * hd or table.dtype != torch.float32
+            or not table.is_contiguous() or table.shape[1] != hd or table.data_ptr() % 16
+            or pages.dtype != torch.bfloat16 or not pages.is_contiguous()
+            or pages.shape[0] != 2 or tuple(pages.shape[3:]) != (nkv, hd)
+            or positions.dtype != torch.int32 or slot_mapping.dtype != torch.int32
+            or not positions.is_contiguous() or not slot_mapping.is_contiguous()
+            or positions.numel() < M or slot_mapping.numel() < M):
+        return None
+    out = torch.empty((M, weight.shape[0]), dtype=torch.bfloat16, device=x.device)
+    f = _fn("gemm_prefill", "gf_gemm_prefill_qkv",
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+             c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p])
+    rc = f(_p(x), x.stride(0), _p(weight), _p(bias_f32), _p(out), out.stride(0), M, K, nh, nkv,
+           hd, _p(table), _p(positions), _p(slot_mapping), _p(pages[0]), _p(pages[1]), int(ctas),
+           _p(error_word(x.device)), _stream())
+    if rc == -6:
+        return None
+    _ok(rc, "gemm_prefill_qkv")
     return out

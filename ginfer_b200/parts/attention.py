@@ -82,8 +82,16 @@ class Attention(Mixer):
 
     def forward(self, x, ctx, cache, residual=None):
         nh, nkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
-        qkv = self.qkv(x)                                         # [T, (nh + 2 nkv) hd]
         fused = self.position.rotary_table()
+        if fused is not None and cache.write and not hasattr(x, "materialize"):
+            # many tokens: one kernel multiplies, adds the bias, rotates q and k and writes the cache
+            qkv = ops.qkv_rope_write(x, self.qkv, fused[0], fused[1], ctx.positions,
+                                     cache.slot_mapping, cache.pages, nh, nkv, hd)
+            if qkv is not None:
+                o = ops.paged_attention(qkv, cache.pages, cache.block_table, ctx, nh, nkv, hd,
+                                        self.scale, cache.window, cache.page_size)
+                return self._project(o, residual)
+        qkv = self.qkv(x)                                         # [T, (nh + 2 nkv) hd]
         if fused is None:                                         # an encoding with code of its own
             q = qkv[:, :nh * hd].unflatten(1, (nh, hd))
             k = qkv[:, nh * hd:(nh + nkv) * hd].unflatten(1, (nkv, hd))
@@ -102,6 +110,9 @@ class Attention(Mixer):
                               cache.pages, nh, nkv, hd)
             o = ops.paged_attention(qkv, cache.pages, cache.block_table, ctx, nh, nkv, hd,
                                     self.scale, cache.window, cache.page_size)
+        return self._project(o, residual)
+
+    def _project(self, o, residual):
         if residual is not None:
             s = ops.add_to(self.out, o, residual)
             if s is not None:

@@ -67,3 +67,89 @@ def test_shapes_it_does_not_take_are_handed_back():
     assert gemm_prefill.gemm(x, torch.zeros(36, 64, dtype=torch.bfloat16, device=DEV)) is None
     assert gemm_prefill.gemm(x, torch.zeros(40, 64, dtype=torch.bfloat16, device=DEV),
                              epi=2) is None                                 # pairs: N % 16
+
+
+def _plain_qkv(x, w, b, table, positions, slots, nh, nkv, hd):
+    """Bias, rounding to bf16, rotation in pairs (j, j + hd / 2), rounding: in float64 on the host."""
+    qkv = _ref(x, w, b).to(torch.bfloat16).double().cpu()
+    T = qkv.shape[0]
+    cs = table.double().cpu()[positions.cpu().long()]            # [T, hd]: cos | sin
+    cos, sin = cs[:, None, :hd // 2], cs[:, None, hd // 2:]
+    heads = qkv.view(T, nh + 2 * nkv, hd).clone()
+    lo, hi = heads[:, :nh + nkv, :hd // 2].clone(), heads[:, :nh + nkv, hd // 2:].clone()
+    heads[:, :nh + nkv, :hd // 2] = lo * cos - hi * sin
+    heads[:, :nh + nkv, hd // 2:] = lo * sin + hi * cos
+    return heads.to(torch.bfloat16).double()
+
+
+@pytest.mark.parametrize("M,K,nh,nkv,hd", [
+    (2048, 1536, 12, 2, 128),      # the benchmark's layer
+    (300, 200, 3, 1, 64),          # a tile cut by M, heads that do not fill a tile of 256 rows
+    (129, 72, 5, 5, 64),           # 15 heads of 64: the last half tile holds one head
+    (1100, 256, 4, 2, 128),
+    (1, 64, 1, 1, 128),
+])
+@pytest.mark.parametrize("bias", [True, False])
+@pytest.mark.parametrize("ctas", [0, 3])
+def test_qkv_epilogue_rotates_and_writes_the_cache(M, K, nh, nkv, hd, bias, ctas):
+    from ginfer_b200.ops import gemm_bf16, gemm_prefill, rope_kv_write
+    g = torch.Generator(device="cpu").manual_seed(M + hd)
+    N = (nh + 2 * nkv) * hd
+    page, max_pos = 16, 4096
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    b = torch.randn(N, generator=g).to(DEV) if bias else None
+    ang = torch.rand(max_pos, hd // 2, generator=g) * 6.283
+    table = torch.cat([ang.cos(), ang.sin()], dim=1).float().contiguous().to(DEV)
+    positions = torch.randint(0, max_pos, (M,), generator=g).int().to(DEV)
+    npages = (M + page - 1) // page + 3
+    slots = torch.randperm(npages * page, generator=g)[:M].int()      # every token a slot of its own
+    if M > 4:
+        slots[M // 2] = -1                                            # one token is not cached
+    slots = slots.to(DEV)
+    pages = torch.full((2, npages, page, nkv, hd), 7.0, dtype=torch.bfloat16, device=DEV)
+
+    got = gemm_prefill.qkv_rope_write(x, w, b, table, hd, positions, slots, pages, nh, nkv, hd,
+                                      min_tokens=1, ctas=ctas)
+    assert got is not None and got.shape == (M, N)
+    gemm_bf16.check_errors()
+
+    want = _plain_qkv(x, w, b, table, positions, slots, nh, nkv, hd)   # [M, heads, hd]
+    torch.testing.assert_close(got.double().cpu().view(M, -1, hd), want, atol=3e-2, rtol=2e-2)
+    # the cache holds exactly what `out` holds for k and v, at the token's slot; nothing else moved
+    flat = pages.view(2, npages * page, nkv, hd)
+    keep = (slots >= 0).nonzero().flatten()
+    idx = slots[keep].long()
+    outh = got.view(M, nh + 2 * nkv, hd)
+    assert torch.equal(flat[0][idx], outh[keep, nh:nh + nkv])
+    assert torch.equal(flat[1][idx], outh[keep, nh + nkv:])
+    untouched = torch.ones(npages * page, dtype=torch.bool, device=DEV)
+    untouched[idx] = False
+    assert (flat[:, untouched] == 7.0).all()
+
+    # and it agrees with the plain product followed by the rotation kernel
+    qkv2 = gemm_prefill.gemm(x, w, b, torch.bfloat16)
+    pages2 = torch.full_like(pages, 7.0)
+    rope_kv_write(qkv2, table, hd, positions, slots, pages2, nh, nkv, hd)
+    torch.testing.assert_close(got.float(), qkv2.float(), atol=3e-2, rtol=2e-2)
+    torch.testing.assert_close(pages.float(), pages2.float(), atol=3e-2, rtol=2e-2)
+
+
+def test_qkv_epilogue_hands_back_what_it_does_not_take():
+    from ginfer_b200.ops import gemm_prefill
+    nh, nkv, hd, M, K = 2, 1, 48, 64, 64
+    x = torch.zeros(M, K, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros((nh + 2 * nkv) * hd, K, dtype=torch.bfloat16, device=DEV)
+    table = torch.zeros(8, hd, device=DEV)
+    pos = torch.zeros(M, dtype=torch.int32, device=DEV)
+    pages = torch.zeros(2, 8, 16, nkv, hd, dtype=torch.bfloat16, device=DEV)
+    args = (pos, pos, pages, nh, nkv, hd)
+    assert gemm_prefill.qkv_rope_write(x, w, None, table, hd, *args, min_tokens=1) is None  # hd 48
+    nh, nkv, hd = 2, 1, 64
+    w = torch.zeros((nh + 2 * nkv) * hd, K, dtype=torch.bfloat16, device=DEV)
+    pages = torch.zeros(2, 8, 16, nkv, hd, dtype=torch.bfloat16, device=DEV)
+    part = torch.zeros(8, 32, device=DEV)                                  # half the head rotated
+    assert gemm_prefill.qkv_rope_write(x, w, None, part, 32, pos, pos, pages, nh, nkv, hd,
+                                       min_tokens=1) is None
+    assert gemm_prefill.qkv_rope_write(x, w, None, None, 0, pos, pos, pages, nh, nkv, hd,
+                                       min_tokens=1) is None               # no rotation at all

@@ -55,3 +55,58 @@ def test_bfloat16_path_agrees_with_the_32_bit_path_at_large_layer_sizes(name):
     print(f"{name}: scale {scale:.3f} worst {worst:.4f} rms {rms:.4f} "
           f"argmax {(a.argmax(-1) == b.argmax(-1)).float().mean().item():.2f}")
     assert rms <= 0.01 and worst <= 0.03, (rms, worst)
+
+
+@pytest.mark.parametrize("head_dim,heads,kv_heads", [(64, 6, 2), (128, 3, 1)])
+def test_a_step_of_many_tokens_agrees_with_portions_and_with_the_32_bit_path(
+        head_dim, heads, kv_heads, monkeypatch):
+    """From 1,024 tokens on a step's joined q/k/v product rotates q and k and writes the cache in
+    its own epilogue (and the gated product joins SiLU*mul).  The same prompt in one step, in two
+    portions below that size (plain products, the rotation kernel) and on the 32-bit path must
+    give the same logits, for the prompt's last token and for the tokens decoded after it, which
+    read the keys and values the epilogue cached."""
+    from ginfer_b200 import ops
+    from ginfer_b200.engine import ModelRunner, StepEntry
+    from ginfer_b200.engine.loading import random_model
+    cfg = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": 2,
+           "hidden_size": 264, "num_attention_heads": heads, "num_key_value_heads": kv_heads,
+           "head_dim": head_dim, "intermediate_size": 520, "vocab_size": 643, "rope_theta": 1e4,
+           "rms_norm_eps": 1e-6, "max_position_embeddings": 1536, "tie_word_embeddings": False,
+           "use_sliding_window": False, "torch_dtype": "bfloat16"}
+    toks = prompt(1100, 643, 5)
+    tail = prompt(3, 643, 6)
+    served = []
+    inner = ops.qkv_rope_write
+
+    def counted(x, *a, **k):
+        y = inner(x, *a, **k)
+        served.append((x.shape[0], y is not None))
+        return y
+    monkeypatch.setattr(ops, "qkv_rope_write", counted)
+
+    def run(dtype, cuts):
+        model, _ = random_model(cfg, 3, dtype)
+        r = ModelRunner(model, page_size=16, max_num_seqs=2, max_seq_len=1536, num_pages=80,
+                        enforce_eager=True)
+        rows, at = [], 0
+        for n in cuts:
+            y = r.step([StepEntry("a", toks[at:at + n], [n - 1])]).clone()
+            at += n
+        rows.append(y)
+        for t in tail:
+            rows.append(r.step([StepEntry("a", [t], [0])]).clone())
+        del r, model
+        torch.cuda.empty_cache()
+        return torch.cat(rows).float().cpu()
+
+    whole = run("bfloat16", [1100])
+    cut = run("bfloat16", [600, 500])
+    full = run("float32", [1100])
+    # both layers of the one long step, and nothing shorter or in 32-bit
+    assert [m for m, ok in served if ok] == [1100, 1100], served
+    scale = full.abs().max().item()
+    for name, other in (("portions", cut), ("32-bit", full)):
+        worst = (whole - other).abs().max().item() / scale
+        rms = (whole - other).pow(2).mean().sqrt().item() / scale
+        print(f"hd {head_dim} against {name}: scale {scale:.3f} worst {worst:.4f} rms {rms:.4f}")
+        assert rms <= 0.01 and worst <= 0.03, (name, rms, worst)
