@@ -11,6 +11,7 @@ that says so.  It is collected last, and it passes alone in a fresh process as w
 other tests.
 """
 import ctypes
+import gc
 import math
 from ctypes import c_char_p, c_float, c_int, c_void_p
 
@@ -56,6 +57,7 @@ def _case(seed, lens, nh, nkv, page):
 def _static(lib, c, nh, nkv, page, window, splits):
     B = c["qkv"].shape[0]
     out = torch.full((B, nh * HD), float("nan"), dtype=torch.bfloat16, device=DEV)
+    gc.collect()            # tensors that earlier tests left in cycles go now, not during the call
     torch.cuda.synchronize()
     before = torch.cuda.memory_allocated(DEV), torch.cuda.memory_reserved(DEV)
     rc = lib.gf_attn_decode_static(
