@@ -63,7 +63,7 @@ def test_cuts_agree_with_plain(folders, name, dtype, cut):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_decode_steps_replayed_from_cuda_graphs(folders, name, dtype):
     """Long decoding, one token a step for two requests side by side, with decode steps replayed
     from CUDA graphs (as serving does) and the block table growing past a graph's width."""
