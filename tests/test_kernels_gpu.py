@@ -218,6 +218,10 @@ ATT_CASES = [
     ([515, 260], [2, 260], 12, 2, 128, 16, 0),
     ([700, 90], [65, 90], 6, 3, 64, 16, 100),
     ([1100], [1100], 14, 2, 64, 32, 0),
+    # head sizes that are no multiples of 32 or 64, and one of three 64-channel parts
+    ([130, 40, 260], [130, 1, 37], 4, 2, 80, 16, 0),
+    ([200, 33], [64, 33], 2, 1, 112, 8, 20),
+    ([300, 70], [5, 70], 6, 2, 192, 16, 50),
 ]
 
 
@@ -280,6 +284,8 @@ DEC_CASES = [
     ([515, 260, 4000], 12, 2, 128, 16, 0),
     ([700, 90], 6, 3, 64, 16, 100),
     ([2049, 17], 40, 2, 64, 16, 0),               # 20 query heads per kv head: two chunks of 16
+    ([130, 40, 700], 6, 2, 80, 16, 0),            # five steps of 16 channels
+    ([300, 70], 6, 2, 192, 8, 50),
 ]
 
 
@@ -305,6 +311,7 @@ DEC_TMA_CASES = [   # what the kernel that loads by TMA serves: page sizes and h
     ([1500, 700], 6, 3, 128, 16, 130),           # a window that starts inside a tile
     ([4100], 18, 2, 64, 16, 0),                   # 9 query heads per kv head: two chunks of 8
     ([300, 70, 8], 4, 2, 256, 8, 0),              # 64 boxes a tile: two for each lane of the loader
+    ([600, 70, 9], 6, 2, 192, 16, 40),            # three 64-channel parts a row
 ]
 
 

@@ -10,8 +10,9 @@ from tiny import CONFIGS, make_folder, prompt
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [5, 17, 33, 70, 130, 49], "B": [1, 40, 90, 200, 66, 133], "C": [3, 64, 97, 35]}
-PAGE = {"A": 16, "B": 8, "C": 4}
+LENGTHS = {"A": [5, 17, 33, 70, 130, 49], "B": [1, 40, 90, 200, 66, 133], "C": [3, 64, 97, 35],
+           "D": [2, 81, 150, 64, 33]}
+PAGE = {"A": 16, "B": 8, "C": 4, "D": 32}
 
 
 def _requests(name):
@@ -41,8 +42,8 @@ def _runner(model_dir, dtype, page, max_tokens, eager=True):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
-@pytest.mark.parametrize("cut", ["whole", "tail", "portions", "mixed", "mixed_singles_first"])
+@pytest.mark.parametrize("name,cut", [(n, c) for n in "ABC" for c in (
+    "whole", "tail", "portions", "mixed", "mixed_singles_first")] + [("D", "tail"), ("D", "mixed")])
 def test_cuts_agree_with_plain(folders, name, dtype, cut):
     model_dir = folders[(name, _storage(dtype))]
     reqs = _requests(name)

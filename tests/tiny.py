@@ -36,7 +36,19 @@ TINY_C = {
     "max_window_layers": 0, "torch_dtype": "float32", "eos_token_id": 300,
 }
 
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# a fourth one with a head size of 80 (five steps of 16: no multiple of 32), wider heads than the
+# model (6 x 80 = 480 channels from a width of 112), one layer: used where a further head size is
+# worth a run, not in every test
+TINY_D = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 1, "hidden_size": 112, "num_attention_heads": 6,
+    "num_key_value_heads": 3, "head_dim": 80, "intermediate_size": 200, "vocab_size": 277,
+    "rope_theta": 200000.0, "rms_norm_eps": 2e-5, "max_position_embeddings": 256,
+    "tie_word_embeddings": True, "use_sliding_window": False, "torch_dtype": "float32",
+    "eos_token_id": 1,
+}
+
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 
 
 def sharpen(model_dir: str, q_scale: float = 12.0) -> None:
