@@ -424,6 +424,8 @@ def main() -> int:
                     help="layer sizes: the benchmark's own (default) or the larger ones the "
                          "baseline names")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--prefill-reps", type=int, default=5,
+                    help="timed repetitions of the 2,048-token prefill (the median is reported)")
     ap.add_argument("--enforce-eager", action="store_true")
     ap.add_argument("--micro", choices=MICRO, default=None,
                     help="run one small kernel workload (for profiling) instead of the benchmark")
@@ -470,7 +472,7 @@ def main() -> int:
     ms, launches = decode_device_timed(eng, B, args.steps, args.warmup, seed=1)
     clock_info = clocks.stop()
     e2e_ms, h2d, d2h = decode_end_to_end(eng, B, args.steps, args.warmup, seed=2)
-    pre_ms = prefill_timed(eng, PREFILL_TOKENS, reps=5, warmup=3, seed=3)
+    pre_ms = prefill_timed(eng, PREFILL_TOKENS, reps=max(1, args.prefill_reps), warmup=3, seed=3)
     points = {}
     if not args.skip_points:
         for b in (1, 64):

@@ -166,6 +166,23 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// 2^x on the FMA and integer pipes, for a share of a tile's exponentials: the special-function
+// unit gives 16 results a cycle and SM, and a tile of 128 x 128 scores wants 16,384 of them.
+// x = n + f with n the nearest integer (read from the low mantissa bits of x + 1.5 * 2^23) and
+// f in [-0.5, 0.5]; 2^f by a cubic whose largest relative error there is 7.5e-5 (the result is
+// rounded to bf16, 3.9e-3, right after); n is added to the exponent field.  x is clamped at -126.
+#ifndef GF_POLY_EXP_EVERY
+#define GF_POLY_EXP_EVERY 4          // every n-th exponential of an unmasked tile; 0: none
+#endif
+__device__ __forceinline__ float poly_exp2(float x) {
+  x = fmaxf(x, -126.f);
+  const float t = x + 12582912.f;
+  const float f = x - (t - 12582912.f);
+  float p = fmaf(0.05517132207751274f, f, 0.24261054396629333f);
+  p = fmaf(p, f, 0.6932609677314758f);
+  p = fmaf(p, f, 0.9999281167984009f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -527,14 +544,31 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const float msub = m_new == -INFINITY ? 0.f : m_new;
         // probabilities (in place) and the row sum, while P V of the tile before may still run
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        if (GF_POLY_EXP_EVERY > 0 && interior) {
+          // no key of this tile is masked for this warp: every score is finite
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc)
+          for (int cc = 0; cc < 2; ++cc)
 #pragma unroll
-          for (int k = 0; k < 32; ++k) {
-            const float e = fast_exp2(fmaf(v[cc][k], scale_log2, -msub));
-            v[cc][k] = e;
-            sum4[k & 3] += e;
-          }
+            for (int k = 0; k < 32; ++k) {
+              const float x = fmaf(v[cc][k], scale_log2, -msub);
+              const float e = (GF_POLY_EXP_EVERY > 0 &&
+                               k % (GF_POLY_EXP_EVERY > 0 ? GF_POLY_EXP_EVERY : 1) ==
+                                   GF_POLY_EXP_EVERY - 1)
+                                  ? poly_exp2(x)
+                                  : fast_exp2(x);
+              v[cc][k] = e;
+              sum4[k & 3] += e;
+            }
+        } else {
+#pragma unroll
+          for (int cc = 0; cc < 2; ++cc)
+#pragma unroll
+            for (int k = 0; k < 32; ++k) {
+              const float e = fast_exp2(fmaf(v[cc][k], scale_log2, -msub));
+              v[cc][k] = e;
+              sum4[k & 3] += e;
+            }
+        }
         const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
         if (tr) { GF_STAMP(0, i, 4); }
         // O and the P buffer are free once P V of the tile before is complete (the item's first

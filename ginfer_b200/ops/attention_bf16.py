@@ -2,6 +2,7 @@
 tensor-core prefill over the paged cache.  The library is compiled for the model's head size."""
 from __future__ import annotations
 
+import os
 from ctypes import c_float, c_int, c_void_p
 
 import torch
@@ -126,6 +127,13 @@ def tc_supports(hd: int, page_size: int) -> bool:
     return hd in (64, 128) and page_size % 8 == 0 and 128 % page_size == 0
 
 
+# GINFER_B200_ATTN_POLY_EXP=n: every n-th exponential of an unmasked tile of the tcgen05 prefill
+# kernel is computed by a polynomial on the FMA pipe instead of the special-function unit (0:
+# none; unset: the kernel's own default).  A build of its own for each value.
+_TC_EXTRA_DEFINES = ((f"GF_POLY_EXP_EVERY={int(os.environ['GINFER_B200_ATTN_POLY_EXP'])}",)
+                     if os.environ.get("GINFER_B200_ATTN_POLY_EXP") else ())
+
+
 def prefill_tc(qkv, pages, block_table, cu_seqlens_q, kv_lens, B, max_q_len, nh, nkv, hd, scale,
                window, page_size, trace=None, out=None):
     """Prefill attention on tcgen05 (``csrc/attention_tc.cu``); ``None`` if it cannot serve the
@@ -143,7 +151,7 @@ def prefill_tc(qkv, pages, block_table, cu_seqlens_q, kv_lens, B, max_q_len, nh,
     f = _fn("attention_tc", "gf_attn_prefill_tc",
             [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
-             c_void_p, c_void_p], (f"GF_HEAD_DIM={hd}",))
+             c_void_p, c_void_p], (f"GF_HEAD_DIM={hd}",) + _TC_EXTRA_DEFINES)
     rc = f(_p(qkv), qkv.stride(0), _p(pages[0]), _p(pages[1]), pages.shape[1], _p(block_table),
            block_table.stride(0), _p(cu_seqlens_q), _p(kv_lens), _p(out), T, B, int(max_q_len),
            nh, nkv, page_size, int(window), float(scale), _p(_dev_state(qkv.device)["err"]),
