@@ -129,7 +129,7 @@ def tc_supports(hd: int, page_size: int) -> bool:
 
 # GINFER_B200_ATTN_POLY_EXP=n: every n-th exponential of an unmasked tile of the tcgen05 prefill
 # kernel is computed by a polynomial on the FMA pipe instead of the special-function unit (0:
-# none; unset: the kernel's own default).  A build of its own for each value.
+# none, which is also the default: no share measured faster).  A build of its own for each value.
 _TC_EXTRA_DEFINES = ((f"GF_POLY_EXP_EVERY={int(os.environ['GINFER_B200_ATTN_POLY_EXP'])}",)
                      if os.environ.get("GINFER_B200_ATTN_POLY_EXP") else ())
 
