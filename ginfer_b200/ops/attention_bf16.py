@@ -130,15 +130,15 @@ def tc_supports(hd: int, page_size: int) -> bool:
 # GINFER_B200_ATTN_POLY_EXP=n: every n-th exponential of an unmasked tile of the tcgen05 prefill
 # kernel is computed by a polynomial on the FMA pipe instead of the special-function unit (0:
 # none, which is also the default: no share measured faster).  A build of its own for each value.
-_TC_EXTRA_DEFINES = ((f"GF_POLY_EXP_EVERY={int(os.environ['GINFER_B200_ATTN_POLY_EXP'])}",)
-                     if os.environ.get("GINFER_B200_ATTN_POLY_EXP") else ())
+POLY_EXP_EVERY = int(os.environ.get("GINFER_B200_ATTN_POLY_EXP") or 0)
 
 
 def prefill_tc(qkv, pages, block_table, cu_seqlens_q, kv_lens, B, max_q_len, nh, nkv, hd, scale,
-               window, page_size, trace=None, out=None):
+               window, page_size, trace=None, out=None, poly_exp_every: int | None = None):
     """Prefill attention on tcgen05 (``csrc/attention_tc.cu``); ``None`` if it cannot serve the
     shapes.  ``trace``: an int64 tensor of ``768 + 4 * CTAs`` slots that receives clock stamps of
-    the first CTA's phases and, behind them, every CTA's (start ns, end ns, SM) (for tuning)."""
+    the first CTA's phases and, behind them, every CTA's (start ns, end ns, SM) (for tuning).
+    ``poly_exp_every``: see ``POLY_EXP_EVERY`` (``None``: that default)."""
     from ctypes import c_float, c_int, c_void_p
 
     from . import _fn, _ok, _p, _stream
@@ -148,10 +148,12 @@ def prefill_tc(qkv, pages, block_table, cu_seqlens_q, kv_lens, B, max_q_len, nh,
     T = qkv.shape[0]
     if out is None:
         out = torch.empty((T, nh * hd), dtype=torch.bfloat16, device=qkv.device)
+    every = POLY_EXP_EVERY if poly_exp_every is None else int(poly_exp_every)
+    defines = (f"GF_HEAD_DIM={hd}",) + ((f"GF_POLY_EXP_EVERY={every}",) if every > 0 else ())
     f = _fn("attention_tc", "gf_attn_prefill_tc",
             [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
-             c_void_p, c_void_p], (f"GF_HEAD_DIM={hd}",) + _TC_EXTRA_DEFINES)
+             c_void_p, c_void_p], defines)
     rc = f(_p(qkv), qkv.stride(0), _p(pages[0]), _p(pages[1]), pages.shape[1], _p(block_table),
            block_table.stride(0), _p(cu_seqlens_q), _p(kv_lens), _p(out), T, B, int(max_q_len),
            nh, nkv, page_size, int(window), float(scale), _p(_dev_state(qkv.device)["err"]),

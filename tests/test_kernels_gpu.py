@@ -277,6 +277,24 @@ def test_attention_tcgen05_prefill(case):
     torch.testing.assert_close(out.double().cpu(), want, atol=1e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("case", [TC_CASES[1], TC_CASES[5], TC_CASES[6]])
+@pytest.mark.parametrize("every", [4, 2])
+def test_attention_tcgen05_prefill_with_a_share_of_exponentials_by_polynomial(case, every):
+    """The build that computes every n-th exponential of an unmasked tile by a cubic on the FMA
+    pipe (off by default) against the oracle and against the default build."""
+    from ginfer_b200.ops import attention_bf16, gemm_bf16
+    lens, qls, nh, nkv, hd, P, window = case
+    dev, want, scale = _paged_case(lens, qls, nh, nkv, hd, P, window, torch.bfloat16)
+    args = (_qkv(dev, nh, nkv, hd), dev["pages"], dev["table"], dev["cu"], dev["kv_lens"],
+            len(lens), max(qls), nh, nkv, hd, scale, window, P)
+    out = attention_bf16.prefill_tc(*args, poly_exp_every=every)
+    assert out is not None
+    gemm_bf16.check_errors()
+    torch.testing.assert_close(out.double().cpu(), want, atol=1e-2, rtol=2e-2)
+    plain = attention_bf16.prefill_tc(*args, poly_exp_every=0)
+    torch.testing.assert_close(out.float(), plain.float(), atol=1e-2, rtol=2e-2)
+
+
 DEC_CASES = [
     ([70, 5, 130, 1], 4, 2, 16, 16, 0),
     ([200, 64, 1, 63, 65], 3, 1, 32, 8, 0),
