@@ -11,8 +11,8 @@ from tiny import CONFIGS, make_folder, prompt
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": [5, 17, 33, 70, 130, 49], "B": [1, 40, 90, 200, 66, 133], "C": [3, 64, 97, 35],
-           "D": [2, 81, 150, 64, 33]}
-PAGE = {"A": 16, "B": 8, "C": 4, "D": 32}
+           "D": [2, 81, 150, 64, 33], "E": [9, 140, 260, 75, 200]}
+PAGE = {"A": 16, "B": 8, "C": 4, "D": 32, "E": 16}
 
 
 def _requests(name):
@@ -43,7 +43,8 @@ def _runner(model_dir, dtype, page, max_tokens, eager=True):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name,cut", [(n, c) for n in "ABC" for c in (
-    "whole", "tail", "portions", "mixed", "mixed_singles_first")] + [("D", "tail"), ("D", "mixed")])
+    "whole", "tail", "portions", "mixed", "mixed_singles_first")] + [("D", "tail"), ("D", "mixed")] + [
+    ("E", c) for c in ("whole", "tail", "portions", "mixed")])
 def test_cuts_agree_with_plain(folders, name, dtype, cut):
     model_dir = folders[(name, _storage(dtype))]
     reqs = _requests(name)
@@ -64,7 +65,7 @@ def test_cuts_agree_with_plain(folders, name, dtype, cut):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "E"])
 def test_decode_steps_replayed_from_cuda_graphs(folders, name, dtype):
     """Long decoding, one token a step for two requests side by side, with decode steps replayed
     from CUDA graphs (as serving does) and the block table growing past a graph's width."""
@@ -85,14 +86,15 @@ def test_decode_steps_replayed_from_cuda_graphs(folders, name, dtype):
             ay += 1
         steps.append({"step": len(steps), "entries": ent, "end": []})
     steps[-1]["end"] = ["x", "y"]
-    runner = _runner(model_dir, dtype, 4, 512, eager=False)
+    # pages of 4 tokens, of 16 where the decode kernel that loads its tiles by TMA is to run
+    runner = _runner(model_dir, dtype, 16 if name == "E" else 4, 512, eager=False)
     rows = replay.run_in_process(runner, steps)
     assert len(runner._graphs) >= 2 and runner.graph_launches > 0
     replay.compare(rows, replay.plain_logits(model_dir, reqs, dtype), dtype, reqs)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "E"])
 @pytest.mark.parametrize("eager", [True, False])
 def test_first_tokens_one_by_one(folders, name, dtype, eager):
     """A sequence fed one token at a time from its very first token (position 0, the first page,

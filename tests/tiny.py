@@ -48,7 +48,19 @@ TINY_D = {
     "eos_token_id": 1,
 }
 
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+# a fifth one with a head size of 64, which the kernels of the large models serve (prefill
+# attention and products on tcgen05, decode attention with tiles by TMA), a window on the second
+# layer that is longer than a key tile
+TINY_E = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 2, "hidden_size": 136, "num_attention_heads": 4,
+    "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 312, "vocab_size": 333,
+    "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "max_position_embeddings": 512,
+    "tie_word_embeddings": False, "use_sliding_window": True, "sliding_window": 70,
+    "max_window_layers": 1, "torch_dtype": "float32", "eos_token_id": 2,
+}
+
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
 
 
 def sharpen(model_dir: str, q_scale: float = 12.0) -> None:
