@@ -9,7 +9,7 @@ returns text; this engine consumes and returns token ids (no tokenizer).
 from __future__ import annotations
 
 import time
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 import numpy as np
 import torch
@@ -18,7 +18,7 @@ from ..config.engine_config import EngineConfig
 from ..ops import gemm_bf16
 from ..sampling import Sampler, SamplingParams
 from .loading import load_model, random_model
-from .request import Request, RequestState
+from .request import Request
 from .runner import ModelRunner, StepEntry
 from .scheduler import Scheduler
 

@@ -6,7 +6,6 @@ import json
 import os
 import sys
 
-import numpy as np
 
 TRACE_PAGE_SIZE = 16          # divides the 64-token rounding of --max-tokens
 TRACE_MAX_LIVE = 4

@@ -7,7 +7,6 @@ tensor that is not on a CUDA device is an error, and so is a library that cannot
 """
 from __future__ import annotations
 
-import ctypes
 from ctypes import c_float, c_int, c_void_p
 
 import torch

@@ -7,8 +7,6 @@ joined at load into one matrix so that one product reads ``y`` once.
 """
 from __future__ import annotations
 
-import torch
-
 from .. import ops
 from .base import FeedForward, Summed, TensorSpec, register_feed_forward
 

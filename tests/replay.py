@@ -10,7 +10,6 @@ import subprocess
 import sys
 
 import numpy as np
-import torch
 
 import plain_qwen2 as plain
 

@@ -1,7 +1,6 @@
 """The persistent kernel that runs every layer of a decode step (off by default): replayed against
 the plain implementation, alone and from CUDA graphs, on the tiny configurations."""
 import pytest
-import torch
 
 import replay
 from test_replay_gpu import PAGE, _requests, _runner, folders  # noqa: F401  (fixture)

@@ -1,13 +1,10 @@
 """Each part of a layer alone against the plain implementation's function for it, and a toy mixer
 with state of its own that is registered, built and stepped without touching the framework."""
-import math
-import os
-
 import pytest
 import torch
 
 import plain_qwen2 as plain
-from tiny import TINY_B, make_folder, prompt
+from tiny import make_folder, prompt
 
 pytestmark = pytest.mark.gpu
 DEV = torch.device("cuda:0")

@@ -6,7 +6,7 @@ import pytest
 import torch
 
 import plain_qwen2 as plain
-from tiny import CONFIGS, make_folder, prompt
+from tiny import make_folder, prompt
 
 
 def test_rms_norm_by_hand():

@@ -1,9 +1,6 @@
 """Replay of the same requests under every way of cutting them into steps, in 32-bit and in
 bfloat16, against the plain implementation."""
-import os
-
 import pytest
-import torch
 
 import replay
 from tiny import CONFIGS, make_folder, prompt
