@@ -24,7 +24,14 @@ def _code(dt: torch.dtype) -> int:
 
 
 def _p(t):
-    return None if t is None else c_void_p(t.data_ptr())
+    """The device address of a tensor for a kernel (``None`` stays ``None``).  A tensor that is
+    not on a CUDA device is refused here: its address would mean nothing to a kernel."""
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise RuntimeError("ginfer_b200 kernels run on a CUDA device only; got a tensor on "
+                           f"{t.device}")
+    return c_void_p(t.data_ptr())
 
 
 def _stream():

@@ -63,6 +63,9 @@ def _lib(head_dim: int):
 
 
 def _ptr(t):
+    if t is not None and not t.is_cuda:
+        raise RuntimeError("ginfer_b200 kernels run on a CUDA device only; got a tensor on "
+                           f"{t.device}")
     return None if t is None else c_void_p(t.data_ptr())
 
 

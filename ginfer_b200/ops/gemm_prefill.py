@@ -20,10 +20,11 @@ def gemm(x, weight, bias_f32=None, out_dtype=torch.bfloat16, epi: int = 0, ctas:
     """``x [M, K] @ weight[N, K]^T``; ``epi`` 0: (+ bias) -> ``[M, N]``; ``epi`` 2: weight rows
     are interleaved (gate_i, up_i) and the result is ``silu(gate) * up`` -> ``[M, N / 2]``.
     ``ctas``: CTAs to launch (0: one an SM).  ``None`` if the kernel cannot serve the shape."""
-    from . import _fn, _ok, _p, _stream
+    from . import _cuda, _fn, _ok, _p, _stream
     from .gemm_bf16 import error_word
     if not supports(x, weight):
         return None
+    _cuda(x, weight, bias_f32)
     M, K = x.shape
     N = weight.shape[0]
     cols = N // 2 if epi == 2 else N
@@ -46,31 +47,42 @@ QKV_MIN_TOKENS = 1024     # below this cuBLAS and the rotation kernel behind it 
 QKV_EPILOGUE = os.environ.get("GINFER_B200_QKV_EPILOGUE", "1") != "0"
 
 
+def qkv_epilogue_serves(x, weight, table, rot, positions, slot_mapping, pages, nh, nkv, hd,
+                        min_tokens: int) -> bool:
+    """Whether :func:`qkv_rope_write` takes this case: at least ``min_tokens`` tokens, head sizes 64
+    and 128 with the whole head rotated, a run that writes its cache, bf16 operands and pages,
+    an fp32 table, int32 positions and slots."""
+    M = x.shape[0]
+    return not (M < min_tokens or hd not in (64, 128) or table is None or rot != hd
+                or slot_mapping is None or x.dtype != torch.bfloat16 or not supports(x, weight)
+                or weight.dtype != torch.bfloat16
+                or weight.shape[0] != (nh + 2 * nkv) * hd or table.dtype != torch.float32
+                or not table.is_contiguous() or table.shape[1] != hd or table.data_ptr() % 16
+                or pages.dtype != torch.bfloat16 or not pages.is_contiguous()
+                or pages.shape[0] != 2 or tuple(pages.shape[3:]) != (nkv, hd)
+                or positions.dtype != torch.int32 or slot_mapping.dtype != torch.int32
+                or not positions.is_contiguous() or not slot_mapping.is_contiguous()
+                or positions.numel() < M or slot_mapping.numel() < M)
+
+
 def qkv_rope_write(x, weight, bias_f32, table, rot, positions, slot_mapping, pages, nh, nkv, hd,
                    min_tokens: int | None = None, ctas: int = 0):
     """The q/k/v product of a step of many tokens with bias, the rotation of q and k and the write
     of k and v to the paged cache in its epilogue (what :func:`ginfer_b200.ops.rope_kv_write`
     does behind a plain product).  ``pages [2, num_pages, page, nkv, hd]`` bf16.  Returns
     ``[T, (nh + 2 nkv) hd]`` with q and k rotated, or ``None`` if the kernel does not serve the
-    case (head sizes 64 and 128, the whole head rotated, at least ``min_tokens`` tokens,
-    ``QKV_MIN_TOKENS`` unless given)."""
-    from . import _fn, _ok, _p, _stream
+    case (:func:`qkv_epilogue_serves`; ``min_tokens`` is ``QKV_MIN_TOKENS`` unless given)."""
+    from . import _cuda, _fn, _ok, _p, _stream
     from .gemm_bf16 import error_word
     M, K = x.shape
     if min_tokens is None:
         if not QKV_EPILOGUE:
             return None
         min_tokens = QKV_MIN_TOKENS
-    if (M < min_tokens or hd not in (64, 128) or table is None or rot != hd
-            or slot_mapping is None or x.dtype != torch.bfloat16 or not supports(x, weight)
-            or weight.shape[0] != (nh + 2 * nkv) * hd or table.dtype != torch.float32
-            or not table.is_contiguous() or table.shape[1] != hd or table.data_ptr() % 16
-            or pages.dtype != torch.bfloat16 or not pages.is_contiguous()
-            or pages.shape[0] != 2 or tuple(pages.shape[3:]) != (nkv, hd)
-            or positions.dtype != torch.int32 or slot_mapping.dtype != torch.int32
-            or not positions.is_contiguous() or not slot_mapping.is_contiguous()
-            or positions.numel() < M or slot_mapping.numel() < M):
+    if not qkv_epilogue_serves(x, weight, table, rot, positions, slot_mapping, pages, nh, nkv, hd,
+                               min_tokens):
         return None
+    _cuda(x, weight, bias_f32, table, positions, slot_mapping, pages)
     out = torch.empty((M, weight.shape[0]), dtype=torch.bfloat16, device=x.device)
     f = _fn("gemm_prefill", "gf_gemm_prefill_qkv",
             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,

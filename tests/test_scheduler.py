@@ -286,3 +286,44 @@ def test_split_choices_of_the_kernels():
     assert gemm_bf16.split_k_for(8, 17920, 1536) == 2                # gate/up: about a tile an SM
     assert gemm_bf16.split_k_for(8, 151936, 1536) == 1               # the head: tiles for all SMs
     assert gemm_bf16.split_k_for(64, 17920, 1536) == 1
+
+
+def test_the_q_k_v_epilogue_is_only_offered_what_it_takes():
+    """The product that rotates q/k and writes the cache in its epilogue hands back every case it
+    does not serve (the plain product and the rotation kernel run then): few tokens, other head
+    sizes, a partly rotated head, no rotation, 32-bit operands, tables or pages of another type;
+    and it refuses tensors that are not on a CUDA device instead of handing their addresses to a
+    kernel."""
+    import pytest
+    import torch
+
+    from ginfer_b200.ops import gemm_prefill
+    nh, nkv, hd, M, K = 4, 2, 64, 2048, 128
+    N = (nh + 2 * nkv) * hd
+    x = torch.zeros(M, K, dtype=torch.bfloat16)
+    w = torch.zeros(N, K, dtype=torch.bfloat16)
+    table = torch.zeros(16, hd)
+    pos = torch.zeros(M, dtype=torch.int32)
+    pages = torch.zeros(2, 4, 16, nkv, hd, dtype=torch.bfloat16)
+
+    def offered(**kw):
+        a = dict(x=x, weight=w, table=table, rot=hd, positions=pos, slot_mapping=pos, pages=pages,
+                 nh=nh, nkv=nkv, hd=hd, min_tokens=gemm_prefill.QKV_MIN_TOKENS)
+        a.update(kw)
+        return gemm_prefill.qkv_epilogue_serves(**a)
+    assert offered()
+    assert not offered(x=x[:1000])                                         # fewer than 1,024 tokens
+    assert offered(x=x[:1000], min_tokens=1)
+    assert not offered(x=x.float()) and not offered(table=table.double())
+    assert not offered(rot=hd // 2, table=torch.zeros(16, hd // 2))        # a partly rotated head
+    assert not offered(table=None, rot=0)
+    assert not offered(slot_mapping=None)                                   # a run that does not write
+    assert not offered(pages=pages.float()) and not offered(pages=pages[:, :, :, :1])
+    assert not offered(positions=pos.long()) and not offered(slot_mapping=pos[:5])
+    assert not offered(hd=32, nh=8, nkv=4, table=torch.zeros(16, 32), rot=32,
+                       pages=torch.zeros(2, 4, 16, 4, 32, dtype=torch.bfloat16))
+    assert not offered(weight=w[:-hd]) and not offered(weight=w.float())    # rows that are no heads
+    with pytest.raises(RuntimeError, match="CUDA device only"):
+        gemm_prefill.qkv_rope_write(x, w, None, table, hd, pos, pos, pages, nh, nkv, hd)
+    with pytest.raises(RuntimeError, match="CUDA device only"):
+        gemm_prefill.gemm(x, w)
