@@ -356,7 +356,12 @@ def run_micro(name: str) -> int:
 
 
 # ----------------------------------------------------------------------------- scenarios
-SCENARIOS = ("serve64", "chunked")
+SCENARIOS = ("serve64", "chunked", "ref256")
+
+# what 11Aln0/ginfer publishes for its own throughput run (README.md:51-53 and the log under
+# media/): one A40, a 1.5B Qwen2-architecture model in bf16
+REF256_PUBLISHED = {"hardware": "A40", "prefill_tok_s": 31590.0, "decode_tok_s": 5457.0,
+                    "total_tok_s": 16138.0}
 
 
 def run_scenario(name: str, shape: str, layers: int | None) -> int:
@@ -364,7 +369,12 @@ def run_scenario(name: str, shape: str, layers: int | None) -> int:
     point (scheduler, chunked prompts, decode graphs), wall clock, second pass reported (the first
     one captures graphs).  ``serve64``: continuous batching of 64 requests, prompts of 128..2048
     tokens, 64..256 generated each.  ``chunked``: 8 prompts of 8,192 tokens fed in 2,048-token
-    portions beside 32 requests that generate 256 tokens each.  One JSON line."""
+    portions beside 32 requests that generate 256 tokens each.  ``ref256``: the reference's own
+    throughput run (``ginfer/test/test_engine.cc:57-112``): 256 prompts of 512 random ids, 128
+    tokens generated for each, EOS ignored, a budget of 16,384 tokens a step, 256 requests at a
+    time, pages of 16; prefill and decode tok/s counted as the reference counts them (a step with
+    a prompt portion counts its tokens, another step its requests, each over its own wall time:
+    ``ginfer/engine/engine.cc:73-121``) beside the figures it publishes.  One JSON line."""
     import random
     import time
 
@@ -384,6 +394,12 @@ def run_scenario(name: str, shape: str, layers: int | None) -> int:
         eng = Engine(config=cfg, dtype="bfloat16", max_num_seqs=64, max_seq_len=8192,
                      max_num_batched_tokens=2048, kvcache_block_size=PAGE,
                      num_kvcache_blocks=64 * (2304 // PAGE + 2))
+    elif name == "ref256":
+        prompts = [[rng.randrange(V) for _ in range(512)] for _ in range(256)]
+        params = [SamplingParams(max_tokens=128, ignore_eos=True)] * 256
+        eng = Engine(config=cfg, dtype="bfloat16", max_num_seqs=256, max_seq_len=CONTEXT,
+                     max_num_batched_tokens=16384, kvcache_block_size=PAGE,
+                     num_kvcache_blocks=256 * (640 // PAGE + 2))
     else:
         prompts = ([[rng.randrange(V) for _ in range(32)] for _ in range(32)] +
                    [[rng.randrange(V) for _ in range(8192)] for _ in range(8)])
@@ -396,6 +412,7 @@ def run_scenario(name: str, shape: str, layers: int | None) -> int:
     for _ in range(2):
         torch.cuda.synchronize()
         t0, s0 = time.perf_counter(), eng.runner.steps_run
+        st0 = dict(vars(eng.stats))
         outs = eng.generate(prompts, params)
         torch.cuda.synchronize()
         dt, steps = time.perf_counter() - t0, eng.runner.steps_run - s0
@@ -406,6 +423,12 @@ def run_scenario(name: str, shape: str, layers: int | None) -> int:
                   "ms_per_step": round(1e3 * dt / steps, 3),
                   "total_tok_s": round((tin + tout) / dt, 1),
                   "generated_tok_s": round(tout / dt, 1), "preemptions": eng.stats.preemptions}
+        if name == "ref256":
+            d = {k: getattr(eng.stats, k) - st0[k] for k in
+                 ("prefill_tokens", "prefill_seconds", "decode_tokens", "decode_seconds")}
+            result["prefill_tok_s"] = round(d["prefill_tokens"] / max(d["prefill_seconds"], 1e-9), 1)
+            result["decode_tok_s"] = round(d["decode_tokens"] / max(d["decode_seconds"], 1e-9), 1)
+            result["reference_published"] = REF256_PUBLISHED
     print(json.dumps(result))
     return 0
 
