@@ -327,3 +327,37 @@ def test_the_q_k_v_epilogue_is_only_offered_what_it_takes():
         gemm_prefill.qkv_rope_write(x, w, None, table, hd, pos, pos, pages, nh, nkv, hd)
     with pytest.raises(RuntimeError, match="CUDA device only"):
         gemm_prefill.gemm(x, w)
+
+
+def test_the_reference_benchmark_workload_is_scheduled_in_nine_prompt_steps():
+    """256 prompts of 512 tokens, 128 tokens generated for each, a budget of 16,384 tokens a step
+    and 256 requests at a time (the reference's own throughput run): about 32 prompts a step,
+    while the requests admitted earlier decode beside them, then decode steps of all 256; nobody
+    is preempted and every page and slot comes back."""
+    page = 16
+    sched, cache = _sched(pages=256 * (640 // page + 2), page=page, seqs=256, budget=16384,
+                          max_len=4096)
+    reqs = [Request(i, [(i + j) % 97 for j in range(512)],
+                    SamplingParams(max_tokens=128, ignore_eos=True)) for i in range(256)]
+    for r in reqs:
+        sched.add(r)
+    steps, prompt_steps = 0, 0
+    while not sched.is_finished():
+        batch, dropped = sched.schedule()
+        assert not dropped and batch
+        assert sum(s.num_tokens for s in batch) <= 16384 and len(batch) <= 256
+        for s in batch:
+            cache.reserve(s.request.request_id, s.num_tokens)
+        for s in batch:
+            cache.commit(s.request.request_id, s.num_tokens)
+        prompt_steps += any(s.num_tokens > 1 for s in batch)
+        sched.postprocess(batch, [5] * sum(1 for s in batch if s.sample))
+        steps += 1
+        assert steps < 400
+    cache.check()
+    # 131,072 prompt tokens are eight budgets, but the requests that decode already take their
+    # token of each step's budget first: the last prompts spill into a ninth step
+    assert prompt_steps == 9
+    assert all(len(r.output) == 128 and r.finish_reason == "max_tokens" for r in reqs)
+    assert sched.num_preemptions == 0
+    assert cache.free_pages() == [256 * (640 // page + 2)] and cache.slots.num_free == 256
