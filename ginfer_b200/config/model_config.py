@@ -27,6 +27,36 @@ class ConfigError(ValueError):
 _TORCH_DTYPES = ("bfloat16", "float16", "float32")
 
 
+def _refuse_what_changes_the_arithmetic(d: Mapping[str, Any], layers: int, window_of) -> None:
+    """Keys that other loaders of Qwen2 folders honour and that would change the result if they
+    were set to anything but their plain value: this engine does not implement them, so a folder
+    that sets them is refused instead of being run as if it had not."""
+    scaling = d.get("rope_scaling")
+    if scaling is not None:
+        kind = scaling
+        if isinstance(scaling, Mapping):
+            kind = scaling.get("rope_type", scaling.get("type"))
+        if kind not in (None, "default"):
+            raise ConfigError(f"config.json: rope_scaling {scaling!r} is not supported (only plain "
+                              "rotary positions at rope_theta)")
+    act = d.get("hidden_act")
+    if act is not None and act not in ("silu", "swish"):
+        raise ConfigError(f"config.json: hidden_act {act!r} is not supported (the feed-forward "
+                          "is SiLU(gate) * up)")
+    if d.get("use_mrope"):
+        raise ConfigError("config.json: use_mrope is not supported")
+    kinds = d.get("layer_types")
+    if kinds is not None:
+        if not isinstance(kinds, (list, tuple)) or len(kinds) != layers:
+            raise ConfigError(f"config.json: layer_types must list {layers} layers")
+        for i, k in enumerate(kinds):
+            want = "sliding_attention" if window_of(i) > 0 else "full_attention"
+            if k != want:
+                raise ConfigError(
+                    f"config.json: layer_types[{i}] is {k!r} but use_sliding_window, "
+                    f"sliding_window and max_window_layers make layer {i} {want!r}")
+
+
 def _require(d: Mapping[str, Any], key: str, typ):
     if key not in d:
         raise ConfigError(f"config.json: required key '{key}' is missing")
@@ -108,6 +138,7 @@ class Qwen2Config:
             extra={k: v for k, v in d.items() if k not in known},
         )
         cfg.validate()
+        _refuse_what_changes_the_arithmetic(d, layers, cfg.layer_window)
         return cfg
 
     @classmethod

@@ -45,12 +45,31 @@ def test_eos_list_and_window_layers():
     ({"eos_token_id": 4096}, "eos"),
     ({"vocab_size": 0}, "positive"),
     ({"hidden_size": "64"}, "integer"),
+    # options of other loaders that would change the result: refused, not ignored
+    ({"rope_scaling": {"rope_type": "yarn", "factor": 4.0}}, "rope_scaling"),
+    ({"rope_scaling": {"type": "linear", "factor": 2.0}}, "rope_scaling"),
+    ({"hidden_act": "gelu"}, "hidden_act"),
+    ({"use_mrope": True}, "use_mrope"),
+    ({"layer_types": ["full_attention"]}, "layer_types must list 2"),
+    ({"layer_types": ["full_attention", "sliding_attention"]}, "layer_types\\[1\\]"),
 ])
 def test_validation_errors(patch, match):
     d = dict(TINY_A)
     d.update(patch)
     with pytest.raises(ConfigError, match=match):
         Qwen2Config.from_dict(d)
+
+
+def test_plain_values_of_options_that_are_not_implemented_are_accepted():
+    d = dict(TINY_A, rope_scaling=None, hidden_act="silu", use_mrope=False, attention_dropout=0.0,
+             layer_types=["full_attention", "full_attention"], use_cache=True)
+    assert Qwen2Config.from_dict(d).layer_window(1) == 0
+    d["rope_scaling"] = {"rope_type": "default"}
+    Qwen2Config.from_dict(d)
+    b = dict(TINY_B, layer_types=["full_attention", "sliding_attention", "sliding_attention"])
+    cfg = Qwen2Config.from_dict(b)
+    assert [cfg.layer_window(i) for i in range(3)] == [0, 48, 48]
+    assert Qwen2Config.from_dict(cfg.to_dict()) == cfg
 
 
 def test_round_trip_and_registry(tmp_path):
