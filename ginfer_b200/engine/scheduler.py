@@ -119,6 +119,10 @@ class Scheduler:
         req.finish_time = time.perf_counter()
         if req in self.running:
             self.running.remove(req)
+        if req in self.waiting:
+            # preempted while its last token was still under way, and that token ended it: a
+            # request left here would be admitted and computed again
+            self.waiting.remove(req)
         if self.cache.has(req.request_id):
             self.cache.release(req.request_id)
 

@@ -146,6 +146,85 @@ def test_out_of_pages_preempts_the_youngest_which_is_computed_again():
     assert cache.free_pages() == [6] and cache.slots.num_free == 4
 
 
+class _PipelinedHost:
+    """Drives a scheduler in the order of ``Engine.step`` with ``pipeline=True``: the step in
+    flight is advanced, the following step is scheduled, prepared and launched (pages reserved
+    and committed), and only then are the tokens of the step in flight resolved."""
+
+    def __init__(self, sched, cache):
+        self.sched, self.cache, self.flight = sched, cache, None
+        self.returned = []
+
+    def _launch(self, batch):
+        for s in batch:
+            assert s.start == self.cache.get(s.request.request_id).num_tokens
+            self.cache.reserve(s.request.request_id, s.num_tokens)
+        for s in batch:
+            self.cache.commit(s.request.request_id, s.num_tokens)
+        return batch
+
+    @staticmethod
+    def _tokens(batch):
+        """What the stand-in model answers: a function of the request's known tokens (its
+        placeholder for the token being chosen left out)."""
+        out = []
+        for s in batch:
+            if s.sample:
+                r = s.request
+                known = (r.prompt + r.output)[:s.start + s.num_tokens]
+                h = 17
+                for t in known:
+                    h = (h * 31 + t) % 1009
+                out.append(h % 97)
+        return out
+
+    def step(self):
+        sched = self.sched
+        if self.flight is None:
+            batch, dropped = sched.schedule()
+            self.returned += dropped
+            if not batch:
+                return
+            self.flight = self._launch(batch)
+        cur = self.flight
+        tokens = self._tokens(cur)           # known to the device only until resolve
+        self.returned += sched.advance(cur)
+        batch, dropped = sched.schedule()
+        self.returned += dropped
+        following = self._launch(batch) if batch else None
+        in_next = {s.request.request_id for s in batch}
+        self.returned += sched.resolve(cur, tokens, in_next)
+        self.flight = following
+        self.cache.check()
+
+    def idle(self):
+        return self.flight is None and self.sched.is_finished()
+
+
+def test_eos_on_a_request_preempted_while_its_token_was_under_way_ends_it_once():
+    # 3 requests of 8 tokens, pages of 4, 6 pages: the youngest is preempted when the others
+    # need their third page, while its first token is still being chosen; that token is its EOS
+    reqs = [_req(i, 8, max_tokens=12, ignore_eos=(i != 2)) for i in range(3)]
+    eos = _PipelinedHost._tokens([type("S", (), dict(request=reqs[2], start=0, num_tokens=8,
+                                                     sample=True))()])[0]
+    sched, cache = _sched(pages=6, page=4, seqs=4, budget=64, max_len=24, eos=(eos,))
+    for r in reqs:
+        sched.add(r)
+    host = _PipelinedHost(sched, cache)
+    seen_waiting_finished = False
+    for _ in range(100):
+        if host.idle():
+            break
+        host.step()
+        seen_waiting_finished |= any(r.state is RequestState.FINISHED for r in sched.waiting)
+    assert host.idle()
+    v = reqs[2]
+    assert v.finish_reason == "eos" and v.output == [eos]
+    assert host.returned.count(v) == 1 and not seen_waiting_finished
+    assert v.num_preemptions >= 1                     # the order the test is about did happen
+    assert cache.free_pages() == [6] and cache.slots.num_free == 4
+
+
 def test_a_request_that_cannot_fit_even_alone_ends_with_out_of_pages():
     sched, cache = _sched(pages=3, page=4, budget=32, max_len=64)
     a = _req(0, 10, max_tokens=30)
