@@ -241,7 +241,7 @@ def prefill_timed(eng, tokens: int, reps: int, warmup: int, seed: int):
 
 # ----------------------------------------------------------------------------- small workloads
 MICRO = ("gemm_gateup_m8", "gemm_down_m8", "gemm_lmhead_m8", "gemm_gateup_m2048", "attn_decode_b8",
-         "attn_decode_b64", "prefill_2layers", "decode_layers_phases")
+         "attn_decode_b64", "prefill_2layers")
 
 
 def run_micro(name: str) -> int:
@@ -310,47 +310,6 @@ def run_micro(name: str) -> int:
             eng.runner.end("p")
         torch.cuda.synchronize()
         print(json.dumps({"micro": name, "tokens": PREFILL_TOKENS}))
-        return 0
-    if name == "decode_layers_phases":
-        # the persistent decode kernel (opt-in) on 4 layers: where a layer's time goes, from the
-        # time stamps the kernel takes at every grid barrier
-        import os
-        os.environ["GINFER_B200_FUSED_DECODE"] = "1"
-        from ginfer_b200.engine import ModelRunner, StepEntry
-        from ginfer_b200.engine.loading import random_model
-        cfg = dict(c)
-        cfg["num_hidden_layers"] = 4
-        B = 8
-        model, _ = random_model(cfg, 0, "bfloat16")
-        runner = ModelRunner(model, page_size=PAGE, max_num_seqs=B, max_seq_len=CONTEXT,
-                             num_pages=B * (PROMPT // PAGE + 8), max_num_batched_tokens=PROMPT,
-                             enforce_eager=True)
-        for b in range(B):
-            runner.step([StepEntry(f"r{b}", torch.randint(0, V, (PROMPT,)).tolist(), [])])
-        for t in range(3):
-            runner.step([StepEntry(f"r{b}", [5 + t], [0]) for b in range(B)])
-        kernel = model.shortcuts[0].kernel
-        ctas = kernel.schedule["ctas"]
-        kernel.stamps = torch.zeros(ctas * 64, dtype=torch.int64, device=dev)
-        runner.step([StepEntry(f"r{b}", [9], [0]) for b in range(B)])
-        torch.cuda.synchronize()
-        kernel.check_errors()
-        st = kernel.stamps.view(ctas, 64).cpu().double()
-        st = (st - st[:, 0].min()) / 1000.0
-        phases = ["qkv", "attention", "out", "gate_up", "down"]
-        rows, prev = [], st[:, 1]
-        for layer in range(1, 4):
-            for ph in range(5):
-                i = 2 + (layer * 5 + ph) * 2
-                if layer == 1 and ph == 0:
-                    prev = st[:, i - 1]
-                work = st[:, i] - prev
-                rows.append({"layer": layer, "phase": phases[ph],
-                             "work_us_mean": round(float(work.mean()), 2),
-                             "work_us_max": round(float(work.max()), 2),
-                             "phase_us": round(float(st[:, i + 1].max() - prev.max()), 2)})
-                prev = st[:, i + 1]
-        print(json.dumps({"micro": name, "schedule": kernel.schedule, "phases": rows}))
         return 0
     raise SystemExit(f"unknown workload {name!r}; known: {MICRO}")
 

@@ -12,6 +12,13 @@
 // 2..5 read the accumulator back with tcgen05.ld and run the epilogue:
 //   EPI_STORE  out = acc (+ bias[n]) as bf16 or fp32
 //   EPI_SILU   W rows are interleaved (gate_i, up_i): out[m, i] = silu(bf16(gate)) * bf16(up)
+//   EPI_RESID  s = resid + acc (+ bias[n]) in fp32, the new residual stream; beside it
+//              bf16(s * gamma[n]) (the operand of the product behind the next RMS norm) and, per
+//              token, this CTA's share of sum_n s^2
+// An RMS normalisation in front of a product costs no kernel of its own: the product before it
+// leaves bf16(s * gamma) and partial sums of squares (EPI_RESID), and the product behind it
+// multiplies its accumulator by 1 / rms[token] = rsqrt(sum of the partials / K + eps) (`in_sumsq`;
+// every epilogue takes it), since (s gamma / rms) W^T = (s gamma) W^T / rms.
 // Products whose tiles alone would leave most SMs idle (the small-N products of a decode step) split
 // the K range, deterministically, in one of two ways.  Cluster mode (split_k 2, 4 or 8): the splits
 // of a tile form a thread-block cluster, park their fp32 partial tiles in their own shared memory,
@@ -31,9 +38,40 @@
 namespace gf {
 
 constexpr int NTHREADS = 192;
-constexpr int EPI_STORE = 0, EPI_SILU = 2;
+constexpr int EPI_STORE = 0, EPI_SILU = 2, EPI_RESID = 3;
+
+struct GemmExtra {
+  // consumer of a deferred RMS normalisation: scale[m] = rsqrt(sum_p in_sumsq[p][m] * inv_k + eps)
+  const float* in_sumsq;     // [in_parts][ss_ld] or null
+  int in_parts;
+  int ss_ld;
+  float in_eps;
+  float inv_k;
+  // EPI_RESID
+  const float* resid;        // [M][ldo]
+  bf16* out_scaled;          // [M][ldo] or null
+  const void* gamma;         // [N], bf16 or fp32
+  int gamma_f32;
+  float* out_sumsq;          // [parts][ss_ld]; part = tile of rows (* splits + split)
+};
 constexpr int kMaxTiles = 1 << 16;
 __device__ unsigned int g_tile_done[kMaxTiles];
+
+#ifdef GF_STAMPS
+// Debug build: every CTA records when it started, issued its prefetch, was released by the kernel
+// ahead, had its accumulator and left (globaltimer, ns), for reading back on the host.
+constexpr unsigned int kStampCap = 1 << 15;
+__device__ unsigned long long g_stamps[kStampCap * 8];
+__device__ unsigned int g_stamp_next;
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define GF_STAMP(i) (g_stamps[(size_t)stamp_slot * 8 + (i)] = gtime())
+#else
+#define GF_STAMP(i) ((void)0)
+#endif
 
 __host__ __device__ constexpr int stages_for(int bn) {
   // Ring of (16 KB + bn * 128 B) stages.  Small token tiles (decode) stay within ~110 KB so that
@@ -50,11 +88,28 @@ template <> __device__ __forceinline__ void store_out<bf16>(bf16* p, float v) {
 }
 template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
 
+__device__ __forceinline__ float gamma_at(const GemmExtra& ex, int n) {
+  return ex.gamma_f32 ? reinterpret_cast<const float*>(ex.gamma)[n]
+                      : __bfloat162float(reinterpret_cast<const bf16*>(ex.gamma)[n]);
+}
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  const float gg = __bfloat162float(__float2bfloat16_rn(g));
+  const float uu = __bfloat162float(__float2bfloat16_rn(u));
+  return gg * (1.0f / (1.0f + expf(-gg))) * uu;
+}
+
 // Epilogue of 16 accumulator columns (tokens m_base .. m_base + 15) of W row n for one thread.
+// `scale`: per-token factors of a deferred normalisation (shared memory, indexed from the tile's
+// first token) or null.  EPI_RESID: sq[j] receives the square of what was stored (0 where nothing).
 template <int EPI, typename OUT>
 __device__ __forceinline__ void epilogue16(float (&v)[16], OUT* __restrict__ out, int ldo,
                                            const float* __restrict__ bias, int n, int m_base,
-                                           int M, int N, int lane) {
+                                           int M, int N, int lane, const float* scale,
+                                           const GemmExtra& ex, float (&sq)[16]) {
+  if (scale) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] *= scale[j];
+  }
   if (EPI == EPI_STORE) {
     const float b = (bias && n < N) ? bias[n] : 0.f;
     if (n < N) {
@@ -62,78 +117,168 @@ __device__ __forceinline__ void epilogue16(float (&v)[16], OUT* __restrict__ out
       for (int j = 0; j < 16; ++j)
         if (m_base + j < M) store_out<OUT>(out + (size_t)(m_base + j) * ldo + n, v[j] + b);
     }
+  } else if (EPI == EPI_RESID) {
+    const float b = (bias && n < N) ? bias[n] : 0.f;
+    const float g = (ex.out_scaled && n < N) ? gamma_at(ex, n) : 0.f;
+    // the residual's loads first and unguarded (clamped): guarded ones would wait in line
+    float r[16];
+    const int nc = min(n, N - 1);
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      r[j] = __ldcg(ex.resid + (size_t)min(m_base + j, M - 1) * ldo + nc);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      sq[j] = 0.f;
+      if (n < N && m_base + j < M) {
+        const size_t at = (size_t)(m_base + j) * ldo + n;
+        const float h = r[j] + (v[j] + b);
+        store_out<OUT>(out + at, h);
+        if (ex.out_scaled) ex.out_scaled[at] = __float2bfloat16_rn(h * g);
+        sq[j] = h * h;
+      }
+    }
   } else {
     // rows come in pairs (gate, up) on adjacent lanes; each lane finishes every other token
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
-      const float mine = __bfloat162float(__float2bfloat16_rn(v[j]));
-      const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+      const float other = __shfl_xor_sync(0xffffffffu, v[j], 1);
       if ((j & 1) == (lane & 1)) {
-        const float g = (lane & 1) ? other : mine, u = (lane & 1) ? mine : other;
+        const float g = (lane & 1) ? other : v[j], u = (lane & 1) ? v[j] : other;
         const int pair = n >> 1;
         if ((n | 1) < N && m_base + j < M)
-          store_out<OUT>(out + (size_t)(m_base + j) * ldo + pair,
-                         g * (1.0f / (1.0f + expf(-g))) * u);
+          store_out<OUT>(out + (size_t)(m_base + j) * ldo + pair, silu_mul(g, u));
       }
     }
   }
 }
 
-// Cluster split-K: every CTA of the cluster sums a band of the tile's rows over all SPLIT peers'
-// parked partial tiles, read through distributed shared memory.  The peers' loads are issued
-// together and the additions stay in rank order.
+// Cluster split-K.  Every CTA parks its partial tile in its own shared memory, token by token:
+// red[token][RED_LD] with the tile's 128 rows side by side.  After the cluster's barrier the
+// first 128 / band CTAs each sum a band of rows (16 at least: a 32-byte sector of bf16 output, so
+// that what they store are whole sectors, which the next kernel's loads need not complete from
+// memory) over all SPLIT peers, read through distributed shared memory; a thread takes four
+// neighbouring rows of one token.  The peers' loads are issued together and the additions stay in
+// rank order.  `scale`: per-token factors in this CTA's shared memory or null.  EPI_RESID: `sqs`
+// (shared memory behind the parked tile, band / 4 * BN floats) takes the squares, which one thread
+// per token adds up in row order into this CTA's part of out_sumsq (parts of idle CTAs are 0).
+constexpr int RED_LD = BM + 4;
+template <int SPLIT> struct Band {
+  static constexpr int rows = (BM / SPLIT + 15) / 16 * 16 < 16 ? 16 : (BM / SPLIT + 15) / 16 * 16;
+};
+
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(bf16* p, const float (&v)[4]) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 w;
+  w.x = *reinterpret_cast<uint32_t*>(&a);
+  w.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = w;
+}
+
 template <int BN, int EPI, typename OUT, int SPLIT>
 __device__ __forceinline__ void cluster_reduce(uint32_t red, const float* __restrict__ bias,
                                                OUT* __restrict__ out, int ldo, int M, int N,
-                                               int n0, int m0) {
+                                               int n0, int m0, const float* scale,
+                                               const GemmExtra& ex, float* sqs) {
   const int rank = (int)cluster_rank();
-  constexpr int band = ((BM + SPLIT - 1) / SPLIT + 1) & ~1;   // rows a CTA adds up (even: row pairs)
-  constexpr int QUADS = BN / 4;                       // a unit of work: one row (pair), 4 tokens
-  if (EPI == EPI_STORE) {
-    for (int u = threadIdx.x; u < band * QUADS; u += NTHREADS) {
-      const int row = rank * band + u % band, c = (u / band) * 4;
-      const int n = n0 + row;
-      if (row >= BM || m0 + c >= M || n >= N) continue;
-      float4 t[SPLIT];
+  constexpr int band = Band<SPLIT>::rows;
+  constexpr int QUADS = band / 4;                     // a unit of work: four rows of one token
+  constexpr int UNITS = QUADS * BN;
+  const bool active = rank * band < BM;
+  // vector stores need four rows that exist and an aligned row of the output
+  const bool vec = (ldo & 3) == 0 && (N & 3) == 0;
+  // EPI_RESID: the residual of this thread's first unit (the only one when the band's units are
+  // no more than the threads, as in decode steps) is asked for before the cluster meets
+  float rs0[4] = {0.f, 0.f, 0.f, 0.f};
+  if (EPI == EPI_RESID && active && threadIdx.x < UNITS) {
+    const int tok = threadIdx.x / QUADS, n = n0 + rank * band + (threadIdx.x % QUADS) * 4;
+    const float* src = ex.resid + (size_t)min(m0 + tok, M - 1) * ldo;
 #pragma unroll
-      for (int p = 0; p < SPLIT; ++p)
-        t[p] = ld_dsmem_f4(red + (uint32_t)((row * (BN + 4) + c) * 4), p);
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < 4; ++j) rs0[j] = __ldcg(src + min(n + j, N - 1));
+  }
+  cluster_sync();                                     // every peer's partial tile is parked
+  if (active) {
+    for (int u = threadIdx.x; u < UNITS; u += NTHREADS) {
+      const int tok = u / QUADS, row = rank * band + (u % QUADS) * 4;
+      const int n = n0 + row, m = m0 + tok;
+      float hh = 0.f;
+      if (m < M && n < N) {
+        float4 t[SPLIT];
 #pragma unroll
-      for (int p = 0; p < SPLIT; ++p) v.x += t[p].x, v.y += t[p].y, v.z += t[p].z, v.w += t[p].w;
-      const float b = bias ? bias[n] : 0.f;
-      const float vv[4] = {v.x + b, v.y + b, v.z + b, v.w + b};
+        for (int p = 0; p < SPLIT; ++p)
+          t[p] = ld_dsmem_f4(red + (uint32_t)((tok * RED_LD + row) * 4), p);
+        float4 a4 = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        if (m0 + c + j < M) store_out<OUT>(out + (size_t)(m0 + c + j) * ldo + n, vv[j]);
+        for (int p = 0; p < SPLIT; ++p)
+          a4.x += t[p].x, a4.y += t[p].y, a4.z += t[p].z, a4.w += t[p].w;
+        float v[4] = {a4.x, a4.y, a4.z, a4.w};
+        if (scale) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) v[j] *= scale[tok];
+        }
+        if (EPI == EPI_SILU) {
+          // rows are (gate, up) pairs: two results
+          const int pair = n >> 1;
+          const float r0 = silu_mul(v[0], v[1]), r1 = silu_mul(v[2], v[3]);
+          OUT* dst = out + (size_t)m * ldo + pair;
+          if (n + 1 < N) store_out<OUT>(dst, r0);
+          if (n + 3 < N) store_out<OUT>(dst + 1, r1);
+        } else {
+          if (bias) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] += bias[min(n + j, N - 1)];
+          }
+          const size_t at = (size_t)m * ldo + n;
+          if (EPI == EPI_RESID) {
+            float rs[4] = {rs0[0], rs0[1], rs0[2], rs0[3]};
+            if (u >= NTHREADS) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) rs[j] = __ldcg(ex.resid + (size_t)m * ldo + min(n + j, N - 1));
+            }
+            float g[4] = {0.f, 0.f, 0.f, 0.f};
+            if (ex.out_scaled) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) g[j] = gamma_at(ex, min(n + j, N - 1));
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              v[j] += rs[j];
+              if (n + j < N) hh += v[j] * v[j];
+              g[j] *= v[j];
+            }
+            if (vec) {
+              store4(out + at, v);
+              if (ex.out_scaled) store4(ex.out_scaled + at, g);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                if (n + j < N) {
+                  store_out<OUT>(out + at + j, v[j]);
+                  if (ex.out_scaled) ex.out_scaled[at + j] = __float2bfloat16_rn(g[j]);
+                }
+            }
+          } else if (vec) {
+            store4(out + at, v);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (n + j < N) store_out<OUT>(out + at + j, v[j]);
+          }
+        }
+      }
+      if (EPI == EPI_RESID) sqs[u] = hh;
     }
-  } else {
-    constexpr int pairs = band / 2;
-    for (int u = threadIdx.x; u < pairs * QUADS; u += NTHREADS) {
-      const int row = rank * band + 2 * (u % pairs), c = (u / pairs) * 4;
-      const int pair = (n0 + row) >> 1;
-      if (row >= BM || m0 + c >= M || n0 + row + 1 >= N) continue;
-      float4 ta[SPLIT], tb[SPLIT];
-#pragma unroll
-      for (int p = 0; p < SPLIT; ++p) {
-        ta[p] = ld_dsmem_f4(red + (uint32_t)((row * (BN + 4) + c) * 4), p);
-        tb[p] = ld_dsmem_f4(red + (uint32_t)(((row + 1) * (BN + 4) + c) * 4), p);
-      }
-      float4 g = make_float4(0.f, 0.f, 0.f, 0.f), up = g;
-#pragma unroll
-      for (int p = 0; p < SPLIT; ++p) {
-        g.x += ta[p].x, g.y += ta[p].y, g.z += ta[p].z, g.w += ta[p].w;
-        up.x += tb[p].x, up.y += tb[p].y, up.z += tb[p].z, up.w += tb[p].w;
-      }
-      const float gv[4] = {g.x, g.y, g.z, g.w}, uv[4] = {up.x, up.y, up.z, up.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float gg = __bfloat162float(__float2bfloat16_rn(gv[j]));
-        const float uu = __bfloat162float(__float2bfloat16_rn(uv[j]));
-        if (m0 + c + j < M)
-          store_out<OUT>(out + (size_t)(m0 + c + j) * ldo + pair,
-                         gg * (1.0f / (1.0f + expf(-gg))) * uu);
-      }
+  }
+  if (EPI == EPI_RESID) {
+    __syncthreads();
+    for (int tok = threadIdx.x; tok < BN; tok += NTHREADS) {
+      float sum = 0.f;
+      if (active)
+        for (int qd = 0; qd < QUADS; ++qd) sum += sqs[tok * QUADS + qd];
+      if (m0 + tok < M)
+        ex.out_sumsq[(size_t)(blockIdx.x * SPLIT + rank) * ex.ss_ld + m0 + tok] = sum;
     }
   }
 }
@@ -142,7 +287,8 @@ template <int BN, int EPI, typename OUT, bool CLUSTER>
 __global__ void __launch_bounds__(NTHREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                const float* __restrict__ bias, OUT* __restrict__ out, int ldo, int M, int N, int K,
-               int split_k, float* __restrict__ workspace, int* __restrict__ err) {
+               int split_k, float* __restrict__ workspace, int* __restrict__ err,
+               const GemmExtra ex) {
   constexpr int STAGES = stages_for(BN);
   constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
   constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
@@ -152,6 +298,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   uint64_t* empty = full + STAGES;
   uint64_t* acc_full = empty + STAGES;
   uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
+  float* scale_s = (float*)(tmem_slot + 2);           // [BN] factors of a deferred normalisation
+  float* sq_s = scale_s + BN;                         // [4][BN] squares per epilogue warp (EPI_RESID)
   __shared__ bool is_last;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -162,6 +310,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   const int nkb = max(0, kb1 - kb0);
 
   pdl_trigger();
+#ifdef GF_STAMPS
+  __shared__ unsigned int stamp_slot;
+  if (threadIdx.x == 0) {
+    stamp_slot = atomicAdd(&g_stamp_next, 1u) % kStampCap;
+    unsigned int smid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    g_stamps[(size_t)stamp_slot * 8 + 0] = ((unsigned long long)N << 32) | (unsigned int)K;
+    g_stamps[(size_t)stamp_slot * 8 + 1] =
+        ((unsigned long long)smid << 32) | (blockIdx.x << 8) | blockIdx.z;
+    GF_STAMP(2);
+  }
+#endif
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full + s, 1);
@@ -192,7 +352,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         mbar_expect_tx(full + i, A_BYTES + B_BYTES);
         tma_load_2d(tiles + i * (A_BYTES + B_BYTES), &tmap_w, full + i, (kb0 + i) * BK, n0);
       }
+      GF_STAMP(3);
       pdl_wait();
+      GF_STAMP(4);
       for (int i = 0; i < pre; ++i)
         tma_load_2d(tiles + i * (A_BYTES + B_BYTES) + A_BYTES, &tmap_x, full + i, (kb0 + i) * BK,
                     m0);
@@ -229,14 +391,84 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     const int q = warp & 3;
     const int n = n0 + q * 32 + lane;
     pdl_wait();                            // nothing is written before the kernel ahead is done
+    // 1 / rms of every token of the tile from the partial sums the product before left behind.
+    // The 128 epilogue threads share the tile's live tokens, 2^k threads a token (at most a
+    // warp), each taking every 2^k-th partial.  The loads go out now, unguarded (clamped: guarded
+    // loads wait in line) and sixteen at a time, and are added up, in a fixed order, only after
+    // the wait for the accumulator, so that their latency hides behind the product.
+    constexpr int SCALE_BATCH = 16;
+    const int live = min(BN, M - m0);
+    int tpt = 1;
+    while (tpt < 32 && tpt * 2 * live <= 128) tpt *= 2;
+    const int e = threadIdx.x - 64, sub = e & (tpt - 1);
+    float part[SCALE_BATCH];
+    if (ex.in_sumsq) {
+      const int tok = e / tpt;                           // the first round's token of this thread
+      const float* src = ex.in_sumsq + m0 + min(tok, live - 1);
+#pragma unroll
+      for (int u = 0; u < SCALE_BATCH; ++u)
+        part[u] = __ldcg(src + (size_t)min(sub + u * tpt, ex.in_parts - 1) * ex.ss_ld);
+    }
+    const float* scale = ex.in_sumsq ? scale_s : nullptr;
     const bool ok = mbar_wait(acc_full, 0, err, 3);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ex.in_sumsq) {
+      for (int t0 = 0; t0 < BN; t0 += 128 / tpt) {         // the same trip count for every thread
+        const int tok = t0 + e / tpt;
+        float sum = 0.f;
+        if (tok < live) {
+          const float* src = ex.in_sumsq + m0 + tok;
+          if (t0 == 0) {
+#pragma unroll
+            for (int u = 0; u < SCALE_BATCH; ++u)
+              sum += sub + u * tpt < ex.in_parts ? part[u] : 0.f;
+          }
+          for (int p0 = sub + (t0 == 0 ? SCALE_BATCH * tpt : 0); p0 < ex.in_parts;
+               p0 += SCALE_BATCH * tpt) {
+            float t[SCALE_BATCH];
+#pragma unroll
+            for (int u = 0; u < SCALE_BATCH; ++u)
+              t[u] = __ldcg(src + (size_t)min(p0 + u * tpt, ex.in_parts - 1) * ex.ss_ld);
+#pragma unroll
+            for (int u = 0; u < SCALE_BATCH; ++u) sum += p0 + u * tpt < ex.in_parts ? t[u] : 0.f;
+          }
+        }
+        for (int o = tpt >> 1; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (sub == 0 && tok < BN) scale_s[tok] = rsqrtf(sum * ex.inv_k + ex.in_eps);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps
+    }
+    if (threadIdx.x == 64) GF_STAMP(5);
     if (ok) {
       const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16);
       if (split_k == 1) {
 #pragma unroll 1
         for (int c = 0; c < BN; c += 16) {
           if (m0 + c >= M) break;
+          float v[16], sq[16];
+          if (nkb > 0) {
+            tmem_ld16(taddr + c, v);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = 0.f;
+          }
+          epilogue16<EPI, OUT>(v, out, ldo, bias, n, m0 + c, M, N, lane, scale ? scale + c : nullptr,
+                               ex, sq);
+          if (EPI == EPI_RESID) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float t = warp_sum(sq[j]);
+              if (lane == 0) sq_s[q * BN + c + j] = t;
+            }
+          }
+        }
+      } else if (CLUSTER) {
+        // park this split's partial tile in shared memory (the ring is drained by now):
+        // red[token][RED_LD], a warp's lanes writing neighbouring rows
+        float* mine = reinterpret_cast<float*>(tiles) + (q * 32 + lane);
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+          if (m0 + c >= M) break;          // the reduction reads live tokens only
           float v[16];
           if (nkb > 0) {
             tmem_ld16(taddr + c, v);
@@ -244,25 +476,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = 0.f;
           }
-          epilogue16<EPI, OUT>(v, out, ldo, bias, n, m0 + c, M, N, lane);
-        }
-      } else if (CLUSTER) {
-        // park this split's partial tile in shared memory (the ring is drained by now):
-        // red[row (128)][RED_LD], rows padded so that float4 stores do not collide
-        float* mine = reinterpret_cast<float*>(tiles) + (size_t)(q * 32 + lane) * (BN + 4);
-#pragma unroll 1
-        for (int c = 0; c < BN; c += 16) {
-          float v[16];
-          if (nkb > 0 && m0 + c < M) {
-            tmem_ld16(taddr + c, v);
-          } else {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = 0.f;
-          }
-#pragma unroll
-          for (int j = 0; j < 16; j += 4)
-            *reinterpret_cast<float4*>(mine + c + j) = make_float4(v[j], v[j + 1], v[j + 2],
-                                                                    v[j + 3]);
+          for (int j = 0; j < 16; ++j) mine[(size_t)(c + j) * RED_LD] = v[j];
         }
       } else {
         // park this split's partial tile: workspace[tile][split][row (128)][col (BN)]
@@ -285,6 +500,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         }
       }
     }
+    if (EPI == EPI_RESID && split_k == 1) {
+      // every epilogue warp arrives, also one whose wait ran out
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      for (int tok = threadIdx.x - 64; tok < BN && ok; tok += 128)
+        if (m0 + tok < M)
+          ex.out_sumsq[(size_t)blockIdx.x * ex.ss_ld + m0 + tok] =
+              (sq_s[tok] + sq_s[BN + tok]) + (sq_s[2 * BN + tok] + sq_s[3 * BN + tok]);
+    }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -293,26 +516,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                  "r"(TMEM_COLS)
                  : "memory");
   }
-  if (split_k == 1) return;
+  if (split_k == 1) {
+    if (threadIdx.x == 0) GF_STAMP(6);
+    return;
+  }
+  const float* scale = ex.in_sumsq ? scale_s : nullptr;
 
   if (CLUSTER) {
-    // every CTA of the cluster sums a band of rows over all peers, in rank order
+    // every CTA of the cluster sums a band of rows over all peers, in rank order (the reduction
+    // begins with the cluster's barrier)
     pdl_wait();
-    cluster_sync();
     const uint32_t red = smem_u32(tiles);
+    float* sqs = reinterpret_cast<float*>(tiles) + (size_t)BN * RED_LD;    // behind the parked tile
     if (split_k == 2)
-      cluster_reduce<BN, EPI, OUT, 2>(red, bias, out, ldo, M, N, n0, m0);
+      cluster_reduce<BN, EPI, OUT, 2>(red, bias, out, ldo, M, N, n0, m0, scale, ex, sqs);
     else if (split_k == 4)
-      cluster_reduce<BN, EPI, OUT, 4>(red, bias, out, ldo, M, N, n0, m0);
+      cluster_reduce<BN, EPI, OUT, 4>(red, bias, out, ldo, M, N, n0, m0, scale, ex, sqs);
     else if (split_k == 8)
-      cluster_reduce<BN, EPI, OUT, 8>(red, bias, out, ldo, M, N, n0, m0);
+      cluster_reduce<BN, EPI, OUT, 8>(red, bias, out, ldo, M, N, n0, m0, scale, ex, sqs);
     else
-      cluster_reduce<BN, EPI, OUT, 12>(red, bias, out, ldo, M, N, n0, m0);
+      cluster_reduce<BN, EPI, OUT, 12>(red, bias, out, ldo, M, N, n0, m0, scale, ex, sqs);
+    if (threadIdx.x == 0) GF_STAMP(6);
     cluster_sync();                                   // nobody leaves while a peer still reads it
+    if (threadIdx.x == 0) GF_STAMP(7);
     return;
   }
 
-  // the split that finishes this tile last adds the partials up in split order
+  // the split that finishes this tile last adds the partials up in split order (the launcher
+  // refuses EPI_RESID here: its sums of squares are formed per split)
   __threadfence();
   __syncthreads();
   const unsigned int tile = blockIdx.y * gridDim.x + blockIdx.x;
@@ -330,7 +561,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 #pragma unroll 1
   for (int c = 0; c < BN; c += 16) {
     if (m0 + c >= M) break;
-    float v[16];
+    float v[16], sq[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j) v[j] = 0.f;
     for (int s = 0; s < split_k; ++s) {
@@ -344,18 +575,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         v[j + 3] += t.w;
       }
     }
-    epilogue16<EPI, OUT>(v, out, ldo, bias, n, m0 + c, M, N, lane);
+    epilogue16<EPI, OUT>(v, out, ldo, bias, n, m0 + c, M, N, lane, scale ? scale + c : nullptr, ex,
+                         sq);
   }
 }
 
 template <int BN, int EPI, typename OUT, bool CLUSTER>
 static int launch_mode(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* out,
                        int ldo, int M, int N, int K, int split_k, float* workspace, int* err,
-                       cudaStream_t st) {
+                       cudaStream_t st, const GemmExtra& ex) {
   constexpr int STAGES = stages_for(BN);
   const size_t ring = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2);
-  const size_t red = CLUSTER ? (size_t)BM * (BN + 4) * sizeof(float) : 0;
-  const size_t smem = 1024 + (ring > red ? ring : red) + (2 * STAGES + 1) * sizeof(uint64_t) + 16;
+  // the parked tile of a cluster split, and behind it the squares of an EPI_RESID band (at most
+  // 16 row quads x BN tokens)
+  const size_t red = CLUSTER ? (size_t)BN * RED_LD * sizeof(float) +
+                                   (EPI == EPI_RESID ? (size_t)16 * BN * sizeof(float) : 0)
+                             : 0;
+  const size_t smem = 1024 + (ring > red ? ring : red) + (2 * STAGES + 1) * sizeof(uint64_t) + 16 +
+                      5 * BN * sizeof(float);
   auto k = gemm_tc_kernel<BN, EPI, OUT, CLUSTER>;
   static bool done = false;
   if (!done) {
@@ -373,31 +610,38 @@ static int launch_mode(const CUtensorMap& mw, const CUtensorMap& mx, const float
   }
   dim3 grid((N + BM - 1) / BM, (M + BN - 1) / BN, split_k);
   return launch_kernel_cluster(k, grid, dim3(NTHREADS), smem, st, CLUSTER ? split_k : 1, mw, mx,
-                               bias, (OUT*)out, ldo, M, N, K, split_k, workspace, err);
+                               bias, (OUT*)out, ldo, M, N, K, split_k, workspace, err, ex);
 }
 
 template <int BN, int EPI, typename OUT>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* out,
                   int ldo, int M, int N, int K, int split_k, float* workspace, int* err,
-                  cudaStream_t st) {
+                  cudaStream_t st, const GemmExtra& ex) {
   if (split_k > 1 && !workspace)
     return launch_mode<BN, EPI, OUT, true>(mw, mx, bias, out, ldo, M, N, K, split_k, workspace,
-                                           err, st);
+                                           err, st, ex);
   return launch_mode<BN, EPI, OUT, false>(mw, mx, bias, out, ldo, M, N, K, split_k, workspace, err,
-                                          st);
+                                          st, ex);
 }
 
 template <int EPI, typename OUT>
 static int dispatch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const float* bias,
                        void* out, int ldo, int M, int N, int K, int split_k, float* workspace,
-                       int* err, cudaStream_t st) {
+                       int* err, cudaStream_t st, const GemmExtra& ex) {
+#define GF_CASE(B) \
+  case B: return launch<B, EPI, OUT>(mw, mx, bias, out, ldo, M, N, K, split_k, workspace, err, st, ex)
   switch (bn) {
-    case 16: return launch<16, EPI, OUT>(mw, mx, bias, out, ldo, M, N, K, split_k, workspace, err, st);
-    case 32: return launch<32, EPI, OUT>(mw, mx, bias, out, ldo, M, N, K, split_k, workspace, err, st);
-    case 64: return launch<64, EPI, OUT>(mw, mx, bias, out, ldo, M, N, K, split_k, workspace, err, st);
-    case 128: return launch<128, EPI, OUT>(mw, mx, bias, out, ldo, M, N, K, split_k, workspace, err, st);
-    case 256: return launch<256, EPI, OUT>(mw, mx, bias, out, ldo, M, N, K, split_k, workspace, err, st);
+    GF_CASE(16);
+    GF_CASE(32);
+    GF_CASE(64);
   }
+  if (EPI != EPI_RESID) {       // the residual epilogue serves the token tiles of decode steps only
+    switch (bn) {
+      GF_CASE(128);
+      GF_CASE(256);
+    }
+  }
+#undef GF_CASE
   return -7;
 }
 
@@ -406,6 +650,18 @@ static int dispatch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, con
 using namespace gf;
 
 GF_DEFINE_PDL_SWITCH
+
+#ifdef GF_STAMPS
+// Copies the records to `host` (kStampCap * 8 words), returns how many were written, resets.
+GF_EXPORT int gf_gemm_bf16_read_stamps(unsigned long long* host) {
+  unsigned int n = 0, zero = 0;
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(&n, g_stamp_next, sizeof(n));
+  cudaMemcpyFromSymbol(host, g_stamps, sizeof(unsigned long long) * kStampCap * 8);
+  cudaMemcpyToSymbol(g_stamp_next, &zero, sizeof(zero));
+  return (int)(n < kStampCap ? n : kStampCap);
+}
+#endif
 
 GF_EXPORT int gf_gemm_bf16_token_tile(int M) {
   return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
@@ -420,19 +676,37 @@ GF_EXPORT long long gf_gemm_bf16_workspace_words(int M, int N, int split_k) {
 }
 
 // out[M, *] = x[M, K] * W[N, K]^T.  epi 0: out[m, n] = acc + bias[n]; epi 2: W rows interleaved
-// (gate_i, up_i), out[m, i] = silu(gate) * up, N even.  out_f32: fp32 output (epi 0 only).
-// ldx, ldo in elements.  split_k > 1 with a workspace: workspace mode; without: cluster mode
-// (split_k 2, 4 or 8).  err: a device int that receives a non-zero code if a wait ran out.
+// (gate_i, up_i), out[m, i] = silu(gate) * up, N even; epi 3: out (fp32) = resid + acc + bias with
+// out_scaled = bf16(out * gamma[n]) (if given) and out_sumsq[part][m] = the part's share of
+// sum_n out^2, parts = gf_gemm_bf16_parts(N, split_k) rows of ss_ld floats; ldo == N, M <= 64,
+// cluster mode or no split.  out_f32: fp32 output (epi 0, 3).  ldx, ldo in elements.
+// in_sumsq (in_parts rows of ss_ld floats): the accumulator of token m is multiplied by
+// rsqrt(sum_p in_sumsq[p][m] / K + in_eps) before bias and epilogue.
+// split_k > 1 with a workspace: workspace mode; without: cluster mode (split_k 2, 4, 8 or 12).
+// err: a device int that receives a non-zero code if a wait ran out.
 // Returns -6 when the shape or alignment cannot be served (the caller uses another product).
-GF_EXPORT int gf_gemm_bf16_tc(const void* x, int ldx, const void* w, const float* bias, void* out,
-                              int ldo, int M, int N, int K, int epi, int out_f32, int split_k,
-                              void* workspace, int* err, void* stream) {
+GF_EXPORT int gf_gemm_bf16_parts(int N, int split_k) {
+  return ((N + BM - 1) / BM) * (split_k < 1 ? 1 : split_k);
+}
+
+GF_EXPORT int gf_gemm_bf16_tc_ex(const void* x, int ldx, const void* w, const float* bias,
+                                 void* out, int ldo, int M, int N, int K, int epi, int out_f32,
+                                 int split_k, void* workspace, int* err, void* stream,
+                                 const float* in_sumsq, int in_parts, int ss_ld, float in_eps,
+                                 const float* resid, void* out_scaled, const void* gamma,
+                                 int gamma_f32, float* out_sumsq) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || ldx % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return -6;
   if (epi == EPI_SILU && ((N & 1) || out_f32)) return -6;
-  if (epi != EPI_STORE && epi != EPI_SILU) return -6;
+  if (epi != EPI_STORE && epi != EPI_SILU && epi != EPI_RESID) return -6;
   const int bn = gf_gemm_bf16_token_tile(M);
   if (split_k < 1) split_k = 1;
+  if (epi == EPI_RESID) {
+    if (!out_f32 || !resid || !out_sumsq || ldo != N || bn > 64 || (split_k > 1 && workspace) ||
+        ss_ld < M || (out_scaled && !gamma))
+      return -6;
+  }
+  if (in_sumsq && (in_parts <= 0 || ss_ld < M)) return -6;
   const long long tiles = (long long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
   // split_k > 1 without a workspace asks for cluster mode
   if (split_k > 1 && !workspace && split_k != 2 && split_k != 4 && split_k != 8 && split_k != 12)
@@ -440,11 +714,34 @@ GF_EXPORT int gf_gemm_bf16_tc(const void* x, int ldx, const void* w, const float
   if (split_k > 1 && workspace && tiles > kMaxTiles) return -6;
   CUtensorMap mw, mx;
   if (!make_map(&mw, w, N, K, K, BM) || !make_map(&mx, x, M, K, ldx, bn)) return -6;
+  GemmExtra ex = {};
+  ex.in_sumsq = in_sumsq;
+  ex.in_parts = in_parts;
+  ex.ss_ld = ss_ld;
+  ex.in_eps = in_eps;
+  ex.inv_k = 1.0f / (float)K;
+  ex.resid = resid;
+  ex.out_scaled = (bf16*)out_scaled;
+  ex.gamma = gamma;
+  ex.gamma_f32 = gamma_f32;
+  ex.out_sumsq = out_sumsq;
   auto st = (cudaStream_t)stream;
   float* ws = (float*)workspace;
   if (epi == EPI_SILU)
-    return dispatch_bn<EPI_SILU, bf16>(bn, mw, mx, bias, out, ldo, M, N, K, split_k, ws, err, st);
+    return dispatch_bn<EPI_SILU, bf16>(bn, mw, mx, bias, out, ldo, M, N, K, split_k, ws, err, st,
+                                       ex);
+  if (epi == EPI_RESID)
+    return dispatch_bn<EPI_RESID, float>(bn, mw, mx, bias, out, ldo, M, N, K, split_k, ws, err, st,
+                                         ex);
   if (out_f32)
-    return dispatch_bn<EPI_STORE, float>(bn, mw, mx, bias, out, ldo, M, N, K, split_k, ws, err, st);
-  return dispatch_bn<EPI_STORE, bf16>(bn, mw, mx, bias, out, ldo, M, N, K, split_k, ws, err, st);
+    return dispatch_bn<EPI_STORE, float>(bn, mw, mx, bias, out, ldo, M, N, K, split_k, ws, err, st,
+                                         ex);
+  return dispatch_bn<EPI_STORE, bf16>(bn, mw, mx, bias, out, ldo, M, N, K, split_k, ws, err, st, ex);
+}
+
+GF_EXPORT int gf_gemm_bf16_tc(const void* x, int ldx, const void* w, const float* bias, void* out,
+                              int ldo, int M, int N, int K, int epi, int out_f32, int split_k,
+                              void* workspace, int* err, void* stream) {
+  return gf_gemm_bf16_tc_ex(x, ldx, w, bias, out, ldo, M, N, K, epi, out_f32, split_k, workspace,
+                            err, stream, nullptr, 0, 0, 0.f, nullptr, nullptr, nullptr, 0, nullptr);
 }

@@ -32,14 +32,6 @@ def require_cuda(device) -> torch.device:
     return device
 
 
-def _attach_shortcuts(model) -> None:
-    """Whole-stack kernels for models whose layers they recognise (bfloat16 decode steps)."""
-    from .fused_decode import recognise
-    fused = recognise(model)
-    if fused is not None:
-        model.shortcuts.append(fused)
-
-
 def load_model(model_path: str, dtype="bfloat16", device="cuda:0"):
     """Read ``config.json``, pick the architecture from the registry, build its plan and load
     ``model.safetensors``.  Returns ``(model, typed config)``."""
@@ -47,7 +39,6 @@ def load_model(model_path: str, dtype="bfloat16", device="cuda:0"):
     arch, cfg = load_model_config(model_path)
     model = DecoderModel(arch.build_plan(cfg))
     load_weights(model, model_path, parse_dtype(dtype), device)
-    _attach_shortcuts(model)
     return model, cfg
 
 
@@ -58,5 +49,4 @@ def random_model(config: dict, seed: int, dtype="bfloat16", device="cuda:0"):
     cfg = arch.config_cls.from_dict(config)
     model = DecoderModel(arch.build_plan(cfg))
     load_random_weights(model, seed, parse_dtype(dtype), device)
-    _attach_shortcuts(model)
     return model, cfg

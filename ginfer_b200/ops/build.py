@@ -164,10 +164,8 @@ def set_pdl(enabled: bool) -> None:
                 lib.gf_set_pdl(ctypes.c_int(1 if _pdl_enabled else 0))
 
 
-# sources that are compiled per head size but take only some head sizes (the tcgen05 attention),
-# or that the build of everything makes for the usual ones only (the persistent decode kernel
-# takes any multiple of 16 up to 256 and is compiled on demand for the others)
-HEAD_DIMS_OF = {"attention_tc": (64, 128), "decode_layers": (16, 32, 48, 64, 128)}
+# sources that are compiled per head size but take only some head sizes (the tcgen05 attention)
+HEAD_DIMS_OF = {"attention_tc": (64, 128)}
 
 
 # every library the framework can ask for: (source name, defines)

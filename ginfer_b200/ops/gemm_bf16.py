@@ -2,7 +2,8 @@
 the accumulator in tensor memory, operands staged by TMA)."""
 from __future__ import annotations
 
-from ctypes import c_int, c_void_p
+from ctypes import c_float, c_int, c_void_p
+from dataclasses import dataclass
 
 import torch
 
@@ -78,38 +79,78 @@ def supports(x: torch.Tensor, weight: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
+@dataclass
+class RowScale:
+    """Partial sums of squares ``sumsq [parts, ld]`` of the rows of a tensor of ``width`` columns
+    with the ``eps`` of an RMS normalisation: a product whose operand is that tensor times gamma
+    multiplies its accumulator by ``rsqrt(sum of the partials / width + eps)`` per token."""
+    sumsq: torch.Tensor
+    eps: float
+
+
+def sumsq_ld(M: int) -> int:
+    return -(-M // 16) * 16
+
+
 def gemm(x, weight, bias_f32=None, out_dtype=torch.bfloat16, epi: int = 0, split_k=None,
-         through_workspace: bool = False):
+         through_workspace: bool = False, scale: RowScale | None = None, resid=None, gamma=None):
     """``x [M, K] @ weight[N, K]^T``; ``epi`` 0: (+ bias) -> ``[M, N]``; ``epi`` 2: weight rows
     are interleaved (gate_i, up_i) and the result is ``silu(gate) * up`` -> ``[M, N / 2]``.
-    ``split_k``: None picks it; 2, 4 or 8 add up inside a cluster; with ``through_workspace`` any
-    number of splits adds up through global memory.  Returns ``None`` if the kernel cannot serve
-    the shape."""
+    ``split_k``: None picks it; 2, 4, 8 or 12 add up inside a cluster; with ``through_workspace``
+    any number of splits adds up through global memory.  ``scale``: the accumulator of every token
+    is multiplied by its factor first (a deferred RMS normalisation).  ``resid`` (fp32 ``[M, N]``): the result
+    is ``(s, scaled, sumsq)`` with ``s = resid + x W^T (+ bias)`` in fp32, ``scaled = bf16(s *
+    gamma)`` (``None`` without ``gamma``) and the partial sums of squares of ``s``'s rows.
+    Returns ``None`` if the kernel cannot serve the shape."""
     from . import _fn, _ok, _p, _stream
     if not supports(x, weight):
         return None
     M, K = x.shape
     N = weight.shape[0]
+    if resid is not None:
+        if (M > RESID_MAX_TOKENS or through_workspace or resid.dtype != torch.float32
+                or resid.shape != (M, N) or not resid.is_contiguous() or epi != 0):
+            return None
+        epi, out_dtype = 3, torch.float32
     cols = N // 2 if epi == 2 else N
     out = torch.empty((M, cols), dtype=out_dtype, device=x.device)
     if M == 0:
-        return out
+        return out if resid is None else None
     sk = split_k_for(M, N, K) if split_k is None else int(split_k)
     ws = None
     if sk > 1 and through_workspace:
         bn = token_tile(M)
         ws = _workspace(-(-N // 128) * -(-M // bn) * sk * 128 * bn, x.device)
+    ld = sumsq_ld(M)
+    in_sumsq, in_parts, in_eps = None, 0, 0.0
+    if scale is not None:
+        if scale.sumsq.stride(0) != ld or scale.sumsq.dtype != torch.float32:
+            return None
+        in_sumsq, in_parts, in_eps = scale.sumsq, scale.sumsq.shape[0], float(scale.eps)
+    scaled = sumsq = None
+    if resid is not None:
+        sumsq = torch.empty((-(-N // 128) * sk, ld), dtype=torch.float32, device=x.device)
+        if gamma is not None:
+            if gamma.numel() != N or gamma.dtype not in (torch.float32, torch.bfloat16):
+                return None
+            scaled = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
     st = _dev_state(x.device)
-    f = _fn("gemm_bf16", "gf_gemm_bf16_tc",
+    f = _fn("gemm_bf16", "gf_gemm_bf16_tc_ex",
             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-             c_int, c_int, c_void_p, c_void_p, c_void_p])
+             c_int, c_int, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p])
     rc = f(_p(x), x.stride(0), _p(weight), _p(bias_f32), _p(out), cols, M, N, K, int(epi),
-           1 if out_dtype == torch.float32 else 0, sk, _p(ws), _p(st["err"]), _stream())
+           1 if out_dtype == torch.float32 else 0, sk, _p(ws), _p(st["err"]), _stream(),
+           _p(in_sumsq), in_parts, ld, in_eps, _p(resid), _p(scaled), _p(gamma),
+           1 if gamma is not None and gamma.dtype == torch.float32 else 0, _p(sumsq))
     if rc in (-6, -7):
         return None
     _ok(rc, "gemm_bf16_tc")
-    return out
+    return out if resid is None else (out, scaled, sumsq)
 
+
+# The residual epilogue takes the token tiles of decode steps.
+RESID_MAX_TOKENS = 64
 
 # The largest token count the gated product runs here for.  In a CUDA graph, 1.5B shapes, weights
 # from HBM: 8 tokens 11.5 us (two K splits) against 12.6 for cuBLAS + SiLU*mul, 16 tokens 11.8
@@ -118,11 +159,15 @@ def gemm(x, weight, bias_f32=None, out_dtype=torch.bfloat16, epi: int = 0, split
 MAX_TOKENS = 16
 
 
+def plain_limit(weight) -> int:
+    """The largest token count for which a plain product with ``weight`` runs here."""
+    return PLAIN_MAX_TOKENS_LONG_K if weight.shape[1] >= LONG_K else PLAIN_MAX_TOKENS
+
+
 def try_linear(x, weight, bias_f32, out_dtype):
     """Run the tcgen05 kernel where it is the faster one (the small batches of decode steps and
     short prompt portions); ``None`` hands the product to cuBLAS."""
-    limit = PLAIN_MAX_TOKENS_LONG_K if weight.shape[1] >= LONG_K else PLAIN_MAX_TOKENS
-    if x.shape[0] > limit:
+    if x.shape[0] > plain_limit(weight):
         return None
     return gemm(x, weight, bias_f32, out_dtype, epi=0)
 
@@ -135,81 +180,3 @@ def try_linear(x, weight, bias_f32, out_dtype):
 PLAIN_MAX_TOKENS = 16
 PLAIN_MAX_TOKENS_LONG_K = 48   # for reductions of at least LONG_K
 LONG_K = 4096
-
-
-# ----------------------------------------------------------------------------- fused with the norm
-FUSED_MAX_TOKENS = 32          # the fused kernels take token tiles of 16 and 32
-SS_LD = 32                     # tokens per row of the partial sums of squares
-
-
-def _cluster_split(N: int, K: int, k_share_max: int | None = None) -> int:
-    """2, 4 or 8 K-splits (a thread-block cluster) for products whose row tiles alone would leave
-    most SMs idle; ``k_share_max`` bounds the K range of one split (elements)."""
-    tiles = -(-N // 128)
-    nkb = -(-K // 64)
-    split = 1
-    while split < 8 and tiles * split * 2 <= NUM_SMS + NUM_SMS // 4 and nkb // (split * 2) >= 2:
-        split *= 2
-    while k_share_max is not None and split < 8 and -(-nkb // split) * 64 > k_share_max:
-        split *= 2
-    return split
-
-
-def gemm_resid(x, weight, bias_f32, resid):
-    """``s = resid + x @ weight^T (+ bias)`` in fp32 with, per token, the partial sums of
-    ``s^2`` (``csrc/gemm_fused_norm.cu``).  Returns ``(s [M, N] fp32, sumsq [parts, 32] fp32)``
-    or ``None`` if the kernel cannot serve the shapes."""
-    from . import _fn, _ok, _p, _stream
-    M, K = x.shape
-    N = weight.shape[0]
-    if M > FUSED_MAX_TOKENS or not supports(x, weight) or resid.dtype != torch.float32:
-        return None
-    if resid.shape != (M, N) or not resid.is_contiguous():
-        return None
-    split = _cluster_split(N, K)
-    parts = -(-N // 128) * split
-    out = torch.empty((M, N), dtype=torch.float32, device=x.device)
-    sumsq = torch.empty((parts, SS_LD), dtype=torch.float32, device=x.device)
-    f = _fn("gemm_fused_norm", "gf_gemm_resid",
-            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-             c_int, c_int, c_int, c_void_p, c_void_p])
-    rc = f(_p(x), x.stride(0), _p(weight), _p(bias_f32), _p(resid), _p(out), _p(sumsq), SS_LD, M,
-           N, K, split, _p(_dev_state(x.device)["err"]), _stream())
-    if rc == -6:
-        return None
-    _ok(rc, "gemm_resid")
-    return out, sumsq
-
-
-def gemm_normed(resid, sumsq, gamma, eps, weight, bias_f32=None, out_dtype=torch.bfloat16,
-                gated: bool = False):
-    """``norm(resid) @ weight^T (+ bias)`` (or ``silu(gate) * up`` over row-interleaved weights)
-    where ``norm`` is the RMS normalisation with ``gamma`` and the statistics a
-    :func:`gemm_resid` left in ``sumsq``.  ``None`` if the kernel cannot serve the shapes."""
-    from ctypes import c_float
-
-    from . import _fn, _ok, _p, _stream
-    M, K = resid.shape
-    N = weight.shape[0]
-    if M > FUSED_MAX_TOKENS or K % 8 or resid.dtype != torch.float32 or not resid.is_contiguous():
-        return None
-    if weight.data_ptr() % 16 or gamma.data_ptr() % 16 or gamma.numel() != K:
-        return None
-    bn = 16 if M <= 16 else 32
-    # the CTA's share of the normalised operand stays in shared memory: at most 64 KB of it
-    split = _cluster_split(N, K, k_share_max=(64 << 10) // (bn * 2))
-    if -(-(-(-K // 64)) // split) * 64 * bn * 2 > (64 << 10):
-        return None
-    cols = N // 2 if gated else N
-    out = torch.empty((M, cols), dtype=out_dtype, device=resid.device)
-    f = _fn("gemm_fused_norm", "gf_gemm_normed",
-            [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_float, c_void_p, c_void_p,
-             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
-    rc = f(_p(resid), _p(sumsq), sumsq.shape[0], sumsq.stride(0), _p(gamma),
-           1 if gamma.dtype == torch.float32 else 0, float(eps), _p(weight), _p(bias_f32), _p(out),
-           cols, M, N, K, 1 if gated else 0, 1 if out_dtype == torch.float32 else 0, split,
-           _p(_dev_state(resid.device)["err"]), _stream())
-    if rc == -6:
-        return None
-    _ok(rc, "gemm_normed")
-    return out

@@ -56,10 +56,10 @@ class Linear:
 
     def __call__(self, x) -> torch.Tensor:
         if hasattr(x, "materialize"):                 # a normalisation not computed yet
-            if self.dtype == torch.bfloat16:
+            if self.dtype == torch.bfloat16 and x.scaled is not None:
                 from . import gemm_bf16
-                y = gemm_bf16.gemm_normed(x.summed.tensor, x.summed.sumsq, x.gamma, x.eps,
-                                          self.weight, self._bias_f32, self.out_dtype)
+                y = gemm_bf16.gemm(x.scaled, self.weight, self._bias_f32, self.out_dtype,
+                                   scale=gemm_bf16.RowScale(x.summed.sumsq, x.eps))
                 if y is not None:
                     return y
             x = x.materialize()
@@ -81,13 +81,21 @@ class Linear:
         return torch.mm(x, self.weight.t())
 
 
-def add_to(linear: "Linear", x: torch.Tensor, residual: torch.Tensor):
-    """``(residual + linear(x), partial sums of its squares)`` from one kernel, or ``None`` if the
-    fused kernel does not serve this case (then the caller adds in the next norm)."""
+def add_to(linear: "Linear", x: torch.Tensor, residual: torch.Tensor, gamma=None):
+    """``(s, partial sums of squares of s's rows, s * gamma in bf16, gamma)`` with ``s = residual
+    + linear(x)`` in fp32, from one kernel (the fields of ``parts.base.Summed``), or ``None`` if
+    the kernel does not serve this case (then the caller adds in the next norm).  ``gamma``: the
+    weight of the RMS norm that follows, if it can be folded."""
     if linear.dtype != torch.bfloat16 or residual.dtype != torch.float32:
         return None
     from . import gemm_bf16
-    return gemm_bf16.gemm_resid(x, linear.weight, linear._bias_f32, residual)
+    if x.shape[0] > gemm_bf16.plain_limit(linear.weight):
+        return None
+    got = gemm_bf16.gemm(x, linear.weight, linear._bias_f32, resid=residual, gamma=gamma)
+    if got is None:
+        return None
+    s, scaled, sumsq = got
+    return s, sumsq, scaled, gamma
 
 
 # From this many tokens on the gated product runs on the persistent tcgen05 kernel of
@@ -95,6 +103,11 @@ def add_to(linear: "Linear", x: torch.Tensor, residual: torch.Tensor):
 # 2,048 tokens 87.7 us against 96.0 for cuBLAS + SiLU*mul, 8,192 tokens 336 against 386, 512 tokens
 # 27.4 against 27.1; at the 7B shape (37888 x 3584) 383 against 392.
 PREFILL_GATED_MIN_TOKENS = 1024
+
+
+def _gemm_bf16():
+    from . import gemm_bf16
+    return gemm_bf16
 
 
 class GatedLinear:
@@ -111,10 +124,11 @@ class GatedLinear:
 
     def __call__(self, x) -> torch.Tensor:
         if hasattr(x, "materialize"):                 # a normalisation not computed yet
-            if self.proj.dtype == torch.bfloat16:
-                from . import gemm_bf16
-                z = gemm_bf16.gemm_normed(x.summed.tensor, x.summed.sumsq, x.gamma, x.eps,
-                                          self.proj.weight, None, torch.bfloat16, gated=True)
+            if self.proj.dtype == torch.bfloat16 and x.scaled is not None \
+                    and x.scaled.shape[0] <= _gemm_bf16().MAX_TOKENS:
+                gb = _gemm_bf16()
+                z = gb.gemm(x.scaled, self.proj.weight, None, torch.bfloat16, epi=2,
+                            scale=gb.RowScale(x.summed.sumsq, x.eps))
                 if z is not None:
                     return z
             x = x.materialize()

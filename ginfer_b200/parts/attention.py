@@ -80,7 +80,7 @@ class Attention(Mixer):
     def cache_spec(self):
         return PagedKVSpec(self.num_kv_heads, self.head_dim, self.window)
 
-    def forward(self, x, ctx, cache, residual=None):
+    def forward(self, x, ctx, cache, residual=None, then=None):
         nh, nkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
         fused = self.position.rotary_table()
         if fused is not None and cache.write and not hasattr(x, "materialize"):
@@ -90,7 +90,7 @@ class Attention(Mixer):
             if qkv is not None:
                 o = ops.paged_attention(qkv, cache.pages, cache.block_table, ctx, nh, nkv, hd,
                                         self.scale, cache.window, cache.page_size)
-                return self._project(o, residual)
+                return self._project(o, residual, then)
         qkv = self.qkv(x)                                         # [T, (nh + 2 nkv) hd]
         if fused is None:                                         # an encoding with code of its own
             q = qkv[:, :nh * hd].unflatten(1, (nh, hd))
@@ -110,11 +110,11 @@ class Attention(Mixer):
                               cache.pages, nh, nkv, hd)
             o = ops.paged_attention(qkv, cache.pages, cache.block_table, ctx, nh, nkv, hd,
                                     self.scale, cache.window, cache.page_size)
-        return self._project(o, residual)
+        return self._project(o, residual, then)
 
-    def _project(self, o, residual):
+    def _project(self, o, residual, then):
         if residual is not None:
-            s = ops.add_to(self.out, o, residual)
+            s = ops.add_to(self.out, o, residual, then.fold_weight() if then is not None else None)
             if s is not None:
                 return Summed(*s)
         return self.out(o)

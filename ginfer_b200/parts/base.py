@@ -100,19 +100,30 @@ class StepContext:
 class Summed:
     """A hidden state whose last residual addition is done: ``tensor [T, H]`` in fp32, with the
     partial sums of squares of its rows that the product which formed it left behind
-    (``sumsq [parts, tokens]``), so that a following RMS normalisation needs no pass of its own."""
+    (``sumsq [parts, ld]``), so that a following RMS normalisation needs no pass of its own.
+    ``scaled`` is ``tensor * gamma`` in the activation dtype for the norm whose weight is
+    ``scaled_by`` (the norm the producer was told comes next), or ``None``."""
     tensor: torch.Tensor
     sumsq: torch.Tensor
+    scaled: torch.Tensor | None = None
+    scaled_by: torch.Tensor | None = None
 
 
 @dataclass
 class LazyNorm:
-    """The RMS normalisation of a :class:`Summed` state, not computed yet.  A product that can
-    normalise its own operand takes it as it is; anything else calls :meth:`materialize`."""
+    """The RMS normalisation of a :class:`Summed` state, not computed yet: what is there is
+    ``scaled = tensor * gamma`` and the sums of squares, and ``norm = scaled / rms`` row by row.
+    A product that can multiply its accumulator by ``1 / rms`` takes it as it is (``x W^T / rms``
+    is the product of the normalised rows); anything else calls :meth:`materialize`."""
     summed: Summed
     gamma: torch.Tensor
     eps: float
     dtype: torch.dtype
+
+    @property
+    def scaled(self) -> torch.Tensor | None:
+        s = self.summed
+        return s.scaled if s.scaled_by is self.gamma else None
 
     def materialize(self) -> torch.Tensor:
         from .. import ops
@@ -147,6 +158,12 @@ class Norm(Part):
         into the product that consumes it; ``None`` otherwise."""
         return None
 
+    def fold_weight(self) -> torch.Tensor | None:
+        """The weight ``gamma`` if this norm is ``x * gamma / rms(x)`` and so can be split into a
+        multiplication by ``gamma`` in the product before it and one by ``1 / rms`` in the product
+        behind it; ``None`` (the default) if it cannot."""
+        return None
+
 
 class PositionEncoding(Part):
     def rotary_table(self) -> tuple[torch.Tensor, int] | None:
@@ -164,8 +181,9 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
-    # A mixer (or feed-forward) that sets these takes a LazyNorm as input, and a ``residual``
-    # keyword: given one it may return ``Summed(residual + output)`` instead of its output.
+    # A mixer (or feed-forward) that sets these takes a LazyNorm as input, and the keywords
+    # ``residual`` and ``then``: given a residual it may return ``Summed(residual + output)``
+    # instead of its output, with ``scaled`` made for the norm ``then`` (the one that follows).
     takes_lazy_norm = False
     adds_residual = False
 
@@ -189,9 +207,17 @@ class Block(Part):
     blocks as ``(x, delta)`` meaning ``x + delta``, so that a block's last addition can be fused
     into the next norm."""
 
+    # A block that sets this takes the keyword ``then``: the norm that will consume its output
+    # (the next run's first norm), so that its last product can prepare that norm's input.
+    takes_next_norm = False
+
     def forward(self, x: torch.Tensor, delta: torch.Tensor | None, ctx: StepContext, cache
                 ) -> tuple[torch.Tensor, torch.Tensor | None]:
         raise NotImplementedError
+
+    def first_norm(self) -> "Norm | None":
+        """The norm this block applies to its input first, if another block may prepare it."""
+        return None
 
 
 class Embedding(Part):

@@ -7,17 +7,22 @@ block's first norm or the final norm), which fuses it with its normalisation.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .base import Block, Summed, make_part, register_block
 
-# Steps of at most this many tokens fold the additions and normalisations into the neighbouring
-# products (the kernels take up to 32).  Measured on a B200 at the 1.5B shape the folded layer is
-# slower than the separate norm kernels (q/k/v 6.7 us against 4.4 + 1.9, gate/up 18.2 against
-# 12.2 + 1.9: each of the 140 gate/up CTAs normalises the whole operand for itself before its first
-# product; the producers pay 1.7 and 3.4 us for the sums of squares), so it is off unless a caller
-# raises it.
-FOLD_MAX_TOKENS = 0
+# Steps of at most this many tokens (bfloat16) fold the additions and normalisations into the
+# neighbouring products: the product before a norm leaves the sum, its product with the norm's
+# weight and partial sums of squares, the product behind it divides by the rms, and a layer of a
+# decode step is 5 kernels (q/k/v, attention, output, gate/up, down) instead of 7.  Off (0) by
+# default: on a B200 at the 1.5B shape, batch 8, the step takes 1.245 ms with it against 1.213 ms
+# without.  The kernels of a step overlap (each starts, and loads its weights, while the one
+# before still runs): the two norm kernels cost 3.1 us each, but they are also 6 us in which the
+# products behind them fetch weights, and the epilogues that replace them lengthen the products
+# (+0.9 us the output product, +2.4 us q/k/v) on the path every token waits for.
+FOLD_MAX_TOKENS = int(os.environ.get("GINFER_B200_FOLD_MAX_TOKENS", "0"))
 
 
 class PreNormBlock(Block):
@@ -37,16 +42,22 @@ class PreNormBlock(Block):
             out.extend(p.tensor_specs())
         return out
 
+    takes_next_norm = True
+
+    def first_norm(self):
+        return self.mixer_norm
+
     def load(self, tensors, dtype, device):
         for p in self.parts():
             p.load(tensors, dtype, device)
 
-    def forward(self, x, delta, ctx, cache):
+    def forward(self, x, delta, ctx, cache, then=None):
         """``x`` is a tensor (with ``delta`` still to be added) or a :class:`Summed` state.  For
         short bf16 steps the additions and normalisations are folded into the neighbouring
         products where the parts can do that: the mixer's and the feed-forward's last product
-        add the residual and leave the statistics of the sum (``Summed``), and their first
-        product normalises its own operand (``LazyNorm``)."""
+        add the residual, leave the statistics of the sum and its product with the next norm's
+        weight (``Summed``), and their first product divides by the rms (``LazyNorm``).
+        ``then``: the norm that consumes this block's output."""
         fold = ctx.dtype == torch.bfloat16 and ctx.num_tokens <= FOLD_MAX_TOKENS
         # the state before the mixer, and its normalisation
         n = None
@@ -59,8 +70,8 @@ class PreNormBlock(Block):
         else:
             h, n = self.mixer_norm.forward(x, delta)            # h = x + delta
         if fold and self.mixer.adds_residual:
-            a = self.mixer.forward(n, ctx, cache, residual=h if h.dtype == torch.float32
-                                   else h.float())
+            a = self.mixer.forward(n, ctx, cache, then=self.feed_forward_norm,
+                                   residual=h if h.dtype == torch.float32 else h.float())
         else:
             a = self.mixer.forward(n, ctx, cache)
         # the state before the feed-forward, and its normalisation
@@ -73,8 +84,9 @@ class PreNormBlock(Block):
                 _, n2 = self.feed_forward_norm.forward(r, None, out_dtype=ctx.dtype)
         else:
             r, n2 = self.feed_forward_norm.forward(h, a)        # r = h + a
-        if fold and self.feed_forward.adds_residual and r.dtype == torch.float32:
-            m = self.feed_forward.forward(n2, ctx, residual=r)
+        if fold and then is not None and self.feed_forward.adds_residual \
+                and r.dtype == torch.float32:
+            m = self.feed_forward.forward(n2, ctx, residual=r, then=then)
         else:
             m = self.feed_forward.forward(n2, ctx)
         if isinstance(m, Summed):

@@ -36,10 +36,11 @@ class SwiGLU(FeedForward):
         self.gate_up = ops.GatedLinear(tensors[self.gate_key], tensors[self.up_key])
         self.down = ops.Linear(tensors[self.down_key])
 
-    def forward(self, x, ctx, residual=None):
+    def forward(self, x, ctx, residual=None, then=None):
         z = self.gate_up(x)            # silu(gate) * up, [T, intermediate]
         if residual is not None:
-            s = ops.add_to(self.down, z, residual)
+            s = ops.add_to(self.down, z, residual,
+                           then.fold_weight() if then is not None else None)
             if s is not None:
                 return Summed(*s)
         return self.down(z)

@@ -21,9 +21,6 @@ class DecoderModel:
         self.blocks = [make_part("block", ls.block, layer_spec=ls) for ls in plan.layers]
         self.final_norm = make_part("norm", plan.final_norm)
         self.head = make_part("head", plan.head)
-        # Objects with ``layers(ctx, bind_cache) -> residual stream | None`` that may run the
-        # embedding and all layers of a step in their own way (the loader attaches them).
-        self.shortcuts: list = []
         self.dtype: torch.dtype | None = None
         self.device: torch.device | None = None
 
@@ -73,26 +70,22 @@ class DecoderModel:
     def forward(self, ctx: StepContext, bind_cache) -> torch.Tensor:
         """Run the step's tokens; ``bind_cache(run_entry)`` gives the cache binding of a run.
         Returns fp32 logits ``[R, vocab]`` at ``ctx.logit_rows``."""
-        x = None
-        for shortcut in self.shortcuts:               # whole stacks of layers in one kernel
-            x = shortcut.layers(ctx, bind_cache)
-            if x is not None:
-                break
         delta = None
-        kw = {"out_dtype": ctx.dtype} if x is not None else {}     # a bare fp32 residual stream
-        if x is None:
-            x = self.embedding.forward(ctx.token_ids, ctx)
-            for e in self.plan.run:
-                x, delta = self.blocks[e.layer].forward(x, delta, ctx, bind_cache(e))
+        x = self.embedding.forward(ctx.token_ids, ctx)
+        run = self.plan.run
+        for i, e in enumerate(run):
+            blk = self.blocks[e.layer]
+            if blk.takes_next_norm and i + 1 < len(run):
+                # the block may prepare the input of the norm that the next run starts with
+                x, delta = blk.forward(x, delta, ctx, bind_cache(e),
+                                       then=self.blocks[run[i + 1].layer].first_norm())
+            else:
+                x, delta = blk.forward(x, delta, ctx, bind_cache(e))
         if ctx.logit_rows.numel() == 0:
             return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=ctx.device)
-        n = None
         if isinstance(x, Summed):
-            if ctx.all_rows_wanted:
-                n = self.final_norm.lazy(x, ctx.dtype)          # folded into the head's product
-            if n is None:
-                _, n = self.final_norm.forward(x.tensor, None, rows=ctx.logit_rows,
-                                               want_sum=False, out_dtype=ctx.dtype)
+            _, n = self.final_norm.forward(x.tensor, None, rows=ctx.logit_rows, want_sum=False,
+                                           out_dtype=ctx.dtype)
         else:
-            _, n = self.final_norm.forward(x, delta, rows=ctx.logit_rows, want_sum=False, **kw)
+            _, n = self.final_norm.forward(x, delta, rows=ctx.logit_rows, want_sum=False)
         return self.head.forward(n, ctx)

@@ -34,5 +34,8 @@ class RMSNorm(Norm):
     def lazy(self, summed, dtype):
         return LazyNorm(summed, self.weight, self.eps, dtype)
 
+    def fold_weight(self):
+        return self.weight
+
 
 register_norm("rmsnorm", RMSNorm)

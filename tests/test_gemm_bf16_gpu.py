@@ -66,55 +66,76 @@ def test_refuses_what_tma_cannot_address():
     assert gemm_bf16.gemm(x, w) is None
 
 
-@pytest.mark.parametrize("M", [1, 8, 16, 17, 32])
-@pytest.mark.parametrize("N,K", [(1536, 1536), (1536, 8960), (96, 224), (200, 80)])
-@pytest.mark.parametrize("bias", [False, True])
-def test_product_with_residual_and_sums_of_squares(M, N, K, bias):
+@pytest.mark.parametrize("M", [1, 8, 16, 17, 32, 64])
+@pytest.mark.parametrize("N,K", [(1536, 1536), (1536, 8960), (96, 224), (200, 80), (3584, 18944)])
+@pytest.mark.parametrize("bias,gamma_dtype", [(False, None), (True, torch.float32),
+                                              (False, torch.bfloat16)])
+def test_product_with_residual_and_sums_of_squares(M, N, K, bias, gamma_dtype):
+    """``s = resid + x W^T (+ b)``, ``bf16(s * gamma)`` and the partial sums of squares of ``s``,
+    whichever way the K range is split."""
     from ginfer_b200.ops import gemm_bf16
     g = torch.Generator(device="cpu").manual_seed(M + N)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
     w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
     b = torch.randn(N, generator=g).to(DEV) if bias else None
+    gamma = None if gamma_dtype is None else \
+        (1 + 0.3 * torch.randn(N, generator=g)).to(gamma_dtype).to(DEV)
     resid = (torch.randn(M, N, generator=g) * 2).to(DEV)
-    got = gemm_bf16.gemm_resid(x, w, b, resid)
+    got = gemm_bf16.gemm(x, w, b, resid=resid, gamma=gamma)
     assert got is not None
-    s, sumsq = got
+    s, scaled, sumsq = got
     want = resid.double() + _ref(x, w, b)
     torch.testing.assert_close(s.double(), want, atol=1e-3, rtol=1e-4)
+    assert sumsq.shape == (-(-N // 128) * gemm_bf16.split_k_for(M, N, K), gemm_bf16.sumsq_ld(M))
     torch.testing.assert_close(sumsq[:, :M].double().sum(0), (want ** 2).sum(1), atol=1e-2,
                                rtol=1e-4)
+    if gamma is None:
+        assert scaled is None
+    else:
+        assert torch.equal(scaled, (s * gamma.float()).to(torch.bfloat16))
     gemm_bf16.check_errors()
 
 
-@pytest.mark.parametrize("M", [1, 8, 16, 23, 32])
+@pytest.mark.parametrize("M", [1, 8, 16, 23, 32, 64])
 @pytest.mark.parametrize("N,K,gated", [(2048, 1536, False), (17920, 1536, True), (389, 96, False),
                                        (448, 96, True), (160, 80, False), (151936 // 16, 1536, False)])
-@pytest.mark.parametrize("gamma_dtype", [torch.float32, torch.bfloat16])
-def test_product_of_a_normalised_operand_equals_norm_then_product(M, N, K, gated, gamma_dtype):
-    """The fused consumer gives what the stand-alone norm kernel followed by the plain product
-    gives (the same rounding points), fed by a producer's statistics."""
+def test_product_behind_a_deferred_normalisation(M, N, K, gated):
+    """A product over ``s * gamma`` whose accumulator is multiplied by ``1 / rms(s)`` token by
+    token, the statistics coming from the product that formed ``s``: against float64, and close
+    to the stand-alone norm kernel followed by the plain product."""
     from ginfer_b200 import ops
     from ginfer_b200.ops import gemm_bf16
     g = torch.Generator(device="cpu").manual_seed(M * 3 + N)
     eps = 1e-5
-    # a producer makes the residual and its statistics: resid = r0 + x0 W0^T with K as its width
     x0 = torch.randn(M, 64, generator=g).to(torch.bfloat16).to(DEV)
     w0 = (torch.randn(K, 64, generator=g) * 0.3).to(torch.bfloat16).to(DEV)
     r0 = torch.randn(M, K, generator=g).to(DEV)
-    prod = gemm_bf16.gemm_resid(x0, w0, None, r0)
+    gamma = (1 + 0.2 * torch.randn(K, generator=g)).to(DEV)
+    prod = gemm_bf16.gemm(x0, w0, None, resid=r0, gamma=gamma)
     assert prod is not None
-    resid, sumsq = prod
-    gamma = (1 + 0.2 * torch.randn(K, generator=g)).to(gamma_dtype).to(DEV)
+    s, scaled, sumsq = prod
     w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
     bias = None if gated else torch.randn(N, generator=g).to(DEV)
     out_dtype = torch.float32 if (not gated and N % 5 == 1) else torch.bfloat16
-    got = gemm_bf16.gemm_normed(resid, sumsq, gamma, eps, w, bias, out_dtype, gated=gated)
+    got = gemm_bf16.gemm(scaled, w, bias, out_dtype, epi=2 if gated else 0,
+                         scale=gemm_bf16.RowScale(sumsq, eps))
     assert got is not None
+    inv = torch.rsqrt((s.double() ** 2).mean(1, keepdim=True) + eps)
+    acc = (scaled.double() @ w.double().t()) * inv
+    if gated:
+        gate = acc[:, 0::2].to(torch.bfloat16).double()
+        up = acc[:, 1::2].to(torch.bfloat16).double()
+        want = gate * torch.sigmoid(gate) * up
+    else:
+        want = acc + bias.double()
+    tol = dict(atol=2e-3, rtol=1e-3) if out_dtype == torch.float32 else dict(atol=3e-2, rtol=2e-2)
+    torch.testing.assert_close(got.double(), want, **tol)
     zero = torch.zeros((M, K), dtype=torch.bfloat16, device=DEV)
-    _, normed = ops.add_rmsnorm(resid, zero, gamma, eps)          # bf16, the stand-alone kernel
-    want = gemm_bf16.gemm(normed, w, bias, out_dtype, epi=2 if gated else 0, split_k=1)
-    # equal up to the order in which the squares (and the split K range) are added: an rms that
-    # differs in its last bit flips the rounding of a few operand elements
-    tol = dict(atol=3e-3, rtol=1e-3) if out_dtype == torch.float32 else dict(atol=3e-2, rtol=2e-2)
-    torch.testing.assert_close(got.float(), want.float(), **tol)
+    _, normed = ops.add_rmsnorm(s, zero, gamma, eps)              # bf16, the stand-alone kernel
+    plain = gemm_bf16.gemm(normed, w, bias, out_dtype, epi=2 if gated else 0, split_k=1)
+    # the two round the operand at different points (before and after the division by rms), so
+    # single elements may land on either side of a bf16 rounding step; on the whole they agree
+    # (within one rounding step of the operands, 2^-7 relative, on average)
+    diff = (got.float() - plain.float()).abs()
+    assert float(diff.mean()) < 2.0 ** -7 * max(1.0, float(plain.float().abs().mean()))
     gemm_bf16.check_errors()

@@ -124,11 +124,18 @@ def test_trace_program_mixed(folders, tmp_path, dtype):
 
 @pytest.mark.parametrize("name", ["A", "B", "C"])
 @pytest.mark.parametrize("cut", ["tail", "mixed"])
-def test_cuts_agree_with_plain_when_norms_are_folded_into_products(folders, name, cut, monkeypatch):
-    """Short bfloat16 steps with the residual additions and the normalisations folded into the
-    neighbouring products (off by default) give the logits of the plain implementation too."""
+@pytest.mark.parametrize("fold", [16, 64])
+def test_cuts_agree_with_plain_when_norms_are_folded_into_products(folders, name, cut, fold,
+                                                                    monkeypatch):
+    """Short bfloat16 steps can fold the residual additions and the normalisations into the
+    neighbouring products (off by default).  With that on, for steps of up to 16 and up to 64
+    tokens, the logits are those of the plain implementation too."""
+    from ginfer_b200.ops import gemm_bf16
     from ginfer_b200.parts import block
-    monkeypatch.setattr(block, "FOLD_MAX_TOKENS", 32)
+    monkeypatch.setattr(block, "FOLD_MAX_TOKENS", fold)
+    monkeypatch.setattr(gemm_bf16, "PLAIN_MAX_TOKENS", fold)
+    monkeypatch.setattr(gemm_bf16, "PLAIN_MAX_TOKENS_LONG_K", max(fold, 48))
+    monkeypatch.setattr(gemm_bf16, "MAX_TOKENS", fold)
     model_dir = folders[(name, "bfloat16")]
     reqs = _requests(name)
     steps = replay.cut_tail_decode(reqs) if cut == "tail" else replay.cut_mixed(reqs, seed=7)[0]
