@@ -20,6 +20,8 @@
 // are fp32 (the reference keeps S, P, the maximum and O in bf16:
 // flash_gqa_varlen_kernel.cu:169-172,220-257); P is rounded to bf16 for the P*V product.
 // Visibility: the query at position p sees key c iff c <= p and (window == 0 or p - c < window).
+#include <mutex>
+
 #include "attention_mma.cuh"
 #include "tc_common.cuh"
 
@@ -101,6 +103,7 @@ struct RopeArgs {
   int write_kv;                // 0: the cache is another layer's to write
 };
 constexpr int kMaxTableCopy = 4096;   // block-table entries a CTA copies to shared memory at most
+constexpr int kMaxDevicesTracked = 64;        // devices whose per-device set-up is remembered
 constexpr int kMaxDecodeGroups = 1 << 16;     // (request, kv head, head chunk) triples with a counter
 __device__ unsigned int g_decode_done[kMaxDecodeGroups];
 
@@ -1009,7 +1012,7 @@ static int attn_decode_impl(const void* q, int q_row_stride, const void* kpages,
                             void* scratch, int B, int nh, int nkv, int page_size, int window,
                             float scale, int splits, const RopeArgs& rope, void* stream) {
   if (B <= 0) return 0;
-  if (nh % nkv || splits < 1) return -3;
+  if (nkv <= 0 || nh <= 0 || nh % nkv || splits < 1) return -3;
   auto st = (cudaStream_t)stream;
   const int G = nh / nkv, chunks = (G + 15) / 16;
   const size_t tiles = (size_t)2 * DEC_STAGES * KT * ROW * sizeof(bf16);
@@ -1018,13 +1021,20 @@ static int attn_decode_impl(const void* q, int q_row_stride, const void* kpages,
   const int tbl_cap = table_stride < kMaxTableCopy ? table_stride : kMaxTableCopy;
   const size_t q_tile = (size_t)18 * HD * sizeof(bf16);        // fused mode: rotated q, new k and v
   const size_t smem = work + (size_t)tbl_cap * sizeof(int) + q_tile;
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)(work + kMaxTableCopy * sizeof(int) + q_tile));
-    if (e != cudaSuccess) return (int)e;
-    attr_done = true;
+  // a kernel's attributes belong to a device: set them once on each device that is used
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevicesTracked) return -9;
+  static std::mutex attr_lock;
+  static bool attr_done[kMaxDevicesTracked] = {}, np_done[kMaxDevicesTracked] = {};
+  {
+    std::lock_guard<std::mutex> hold(attr_lock);
+    if (!attr_done[dev]) {
+      cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)(work + kMaxTableCopy * sizeof(int) + q_tile));
+      if (e != cudaSuccess) return (int)e;
+      attr_done[dev] = true;
+    }
   }
   float* po = (float*)scratch;
   float* pml = po ? po + (size_t)B * nh * splits * HD : nullptr;
@@ -1032,12 +1042,14 @@ static int attn_decode_impl(const void* q, int q_row_stride, const void* kpages,
   if (splits > 1 && !scratch) {
     // cluster mode: the splits of a group merge through distributed shared memory
     if (splits != 2 && splits != 4 && splits != 8 && splits != 16) return -4;
-    static bool np_done = false;
-    if (!np_done) {
-      cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel,
-                                           cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-      if (e != cudaSuccess) return (int)e;
-      np_done = true;
+    {
+      std::lock_guard<std::mutex> hold(attr_lock);
+      if (!np_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel,
+                                             cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e != cudaSuccess) return (int)e;
+        np_done[dev] = true;
+      }
     }
     return launch_kernel_cluster_dims(attn_decode_kernel, grid, dim3(NTHREADS), smem, st, splits,
                                       true, (const bf16*)q, q_row_stride, (const bf16*)kpages,
@@ -1177,8 +1189,9 @@ namespace {
 // cudaGetSymbolAddress, never an address a kernel could use.
 static __device__ __align__(256) unsigned char g_static_scratch[GF_ATTN_STATIC_SCRATCH_BYTES];
 
-constexpr int kMaxDevices = 64;
+constexpr int kMaxDevices = kMaxDevicesTracked;
 void* g_static_scratch_addr[kMaxDevices] = {};     // device address per device, found on first use
+std::mutex g_static_lock;                          // guards the look-up: first calls may coincide
 thread_local char g_static_error[256] = "";
 
 }  // namespace
@@ -1207,19 +1220,24 @@ GF_EXPORT int gf_attn_decode_static(const void* q, int q_row_stride, const void*
              cudaGetErrorString(e), dev);
     return e != cudaSuccess ? (int)e : -9;
   }
-  if (!g_static_scratch_addr[dev]) {
-    // once per device, with that device current: the array's address on this device
-    void* p = nullptr;
-    e = cudaGetSymbolAddress(&p, g_static_scratch);
-    if (e != cudaSuccess || !p) {
-      snprintf(g_static_error, sizeof g_static_error,
-               "gf_attn_decode_static: cudaGetSymbolAddress failed on device %d: %s", dev,
-               cudaGetErrorString(e));
-      return e != cudaSuccess ? (int)e : -9;
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> hold(g_static_lock);
+    if (!g_static_scratch_addr[dev]) {
+      // once per device, with that device current: the array's address on this device
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_static_scratch);
+      if (e != cudaSuccess || !p) {
+        snprintf(g_static_error, sizeof g_static_error,
+                 "gf_attn_decode_static: cudaGetSymbolAddress failed on device %d: %s", dev,
+                 cudaGetErrorString(e));
+        return e != cudaSuccess ? (int)e : -9;
+      }
+      g_static_scratch_addr[dev] = p;
     }
-    g_static_scratch_addr[dev] = p;
+    scratch = g_static_scratch_addr[dev];
   }
   return gf_attn_decode(q, q_row_stride, kpages, vpages, block_table, table_stride, cu_seqlens_q,
-                        positions, out, splits > 1 ? g_static_scratch_addr[dev] : nullptr, B, nh,
-                        nkv, page_size, window, scale, splits, stream);
+                        positions, out, splits > 1 ? scratch : nullptr, B, nh, nkv, page_size,
+                        window, scale, splits, stream);
 }

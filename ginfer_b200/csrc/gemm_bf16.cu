@@ -32,7 +32,10 @@
 // SwiGLU kernel (swiglu_kernel.cu:6-31).
 //
 // Every wait on an mbarrier is bounded: after kSpinLimit polls the waiter records an error code in
-// *err and leaves its loop; all roles then meet at the final barrier and tensor memory is freed.
+// *err and leaves its loop; all roles then meet at the final barrier, the CTA waits (bounded again)
+// for those of its own copies that nobody consumed, and tensor memory is freed.  A build with
+// -DGF_TEST_SKIP_STAGE (and a small -DGF_SPIN_LIMIT) leaves out the loads of one K block so that a
+// test can watch this happen: the MMA issuer's wait runs out, the kernel returns, *err says 2.
 #include "tc_common.cuh"
 
 namespace gf {
@@ -301,6 +304,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   float* scale_s = (float*)(tmem_slot + 2);           // [BN] factors of a deferred normalisation
   float* sq_s = scale_s + BN;                         // [4][BN] squares per epilogue warp (EPI_RESID)
   __shared__ bool is_last;
+  __shared__ int gave_up;                             // a wait of this CTA ran out
+  __shared__ int issued_s;                            // K blocks whose loads the producer got to
+#ifdef GF_TEST_SKIP_STAGE
+  constexpr int kSkipped = 1;                         // the K block whose loads never go out
+#else
+  constexpr int kSkipped = -1;
+#endif
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BM, m0 = blockIdx.y * BN, split = blockIdx.z;
@@ -323,6 +333,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   }
 #endif
   if (threadIdx.x == 0) {
+    gave_up = 0;
+    issued_s = 0;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full + s, 1);
       mbar_init(empty + s, 1);
@@ -349,23 +361,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       // wait for that kernel and add the activations to the same stages.
       const int pre = nkb < STAGES ? nkb : STAGES;
       for (int i = 0; i < pre; ++i) {
+        if (i == kSkipped) continue;
         mbar_expect_tx(full + i, A_BYTES + B_BYTES);
         tma_load_2d(tiles + i * (A_BYTES + B_BYTES), &tmap_w, full + i, (kb0 + i) * BK, n0);
       }
       GF_STAMP(3);
       pdl_wait();
       GF_STAMP(4);
-      for (int i = 0; i < pre; ++i)
+      for (int i = 0; i < pre; ++i) {
+        if (i == kSkipped) continue;
         tma_load_2d(tiles + i * (A_BYTES + B_BYTES) + A_BYTES, &tmap_x, full + i, (kb0 + i) * BK,
                     m0);
+      }
+      int issued = pre;
       for (int i = pre; i < nkb; ++i) {
         const int s = i % STAGES;
-        if (!mbar_wait(empty + s, ((i / STAGES) & 1) ^ 1, err, 1)) break;
+        if (!mbar_wait(empty + s, ((i / STAGES) & 1) ^ 1, err, 1)) {
+          gave_up = 1;
+          break;
+        }
         mbar_expect_tx(full + s, A_BYTES + B_BYTES);
         unsigned char* a = tiles + s * (A_BYTES + B_BYTES);
         tma_load_2d(a, &tmap_w, full + s, (kb0 + i) * BK, n0);
         tma_load_2d(a + A_BYTES, &tmap_x, full + s, (kb0 + i) * BK, m0);
+        issued = i + 1;
       }
+      issued_s = issued;
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -374,7 +395,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       for (int i = 0; i < nkb && ok; ++i) {
         const int s = i % STAGES;
         ok = mbar_wait(full + s, (i / STAGES) & 1, err, 2);
-        if (!ok) break;
+        if (!ok) {
+          gave_up = 1;
+          break;
+        }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t a = smem_u32(tiles + s * (A_BYTES + B_BYTES));
         const uint64_t ad = umma_desc(a), bd = umma_desc(a + A_BYTES);
@@ -411,6 +435,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     }
     const float* scale = ex.in_sumsq ? scale_s : nullptr;
     const bool ok = mbar_wait(acc_full, 0, err, 3);
+    if (!ok) gave_up = 1;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ex.in_sumsq) {
       for (int t0 = 0; t0 < BN; t0 += 128 / tpt) {         // the same trip count for every thread
@@ -511,6 +536,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (gave_up) {
+    // a role left its loop early: copies of this CTA that nobody consumed may still be on their
+    // way into its shared memory.  Wait for the last one asked for in each stage (bounded).
+    if (threadIdx.x == 0) {
+      for (int s = 0; s < STAGES; ++s) {
+        int last = -1;
+        for (int i = s; i < issued_s; i += STAGES)
+          if (i != kSkipped) last = i;
+        if (last >= 0) mbar_wait(full + s, (last / STAGES) & 1, nullptr, 0);
+      }
+    }
+    __syncthreads();
+  }
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem),
                  "r"(TMEM_COLS)

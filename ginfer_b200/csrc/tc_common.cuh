@@ -10,7 +10,10 @@ namespace gf {
 constexpr int BM = 128;            // W rows per CTA = TMEM lanes
 constexpr int BK = 64;             // K elements per stage: one 128-byte swizzle row of bf16
 constexpr int UMMA_K = 16;
-constexpr uint32_t kSpinLimit = 1u << 22;
+#ifndef GF_SPIN_LIMIT
+#define GF_SPIN_LIMIT (1u << 22)     // polls of an mbarrier before a waiter gives up (~0.3 s)
+#endif
+constexpr uint32_t kSpinLimit = GF_SPIN_LIMIT;
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
@@ -38,7 +41,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* e
     if (done) return true;
     if (spin > 1024) __nanosleep(64);
   }
-  if (err) atomicExch(err, code);
+  if (err) atomicCAS(err, 0, code);      // the first wait that ran out names the role
   return false;
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar,

@@ -67,9 +67,7 @@ class ModelRunner:
         specs = model.cache_specs()
         self.groups, self._group_of_cache = plan_groups(specs)
         itemsize = torch.empty((), dtype=self.dtype).element_size()
-        if num_pages is None:
-            num_pages = self._pages_from_memory(gpu_memory_utilization, itemsize)
-        counts = [int(num_pages)] * len(self.groups)
+        counts = self._page_counts(num_pages, gpu_memory_utilization, itemsize)
         self.cache = NativeCacheManager([g.window for g in self.groups], counts, self.page_size,
                                         self.max_num_seqs, self.max_seq_len)
         self.storage = CacheStorage(specs, self.groups, counts, self.page_size,
@@ -86,13 +84,37 @@ class ModelRunner:
         self.h2d_bytes = 0            # bytes of step integers copied to the device so far
         self.graph_launches = 0       # kernel launches replayed from CUDA graphs so far
 
-    def _pages_from_memory(self, utilization: float, itemsize: int) -> int:
+    def _page_counts(self, num_pages, utilization: float, itemsize: int) -> list[int]:
+        """Pages for every cache group.  A group never gets more than it can hold at once
+        (:meth:`GroupLayout.pages_for`: a windowed group needs few).  ``num_pages``: a count for
+        every group, or one per group, or ``None``: the share ``utilization`` of the free device
+        memory is divided so that the groups can hold the same number of tokens, what the
+        windowed groups do not need going to the others."""
+        caps = [g.pages_for(self.max_num_seqs, self.max_seq_len, self.max_num_batched_tokens,
+                            self.page_size) for g in self.groups]
+        if num_pages is not None:
+            asked = list(num_pages) if isinstance(num_pages, (list, tuple)) \
+                else [num_pages] * len(self.groups)
+            if len(asked) != len(self.groups):
+                raise ValueError(f"{len(asked)} page counts for {len(self.groups)} cache groups")
+            return [max(1, min(int(n), cap)) for n, cap in zip(asked, caps)]
         free, _total = torch.cuda.mem_get_info(self.device)
-        per_page = sum(g.bytes_per_page(self.page_size, itemsize) for g in self.groups) or 1
-        want = int(free * utilization) // per_page
-        # nobody needs more pages than every slot filled to max_seq_len
-        cap = self.max_num_seqs * (-(-self.max_seq_len // self.page_size))
-        return max(1, min(want, cap))
+        budget = int(free * utilization)
+        per_page = [g.bytes_per_page(self.page_size, itemsize) for g in self.groups]
+        counts = [0] * len(self.groups)
+        open_groups = list(range(len(self.groups)))
+        while open_groups:          # equal counts for the groups still open; the capped ones leave
+            share = budget // max(1, sum(per_page[g] for g in open_groups))
+            capped = [g for g in open_groups if caps[g] <= share]
+            if not capped:
+                for g in open_groups:
+                    counts[g] = max(1, share)
+                break
+            for g in capped:
+                counts[g] = caps[g]
+                budget -= caps[g] * per_page[g]
+                open_groups.remove(g)
+        return counts
 
     # ------------------------------------------------------------------ requests
     def end(self, request_id) -> None:
@@ -127,6 +149,9 @@ class ModelRunner:
         if (q_lens <= 0).any():
             raise ValueError("an entry brings no tokens")
         T = int(q_lens.sum())
+        if T > self.max_num_batched_tokens:
+            raise ValueError(f"a step of {T} tokens; max_num_batched_tokens is "
+                             f"{self.max_num_batched_tokens} (the cache pools are sized for it)")
         # pages: check the whole step before taking any (one call into the native manager)
         slots = np.fromiter((cache.requests[i].slot if i in cache.requests else -1 for i in ids),
                             dtype=np.int32, count=B)
@@ -269,7 +294,7 @@ class ModelRunner:
         app("seq_of_token", range(B, Bp))
         app("cu_seqlens_q", range(B + 1, Bp + 1))
         app("kv_lens", [1] * extra)
-        app("slot_ids", [0] * extra)
+        app("slot_ids", [self.storage.scratch_slot] * extra)
         app("logit_rows", range(B, Bp))
         for g in range(self.cache.num_groups):
             scratch = self.storage.num_pages[g]
@@ -282,7 +307,8 @@ class ModelRunner:
         f = dict(facts, B=Bp, T=Bp,
                  q_lens=np.concatenate([facts["q_lens"], np.ones(extra, dtype=np.int64)]),
                  q_starts=np.concatenate([facts["q_starts"], np.zeros(extra, dtype=np.int64)]),
-                 slot_ids=np.concatenate([facts["slot_ids"], np.zeros(extra, dtype=np.int64)]))
+                 slot_ids=np.concatenate([facts["slot_ids"], np.full(extra, self.storage.scratch_slot,
+                                                                       dtype=np.int64)]))
         return a, f
 
     def _padding_step(self, Bp: int, width: int):
@@ -306,9 +332,7 @@ class ModelRunner:
         capture the CUDA graphs of decode steps now, for every batch-size bucket up to
         ``max_num_seqs`` and every table width up to ``max_width`` pages (default: four width
         steps), instead of when a step first needs one.  Returns how many graphs were captured.
-        Models with per-request state are left alone (the padding row would write slot 0)."""
-        if self.storage.state:
-            return 0
+        The padding rows' per-request state is the scratch slot's."""
         with torch.cuda.device(self.device):
             arrays, facts = self._padding_step(1, 1)
             dev = self.upload(arrays)
@@ -333,7 +357,7 @@ class ModelRunner:
     def _graph_key(self, entries, facts):
         """Decode steps in which every request wants its token's logits replay a CUDA graph; so
         do steps with prompt portions whose shape has come before (see PORTION_GRAPH_*)."""
-        if self.enforce_eager or self.storage.state:
+        if self.enforce_eager:
             return None
         if facts["max_q_len"] == 1:
             if any(len(e.want) != 1 for e in entries):
@@ -362,7 +386,12 @@ class ModelRunner:
         ctx.max_kv_len = min(facts["width"] * self.page_size, self.max_seq_len)
         ctx.capturing = True
         bind = self.binder(dev)
-        self.model.forward(ctx, bind)                 # once eagerly: libraries, handles, attributes
+        # once eagerly: libraries, handles, attributes.  Pages take the same values again when the
+        # graph runs; per-request state would be advanced twice, so it is put back.
+        kept = {cid: t.clone() for cid, t in self.storage.state.items()}
+        self.model.forward(ctx, bind)
+        for cid, t in kept.items():
+            self.storage.state[cid].copy_(t)
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
         if self._graph_pool is None:

@@ -8,7 +8,7 @@ from ctypes import c_float, c_int, c_void_p
 import torch
 
 KEY_TILE = 64
-TARGET_CTAS = 148 * 2          # two resident CTAs of the decode kernel per SM
+CTAS_PER_SM = 2                # resident CTAs of the decode kernel on one SM
 MAX_SPLITS = 64
 
 _scratch: dict = {}
@@ -18,12 +18,15 @@ def supports(hd: int, nh: int, nkv: int) -> bool:
     return hd % 16 == 0 and 16 <= hd <= 256 and nh % nkv == 0
 
 
-def decode_splits(batch: int, nh: int, nkv: int, max_keys: int) -> int:
+def decode_splits(batch: int, nh: int, nkv: int, max_keys: int, sms: int | None = None) -> int:
     """How many ways to split each request's keys so that the grid fills the GPU: a power of two
-    up to 8, so that the splits of a request can form a thread-block cluster."""
+    up to 8, so that the splits of a request can form a thread-block cluster.  ``sms``: the
+    device's SM count (asked of the current device if ``None``)."""
+    from .gemm_bf16 import num_sms
     chunks = (nh // nkv + 15) // 16
     base = max(1, batch * nkv * chunks)
-    want = min(max(1, TARGET_CTAS // base), max(1, -(-max_keys // KEY_TILE)))
+    target = (sms or num_sms()) * CTAS_PER_SM
+    want = min(max(1, target // base), max(1, -(-max_keys // KEY_TILE)))
     splits = 1
     while splits * 2 <= min(want, 8):                 # clusters of 16 schedule badly: 8 at most
         splits *= 2

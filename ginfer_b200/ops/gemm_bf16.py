@@ -7,8 +7,23 @@ from dataclasses import dataclass
 
 import torch
 
-NUM_SMS = 148
+B200_SMS = 148                 # what the split choices assume where no device can be asked
 _state: dict = {}
+_sms: dict = {}
+
+
+def num_sms(device=None) -> int:
+    """Streaming multiprocessors of ``device`` (the current one if ``None``), read from the
+    device; without a CUDA device (host-side tests of the split choices) a B200's count."""
+    if not torch.cuda.is_available():
+        return B200_SMS
+    key = torch.device(device).index if device is not None else None
+    if key is None:
+        key = torch.cuda.current_device()
+    n = _sms.get(key)
+    if n is None:
+        n = _sms[key] = torch.cuda.get_device_properties(key).multi_processor_count
+    return n
 
 
 def _dev_state(device):
@@ -49,17 +64,19 @@ def token_tile(M: int) -> int:
     return 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
 
 
-def split_k_for(M: int, N: int, K: int) -> int:
+def split_k_for(M: int, N: int, K: int, sms: int | None = None) -> int:
     """Split the K range of products whose tiles alone would leave most SMs idle: 2, 4, 8 or 12
-    splits, which form a thread-block cluster and add up through distributed shared memory."""
+    splits, which form a thread-block cluster and add up through distributed shared memory.
+    ``sms``: the device's SM count (asked of the current device if ``None``)."""
+    sms = sms or num_sms()
     tiles = -(-N // 128) * -(-M // token_tile(M))
     nkb = -(-K // 64)
     split = 1
-    while split < 8 and tiles * split * 2 <= NUM_SMS + NUM_SMS // 4 and nkb // (split * 2) >= 2:
+    while split < 8 and tiles * split * 2 <= sms + sms // 4 and nkb // (split * 2) >= 2:
         split *= 2
-    if split == 8 and tiles * 12 <= NUM_SMS and nkb // 12 >= 8:
+    if split == 8 and tiles * 12 <= sms and nkb // 12 >= 8:
         split = 12      # a long reduction on few tiles (the down product): 144 CTAs instead of 96
-    if split == 1 and M <= 16 and NUM_SMS // 2 < tiles <= NUM_SMS and nkb >= 16:
+    if split == 1 and M <= 16 and sms // 2 < tiles <= sms and nkb >= 16:
         split = 2       # about one tile an SM (gate/up): pairs of CTAs have more under way
     return split
 

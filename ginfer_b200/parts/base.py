@@ -37,11 +37,18 @@ class TensorSpec:
 # ----------------------------------------------------------------------------- caches of a mixer
 @dataclass(frozen=True)
 class PagedKVSpec:
-    """Keys and values of every position (``window == 0``) or of the last ``window`` positions,
-    kept in pages."""
+    """What a mixer keeps of every position (``window == 0``) or of the last ``window``
+    positions, in pages.  By default keys and values of ``num_kv_heads`` heads of ``head_dim``
+    each.  ``planes`` names another lay-out: one ``(heads, width)`` per tensor kept of a token
+    (one latent vector: ``((1, width),)``; keys and values of different widths:
+    ``((heads, k_width), (heads, v_width))``)."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
+    planes: tuple[tuple[int, int], ...] | None = None
+
+    def layout(self) -> tuple[tuple[int, int], ...]:
+        return self.planes or ((self.num_kv_heads, self.head_dim),) * 2
 
 
 @dataclass(frozen=True)
@@ -53,7 +60,9 @@ class StateSpec:
 
 @dataclass
 class PagedKVBinding:
-    pages: torch.Tensor          # [2, num_pages, page_size, num_kv_heads, head_dim]; 0 = K, 1 = V
+    # [2, num_pages, page_size, num_kv_heads, head_dim] (0 = K, 1 = V); for a spec with ``planes``
+    # a tuple of tensors [num_pages, page_size, heads, width], one per plane
+    pages: torch.Tensor | tuple
     block_table: torch.Tensor    # [B, W] int32, logical page -> physical page, -1 where none
     slot_mapping: torch.Tensor   # [T] int32, physical token slot (page * page_size + offset)
     page_size: int

@@ -45,8 +45,11 @@ class Sampler:
     def __init__(self, device):
         self.device = torch.device(device)
         cuda = self.device.type == "cuda"
-        self._host = torch.empty((2, 1024), dtype=torch.float32, pin_memory=True) if cuda else None
-        # two result buffers: a step's tokens may be read while the next step's are on their way
+        # two buffers each way, taken in turns: a step's temperatures and uniforms may still be on
+        # their way to the device, and its tokens still unread, when the next step is prepared
+        self._host = [torch.empty(2 * 1024, dtype=torch.float32, pin_memory=True)
+                      for _ in range(2)] if cuda else None
+        self._sent = [None, None]            # the copy out of each host buffer has happened
         self._out = [torch.empty(1024, dtype=torch.int32, pin_memory=True) for _ in range(2)] \
             if cuda else None
         self._turn = 0
@@ -59,18 +62,23 @@ class Sampler:
         R = logits.shape[0]
         if R == 0:
             return Pending(torch.empty(0, dtype=torch.int32), 0, None)
+        self._turn ^= 1
         if all(t <= 0 for t in temperatures):
             picks = ops.argmax(logits)
         else:
-            if R > self._host.shape[1]:
-                self._host = torch.empty((2, 2 * R), dtype=torch.float32, pin_memory=True)
-            h = self._host.numpy()
-            h[0, :R] = np.asarray(temperatures, dtype=np.float32)
-            h[1, :R] = np.asarray([uniform(s, i) for s, i in zip(seeds, indices)],
-                                  dtype=np.float32)
-            d = self._host[:, :R].to(self.device, non_blocking=True)
-            picks = ops.sample(logits, d[0].contiguous(), d[1].contiguous())
-        self._turn ^= 1
+            k = self._turn
+            if self._sent[k] is not None:
+                self._sent[k].synchronize()          # two steps back: long done
+            if 2 * R > self._host[k].numel():
+                self._host[k] = torch.empty(4 * R, dtype=torch.float32, pin_memory=True)
+            h = self._host[k].numpy()                # [temperatures | uniforms], contiguous
+            h[:R] = np.asarray(temperatures, dtype=np.float32)
+            h[R:2 * R] = np.asarray([uniform(s, i) for s, i in zip(seeds, indices)],
+                                    dtype=np.float32)
+            d = self._host[k][:2 * R].to(self.device, non_blocking=True)
+            self._sent[k] = torch.cuda.Event()
+            self._sent[k].record()
+            picks = ops.sample(logits, d[:R], d[R:])
         if R > self._out[self._turn].numel():
             self._out[self._turn] = torch.empty(2 * R, dtype=torch.int32, pin_memory=True)
         out = self._out[self._turn]

@@ -77,10 +77,58 @@ def check_and_convert(specs, available: dict, fetch, model_dir: str, compute: to
     if missing or unexpected or wrong_shape or wrong_dtype:
         raise WeightError(model_dir, sorted(missing), sorted(unexpected), wrong_shape, wrong_dtype)
     out = {}
+    up = Uploader(device) if torch.device(device).type == "cuda" else None
     for n, s in wanted.items():
         t = fetch(n)
-        out[n] = t.to(device=device, dtype=kept_dtype(s.role, t.dtype, compute)).contiguous()
+        kept = kept_dtype(s.role, t.dtype, compute)
+        if up is not None:
+            out[n] = up.put(t, kept)
+        else:
+            out[n] = t.to(device=device, dtype=kept).contiguous()
+    if up is not None:
+        up.finish()
     return out
+
+
+class Uploader:
+    """Tensors of a file mapping to the device through two pinned staging buffers: the host copies
+    the next piece out of the mapping while the device still receives the one before, and a
+    tensor stored in another dtype than it is kept in is converted on the device.  The reference
+    copies each tensor synchronously from pageable memory
+    (``ginfer/core/tensor/tensor.cc:76-90``).  Each tensor keeps an allocation of its own (no
+    slab): parts join tensors when they load (q|k|v, gate|up) and the originals are then freed."""
+
+    def __init__(self, device, staging_bytes: int = 64 << 20):
+        self.device = torch.device(device)
+        self.size = int(staging_bytes)
+        self.bufs = [torch.empty(self.size, dtype=torch.uint8, pin_memory=True) for _ in range(2)]
+        self.free = [torch.cuda.Event(), torch.cuda.Event()]      # the buffer's copy has left it
+        self.used = [False, False]
+        self.turn = 0
+        self.bytes = 0
+
+    def put(self, t: torch.Tensor, kept: torch.dtype) -> torch.Tensor:
+        """``t`` (CPU, contiguous) as a device tensor of dtype ``kept``."""
+        t = t.contiguous()
+        raw = t.reshape(-1).view(torch.uint8)
+        with torch.cuda.device(self.device):
+            dev = torch.empty(t.shape, dtype=t.dtype, device=self.device)
+            dst = dev.reshape(-1).view(torch.uint8)
+            for off in range(0, raw.numel(), self.size):
+                n = min(self.size, raw.numel() - off)
+                i = self.turn
+                self.turn ^= 1
+                if self.used[i]:
+                    self.free[i].synchronize()
+                self.bufs[i][:n].copy_(raw[off:off + n])          # out of the mapping
+                dst[off:off + n].copy_(self.bufs[i][:n], non_blocking=True)
+                self.free[i].record()
+                self.used[i] = True
+            self.bytes += raw.numel()
+            return dev if kept == t.dtype else dev.to(kept)
+
+    def finish(self) -> None:
+        torch.cuda.synchronize(self.device)
 
 
 def load_weights(model, model_dir: str, dtype: torch.dtype, device) -> None:

@@ -4,7 +4,9 @@ It shares no code with ``ginfer_b200``.  It is written from the reference's form
 each function cites file:line of that project).  The reference cannot be built or imported on the
 test machine (its build downloads nine packages, it has no CPU kernels, and its attention kernels
 take head sizes 64 and 128 only), so nothing here was compared with the reference's own output:
-this file rests on the formulas.
+this file rests on the formulas.  ``tests/test_plain.py`` holds its parts against hand-made
+cases and against the formulas that the reference's own Python tests use as their oracles
+(``python/test/test_op.py``).
 
 Arithmetic is float64 on the CPU unless ``dtype`` says otherwise, except where the reference fixes
 a 32-bit quantity that changes the result's meaning: the rotary angle is the fp32 product of the

@@ -57,8 +57,12 @@ def cut_portions(requests, sizes=(7, 2, 13, 3, 16, 2, 5, 31, 2, 1, 17)):
     return steps
 
 
+# portion sizes that reach the kernels of long prompts: 64 rows and more
+LONG_SIZES = (70, 128, 65, 200, 64, 97)
+
+
 def cut_mixed(requests, max_live: int = 4, seed: int = 0, decode_tail: int = 12,
-              singles_first: bool = False):
+              singles_first: bool = False, sizes=(2, 3, 5, 8, 13, 21, 34)):
     """Up to ``max_live`` live requests; each step holds portions of some beside single tokens of
     others; a request is sometimes left out of a step.  ``singles_first``: a step's single tokens
     come before its portions (the order in which a scheduler that decodes first sends them).  Returns ``(steps, max_tokens)`` where
@@ -79,7 +83,7 @@ def cut_mixed(requests, max_live: int = 4, seed: int = 0, decode_tail: int = 12,
                 continue                                   # left out of this step
             left = len(toks) - at
             if left > decode_tail:
-                n = min(left - decode_tail, rng.choice([2, 3, 5, 8, 13, 21, 34]))
+                n = min(left - decode_tail, rng.choice(list(sizes)))
             else:
                 n = 1
             entries.append({"id": rid, "tokens": toks[at:at + n], "want": list(range(n))})

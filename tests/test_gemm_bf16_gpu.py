@@ -139,3 +139,39 @@ def test_product_behind_a_deferred_normalisation(M, N, K, gated):
     diff = (got.float() - plain.float()).abs()
     assert float(diff.mean()) < 2.0 ** -7 * max(1.0, float(plain.float().abs().mean()))
     gemm_bf16.check_errors()
+
+
+@pytest.mark.parametrize("M,N,K,split_k", [(8, 256, 512, 1), (8, 1536, 1536, 8), (40, 384, 2048, 4)])
+def test_a_wait_that_runs_out_is_reported_and_the_kernel_returns(M, N, K, split_k):
+    """Every wait inside the kernel has a limit.  A build of the same source that leaves out the
+    loads of one K block (``-DGF_TEST_SKIP_STAGE``) and polls 3,000 times instead of four million
+    makes the MMA issuer's wait for that block run out (role 2), and where a CTA has more K
+    blocks than stages also the producer's wait for the stage that is never freed (role 1): the
+    kernel must come back, name the role that gave up first in the error word, free its tensor
+    memory, and leave the device usable: the regular build then computes the same product
+    correctly.  Nothing here faults or hangs: the kernel only stops waiting."""
+    from ctypes import c_int, c_void_p
+
+    from ginfer_b200 import ops
+    from ginfer_b200.ops import gemm_bf16
+    lib = ops.load_library("gemm_bf16", ("GF_SPIN_LIMIT=3000", "GF_TEST_SKIP_STAGE=1"))
+    f = lib.gf_gemm_bf16_tc
+    f.restype = c_int
+    f.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                  c_int, c_int, c_void_p, c_void_p, c_void_p]
+    g = torch.Generator(device="cpu").manual_seed(K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for _ in range(2):                        # twice: tensor memory was freed the first time
+        err.zero_()
+        rc = f(x.data_ptr(), K, w.data_ptr(), None, out.data_ptr(), N, M, N, K, 0, 0, split_k,
+               None, err.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        torch.cuda.synchronize()              # the kernel came back
+        blocks = -(-K // 64) // split_k       # K blocks of a CTA; its ring has 6 stages
+        assert int(err.item()) in ((2,) if blocks <= 6 else (1, 2))
+    got = gemm_bf16.gemm(x, w, None, torch.bfloat16, split_k=split_k)
+    torch.testing.assert_close(got.double(), _ref(x, w), atol=2e-2, rtol=1e-2)
+    gemm_bf16.check_errors()

@@ -179,6 +179,16 @@ def test_a_toy_mixer_with_state_of_its_own_registers_builds_and_steps(tmp_path):
             return StateSpec((self.h + 1,), torch.float32)      # the sum and the count
 
         def forward(self, x, ctx, cache):
+            if ctx.decode_only:
+                # one token a request: device indices only, so that the step can be captured in
+                # a CUDA graph and replayed for other requests and slots
+                slots = ctx.slot_ids.long()
+                st = cache.state[slots]
+                sums = st[:, :self.h] + x.float()
+                counts = st[:, self.h] + 1
+                if cache.write:
+                    cache.state[slots] = torch.cat([sums, counts[:, None]], dim=1)
+                return (sums / counts[:, None] * self.scale).to(x.dtype)
             out = torch.empty_like(x)
             at = 0
             for b, n in enumerate(ctx.q_lens_host):             # plain torch: a toy, not a kernel
@@ -266,12 +276,138 @@ def test_a_toy_mixer_with_state_of_its_own_registers_builds_and_steps(tmp_path):
                 r.end(rid)
     for rid in reqs:
         torch.testing.assert_close(torch.cat(got[rid]), whole[rid], atol=2e-5, rtol=1e-4)
+    # decoding from CUDA graphs: models with state in slots warm up and replay like the others
+    # (the rows that pad a batch up to a graph's size use the slot that no request owns)
+    r = ModelRunner(model, page_size=8, max_num_seqs=12, max_seq_len=128, num_pages=24,
+                    enforce_eager=False)
+    r.warmup()
+    names = list(reqs) + ["d", "e", "f", "g", "h", "i"]
+    toks = {**reqs, **{k: prompt(12 + i, 120, 10 + i) for i, k in enumerate(names[3:])}}
+    alone = {}
+    for k in names[3:]:
+        r0 = runner()
+        alone[k] = r0.step([StepEntry(k, toks[k], list(range(len(toks[k]))))]).cpu()
+    alone.update(whole)
+    r.step([StepEntry(k, toks[k][:8], []) for k in names])          # nine requests: a graph of 16
+    for i in range(8, 12):
+        out = r.step([StepEntry(k, [toks[k][i]], [0]) for k in names]).cpu()
+        for j, k in enumerate(names):
+            torch.testing.assert_close(out[j], alone[k][i], atol=2e-5, rtol=1e-4)
+    assert r.graph_launches > 0 and any(k[0] == 16 for k in r._graphs)
     # the state really is used: the mean mixer sees earlier tokens
     other = list(reqs["a"])
     other[0] = (other[0] + 1) % 120
     r2 = runner()
     changed = r2.step([StepEntry("a", other, [49])]).cpu()
     assert not torch.allclose(changed[0], whole["a"][49], atol=1e-4)
+
+
+def test_a_toy_mixer_that_caches_one_vector_a_token_registers_builds_and_steps(tmp_path):
+    """Defined here, not in the framework: a mixer whose paged cache holds ONE vector of 24
+    channels per token (neither keys and values nor heads: ``PagedKVSpec(planes=((1, 24),))``)
+    and whose output mixes each token with the mean of the cached vectors of the last ``window``
+    positions.  The cache manager, the storage and the step function take it as they take
+    attention: pages, block table, slot mapping, a window that gives pages back."""
+    from ginfer_b200.config import register_architecture
+    from ginfer_b200.engine import ModelRunner, StepEntry
+    from ginfer_b200.engine.loading import load_model
+    from ginfer_b200.parts import (LayerSpec, Mixer, ModelPlan, PagedKVSpec, PartSpec,
+                                   TensorSpec, register_mixer, sequential_run)
+    from ginfer_b200.weights import write_random_model
+    WIDTH = 24
+
+    class LatentMean(Mixer):
+        def __init__(self, hidden_size, window, prefix="latent"):
+            self.h, self.window, self.prefix = hidden_size, window, prefix
+
+        def tensor_specs(self):
+            return [TensorSpec(f"{self.prefix}.down.weight", (WIDTH, self.h)),
+                    TensorSpec(f"{self.prefix}.up.weight", (self.h, WIDTH))]
+
+        def load(self, tensors, dtype, device):
+            self.down = tensors[f"{self.prefix}.down.weight"].float()
+            self.up = tensors[f"{self.prefix}.up.weight"].float()
+
+        def cache_spec(self):
+            return PagedKVSpec(1, WIDTH, self.window, planes=((1, WIDTH),))
+
+        def forward(self, x, ctx, cache):
+            (plane,) = cache.pages                              # [pages, page, 1, WIDTH]
+            flat = plane.view(-1, WIDTH)
+            lat = x.float() @ self.down.t()
+            if cache.write:
+                flat[cache.slot_mapping.long()] = lat.to(flat.dtype)
+            out = torch.empty_like(x)
+            at = 0
+            for b, (n, start) in enumerate(zip(ctx.q_lens_host, ctx.q_starts_host)):
+                table = cache.block_table[b].long()
+                for i in range(n):                              # plain torch: a toy, not a kernel
+                    p = start + i
+                    pos = torch.arange(max(0, p - self.window + 1), p + 1, device=x.device)
+                    rows = table[pos // cache.page_size] * cache.page_size + pos % cache.page_size
+                    mean = flat[rows].float().mean(0)
+                    out[at + i] = ((lat[at + i] + mean) @ self.up.t()).to(x.dtype)
+                at += n
+            return out
+
+    register_mixer("latent_mean", LatentMean)
+
+    class ToyConfig:
+        torch_dtype = "float32"
+
+        def __init__(self, d):
+            self.d = dict(d)
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d)
+
+        def to_dict(self):
+            return dict(self.d)
+
+    def toy_plan(cfg):
+        H, V = cfg.d["hidden_size"], cfg.d["vocab_size"]
+        norm = lambda name: PartSpec("rmsnorm", dict(size=H, eps=1e-5, weight_name=name))
+        ffn = PartSpec("swiglu", dict(hidden_size=H, intermediate_size=96))
+        attn = PartSpec("attention", dict(
+            hidden_size=H, num_heads=4, num_kv_heads=2, head_dim=16,
+            position=PartSpec("rotary", dict(head_dim=16, theta=1e4, max_positions=256))))
+        layers = (LayerSpec("toy.0", PartSpec("latent_mean", dict(hidden_size=H, window=21)), ffn,
+                            norm("n1"), norm("n2")),
+                  LayerSpec("toy.1", attn, ffn, norm("n1"), norm("n2")))
+        return ModelPlan(hidden_size=H, vocab_size=V, max_positions=256,
+                         embedding=PartSpec("token", dict(vocab_size=V, hidden_size=H, name="emb")),
+                         layers=layers, run=sequential_run(2), final_norm=norm("final"),
+                         head=PartSpec("linear", dict(vocab_size=V, hidden_size=H, tied_to="emb")))
+
+    register_architecture("ToyLatentLM", ToyConfig, toy_plan)
+    cfg = {"architectures": ["ToyLatentLM"], "hidden_size": 64, "vocab_size": 120}
+    d = str(tmp_path / "latent")
+    write_random_model(d, cfg, seed=4, storage_dtype="float32")
+    model, _ = load_model(d, "float32")
+    r = ModelRunner(model, page_size=8, max_num_seqs=2, max_seq_len=128, num_pages=32,
+                    max_num_batched_tokens=96)
+    # two cache groups: the latent one (a plane of its own, windowed: few pages) and attention's
+    kinds = sorted((g.planes, g.stacked, g.window) for g in r.groups)
+    assert kinds == [(((1, WIDTH),), False, 21), (((2, 16), (2, 16)), True, 0)]
+    latent = next(i for i, g in enumerate(r.groups) if not g.stacked)
+    # 2 requests keep 3 + 2 pages of their windows live, a step brings at most 12 pages
+    assert r.cache.pools[latent].num_pages == 22 and r.cache.pools[1 - latent].num_pages == 32
+    assert isinstance(r.storage.pages_of(0), tuple) and r.storage.pages_of(0)[0].shape[1:] == \
+        (8, 1, WIDTH)
+    toks = prompt(90, 120, 5)
+    whole = r.step([StepEntry("w", toks, list(range(90)))]).cpu()
+    r.end("w")
+    got, at = [], 0
+    for n in (30, 1, 17, 2, 40):                                # the window passes pages: given back
+        got.append(r.step([StepEntry("p", toks[at:at + n], list(range(n)))]).cpu())
+        at += n
+        r.cache.check()
+    torch.testing.assert_close(torch.cat(got), whole, atol=2e-5, rtol=1e-4)
+    moved = list(toks)
+    moved[70] = (moved[70] + 1) % 120                           # within the window of token 89
+    r.end("p")
+    assert not torch.allclose(r.step([StepEntry("m", moved, [89])]).cpu()[0], whole[89], atol=1e-4)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

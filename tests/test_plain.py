@@ -118,6 +118,53 @@ def test_forward_is_causal_and_uses_every_option(tmp_path, name):
         assert not torch.allclose(plain.forward(w, cfg, toks, run=shared), full, atol=1e-6)
 
 
+def test_parts_agree_with_the_oracles_of_the_reference_tests():
+    """The reference checks its kernels against formulas written out in its own Python tests
+    (``python/test/test_op.py``): RMSNorm ``x * gamma / sqrt(mean(x^2) + eps)`` (:30-38), rotary
+    encoding with frequencies ``theta^(-2i / head_dim)`` over the pairs ``(i, i + head_dim / 2)``
+    (:187-210), ``gate * sigmoid(gate) * up`` (:244-256), and grouped-query attention as
+    scaled-dot-product attention over keys repeated per group with a lower-right causal mask
+    (:96-120).  The plain implementation's parts, written from the kernels' sources, give the
+    same numbers as those formulas restated here (the sliding window has no counterpart there:
+    the hand-made cases above define it)."""
+    g = torch.Generator().manual_seed(0)
+    x = torch.rand(3, 127, 128, generator=g, dtype=torch.float64)
+    gamma = torch.rand(128, generator=g, dtype=torch.float64)
+    ref = x * gamma / torch.sqrt((x ** 2).mean(-1, keepdim=True) + 1e-5)
+    assert torch.allclose(plain.rms_norm(x, gamma, 1e-5), ref, atol=1e-12)
+    # rotary: [seq, heads, head_dim], positions 0 .. seq - 1
+    for seq, heads, hd, theta in ((128, 32, 128, 10000.0), (64, 12, 64, 10000.0)):
+        x = torch.randn(seq, heads, hd, generator=g, dtype=torch.float64)
+        half = hd // 2
+        freqs = np.array([1.0 / theta ** (2.0 * i / hd) for i in range(half)], dtype=np.float32)
+        ang = np.outer(np.arange(seq, dtype=np.float32), freqs)
+        sin, cos = torch.from_numpy(np.sin(ang))[:, None, :], torch.from_numpy(np.cos(ang))[:, None, :]
+        lo, hi = x[..., :half], x[..., half:]
+        ref = torch.cat([lo * cos - hi * sin, lo * sin + hi * cos], dim=-1)
+        c, s_ = plain.rotary_cos_sin(torch.arange(seq), hd, theta)
+        assert torch.allclose(plain.apply_rotary(x, c, s_), ref, atol=1e-5)
+    # gate * sigmoid(gate) * up, as the feed-forward's middle
+    gate = torch.randn(4, 256, generator=g, dtype=torch.float64)
+    up = torch.randn(4, 256, generator=g, dtype=torch.float64)
+    eye = torch.eye(256, dtype=torch.float64)
+    ref = gate * torch.sigmoid(gate) * up
+    both = torch.cat([gate, up], dim=-1)                  # x = [gate | up]: the products pick them
+    w_gate, w_up = torch.cat([eye, 0 * eye], 1), torch.cat([0 * eye, eye], 1)
+    assert torch.allclose(plain.swiglu(both, w_gate, w_up, eye), ref, atol=1e-12)
+    # attention: q_len == kv_len here (the plain implementation takes whole sequences)
+    for heads, kv_heads, hd, T in ((12, 2, 128, 33), (32, 8, 128, 9), (12, 12, 64, 127)):
+        q = torch.randn(T, heads, hd, generator=g, dtype=torch.float64)
+        k = torch.randn(T, kv_heads, hd, generator=g, dtype=torch.float64)
+        v = torch.randn(T, kv_heads, hd, generator=g, dtype=torch.float64)
+        rep = heads // kv_heads
+        kk = k.permute(1, 0, 2).repeat_interleave(rep, dim=0)
+        vv = v.permute(1, 0, 2).repeat_interleave(rep, dim=0)
+        mask = torch.ones(T, T, dtype=torch.bool).tril(diagonal=0)
+        ref = torch.nn.functional.scaled_dot_product_attention(q.permute(1, 0, 2), kk, vv,
+                                                               attn_mask=mask).permute(1, 0, 2)
+        assert torch.allclose(plain.gqa_attention(q, k, v, 0), ref, atol=1e-10)
+
+
 def test_choosing_tokens():
     row = torch.tensor([0.1, 2.0, 2.0, -1.0])
     assert plain.greedy_token(row) == 1                         # lowest index among equals

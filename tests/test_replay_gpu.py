@@ -9,12 +9,15 @@ pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": [5, 17, 33, 70, 130, 49], "B": [1, 40, 90, 200, 66, 133], "C": [3, 64, 97, 35],
            "D": [2, 81, 150, 64, 33], "E": [9, 140, 260, 75, 200]}
-PAGE = {"A": 16, "B": 8, "C": 4, "D": 32, "E": 16}
+PAGE = {"A": 16, "B": 8, "C": 4, "D": 32, "E": 16, "F": 16}
+# long requests for the cuts whose portions are 64 tokens and more
+LONG_LENGTHS = {"E": [530, 333, 410, 150], "F": [520, 290, 400, 135]}
 
 
-def _requests(name):
+def _requests(name, lengths=None):
     v = CONFIGS[name]["vocab_size"]
-    return {f"r{i}": prompt(n, v, seed=100 * i + n) for i, n in enumerate(LENGTHS[name])}
+    return {f"r{i}": prompt(n, v, seed=100 * i + n)
+            for i, n in enumerate(lengths or LENGTHS[name])}
 
 
 def _storage(dtype):
@@ -55,6 +58,29 @@ def test_cuts_agree_with_plain(folders, name, dtype, cut):
         steps, _ = replay.cut_mixed(reqs, seed=7, singles_first=cut.endswith("first"))
     max_tokens = replay.peak_tokens(steps)          # so few pages that they are used again
     runner = _runner(model_dir, dtype, PAGE[name], max_tokens)
+    rows = replay.run_in_process(runner, steps)
+    replay.compare(rows, replay.plain_logits(model_dir, reqs, dtype), dtype, reqs)
+    assert not runner.cache.requests and all(
+        f == p.num_pages for f, p in zip(runner.cache.free_pages(), runner.cache.pools))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["E", "F"])
+@pytest.mark.parametrize("cut", ["portions_long", "mixed_long", "mixed_long_singles_first"])
+def test_long_portions_agree_with_plain(folders, name, dtype, cut):
+    """Portions of 64 to 200 tokens, at head sizes 64 and 128: in bfloat16 the tcgen05 attention
+    kernel then runs for portions that do not start their request (positions offset from the
+    rows), several requests a launch, and beside single tokens that go to the decode kernel."""
+    model_dir = folders[(name, _storage(dtype))]
+    reqs = _requests(name, LONG_LENGTHS[name])
+    if cut == "portions_long":
+        steps = replay.cut_portions(reqs, sizes=replay.LONG_SIZES)
+    else:
+        steps, _ = replay.cut_mixed(reqs, seed=11, sizes=replay.LONG_SIZES, decode_tail=6,
+                                    singles_first=cut.endswith("first"))
+    assert any(len(e["tokens"]) >= 64 and len(s["entries"]) > 1
+               for s in steps for e in s["entries"]) or cut == "portions_long"
+    runner = _runner(model_dir, dtype, PAGE[name], replay.peak_tokens(steps))
     rows = replay.run_in_process(runner, steps)
     replay.compare(rows, replay.plain_logits(model_dir, reqs, dtype), dtype, reqs)
     assert not runner.cache.requests and all(
@@ -144,26 +170,37 @@ def test_cuts_agree_with_plain_when_norms_are_folded_into_products(folders, name
     replay.compare(rows, replay.plain_logits(model_dir, reqs, "bfloat16"), "bfloat16", reqs)
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["B", "E"])
 def test_prompt_portions_of_a_shape_that_comes_again_are_replayed_from_graphs(folders, name):
     """Steps with prompt portions whose shape (portion lengths, wanted rows, table width) has come
-    before are replayed from a CUDA graph: four requests of 300 tokens, fed as 260 + 40, one after
-    the other; from the third on the 260-token step is a replay.  All agree with plain."""
+    before are replayed from a CUDA graph, whatever position the portion starts at: three
+    requests of 560 tokens, each fed as 260 + 260 + 40.  The 260-token step comes a second time
+    at position 260 of the first request (the graph is captured there) and is replayed at
+    positions 0 and 260 of the others.  All agree with plain."""
     model_dir = folders[(name, "bfloat16")]
     v = CONFIGS[name]["vocab_size"]
-    reqs = {f"q{i}": prompt(300, v, seed=50 + i) for i in range(4)}
+    reqs = {f"q{i}": prompt(560, v, seed=50 + i) for i in range(3)}
     steps = []
     for rid, toks in reqs.items():
-        steps.append({"step": len(steps), "end": [], "entries": [
-            {"id": rid, "tokens": toks[:260], "want": list(range(260))}]})
-        steps.append({"step": len(steps), "end": [rid], "entries": [
-            {"id": rid, "tokens": toks[260:], "want": list(range(40))}]})
-    runner = _runner(model_dir, "bfloat16", PAGE[name], 320, eager=False)
-    before = runner.graph_launches
-    rows = replay.run_in_process(runner, steps)
+        for lo, hi in ((0, 260), (260, 520), (520, 560)):
+            steps.append({"step": len(steps), "end": [rid] if hi == 560 else [], "entries": [
+                {"id": rid, "tokens": toks[lo:hi], "want": list(range(hi - lo))}]})
+    # pages of 16: positions 0 and 260 of a 260-token portion then share a block-table width
+    runner = _runner(model_dir, "bfloat16", 16, 576, eager=False)
+    from ginfer_b200.engine import StepEntry
+    outs, replayed = {}, []
+    for s in steps:
+        before = runner.graph_launches
+        e = s["entries"][0]
+        outs[s["step"]] = runner.step([StepEntry(e["id"], e["tokens"], e["want"])]).cpu().numpy()
+        replayed.append(runner.graph_launches > before)
+        for r in s["end"]:
+            runner.end(r)
+    # captured in the second step (position 260); replayed at 0 and at 260 afterwards
+    assert replayed == [False, True, False, True, True, False, True, True, False], replayed
+    rows = replay.collect(steps, lambda i: outs[i])
     replay.compare(rows, replay.plain_logits(model_dir, reqs, "bfloat16"), "bfloat16", reqs)
-    assert runner.graph_launches > before, "no step was replayed from a graph"
-    assert any(isinstance(k[0], str) for k in runner._graphs)
+    assert sum(isinstance(k[0], str) for k in runner._graphs) == 1
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -365,6 +365,52 @@ def test_split_choices_of_the_kernels():
     assert gemm_bf16.split_k_for(8, 17920, 1536) == 2                # gate/up: about a tile an SM
     assert gemm_bf16.split_k_for(8, 151936, 1536) == 1               # the head: tiles for all SMs
     assert gemm_bf16.split_k_for(64, 17920, 1536) == 1
+    # the choices follow the device's SM count, which is asked of the device, not written down
+    assert gemm_bf16.num_sms() == gemm_bf16.B200_SMS                 # no device here: a B200's
+    assert gemm_bf16.split_k_for(8, 17920, 1536, sms=64) == 1        # 140 tiles on 64 SMs: none
+    assert gemm_bf16.split_k_for(8, 1536, 8960, sms=64) == 4         # fewer SMs, fewer splits
+    assert attention_bf16.decode_splits(64, 12, 2, 576, sms=32) == 1
+
+
+def test_pages_a_cache_group_can_hold_at_once():
+    """A windowed group is never given more pages than its requests can keep live (the pages
+    that still hold a position inside some request's window, plus one step's new tokens); a
+    group that keeps every position can hold every slot filled to the limit."""
+    from ginfer_b200.cache.storage import GroupLayout
+    full = GroupLayout(((2, 16), (2, 16)), True, 0, (0, 1))
+    win = GroupLayout(((2, 16), (2, 16)), True, 48, (2,))
+    assert full.pages_for(4, 256, 64, 16) == 4 * 16
+    # window 48 on pages of 16: positions len-47 .. len-1 touch at most 4 pages, one more while a
+    # step's tokens are reserved before the old pages are given back; 64 new tokens take 4 pages
+    assert win.pages_for(4, 256, 64, 16) == 4 * 5 + 4
+    assert win.pages_for(4, 32, 64, 16) == 4 * 2                    # never more than a full group
+    assert full.bytes_per_page(16, 2) == 2 * 16 * 64 * 2 and win.bytes_per_page(16, 2) == 16 * 64 * 2
+    # the bound holds for the cache manager's own rules, whatever the portions
+    import random
+    rng = random.Random(0)
+    for page, window, seqs, budget in ((4, 9, 3, 7), (8, 48, 4, 32), (16, 70, 2, 200), (4, 4, 5, 64)):
+        g = GroupLayout(((1, 8),) * 2, True, window, (0,))
+        cap = g.pages_for(seqs, 4096, budget, page)
+        m = _MANAGER[0]([window], cap, page, seqs, 4096)
+        for i in range(seqs):
+            m.admit(i)
+        for _ in range(300):
+            left = budget
+            step = []
+            for i in rng.sample(range(seqs), seqs):
+                n = rng.randint(0, left)
+                if n:
+                    step.append((i, n))
+                    left -= n
+            for i, n in step:
+                m.reserve(i, n)                                      # never out of pages
+            for i, n in step:
+                m.commit(i, n)
+            m.check()
+            for i in range(seqs):
+                if m.get(i).num_tokens > 3000:
+                    m.release(i)
+                    m.admit(i)
 
 
 def test_the_q_k_v_epilogue_is_only_offered_what_it_takes():

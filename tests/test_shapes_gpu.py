@@ -1,11 +1,14 @@
-"""Layer sizes of larger models than the tiny ones (the Qwen2.5-7B and -32B shapes, one layer, a
-small vocabulary): the bfloat16 path (tcgen05 products, bf16 attention kernels, CUDA graphs)
-against the 32-bit path of the same engine (FMA products, fp32-arithmetic attention), which shares
-no kernel with it beyond the element-wise ones."""
+"""Layer sizes of larger models than the tiny ones (the Qwen2-1.5B, Qwen2.5-7B and -32B shapes, one
+layer, a small vocabulary): the bfloat16 path (tcgen05 products, bf16 attention kernels, CUDA
+graphs) against the plain implementation where that is affordable on the CPU, and against the
+32-bit path of the same engine (FMA products, fp32-arithmetic attention), which shares no kernel
+with it beyond the element-wise ones."""
+import numpy as np
 import pytest
 import torch
 
-from tiny import prompt
+import replay
+from tiny import make_folder, prompt
 
 pytestmark = pytest.mark.gpu
 
@@ -18,6 +21,42 @@ SHAPES = {
     "odd": dict(hidden_size=1192, num_attention_heads=5, num_key_value_heads=5,
                 intermediate_size=3000, head_dim=64),
 }
+
+
+# the benchmark's own layer sizes (Qwen2-1.5B)
+SHAPES_PLAIN = {
+    "1.5b": dict(hidden_size=1536, num_attention_heads=12, num_key_value_heads=2,
+                 intermediate_size=8960, head_dim=128),
+    "odd": SHAPES["odd"],
+}
+
+
+@pytest.mark.parametrize("name", list(SHAPES_PLAIN))
+@pytest.mark.parametrize("cut", ["tail", "mixed_long"])
+def test_bfloat16_path_agrees_with_plain_at_real_layer_sizes(tmp_path, name, cut):
+    """One layer of the benchmark's sizes (and of sizes that fit no tile), stepped in bfloat16 as
+    most of each request at once and its last tokens one by one (decode graphs), and as portions
+    of 64 to 200 tokens beside single tokens: every row against the plain implementation."""
+    from ginfer_b200.engine import ModelRunner
+    from ginfer_b200.engine.loading import load_model
+    cfg = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": 1,
+           "vocab_size": 643, "rope_theta": 1e6, "rms_norm_eps": 1e-6,
+           "max_position_embeddings": 512, "tie_word_embeddings": False,
+           "use_sliding_window": False, "torch_dtype": "bfloat16"}
+    cfg.update(SHAPES_PLAIN[name])
+    d = make_folder(tmp_path, f"shape_{name}", seed=11, storage="bfloat16", sharp=False,
+                    config=cfg)
+    reqs = {f"r{i}": prompt(n, 643, seed=20 + i) for i, n in enumerate((230, 71, 150))}
+    if cut == "tail":
+        steps = replay.cut_tail_decode(reqs, tail=6)
+    else:
+        steps, _ = replay.cut_mixed(reqs, seed=5, sizes=replay.LONG_SIZES, decode_tail=4)
+    model, _ = load_model(d, "bfloat16")
+    runner = ModelRunner(model, page_size=16, max_num_seqs=4, max_seq_len=256,
+                         num_pages=replay.peak_tokens(steps) // 16, max_num_batched_tokens=512,
+                         enforce_eager=False)
+    rows = replay.run_in_process(runner, steps)
+    replay.compare(rows, replay.plain_logits(d, reqs, "bfloat16"), "bfloat16", reqs)
 
 
 @pytest.mark.parametrize("name", list(SHAPES))
@@ -58,21 +97,25 @@ def test_bfloat16_path_agrees_with_the_32_bit_path_at_large_layer_sizes(name):
 
 
 @pytest.mark.parametrize("head_dim,heads,kv_heads", [(64, 6, 2), (128, 3, 1)])
-def test_a_step_of_many_tokens_agrees_with_portions_and_with_the_32_bit_path(
-        head_dim, heads, kv_heads, monkeypatch):
+def test_a_step_of_many_tokens_agrees_with_portions_plain_and_the_32_bit_path(
+        tmp_path, head_dim, heads, kv_heads, monkeypatch):
     """From 1,024 tokens on a step's joined q/k/v product rotates q and k and writes the cache in
-    its own epilogue (and the gated product joins SiLU*mul).  The same prompt in one step, in two
-    portions below that size (plain products, the rotation kernel) and on the 32-bit path must
-    give the same logits, for the prompt's last token and for the tokens decoded after it, which
-    read the keys and values the epilogue cached."""
+    its own epilogue (and the gated product joins SiLU*mul).  The same prompt in one step, as a
+    short portion followed by one of 1,030 tokens (the epilogue then works at positions and cache
+    slots offset from its rows), in two portions below that size (plain products, the rotation
+    kernel) and on the 32-bit path must give the same logits, for the prompt's last token and for
+    the tokens decoded after it, which read the keys and values the epilogue cached; the
+    bfloat16 runs are also held against the plain implementation."""
     from ginfer_b200 import ops
     from ginfer_b200.engine import ModelRunner, StepEntry
-    from ginfer_b200.engine.loading import random_model
+    from ginfer_b200.engine.loading import load_model
     cfg = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": 2,
            "hidden_size": 264, "num_attention_heads": heads, "num_key_value_heads": kv_heads,
            "head_dim": head_dim, "intermediate_size": 520, "vocab_size": 643, "rope_theta": 1e4,
            "rms_norm_eps": 1e-6, "max_position_embeddings": 1536, "tie_word_embeddings": False,
            "use_sliding_window": False, "torch_dtype": "bfloat16"}
+    d = make_folder(tmp_path, f"many_{head_dim}", seed=3, storage="bfloat16", sharp=False,
+                    config=cfg)
     toks = prompt(1100, 643, 5)
     tail = prompt(3, 643, 6)
     served = []
@@ -85,7 +128,7 @@ def test_a_step_of_many_tokens_agrees_with_portions_and_with_the_32_bit_path(
     monkeypatch.setattr(ops, "qkv_rope_write", counted)
 
     def run(dtype, cuts):
-        model, _ = random_model(cfg, 3, dtype)
+        model, _ = load_model(d, dtype)
         r = ModelRunner(model, page_size=16, max_num_seqs=2, max_seq_len=1536, num_pages=80,
                         enforce_eager=True)
         rows, at = [], 0
@@ -100,13 +143,22 @@ def test_a_step_of_many_tokens_agrees_with_portions_and_with_the_32_bit_path(
         return torch.cat(rows).float().cpu()
 
     whole = run("bfloat16", [1100])
+    assert [m for m, ok in served if ok] == [1100, 1100], served     # both layers, one long step
+    served.clear()
+    second = run("bfloat16", [70, 1030])
+    assert [m for m, ok in served if ok] == [1030, 1030], served
     cut = run("bfloat16", [600, 500])
     full = run("float32", [1100])
-    # both layers of the one long step, and nothing shorter or in 32-bit
-    assert [m for m, ok in served if ok] == [1100, 1100], served
     scale = full.abs().max().item()
-    for name, other in (("portions", cut), ("32-bit", full)):
+    for name, other in (("a later portion", second), ("portions", cut), ("32-bit", full)):
         worst = (whole - other).abs().max().item() / scale
         rms = (whole - other).pow(2).mean().sqrt().item() / scale
         print(f"hd {head_dim} against {name}: scale {scale:.3f} worst {worst:.4f} rms {rms:.4f}")
         assert rms <= 0.01 and worst <= 0.03, (name, rms, worst)
+    # against the plain implementation: rows 1099 .. 1102 of the whole sequence
+    seq = toks + tail
+    ref = replay.plain_logits(d, {"a": seq}, "bfloat16")["a"][1099:1103]
+    atol, rtol = replay.tolerances("bfloat16", float(np.abs(ref).max()))
+    for name, got in (("one step", whole), ("a later portion", second), ("portions", cut)):
+        err = np.abs(got.double().numpy() - ref)
+        assert (err <= atol + rtol * np.abs(ref)).all(), (name, float(err.max()), atol)

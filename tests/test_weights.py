@@ -2,6 +2,7 @@
 the random-weights mode (no GPU)."""
 import json
 import os
+import shutil
 import struct
 
 import pytest
@@ -140,3 +141,44 @@ def test_how_tensors_are_kept(tmp_path):
     out32 = check_and_convert(m.tensor_specs(), avail, lambda n: idx[n][0].get(idx[n][1]), d,
                               f32, "cpu")
     assert all(t.dtype == f32 for t in out32.values())
+
+
+def test_a_folder_in_two_shards_loads_like_the_single_file(tmp_path):
+    """``model.safetensors.index.json`` with its ``weight_map`` over two shards (how the larger
+    checkpoints of this family ship): the same tensors reach the model as from one file."""
+    d = make_folder(tmp_path, "B", seed=6, storage="bfloat16", sharp=False)
+    single = open_model_tensors(d)
+    names = sorted(single)
+    half = len(names) // 2
+    d2 = str(tmp_path / "sharded")
+    os.makedirs(d2)
+    shutil.copy(os.path.join(d, "config.json"), d2)
+    shards = {"model-00001-of-00002.safetensors": names[:half],
+              "model-00002-of-00002.safetensors": names[half:]}
+    weight_map = {}
+    for fname, part in shards.items():
+        write_safetensors(os.path.join(d2, fname),
+                          {n: single[n][0].get(single[n][1]).clone() for n in part})
+        weight_map.update({n: fname for n in part})
+    json.dump({"metadata": {"total_size": 0}, "weight_map": weight_map},
+              open(os.path.join(d2, "model.safetensors.index.json"), "w"))
+    sharded = open_model_tensors(d2)
+    assert sorted(sharded) == names
+    assert len({id(f) for f, _ in sharded.values()}) == 2
+    m = _model(TINY_B)
+
+    def bound(folder):
+        idx = open_model_tensors(folder)
+        avail = {n: (f.entries[k].shape, f.entries[k].dtype) for n, (f, k) in idx.items()}
+        return check_and_convert(m.tensor_specs(), avail, lambda n: idx[n][0].get(idx[n][1]),
+                                 folder, torch.bfloat16, "cpu", ignored=m.plan.ignored_tensors)
+    one, two = bound(d), bound(d2)
+    assert sorted(one) == sorted(two) == names
+    assert all(torch.equal(one[n], two[n]) for n in names)
+    # a tensor the index names but no shard holds is reported like any missing tensor
+    del weight_map[names[0]]
+    json.dump({"weight_map": weight_map},
+              open(os.path.join(d2, "model.safetensors.index.json"), "w"))
+    with pytest.raises(WeightError) as ei:
+        bound(d2)
+    assert ei.value.missing == [names[0]]

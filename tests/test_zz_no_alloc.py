@@ -54,20 +54,25 @@ def _case(seed, lens, nh, nkv, page):
                 positions=torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV))
 
 
-def _static(lib, c, nh, nkv, page, window, splits):
+def _static(lib, c, nh, nkv, page, window, splits, check_device=True):
     B = c["qkv"].shape[0]
     out = torch.full((B, nh * HD), float("nan"), dtype=torch.bfloat16, device=DEV)
     gc.collect()            # tensors that earlier tests left in cycles go now, not during the call
     torch.cuda.synchronize()
     before = torch.cuda.memory_allocated(DEV), torch.cuda.memory_reserved(DEV)
+    free_before = torch.cuda.mem_get_info(DEV)[0]          # the driver's own count of free bytes
     rc = lib.gf_attn_decode_static(
         c["qkv"].data_ptr(), c["qkv"].stride(0), c["pages"][0].data_ptr(),
         c["pages"][1].data_ptr(), c["table"].data_ptr(), c["table"].stride(0),
         c["cu"].data_ptr(), c["positions"].data_ptr(), out.data_ptr(), B, nh, nkv, page, window,
         1.0 / math.sqrt(HD), splits, torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
-    # the call took nothing from PyTorch's allocator (the only allocator in this process)
+    # the call took nothing from PyTorch's allocator, and nothing from the device behind its back
+    # (a cudaMalloc inside the library would show in the driver's count; the first call of a
+    # process may load the kernel's module, so the caller makes one call before it counts)
     assert (torch.cuda.memory_allocated(DEV), torch.cuda.memory_reserved(DEV)) == before
+    if check_device:
+        assert torch.cuda.mem_get_info(DEV)[0] == free_before
     return rc, out
 
 
@@ -75,11 +80,20 @@ def test_static_scratch_entry_point_matches_the_regular_one_twice_in_a_row():
     from ginfer_b200.ops import attention_bf16
     lib = _library()
     nh, nkv, page = 6, 2, 16
+    warm = _case(0, [30, 50], nh, nkv, page)
+    _static(lib, warm, nh, nkv, page, 0, 3, check_device=False)      # loads what a first call loads
     for seed, lens, window, splits in [(1, [700, 90, 1, 333], 0, 7), (2, [64, 1500, 257], 100, 5),
-                                       (3, [40, 41], 0, 1)]:
+                                       (3, [40, 41], 0, 1), (4, [900, 12, 77], 0, 8)]:
         c = _case(seed, lens, nh, nkv, page)
         rc, got = _static(lib, c, nh, nkv, page, window, splits)
         assert rc == 0, lib.gf_attn_decode_static_error()
+        # the regular entry point with a scratch buffer of the caller's runs the same kernel with
+        # the same splits: the same bits
+        same = attention_bf16.decode(c["qkv"], c["pages"], c["table"], c["cu"], c["positions"],
+                                     len(lens), nh, nkv, HD, 1.0 / math.sqrt(HD), window, page,
+                                     splits, through_scratch=True, use_tma=False)
+        assert torch.equal(got, same)
+        # and the path serving takes (tiles by TMA, splits merged inside a cluster) agrees
         want = attention_bf16.decode(c["qkv"], c["pages"], c["table"], c["cu"], c["positions"],
                                      len(lens), nh, nkv, HD, 1.0 / math.sqrt(HD), window, page,
                                      splits)
@@ -91,6 +105,7 @@ def test_static_scratch_entry_point_refuses_what_does_not_fit():
     lib = _library()
     nh, nkv, page = 32, 2, 16
     c = _case(4, [100] * 64, nh, nkv, page)
+    _static(lib, _case(0, [30, 50], nh, nkv, page), nh, nkv, page, 0, 3, check_device=False)
     rc, out = _static(lib, c, nh, nkv, page, 0, 16)     # 64 * 32 * 16 * 66 * 4 bytes = 8.6 MB
     torch.cuda.synchronize()
     assert rc == -8

@@ -55,12 +55,28 @@ TINY_E = {
     "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
     "num_hidden_layers": 2, "hidden_size": 136, "num_attention_heads": 4,
     "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 312, "vocab_size": 333,
-    "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "max_position_embeddings": 512,
+    "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "max_position_embeddings": 1024,
     "tie_word_embeddings": False, "use_sliding_window": True, "sliding_window": 70,
     "max_window_layers": 1, "torch_dtype": "float32", "eos_token_id": 2,
 }
 
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
+# a sixth one with the head size of the large models' checkpoints (128), three heads in one
+# group, a window of 150 (more than two key tiles) on its second layer
+TINY_F = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 2, "hidden_size": 200, "num_attention_heads": 3,
+    "num_key_value_heads": 1, "head_dim": 128, "intermediate_size": 328, "vocab_size": 311,
+    "rope_theta": 10000.0, "rms_norm_eps": 1e-6, "max_position_embeddings": 1024,
+    "tie_word_embeddings": False, "use_sliding_window": True, "sliding_window": 150,
+    "max_window_layers": 1, "torch_dtype": "float32", "eos_token_id": 5,
+}
+
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "F": TINY_F}
+# How much a configuration's q and k projections are scaled up (``sharpen``).  Scores grow with
+# the head size at a given factor; F (128 channels a head) takes 8 where the others take 12, so
+# that its scores spread as far as E's and the 32-bit path's summation order stays below the
+# comparison's tolerance.
+SHARPNESS = {"F": 8.0}
 
 
 def sharpen(model_dir: str, q_scale: float = 12.0) -> None:
@@ -81,16 +97,18 @@ def sharpen(model_dir: str, q_scale: float = 12.0) -> None:
 
 
 def make_folder(tmp_path, name: str, seed: int = 0, storage: str = "float32",
-                sharp: bool = True) -> str:
-    """A model folder of configuration ``name``.  Folders stored in bfloat16 are sharpened half
-    as much: peaked attention also amplifies the flips of bfloat16 rounding, and at a factor of
-    12 those alone reach 1 % of the logits' scale in the three-layer configuration."""
+                sharp: bool = True, config: dict | None = None) -> str:
+    """A model folder of configuration ``name`` (one of ``CONFIGS``, or ``config`` under that
+    name).  Folders stored in bfloat16 are sharpened half as much: peaked attention also
+    amplifies the flips of bfloat16 rounding, and at a factor of 12 those alone reach 1 % of the
+    logits' scale in the three-layer configuration."""
     from ginfer_b200.weights import write_random_model
     d = os.path.join(str(tmp_path), f"tiny_{name}_{storage}_{seed}")
     if not os.path.exists(os.path.join(d, "model.safetensors")):
-        write_random_model(d, dict(CONFIGS[name]), seed, storage_dtype=storage)
+        write_random_model(d, dict(config or CONFIGS[name]), seed, storage_dtype=storage)
         if sharp:
-            sharpen(d, 12.0 if storage == "float32" else 6.0)
+            factor = SHARPNESS.get(name, 12.0)
+            sharpen(d, factor if storage == "float32" else factor / 2)
     return d
 
 
