@@ -153,9 +153,20 @@ def prefill_flops(c, layers: int, T: int, wanted_rows: int = 1) -> float:
 
 
 # ----------------------------------------------------------------------------- timed pieces
-def decode_device_timed(eng, batch: int, steps: int, warmup: int, seed: int):
+def decode_device_timed(eng, batch: int, steps: int, warmup: int, seed: int, reps: int = 1):
     """Prefill ``batch`` prompts of PROMPT tokens, then time ``steps`` decode steps (step function
-    plus arg-max) with CUDA events.  Returns (ms per step, launches in the timed region)."""
+    plus arg-max) with CUDA events, ``reps`` times over (each repetition on a fresh batch of
+    requests, so that every one decodes at the same context lengths).  Returns (median ms per
+    step, launches in one timed region, all the per-repetition times)."""
+    times, launches = [], 0
+    for r in range(reps):
+        ms, launches = _decode_device_timed_once(eng, batch, steps, warmup, seed + 1000 * r)
+        times.append(ms)
+    times.sort()
+    return times[len(times) // 2], launches, times
+
+
+def _decode_device_timed_once(eng, batch: int, steps: int, warmup: int, seed: int):
     import torch
 
     from ginfer_b200 import ops
@@ -187,10 +198,18 @@ def decode_device_timed(eng, batch: int, steps: int, warmup: int, seed: int):
     return ms, launches
 
 
-def decode_end_to_end(eng, batch: int, steps: int, warmup: int, seed: int):
-    """The same through the public entry point: requests are added with host token ids,
-    ``Engine.step`` schedules, copies the step's integers from pinned memory, runs, samples and
-    reads the ids back.  Returns (ms per step, h2d bytes per step, d2h bytes per step)."""
+def decode_end_to_end(eng, batch: int, steps: int, warmup: int, seed: int, reps: int = 1):
+    """The same through the public entry point, ``reps`` times over; the median."""
+    runs = [_decode_end_to_end_once(eng, batch, steps, warmup, seed + 1000 * r)
+            for r in range(reps)]
+    runs.sort()
+    return runs[len(runs) // 2]
+
+
+def _decode_end_to_end_once(eng, batch: int, steps: int, warmup: int, seed: int):
+    """Requests are added with host token ids, ``Engine.step`` schedules, copies the step's
+    integers from pinned memory, runs, samples and reads the ids back.  Returns (ms per step, h2d
+    bytes per step, d2h bytes per step)."""
     import torch
 
     from ginfer_b200.sampling import SamplingParams
@@ -382,6 +401,18 @@ def run_scenario(name: str, shape: str, layers: int | None) -> int:
                   "ms_per_step": round(1e3 * dt / steps, 3),
                   "total_tok_s": round((tin + tout) / dt, 1),
                   "generated_tok_s": round(tout / dt, 1), "preemptions": eng.stats.preemptions}
+        reqs = eng.last_requests
+        ttft = sorted(1e3 * (r.first_token_time - r.arrival_time) for r in reqs
+                      if r.first_token_time is not None)
+        tpot = sorted(1e3 * (r.finish_time - r.first_token_time) / (len(r.output) - 1)
+                      for r in reqs if r.finish_time and len(r.output) > 1)
+
+        def pct(v, q):
+            return round(v[min(len(v) - 1, int(q * len(v)))], 3) if v else None
+        # as the reference logs them per sequence (ginfer/engine/engine.cc:54-71): time to the
+        # first token from arrival, and the time per token after it
+        result["ttft_ms"] = {"p50": pct(ttft, 0.5), "p99": pct(ttft, 0.99)}
+        result["tpot_ms"] = {"p50": pct(tpot, 0.5), "p99": pct(tpot, 0.99)}
         if name == "ref256":
             d = {k: getattr(eng.stats, k) - st0[k] for k in
                  ("prefill_tokens", "prefill_seconds", "decode_tokens", "decode_seconds")}
@@ -408,6 +439,9 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--prefill-reps", type=int, default=5,
                     help="timed repetitions of the 2,048-token prefill (the median is reported)")
+    ap.add_argument("--reps", type=int, default=5,
+                    help="repetitions of the timed region of K decode steps (the median is "
+                         "reported: a region of K steps is tens of milliseconds)")
     ap.add_argument("--enforce-eager", action="store_true")
     ap.add_argument("--micro", choices=MICRO, default=None,
                     help="run one small kernel workload (for profiling) instead of the benchmark")
@@ -451,19 +485,29 @@ def main() -> int:
 
     clocks = ClockSampler()
     clocks.start()
-    ms, launches = decode_device_timed(eng, B, args.steps, args.warmup, seed=1)
+    reps = max(1, args.reps)
+    ms, launches, all_ms = decode_device_timed(eng, B, args.steps, args.warmup, seed=1, reps=reps)
     clock_info = clocks.stop()
-    e2e_ms, h2d, d2h = decode_end_to_end(eng, B, args.steps, args.warmup, seed=2)
+    e2e_ms, h2d, d2h = decode_end_to_end(eng, B, args.steps, args.warmup, seed=2, reps=reps)
     pre_ms = prefill_timed(eng, PREFILL_TOKENS, reps=max(1, args.prefill_reps), warmup=3, seed=3)
-    points = {}
+
+    def hbm_fraction(batch: int, step_ms: float, steps: int) -> tuple[float, float]:
+        """(GB/s, fraction of the copy bandwidth) of a decode step: every weight once and the
+        cache of the live requests at their mean length over the timed steps."""
+        mean_ctx = PROMPT + args.warmup + steps / 2
+        nbytes = weight_bytes(cfg, layers) + batch * mean_ctx * kv_bytes_per_token(cfg, layers)
+        gbs = nbytes / (step_ms * 1e-3) / 1e9
+        return gbs, gbs / peaks["hbm_gbs"]
+
+    points, points_frac = {}, {}
     if not args.skip_points:
         for b in (1, 64):
-            pms, _ = decode_device_timed(eng, b, min(args.steps, 64), args.warmup, seed=10 + b)
+            k = min(args.steps, 64)
+            pms, _, _ = decode_device_timed(eng, b, k, args.warmup, seed=10 + b, reps=min(reps, 3))
             points[f"decode_b{b}"] = round(b / (pms * 1e-3), 1)
+            points_frac[f"decode_b{b}"] = round(hbm_fraction(b, pms, k)[1], 4)
 
-    mean_ctx = PROMPT + args.warmup + args.steps / 2
-    step_bytes = weight_bytes(cfg, layers) + B * mean_ctx * kv_bytes_per_token(cfg, layers)
-    achieved = step_bytes / (ms * 1e-3) / 1e9
+    achieved, frac = hbm_fraction(B, ms, args.steps)
     flops = prefill_flops(cfg, layers, PREFILL_TOKENS)
     value = B / (ms * 1e-3)
     line = {
@@ -482,7 +526,7 @@ def main() -> int:
             "kv_block": PAGE, "parallelism": "single GPU",
             "l2": f"inputs larger than L2 ({weight_bytes(cfg, layers) / 1e9:.1f} GB of weights read "
                   "per step)",
-            "cuda_graphs": not args.enforce_eager, "peaks": peak_src,
+            "cuda_graphs": not args.enforce_eager, "peaks": peak_src, "timed_regions": reps,
         },
         "e2e": {"value": round(B / (e2e_ms * 1e-3), 1), "unit": "tok/s",
                 "ms_per_step": round(e2e_ms, 4), "h2d_bytes_per_step": h2d,
@@ -492,9 +536,10 @@ def main() -> int:
                     "ms": round(pre_ms, 3),
                     "frac": round(flops / (pre_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1),
-                     "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / peaks["hbm_gbs"], 4)},
+                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(frac, 4)},
         "points": points,
+        "points_roofline_frac": points_frac,
+        "ms_per_step_all": [round(t, 4) for t in all_ms],
         "clocks": clock_info,
     }
     print(json.dumps(line))

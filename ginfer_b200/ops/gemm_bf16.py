@@ -76,7 +76,7 @@ def split_k_for(M: int, N: int, K: int, sms: int | None = None) -> int:
         split *= 2
     if split == 8 and tiles * 12 <= sms and nkb // 12 >= 8:
         split = 12      # a long reduction on few tiles (the down product): 144 CTAs instead of 96
-    if split == 1 and M <= 16 and sms // 2 < tiles <= sms and nkb >= 16:
+    if split == 1 and M <= 64 and sms // 2 < tiles <= sms and nkb >= 16:
         split = 2       # about one tile an SM (gate/up): pairs of CTAs have more under way
     return split
 
@@ -170,10 +170,14 @@ def gemm(x, weight, bias_f32=None, out_dtype=torch.bfloat16, epi: int = 0, split
 RESID_MAX_TOKENS = 64
 
 # The largest token count the gated product runs here for.  In a CUDA graph, 1.5B shapes, weights
-# from HBM: 8 tokens 11.5 us (two K splits) against 12.6 for cuBLAS + SiLU*mul, 16 tokens 11.8
-# against 12.6, 32 tokens 13.3 against 12.7, 64 tokens 14.8 against 13.7: every CTA streams the whole
-# activation matrix beside its weights, which costs as much as the weights from 32 tokens on.
-MAX_TOKENS = 16
+# from HBM, two K splits (us, here / cuBLAS + SiLU*mul): 8 tokens 11.2 / 12.7, 16 tokens 11.9 / 12.9,
+# 32 tokens 12.7 / 13.2, 48 tokens 13.2 / 13.3, 64 tokens 14.2 / 14.0 (one split: 20.5: a CTA's ring
+# holds four 16 KB weight tiles beside the 8 KB token tiles, and two CTAs an SM keep twice as many
+# bytes under way).  Inside a decode step of 4 layers the kernel up to 64 tokens, for the gated
+# and the down product, takes 312 / 365 / 352 us at batch 32 / 48 / 64 against 323 / 370 / 362 with
+# cuBLAS from 17 tokens on: it starts while the kernel before it runs and has its first weights
+# by then, which a library kernel does not.
+MAX_TOKENS = 64
 
 
 def plain_limit(weight) -> int:
@@ -192,8 +196,8 @@ def try_linear(x, weight, bias_f32, out_dtype):
 # Plain products leave for cuBLAS above this many tokens.  In a CUDA graph on a B200, 1.5B shapes,
 # weights from HBM (us, here / cuBLAS): q/k/v 8 tokens 4.2 / 5.6, 16 tokens 4.6 / 4.6, 32 tokens
 # 6.3 / 4.6; output 4.3 / 5.0, 4.7 / 4.6, 6.5 / 4.5; down (a reduction of 8,960) 8 tokens 8.6 / 16.9,
-# 32 tokens 10.5 / 13.2, 48 tokens 12.6 / 13.2, 64 tokens 14.1 / 13.3.  With these limits the decode
-# step at batch 32 and 64 is 8 % faster than with 32 tokens for all.
+# 32 tokens 10.6 / 13.4, 48 tokens 12.4 / 13.6, 64 tokens 13.8 / 13.7; q/k/v and output at 64 tokens
+# 6.8 / 5.0 and 6.5 / 4.8 (their epilogue, the reduction of the K splits, grows with the tokens).
 PLAIN_MAX_TOKENS = 16
-PLAIN_MAX_TOKENS_LONG_K = 48   # for reductions of at least LONG_K
+PLAIN_MAX_TOKENS_LONG_K = 64   # for reductions of at least LONG_K
 LONG_K = 4096

@@ -364,7 +364,8 @@ def test_split_choices_of_the_kernels():
     assert gemm_bf16.split_k_for(8, 1536, 8960) == 12                # down: 12 tiles, long K
     assert gemm_bf16.split_k_for(8, 17920, 1536) == 2                # gate/up: about a tile an SM
     assert gemm_bf16.split_k_for(8, 151936, 1536) == 1               # the head: tiles for all SMs
-    assert gemm_bf16.split_k_for(64, 17920, 1536) == 1
+    assert gemm_bf16.split_k_for(64, 17920, 1536) == 2               # still two: more bytes under way
+    assert gemm_bf16.split_k_for(128, 17920, 1536) == 1
     # the choices follow the device's SM count, which is asked of the device, not written down
     assert gemm_bf16.num_sms() == gemm_bf16.B200_SMS                 # no device here: a B200's
     assert gemm_bf16.split_k_for(8, 17920, 1536, sms=64) == 1        # 140 tiles on 64 SMs: none
