@@ -1,7 +1,23 @@
-"""The cache manager the engine runs: :class:`NativeCacheManager` keeps pools, slots, block tables
-and the reserve/commit/release rules in C++ (``csrc/cache_core.cu``, host code only) behind the
-interface of :class:`ginfer_b200.cache.manager.CacheManager`, which stays as the readable statement
-of the rules and as the oracle the tests compare this one with, operation by operation.
+"""The cache manager: :class:`NativeCacheManager` keeps pools, slots, block tables and the
+reserve/commit/release rules in C++ (``csrc/cache_core.cu``, host code only).
+
+Reference: ``ginfer/engine/block_manager.{h,cc}``.  There one page id addresses all layers at
+once, a prompt's pages are all taken at admission (``block_manager.cc:63-110``), decoding takes a
+page when a token opens one (``:121-135``), and pages return when a request finishes or is
+preempted (``ginfer/engine/scheduler.cc:73-77,92-94``).  Here
+
+* layers with different needs form groups (all keys; the last ``window`` keys), each with a pool
+  (a stack of free pages and an owner array: a page handed out twice, returned twice or returned
+  by a stranger is an error) and block tables of its own;
+* pages are taken for the tokens of one step at a time (``reserve``), in every group or in none,
+  so prompts can be fed in portions;
+* a windowed group gives a page back as soon as no later token can see it (``commit``: a page is
+  dead once its last position is ``<= len - window``);
+* each request also holds a slot for state of fixed size, from admission until it ends (also
+  across a preemption that gives its pages back); ``check()`` proves that no page is lost, held
+  twice or listed without being held.
+
+The tests hold every operation against the same rules written in plain Python.
 
 The block tables are numpy arrays owned here and written by the C++ side, so the step function
 gathers slot mappings and table rows from them as before.  Besides the per-request calls there are
@@ -15,8 +31,7 @@ from ctypes import POINTER, c_char_p, c_int, c_longlong, c_void_p
 
 import numpy as np
 
-from .page_pool import OutOfPages, PagePoolError
-from .slots import NoFreeSlot
+from .errors import NoFreeSlot, OutOfPages, PagePoolError
 
 _OK, _OUT_OF_PAGES, _POOL_ERROR, _NO_FREE_SLOT, _BAD_VALUE, _NOT_LIVE, _CHECK_FAILED = range(7)
 

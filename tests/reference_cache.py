@@ -1,4 +1,6 @@
-"""Host-side bookkeeping of the cache: pages per request and layer group, block tables, slots.
+"""The cache manager's rules in plain Python: the oracle that the tests compare the C++ manager
+(``ginfer_b200/csrc/cache_core.cu`` behind ``ginfer_b200.cache.NativeCacheManager``, the one the
+engine runs) with, operation by operation.  Not part of the product.
 
 Reference: ``ginfer/engine/block_manager.{h,cc}``.  There one page id addresses all layers at
 once, a prompt's pages are all taken at admission (``block_manager.cc:63-110``), decoding takes a
@@ -12,7 +14,12 @@ preempted (``ginfer/engine/scheduler.cc:73-77,92-94``).  Here
 * a windowed group gives a page back as soon as no later token can see it (:meth:`commit`);
 * each request also holds a slot for state of fixed size.
 
-Nothing here touches the device; the tensors live in :mod:`ginfer_b200.cache.storage`.
+
+A pool of pages is a stack of free pages (the page given back last is handed out first; the
+reference keeps a free deque and a used set and searches the deque on every allocation,
+``ginfer/engine/block_manager.cc:41-61``) with an owner array that makes double hand-outs and
+double returns errors.  A request takes a slot when it is admitted and keeps it until it ends,
+also across a preemption that gives its pages back.
 """
 from __future__ import annotations
 
@@ -20,8 +27,94 @@ from dataclasses import dataclass, field
 
 import numpy as np
 
-from .page_pool import OutOfPages, PagePool
-from .slots import SlotPool
+from ginfer_b200.cache.errors import NoFreeSlot, OutOfPages, PagePoolError
+
+
+class PagePool:
+    FREE = -1
+
+    def __init__(self, num_pages: int):
+        if num_pages <= 0:
+            raise ValueError("a page pool needs at least one page")
+        self.num_pages = int(num_pages)
+        self._free = list(range(self.num_pages - 1, -1, -1))       # pop() gives page 0 first
+        self._owner = np.full(self.num_pages, self.FREE, dtype=np.int64)
+
+    @property
+    def num_free(self) -> int:
+        return len(self._free)
+
+    def take(self, n: int, owner: int) -> list[int]:
+        if owner < 0:
+            raise ValueError("owner ids are non-negative")
+        if n > len(self._free):
+            raise OutOfPages(f"{n} pages asked, {len(self._free)} free of {self.num_pages}")
+        out = [self._free.pop() for _ in range(n)]
+        for p in out:
+            if self._owner[p] != self.FREE:
+                raise PagePoolError(f"page {p} was on the free list while held by "
+                                    f"{self._owner[p]}")
+            self._owner[p] = owner
+        return out
+
+    def give_back(self, pages, owner: int) -> None:
+        for p in pages:
+            p = int(p)
+            if not (0 <= p < self.num_pages):
+                raise PagePoolError(f"page {p} is not of this pool")
+            if self._owner[p] == self.FREE:
+                raise PagePoolError(f"page {p} is returned twice")
+            if self._owner[p] != owner:
+                raise PagePoolError(f"page {p} is held by {self._owner[p]}, not by {owner}")
+            self._owner[p] = self.FREE
+            self._free.append(p)
+
+    def owner_of(self, page: int) -> int:
+        return int(self._owner[page])
+
+    def held_by(self, owner: int) -> list[int]:
+        return [int(p) for p in np.nonzero(self._owner == owner)[0]]
+
+    def check(self) -> None:
+        """Every page is either free once or held once."""
+        free = sorted(self._free)
+        if len(set(free)) != len(free):
+            raise PagePoolError("a page is on the free list twice")
+        held = set(int(p) for p in np.nonzero(self._owner != self.FREE)[0])
+        if held & set(free):
+            raise PagePoolError(f"pages both free and held: {sorted(held & set(free))}")
+        if len(held) + len(free) != self.num_pages:
+            lost = set(range(self.num_pages)) - held - set(free)
+            raise PagePoolError(f"pages lost: {sorted(lost)}")
+
+
+class SlotPool:
+    def __init__(self, num_slots: int):
+        if num_slots <= 0:
+            raise ValueError("at least one slot is needed")
+        self.num_slots = int(num_slots)
+        self._free = list(range(self.num_slots - 1, -1, -1))
+        self._holder: dict[int, object] = {}
+
+    @property
+    def num_free(self) -> int:
+        return len(self._free)
+
+    def take(self, holder) -> int:
+        if not self._free:
+            raise NoFreeSlot(f"all {self.num_slots} request slots are taken")
+        s = self._free.pop()
+        self._holder[s] = holder
+        return s
+
+    def give_back(self, slot: int) -> None:
+        if slot not in self._holder:
+            raise RuntimeError(f"slot {slot} is returned twice or was never taken")
+        del self._holder[slot]
+        self._free.append(slot)
+
+    def holder_of(self, slot: int):
+        return self._holder.get(slot)
 
 
 @dataclass

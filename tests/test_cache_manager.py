@@ -5,10 +5,10 @@ import random
 import numpy as np
 import pytest
 
-from ginfer_b200.cache.manager import CacheManager as PyCacheManager
+from ginfer_b200.cache import NoFreeSlot, OutOfPages, PagePoolError
 from ginfer_b200.cache.native import NativeCacheManager
-from ginfer_b200.cache.page_pool import OutOfPages, PagePool, PagePoolError
-from ginfer_b200.cache.slots import NoFreeSlot, SlotPool
+from reference_cache import CacheManager as PyCacheManager
+from reference_cache import PagePool, SlotPool
 
 
 @pytest.fixture(params=["python", "native"])

@@ -3,11 +3,12 @@ import random
 
 import pytest
 
-from ginfer_b200.cache.manager import CacheManager as PyCacheManager
 from ginfer_b200.cache.native import NativeCacheManager
 from ginfer_b200.engine.request import Request, RequestState
 from ginfer_b200.engine.scheduler import Scheduler
 from ginfer_b200.sampling import SamplingParams, uniform
+from reference_cache import CacheManager as PyCacheManager
+from reference_scheduler import PythonScheduler
 
 
 _MANAGER = [NativeCacheManager]
@@ -22,7 +23,10 @@ def _both_managers(request):
 
 def _sched(pages=16, page=4, seqs=4, budget=16, max_len=64, eos=(), windows=(0,)):
     cache = _MANAGER[0](list(windows), pages, page, seqs, max_len)
-    return Scheduler(cache, seqs, budget, max_len, eos), cache
+    # the engine's scheduler (decision in C++) over the engine's manager; the same rules in
+    # plain Python over the plain-Python manager
+    cls = Scheduler if _MANAGER[0] is NativeCacheManager else PythonScheduler
+    return cls(cache, seqs, budget, max_len, eos), cache
 
 
 def _next_token(req):
@@ -314,8 +318,9 @@ def test_native_decisions_are_the_python_decisions(seed):
     logs = []
     for manager in (PyCacheManager, NativeCacheManager):
         cache = manager(list(windows), pages, page, 3, max_len)
-        sched = Scheduler(cache, 3, budget, max_len, ())
-        assert hasattr(cache, "decide") == (manager is NativeCacheManager)
+        native = manager is NativeCacheManager
+        sched = (Scheduler if native else PythonScheduler)(cache, 3, budget, max_len, ())
+        assert hasattr(cache, "decide") == native
         reqs = [_req(i, n, max_tokens=mt) for i, n, mt, _ in plan]
         pending = list(zip(reqs, (gap for *_, gap in plan)))
         log, steps = [], 0
