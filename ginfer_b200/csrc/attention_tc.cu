@@ -1,24 +1,51 @@
 // Prefill attention on the 5th-generation tensor cores: varlen, causal (+ sliding window), GQA,
 // over the paged cache.  Compiled for one head size (-DGF_HEAD_DIM = 64 or 128).
 //
-// One CTA owns 128 query rows of one head of one request.  Keys are visited in tiles of 128.  For a
-// tile j:   S = Q K_j^T      tcgen05.mma, A = Q and B = K_j in shared memory (K-major, 128B
-//                             swizzle, written by TMA), D = S in tensor memory (128 lanes x 128 fp32)
-//           P = softmax part  four warps, one thread per query row: tcgen05.ld of its row of S
-//                             (S is double buffered: S_{j+1} is computed meanwhile), running
-//                             maximum and sum in fp32, P rounded to bf16 into shared memory
-//           O += P V_j        tcgen05.mma, A = P (K-major), B = V_j as stored ([key][channel], that
-//                             is MN-major), D = O in tensor memory (128 lanes x HD fp32)
-// The accumulator O is rescaled in tensor memory only when a row's maximum has grown by more than
+// One CTA owns 128 query rows of one head of one request.  Keys are visited in tiles of 128, and
+// the tiles are dealt to two streams: stream 0 takes the item's tiles 0, 2, 4, ..., stream 1 the
+// tiles 1, 3, 5, ...  Each stream has its own S, running maximum, sum and accumulator O_s, as if it
+// were an attention over its own keys; at the end of the item the two are added up with the
+// factors that bring them to a common maximum.  For a tile j of stream s:
+//           S_s = Q K_j^T     tcgen05.mma, A = Q and B = K_j in shared memory (K-major, 128B
+//                             swizzle, written by TMA), D = S_s in tensor memory (128 lanes x 128 fp32)
+//           P_s = softmax     four warps a stream, one thread per query row: tcgen05.ld of its row
+//                             of S_s, running maximum and sum in fp32, P_s rounded to bf16 and
+//                             written back by tcgen05.st over the first 64 columns of S_s
+//           O_s += P_s V_j    tcgen05.mma, A = P_s from tensor memory, B = V_j as stored
+//                             ([key][channel], that is MN-major), D = O_s in tensor memory
+// The tensor core alternates between the streams (P V and the next S of stream 0, then of stream
+// 1), so that it works for one while the softmax warps of the other are busy: neither the tensor
+// core nor the exponential unit waits for the other for long.  P never passes through shared
+// memory, which halves the operand traffic of P V.
+// An accumulator is rescaled in tensor memory only when a row's maximum has grown by more than
 // 2^8 since the last rescale (the probabilities then stay below 2^8, well inside bf16 and fp32).
 // K and V tiles come page by page through TMA: the cache of one layer is a 2-D tensor
 // [token slots, kv_heads * HD]; a page is a box of page_size rows; pages past the request's end are
 // loaded from out-of-range coordinates, which TMA fills with zeros.
 //
 // Warps: 0..3 = TMA loaders (K: 0-1, V: 2-3; every lane issues one box), 4 = tensor-memory
-// allocation and MMA issue (one thread), 5..12 = softmax and epilogue (two threads per query row).  The reference's prefill kernel is a 64x64 mma.sync
-// flash loop with S, P and the row maximum held in bf16
+// allocation and MMA issue (5..7 only fill its warp group), 8..11 = softmax and epilogue of stream
+// 0, 12..15 = of stream 1.  The kernel starts with 128 registers a thread; the first two warp
+// groups give registers back and the softmax groups take them (setmaxnreg), so that a softmax
+// thread holds its whole row of S.  The reference's prefill kernel is a 64x64 mma.sync flash loop
+// with S, P and the row maximum held in bf16
 // (ginfer/core/op/kernels/cuda/page_attn_kernel/flash_gqa_varlen_kernel.cu:420-512).
+//
+// What the structure answers to (measured on a B200; cycles per 128 x 128 tile): one query tile
+// with S double buffered and P through shared memory, two threads a row: 2,750, bound by the
+// chain load S - maximum - exponentials - store P of one tile at a time.  Two streams as above
+// with a thread a row that reads S twice in chunks: the same 2,600 (the branch on "no key of
+// this tile is masked" inside the loop over a chunk's keys had become the masked arithmetic for
+// every key: four times slower, until it stood outside).  Packed fp32 arithmetic (fma.rn.f32x2,
+// add.rn.f32x2, the three-input max): a lone warp on a scheduler spends 335 instead of 614 cycles
+// on 32 scores.  The whole row in registers: 2,250.  The three waits of a group made by three
+// lanes at once: 1,950 (a wait costs its thread 300 cycles while the tensor core reads its
+// operands from shared memory, 60 otherwise).  The 16 products of a tile take 1,350 of them.
+// Tried and slower: a thread for each stream (the streams fall into step: both wait for the
+// tensor core, then both for the exponentials), the same with a token that makes them take turns,
+// the K and V waits moved to a softmax thread, a second warp that waits ahead and meets the
+// issuing warp at a hardware barrier (faster on long rows of tiles, slower on short ones), and a
+// share of the exponentials by polynomial (the exponential unit is not what the tile waits for).
 //
 // Every wait on an mbarrier is bounded; when one runs out, the waiter records a code in *err, an
 // abort flag in shared memory tells the other roles to leave their loops, all meet at the final
@@ -37,16 +64,24 @@ constexpr int HD = GF_HEAD_DIM;
 static_assert(HD == 64 || HD == 128, "the tcgen05 attention kernel takes head sizes 64 and 128");
 constexpr int QT = 128;                    // query rows per CTA = TMEM lanes
 constexpr int KT = 128;                    // keys per tile
+constexpr int NS = 2;                      // streams the key tiles are dealt to
 constexpr int HALVES = HD / 64;            // 64-channel swizzle atoms per row
-constexpr int K_STAGES = HD == 128 ? 3 : 4;   // K_j is free as soon as S_j is computed
-constexpr int V_STAGES = HD == 128 ? 2 : 3;   // V_j is free once O += P_j V_j is complete
-constexpr int NTHREADS = 416;              // four loader warps, MMA warp, eight softmax warps
+// Each stream has a ring of K tiles and a ring of V tiles of its own (so that every role meets
+// every phase of the barriers it waits on): K_j is free as soon as S = Q K_j^T is computed, V_j
+// once O += P V_j is complete.
+constexpr int KS = 2;                              // K tiles a stream
+constexpr int VS = HD == 128 ? 1 : 2;              // V tiles a stream
+constexpr int K_STAGES = NS * KS, V_STAGES = NS * VS;
+constexpr int NTHREADS = 512;              // four warp groups: loaders, MMA issue, softmax of stream 0, of stream 1
+// Registers a thread: the kernel starts with 128 for all; the loader and MMA groups give registers
+// back, the softmax groups take them, so that a softmax thread holds its whole row of S.
+constexpr int REGS_SMALL = 64, REGS_SOFTMAX = 192;
+static_assert(256 * REGS_SMALL + 256 * REGS_SOFTMAX <= 65536, "the register file of an SM");
 constexpr uint32_t ATOM_BYTES = 128 * 64 * 2;            // a [128][64] bf16 tile: 16 KB
 constexpr uint32_t Q_BYTES = HALVES * ATOM_BYTES;
 constexpr uint32_t K_BYTES = HALVES * ATOM_BYTES;        // [128 keys][HD]
 constexpr uint32_t V_BYTES = HALVES * ATOM_BYTES;
-constexpr uint32_t P_BYTES = 2 * ATOM_BYTES;             // [128 rows][128 keys]
-constexpr uint32_t TMEM_COLS = 512;                      // S0: 0..127, S1: 128..255, O: 256..
+constexpr uint32_t TMEM_COLS = 512;     // S_0 / P_0: 0..127, S_1 / P_1: 128..255, O_0, O_1: 256..
 constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float kRescaleStep = 8.f;        // log2 units a maximum may grow before O is rescaled
@@ -62,7 +97,10 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// Bounded wait; gives up early when another role has raised the abort flag.
+// Bounded wait; gives up early when another role has raised the abort flag.  kFast: the waiter is
+// on the critical path between the tensor core and the softmax warps and polls without sleeping
+// for a good while.
+template <bool kFast = false>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* err, int code) {
   const uint32_t addr = smem_u32(bar);
@@ -76,13 +114,48 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
         : "r"(addr), "r"(parity)
         : "memory");
     if (done) return true;
-    if (spin > 64) {
+    if (spin > (kFast ? 4096u : 64u)) {
       if (*abort_flag) return false;
       __nanosleep(32);
+    } else if (kFast && (spin & 255u) == 255u && *abort_flag) {
+      return false;
     }
   }
   *abort_flag = 1;
   if (err) atomicExch(err, code);
+  return false;
+}
+// The same for a whole warp, each lane with a barrier of its own (lanes without one pass
+// `active` = false): returns when all of them are complete.  A wait costs its thread a few hundred
+// cycles while the tensor core streams its operands out of shared memory, complete or not; three
+// lanes make three waits in the time of one.
+__device__ __forceinline__ bool mbar_wait_lanes(uint64_t* bar, uint32_t parity, bool active,
+                                                volatile int* abort_flag, int* err, int code) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    uint32_t done = 1;
+    if (active) {
+      asm volatile(
+          "{\n\t.reg .pred p;\n\t"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(done)
+          : "r"(addr), "r"(parity)
+          : "memory");
+    }
+    if (__all_sync(0xffffffffu, done != 0)) return true;
+    active = active && !done;
+    if (spin > 4096u) {
+      if (*abort_flag) return false;
+      __nanosleep(32);
+    } else if ((spin & 255u) == 255u && *abort_flag) {
+      return false;
+    }
+  }
+  if ((threadIdx.x & 31) == 0) {
+    *abort_flag = 1;
+    if (err) atomicExch(err, code);
+  }
   return false;
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar,
@@ -93,18 +166,24 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
       ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
       : "memory");
 }
-// Shared-memory operand descriptors (sm_100 version, 128-byte swizzle).
+// Shared-memory operand descriptors (sm_100 version, 128-byte swizzle), as a low word that holds
+// the address (in 16-byte units; the issuing thread adds a tile's or a K step's offset to it with
+// one 32-bit addition) and a high word that is the same for every operand of this kernel.
 // K-major [rows][64]: rows 128 B apart, 8-row groups 1024 B apart.
-__device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
-  return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
-         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
 // MN-major (V as stored: [key][channel]): a 128-byte row holds 64 channels of one key; 8 keys make
 // a 1024-byte group (stride byte offset); the next 64 channels start one atom (16 KB) further on
 // (leading byte offset).
-__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr) {
-  return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)(ATOM_BYTES >> 4) << 16) |
-         ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo_kmajor(uint32_t saddr) {
+  return ((saddr & 0x3FFFF) >> 4) | (1u << 16);
+}
+__device__ __forceinline__ uint32_t desc_lo_mnmajor(uint32_t saddr) {
+  return ((saddr & 0x3FFFF) >> 4) | ((ATOM_BYTES >> 4) << 16);
+}
+__device__ __forceinline__ uint64_t make_desc(uint32_t lo) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(DESC_HI));
+  return d;
 }
 // D fp32, A and B bf16, M = 128, N = n; b_mn: B is MN-major.
 __host__ __device__ constexpr uint32_t idesc(int n, bool b_mn) {
@@ -117,6 +196,16 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t b
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(id), "r"(accumulate)
+      : "memory");
+}
+// The same with A taken from tensor memory: 128 lanes (rows) x 8 columns, two bf16 a column (the
+// element with the lower K index in the low half).
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t id,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(id), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
@@ -138,6 +227,18 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
       : "r"(taddr));
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 // The registers written by tmem_ld32 hold data only after this.
 __device__ __forceinline__ void tmem_ld_wait() {
@@ -161,6 +262,15 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
       "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
       : "memory");
 }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]),
+      "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]),
+      "r"(v[15])
+      : "memory");
+}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -172,8 +282,8 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // f in [-0.5, 0.5]; 2^f by a cubic whose largest relative error there is 7.5e-5 (the result is
 // rounded to bf16, 3.9e-3, right after); n is added to the exponent field.  x is clamped at -125,
 // so that the result stays a normal number (about 2e-38: nothing, beside a row's largest term).
-// Off unless the build asks for it: shares of 1/8, 1/4, 1/3 and 1/2 measured 6.51, 6.60, 6.68 and
-// 6.55 ms a 2,048-token prefill of the 1.5B shape against 6.54 ms without, all within the noise.
+// Off unless the build asks for it: no share measured faster (a lone warp spends 335 cycles on 32
+// scores with the unit, 450 with a quarter of them by polynomial).
 #ifndef GF_POLY_EXP_EVERY
 #define GF_POLY_EXP_EVERY 0          // every n-th exponential of an unmasked tile; 0: none
 #endif
@@ -190,6 +300,30 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+// Two fp32 operations in one instruction (sm_100): the operands are pairs in 64-bit registers.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+  return d;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 
 struct Barriers {
   uint64_t q_full;
@@ -198,14 +332,15 @@ struct Barriers {
   uint64_t k_empty[K_STAGES];
   uint64_t v_full[V_STAGES];
   uint64_t v_empty[V_STAGES];
-  uint64_t s_full[2];     // S_j is complete in tensor memory (buffer j % 2)
-  uint64_t p_ready;       // P_j is in shared memory and O is rescaled (256 arrivals)
-  uint64_t max_ready;     // both halves of every row have posted their maximum (256 arrivals)
-  uint64_t pv_done;       // O += P_j V_j is complete
-  uint64_t o_free;        // the softmax warps have read an item's O out (256 arrivals)
+  uint64_t s_full[NS];    // S of stream s is complete in tensor memory
+  uint64_t p_ready[NS];   // P of stream s stands in tensor memory and O_s is rescaled (128 arrivals)
+  uint64_t pv_done[NS];   // O_s += P_s V is complete
+  uint64_t stat_ready;    // every row's (maximum, sum) of both streams is posted (256 arrivals)
+  uint64_t o_free;        // the softmax warps have read an item's O_0 and O_1 out (256 arrivals)
   uint32_t tmem_base;
   int abort_flag;
-  float row_max[2][2][QT];   // [tile parity][half][row]
+  float stat_m[NS][QT];   // [stream][row]: the row's reference maximum and sum at the item's end
+  float stat_l[NS][QT];
 };
 
 // One work item: 128 query rows of one head of one request, and the key tiles they see.
@@ -213,7 +348,7 @@ struct Item {
   int b, head, r0, rows, q_begin, pos0, key_lo, p_last, j0, ntiles, kvh;
 };
 
-__global__ void __launch_bounds__(NTHREADS)
+__global__ void __launch_bounds__(NTHREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
                        const __grid_constant__ CUtensorMap tmap_k,
                        const __grid_constant__ CUtensorMap tmap_v,
@@ -228,13 +363,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
   unsigned char* q_s = smem_raw;
   unsigned char* k_s = q_s + Q_BYTES;                      // [K_STAGES][K_BYTES]
   unsigned char* v_s = k_s + K_STAGES * K_BYTES;           // [V_STAGES][V_BYTES]
-  unsigned char* p_s = v_s + V_STAGES * V_BYTES;
-  Barriers* bars = reinterpret_cast<Barriers*>(p_s + P_BYTES);
+  Barriers* bars = reinterpret_cast<Barriers*>(v_s + V_STAGES * V_BYTES);
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // optional time stamps of the first CTA's first item (dbg: 16 slots per tile per role)
+  // optional time stamps of the first CTA's first item (dbg: 8 slots per tile per role)
+#ifdef GF_TRACE
   bool trace = dbg != nullptr && blockIdx.x == 0;
+#else
+  constexpr bool trace = false;     // the phase stamps are compiled in only with -DGF_TRACE
+#endif
 #define GF_STAMP(role, i, slot) \
   if (trace && (i) < 32) dbg[((role) * 32 + (i)) * 8 + (slot)] = clock64()  /* dbg: 3 * 32 * 8 */
   // with dbg: every CTA also leaves (start ns, end ns, SM) behind the first CTA's stamps
@@ -257,10 +395,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
   // tiles from the last (heaviest: most keys under the causal mask) to the first, then requests;
   // CTA c takes items c, 2G - 1 - c, 2G + c, ... (G CTAs): the CTAs that got the lightest items of
   // one round get the heaviest of the next.  Barrier phases run on over the items (every role
-  // counts tiles and items for itself), so the loads and the first S product of the next item
+  // counts tiles and items for itself), so the loads and the first S products of the next item
   // overlap the last P V, the read-out and the stores of this one.
   const int items = nh * q_tiles * B;
   auto item_of = [&](int n, Item& it) -> int {   // 0: no more items, 1: it, 2: an empty item
+    // (the roles copy the fields they use into variables of their own: the struct lies in local
+    // memory, and a thread that issues products or copies would wait for loads from it)
     const int G = gridDim.x;
     const int idx = n * G + ((n & 1) ? G - 1 - (int)blockIdx.x : (int)blockIdx.x);
     if (idx >= items) return 0;
@@ -282,6 +422,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
     it.ntiles = it.p_last / KT - it.j0 + 1;
     return 1;
   };
+  // stream s takes the item's key tiles s, s + 2, ...: how many
+  auto tiles_of = [](int ntiles, int s) { return (ntiles - s + 1) >> 1; };
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
@@ -294,12 +436,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
       mbar_init(&bars->v_full[s], 2);
       mbar_init(&bars->v_empty[s], 1);
     }
-    mbar_init(&bars->s_full[0], 1);
-    mbar_init(&bars->s_full[1], 1);
-    mbar_init(&bars->p_ready, 256);
-    mbar_init(&bars->max_ready, 256);
-    mbar_init(&bars->pv_done, 1);
-    mbar_init(&bars->o_free, 256);
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(&bars->s_full[s], 1);
+      mbar_init(&bars->p_ready[s], QT);
+      mbar_init(&bars->pv_done[s], 1);
+    }
+    mbar_init(&bars->stat_ready, NS * QT);
+    mbar_init(&bars->o_free, NS * QT);
     bars->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_q) : "memory");
@@ -316,9 +459,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = bars->tmem_base;
-  const uint32_t tmem_s = tmem, tmem_o = tmem + 256;          // S buffer b at tmem_s + 128 * b
+  // S (and, over its first 64 columns, P) of stream s at column 128 s; O of stream s behind them
+  const uint32_t tmem_s = tmem, tmem_o = tmem + NS * KT;
 
   if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_SMALL));
     // ------------------------------------------------------------------ loaders
     // Four warps: warps 0-1 bring K tiles, warps 2-3 V tiles, each every other box of its
     // operand (a box = one page x 64 channels; issuing a TMA copy costs its thread ~80 cycles and
@@ -331,14 +476,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const int ops = pages_per_tile * HALVES;                   // boxes per tile of one operand
     const int my_ops = (ops - part + 1) / 2;                   // boxes part, part + 2, ...
     constexpr int MAX_OPS = ((KT / 8) * HALVES / 2 + 31) / 32; // page sizes down to 8
-    const int nstages = is_v ? V_STAGES : K_STAGES;
+    const int per_stream = is_v ? VS : KS;
     const uint32_t tile_bytes = is_v ? V_BYTES : K_BYTES;
     unsigned char* ring = is_v ? v_s : k_s;
     uint64_t* full = is_v ? bars->v_full : bars->k_full;
     uint64_t* empty = is_v ? bars->v_empty : bars->k_empty;
     const CUtensorMap* map = is_v ? &tmap_v : &tmap_k;
     const uint32_t my_bytes = (uint32_t)my_ops * (uint32_t)page_size * 128u;
-    int cnt = 0, seq = 0;                                      // tiles and items so far
+    int cs[NS] = {0, 0};                                       // tiles of each stream so far
+    int seq = 0;                                               // items so far
     bool go = true;
     Item it;
     for (int n = 0; go; ++n) {
@@ -346,6 +492,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
       if (kind == 0) break;
       if (kind == 2) continue;
       const int* tbl = block_table + (size_t)it.b * table_stride;
+      const int ntiles = it.ntiles, j0 = it.j0, p_last = it.p_last, key_lo = it.key_lo,
+                kv_col = it.kvh * HD;
       if (warp == 0 && lane == 0) {
         // Q's buffer is free once the last S product of the item before has read it
         if (!mbar_wait(&bars->q_empty, (uint32_t)(seq & 1) ^ 1u, abort_flag, err, 13)) break;
@@ -356,16 +504,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
       }
       int rows_next[MAX_OPS];
       auto lookup = [&](int i) {
-        const int key0 = (it.j0 + i) * KT;
+        const int key0 = (j0 + i) * KT;
 #pragma unroll
         for (int u = 0; u < MAX_OPS; ++u) {
           const int op = part + 2 * (lane + 32 * u);
           rows_next[u] = oob_row;
-          if (op < ops && i < it.ntiles) {
+          if (op < ops && i < ntiles) {
             const int c = key0 + (op / HALVES) * page_size;    // first key of this page
             // pages past the request's last key (or wholly before the window) come from an
             // out-of-range row: TMA fills them with zeros
-            if (c <= it.p_last && c + page_size > it.key_lo) {
+            if (c <= p_last && c + page_size > key_lo) {
               const int page = tbl[c / page_size];
               if (page >= 0) rows_next[u] = page * page_size;
             }
@@ -373,15 +521,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
       };
       lookup(0);
-      for (int i = 0; i < it.ntiles; ++i, ++cnt) {
+      for (int i = 0; i < ntiles; ++i) {
         int rows_now[MAX_OPS];
 #pragma unroll
         for (int u = 0; u < MAX_OPS; ++u) rows_now[u] = rows_next[u];
-        const int st = cnt % nstages;
+        int& cnt = (i & 1) ? cs[1] : cs[0];                    // tile i goes to stream i % 2
+        const int st = (i & 1) * per_stream + cnt % per_stream;
         int ok = 1;
         if (lane == 0) {
           if (warp == 0) { GF_STAMP(2, i, 0); }
-          ok = mbar_wait(&empty[st], ((cnt / nstages) & 1) ^ 1, abort_flag, err, 1);
+          ok = mbar_wait(&empty[st], ((cnt / per_stream) & 1) ^ 1, abort_flag, err, 1);
           if (ok && my_bytes) mbar_expect_tx(&full[st], my_bytes);
           else if (ok) mbar_arrive(&full[st]);
           if (warp == 0) { GF_STAMP(2, i, 1); }
@@ -395,265 +544,303 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
             const int pg = op / HALVES, h = op - pg * HALVES;
             tma_load_2d(ring + (size_t)st * tile_bytes + h * ATOM_BYTES +
                             (size_t)pg * page_size * 128,
-                        map, &full[st], it.kvh * HD + h * 64, rows_now[u]);
+                        map, &full[st], kv_col + h * 64, rows_now[u]);
           }
         }
         if (warp == 0 && lane == 0) { GF_STAMP(2, i, 2); }
+        ++cnt;
         lookup(i + 1);                                          // overlaps the next wait
       }
       ++seq;
+#ifdef GF_TRACE
       trace = false;
+#endif
     }
-  } else if (warp == 4) {
+  } else if (warp < 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_SMALL));
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // With t counting a stream's own tiles (stream s holds the item's tiles s, s + 2, ...), the
+    // tensor core runs       O_0 += P_0 V_{2t},      S_0 = Q K_{2t+2}^T,
+    //                        O_1 += P_1 V_{2t+1},    S_1 = Q K_{2t+3}^T
+    // in this order, so that it works for one stream while the softmax warps of the other turn
+    // their S into P.  The products of one thread complete in the order of issue, so the S
+    // product that overwrites P_s (they share columns) runs behind the P V that reads it.
+    if (warp == 4) {
+      // The whole warp runs the loop; lane 0 issues the products, and lanes 0, 1 and 2 make the
+      // three waits of a group (P, the V tile, the next K tile) at the same time.
       constexpr uint32_t id_qk = idesc(KT, false), id_pv = idesc(HD, true);
-      const uint32_t qa = smem_u32(q_s), pa = smem_u32(p_s);
-      int cnt = 0, seq = 0;                                    // tiles and items so far
+      const uint32_t q_desc = desc_lo_kmajor(smem_u32(q_s)), k_desc = desc_lo_kmajor(smem_u32(k_s)),
+                     v_desc = desc_lo_mnmajor(smem_u32(v_s));
+      int seq = 0;                                             // items so far
+      int ck0 = 0, ck1 = 0, cv0 = 0, cv1 = 0;                  // S and P V products of each stream so far
       bool ok = true;
       Item it;
       for (int n = 0; ok; ++n) {
         const int kind = item_of(n, it);
         if (kind == 0) break;
         if (kind == 2) continue;
-        const int c0 = cnt;                                    // the item's first tile
+        const int ntiles = it.ntiles;
         ok = mbar_wait(&bars->q_full, (uint32_t)(seq & 1), abort_flag, err, 2);
-        // S_i = Q K_i^T into S buffer (c0 + i) % 2: issued one tile ahead of P V, so that the
-        // tensor core works on tile i + 1 while the softmax warps work on tile i
-        auto issue_qk = [&](int i) -> bool {
-          const int c = c0 + i, s = c % K_STAGES;
-          if (!mbar_wait(&bars->k_full[s], (c / K_STAGES) & 1, abort_flag, err, 3)) return false;
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t ka = smem_u32(k_s + s * K_BYTES);
+        // S_s = Q K^T for the stream's next tile; `last`: the item's last tile
+        auto issue_qk = [&](int s, bool last) {
+          int& ck = s ? ck1 : ck0;
+          const int st = s * KS + ck % KS;
+          if (lane == 0) {
+            const uint32_t kd = k_desc + st * (K_BYTES >> 4);
 #pragma unroll
-          for (int k = 0; k < HD / 16; ++k) {
-            const uint32_t off = (k / 4) * ATOM_BYTES + (k % 4) * 32;   // 16 channels = 32 bytes
-            umma(tmem_s + 128 * (c & 1), desc_kmajor(qa + off), desc_kmajor(ka + off), id_qk,
-                 k > 0 ? 1u : 0u);
+            for (int k = 0; k < HD / 16; ++k) {
+              const uint32_t off = ((k / 4) * ATOM_BYTES + (k % 4) * 32) >> 4;   // 16 channels = 32 bytes
+              umma(tmem_s + KT * s, make_desc(q_desc + off), make_desc(kd + off), id_qk,
+                   k > 0 ? 1u : 0u);
+            }
+            // (S complete means its K tile is free: the stream's softmax warps, who wait for S
+            // anyway, say so to the loaders; a commit costs this thread as much as a product)
+            umma_commit(&bars->s_full[s]);
+            if (last) umma_commit(&bars->q_empty);  // Q has been read for the last time
           }
-          umma_commit(&bars->k_empty[s]);       // K_i may be overwritten once S_i is computed
-          umma_commit(&bars->s_full[c & 1]);
-          if (i == it.ntiles - 1) umma_commit(&bars->q_empty);   // Q has been read for the last time
-          return true;
+          ++ck;
         };
-        if (ok) ok = issue_qk(0);
-        for (int i = 0; i < it.ntiles && ok; ++i) {
-          const int c = c0 + i, s = c % V_STAGES;
-          // S buffer (c + 1) % 2 held the tile before this one: the softmax warps were done with
-          // it before they announced its P, which this thread waited for in the last round
-          GF_STAMP(1, i, 0);
-          if (i + 1 < it.ntiles) ok = issue_qk(i + 1);
-          if (!ok) break;
-          GF_STAMP(1, i, 1);
-          ok = mbar_wait(&bars->v_full[s], (c / V_STAGES) & 1, abort_flag, err, 9);
-          GF_STAMP(1, i, 2);
-          if (ok) ok = mbar_wait(&bars->p_ready, c & 1, abort_flag, err, 4);
-          // the first P V of an item overwrites O: the item before must have been read out
-          if (ok && i == 0)
-            ok = mbar_wait(&bars->o_free, (uint32_t)(seq & 1) ^ 1u, abort_flag, err, 14);
-          if (!ok) break;
-          GF_STAMP(1, i, 3);
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t va = smem_u32(v_s + s * V_BYTES);
 #pragma unroll
-          for (int k = 0; k < KT / 16; ++k) {
-            const uint32_t poff = (k / 4) * ATOM_BYTES + (k % 4) * 32;  // 16 keys along P's rows
-            const uint32_t voff = k * 16 * 128;                         // 16 keys = 16 rows of V
-            umma(tmem_o, desc_kmajor(pa + poff), desc_mnmajor(va + voff), id_pv,
-                 (i > 0 || k > 0) ? 1u : 0u);
-          }
-          umma_commit(&bars->v_empty[s]);         // V_i may be overwritten
-          umma_commit(&bars->pv_done);            // O holds tiles 0 .. i
-          GF_STAMP(1, i, 4);
+        for (int s = 0; s < NS; ++s) {
+          if (s >= ntiles || !ok) continue;
+          const int ck = s ? ck1 : ck0;
+          ok = mbar_wait<true>(&bars->k_full[s * KS + ck % KS], (ck / KS) & 1, abort_flag, err, 3);
+          if (!ok) continue;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          issue_qk(s, s == ntiles - 1);
         }
-        cnt = c0 + it.ntiles;
+        const int n0 = tiles_of(ntiles, 0);
+        for (int t = 0; t < n0 && ok; ++t) {
+#pragma unroll
+          for (int s = 0; s < NS; ++s) {
+            const int i = NS * t + s;
+            if (i >= ntiles || !ok) continue;
+            int& cv = s ? cv1 : cv0;
+            const int ck = s ? ck1 : ck0;
+            const int st = s * VS + cv % VS;
+            if (lane == 0) { GF_STAMP(1, t, 4 * s); }
+            // the item's first P V overwrites O: the item before must have been read out
+            if (i == 0)
+              ok = mbar_wait(&bars->o_free, (uint32_t)(seq & 1) ^ 1u, abort_flag, err, 14);
+            if (lane == 0) { GF_STAMP(1, t, 4 * s + 1); }
+            // lane 0: P of this tile; lane 1: its V tile; lane 2: the K tile of the next S product
+            {
+              uint64_t* bar = lane == 0   ? &bars->p_ready[s]
+                              : lane == 1 ? &bars->v_full[st]
+                                          : &bars->k_full[s * KS + ck % KS];
+              const uint32_t par = lane == 0 ? (cv & 1) : lane == 1 ? ((cv / VS) & 1) : ((ck / KS) & 1);
+              const bool active = lane < 2 || (lane == 2 && i + NS < ntiles);
+              if (ok) ok = mbar_wait_lanes(bar, par, active, abort_flag, err, 4);
+            }
+            if (!ok) continue;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (lane == 0) {
+              GF_STAMP(1, t, 4 * s + 2);
+              const uint32_t vd = v_desc + st * (V_BYTES >> 4);
+#pragma unroll
+              for (int k = 0; k < KT / 16; ++k) {
+                // 16 keys: 8 columns of P (two bf16 a column), 16 rows of V
+                umma_ts(tmem_o + HD * s, tmem_s + KT * s + 8 * k,
+                        make_desc(vd + ((k * 16 * 128) >> 4)), id_pv, (t > 0 || k > 0) ? 1u : 0u);
+              }
+            }
+            if (i + NS < ntiles) issue_qk(s, i + NS == ntiles - 1);
+            if (lane == 0) {
+              umma_commit(&bars->v_empty[st]);        // the V tile may be overwritten
+              if (i + NS >= ntiles) umma_commit(&bars->pv_done[s]);   // O_s holds all of the stream's tiles
+              GF_STAMP(1, t, 4 * s + 3);
+            }
+            ++cv;
+          }
+        }
         ++seq;
+#ifdef GF_TRACE
         trace = false;
+#endif
       }
     }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS_SOFTMAX));
     // ------------------------------------------------------------------ softmax + epilogue
-    // Eight warps: two threads per query row, each with 64 of the tile's 128 keys (and half of
-    // O's channels), so that every scheduler has two warps to switch between.  The two threads of
-    // a row agree on the row maximum through shared memory and an mbarrier (a bounded wait; a
-    // named barrier could not be left if the other thread gave up).
+    // Eight warps: four for each stream, one thread per query row with all 128 keys of a tile, so
+    // that no two threads share a row while the tiles are visited, and the two groups are at
+    // different points of their tiles: one group's exponentials run beside the other's loads,
+    // maxima and stores.  Each stream keeps a maximum, a sum and an accumulator O_s of its own;
+    // at the end of the item the two are added up with the factors that bring them to a common
+    // maximum.  A thread holds its whole row of S in registers (these warp groups have taken the
+    // registers the others gave back) and writes P as bf16 over the first columns of S; the
+    // tensor core takes P from there.
     const int qd = warp & 3;                                   // TMEM lane quarter of this warp
-    const int half = (warp - 5) >> 2;                          // which 64 keys / which channels
+    const int s = (warp - 8) >> 2;                             // stream of this warp
     const int r = qd * 32 + lane;                              // query row of this thread
     const uint32_t lane_addr = (uint32_t)(qd * 32) << 16;
-    int cnt = 0, mr = 0;                                       // tiles, and uses of max_ready
+    const uint32_t my_s = tmem_s + KT * s + lane_addr, my_o = tmem_o + HD * s + lane_addr;
+    int cnt = 0, seq = 0;                                      // tiles of this stream, items so far
+    int had = 0;                                               // items in which this stream had tiles
     bool ok = true;
     Item it;
     for (int n = 0; ok; ++n) {
       const int kind = item_of(n, it);
       if (kind == 0) break;
       if (kind == 2) continue;
-      const int c0 = cnt;
-      const int p = it.pos0 + it.r0 + r;                       // this row's position
-      const bool live = r < it.rows;
+      const int ntiles = it.ntiles, rows = it.rows, j0 = it.j0, row0 = it.q_begin + it.r0,
+                head = it.head, pos00 = it.pos0 + it.r0;      // position of the item's first row
+      const int mine = tiles_of(ntiles, s);
+      const int p = pos00 + r;                                 // this row's position
+      const bool live = r < rows;
       const int lo = window > 0 ? max(0, p - window + 1) : 0;
+      const int wp0 = pos00 + qd * 32;                         // position of the warp's first row
+      const bool tr = r == 0;
       float m_used = -INFINITY;        // the maximum the accumulated P and l are scaled by
-      float l = 0.f;                   // this thread's half of the row sum
-      for (int i = 0; i < it.ntiles; ++i) {
-        const int c = c0 + i;
-        const bool tr = r == 0 && half == 0;
+      float l = 0.f;                   // the row sum
+      for (int t = 0; t < mine; ++t, ++cnt) {
+        const int i = 2 * t + s;
         if (tr) { GF_STAMP(0, i, 0); }
-        ok = mbar_wait(&bars->s_full[c & 1], (c >> 1) & 1, abort_flag, err, 5);
+        ok = mbar_wait<true>(&bars->s_full[s], cnt & 1, abort_flag, err, 5);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (tr) { GF_STAMP(0, i, 1); }
-        const int col0 = (it.j0 + i) * KT + 64 * half;         // first key of this thread's half
-        // every row of this warp sees all of these keys: no comparisons
-        const int wp0 = it.pos0 + it.r0 + qd * 32;
-        const bool interior = col0 + 63 <= wp0 && qd * 32 + 32 <= it.rows &&
+        if (r == 0) mbar_arrive(&bars->k_empty[s * KS + cnt % KS]);   // S is computed: its K tile is free
+        const int col0 = (j0 + i) * KT;                        // first key of the tile
+        // every row of this warp sees all of the tile's keys: no comparisons
+        const bool interior = col0 + KT - 1 <= wp0 && qd * 32 + 32 <= rows &&
                               (window <= 0 || col0 >= wp0 + 31 - window + 1);
-        float v[2][32];
-        const uint32_t srow = tmem_s + 128 * (c & 1) + 64 * half + lane_addr;
-        tmem_ld32(srow, v[0]);
-        tmem_ld32(srow + 32, v[1]);
+        // ---- the whole row of S into registers
+        float v[KT];
+#pragma unroll
+        for (int cc = 0; cc < KT / 32; ++cc)
+          tmem_ld32(my_s + 32 * cc, *reinterpret_cast<float(*)[32]>(v + 32 * cc));
         tmem_ld_wait();
-        if (tr) { GF_STAMP(0, i, 2); }
-        // four running maxima (and four sums below) instead of one chain of dependent operations
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-        if (interior) {
+        if (!interior) {
 #pragma unroll
-          for (int cc = 0; cc < 2; ++cc)
-#pragma unroll
-            for (int k = 0; k < 32; ++k) mx4[k & 3] = fmaxf(mx4[k & 3], v[cc][k]);
-        } else {
-#pragma unroll
-          for (int cc = 0; cc < 2; ++cc)
-#pragma unroll
-            for (int k = 0; k < 32; ++k) {
-              const int key = col0 + 32 * cc + k;
-              v[cc][k] = (live && key >= lo && key <= p) ? v[cc][k] : -INFINITY;
-              mx4[k & 3] = fmaxf(mx4[k & 3], v[cc][k]);
-            }
+          for (int k = 0; k < KT; ++k) {
+            const int key = col0 + k;
+            v[k] = (live && key >= lo && key <= p) ? v[k] : -INFINITY;
+          }
         }
-        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-        // the row's maximum over both halves
-        bars->row_max[mr & 1][half][r] = mx;
-        mbar_arrive(&bars->max_ready);
-        ok = mbar_wait(&bars->max_ready, mr & 1, abort_flag, err, 10);
-        if (!ok) break;
-        if (tr) { GF_STAMP(0, i, 3); }
-        mx = fmaxf(mx, bars->row_max[mr & 1][half ^ 1][r]) * scale_log2;   // scale > 0
-        ++mr;
+        // ---- the row's maximum (eight running maxima instead of one chain)
+        float mx8[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) mx8[j] = -INFINITY;
+#pragma unroll
+        for (int k = 0; k < KT; k += 2) mx8[(k >> 1) & 7] = max3(mx8[(k >> 1) & 7], v[k], v[k + 1]);
+        const float mx = fmaxf(max3(mx8[0], mx8[1], mx8[2]), max3(mx8[3], mx8[4], max3(mx8[5], mx8[6], mx8[7]))) *
+                         scale_log2;                            // scale > 0
+        if (tr) { GF_STAMP(0, i, 2); }
         // lazy rescale: keep the old reference maximum unless the row's maximum outgrew it
         float m_new = m_used;
         if (mx > m_used + kRescaleStep || m_used == -INFINITY) m_new = fmaxf(m_used, mx);
         const float corr = (m_new == m_used) ? 1.f
                            : (m_used == -INFINITY ? 0.f : fast_exp2(m_used - m_new));
         const float msub = m_new == -INFINITY ? 0.f : m_new;
-        // probabilities (in place) and the row sum, while P V of the tile before may still run
-        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-        if (GF_POLY_EXP_EVERY > 0 && interior) {
-          // no key of this tile is masked for this warp: every score is finite
-#pragma unroll
-          for (int cc = 0; cc < 2; ++cc)
-#pragma unroll
-            for (int k = 0; k < 32; ++k) {
-              const float x = fmaf(v[cc][k], scale_log2, -msub);
-              const float e = (GF_POLY_EXP_EVERY > 0 &&
-                               k % (GF_POLY_EXP_EVERY > 0 ? GF_POLY_EXP_EVERY : 1) ==
-                                   GF_POLY_EXP_EVERY - 1)
-                                  ? poly_exp2(x)
-                                  : fast_exp2(x);
-              v[cc][k] = e;
-              sum4[k & 3] += e;
-            }
-        } else {
-#pragma unroll
-          for (int cc = 0; cc < 2; ++cc)
-#pragma unroll
-            for (int k = 0; k < 32; ++k) {
-              const float e = fast_exp2(fmaf(v[cc][k], scale_log2, -msub));
-              v[cc][k] = e;
-              sum4[k & 3] += e;
-            }
-        }
-        const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-        if (tr) { GF_STAMP(0, i, 4); }
-        // O and the P buffer are free once P V of the tile before is complete (the item's first
-        // tile: the epilogue of the item before has waited for its last P V already)
-        if (i > 0) {
-          ok = mbar_wait(&bars->pv_done, (c - 1) & 1, abort_flag, err, 6);
-          if (!ok) break;
-          if (tr) { GF_STAMP(0, i, 5); }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          if (__any_sync(0xffffffffu, corr != 1.f)) {          // this thread's half of O's row
+        // S of this tile is complete, so the stream's P V of the tile before (issued ahead of
+        // it) is too: O_s is at rest and may be rescaled (the stream's first P V overwrites O_s)
+        if (t > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
 #pragma unroll 1
-            for (int cc = 0; cc < HD / 2; cc += 32) {
-              float o[32];
-              tmem_ld32(tmem_o + lane_addr + half * (HD / 2) + cc, o);
-              tmem_ld_wait();
+          for (int cc = 0; cc < HD; cc += 16) {
+            float o[16];
+            tmem_ld16(my_o + cc, o);
+            tmem_ld_wait();
+            uint32_t ob[16];
 #pragma unroll
-              for (int k = 0; k < 32; ++k) o[k] *= corr;
-              tmem_st32(tmem_o + lane_addr + half * (HD / 2) + cc, o);
+            for (int k = 0; k < 16; ++k) ob[k] = __float_as_uint(o[k] * corr);
+            tmem_st16(my_o + cc, ob);
+          }
+        }
+        // ---- probabilities (bf16, over the first 64 columns of S) and the row sum
+        uint64_t sum2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};       // four partial sums
+        const uint64_t scale2 = pack2(scale_log2, scale_log2), msub2 = pack2(-msub, -msub);
+#pragma unroll
+        for (int cc = 0; cc < KT / 32; ++cc) {
+          uint32_t w[16];
+#pragma unroll
+          for (int k = 0; k < 32; k += 2) {
+            float a0, a1, e0, e1;
+            unpack2(fma2(pack2(v[32 * cc + k], v[32 * cc + k + 1]), scale2, msub2), a0, a1);
+            if (GF_POLY_EXP_EVERY > 0 &&
+                (k / 2) % (GF_POLY_EXP_EVERY > 0 ? GF_POLY_EXP_EVERY : 1) == GF_POLY_EXP_EVERY - 1) {
+              e0 = poly_exp2(a0);             // clamps at -125: a masked key gives 2^-125 = nothing
+              e1 = poly_exp2(a1);
+            } else {
+              e0 = fast_exp2(a0);
+              e1 = fast_exp2(a1);
             }
-            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            sum2[(k >> 1) & 1] = add2(sum2[(k >> 1) & 1], pack2(e0, e1));
+            w[k / 2] = pack_bf16(e0, e1);
           }
+          tmem_st16(my_s + 16 * cc, w);
         }
-        l = l * corr + sum;
+        {
+          float s0, s1, s2, s3;
+          unpack2(sum2[0], s0, s1);
+          unpack2(sum2[1], s2, s3);
+          l = l * corr + ((s0 + s1) + (s2 + s3));
+        }
         m_used = m_new;
-        // P (bf16, K-major with 128-byte swizzle) -> shared memory: keys 64 * half .. + 63 are
-        // atom `half`, eight 16-byte chunks per row
-        unsigned char* prow = p_s + half * ATOM_BYTES + (size_t)r * 128;
-#pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-#pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {                     // 8 keys = one 16-byte chunk
-            const int chunk = cc * 4 + ch;
-            uint4 w;
-            w.x = pack_bf16(v[cc][ch * 8 + 0], v[cc][ch * 8 + 1]);
-            w.y = pack_bf16(v[cc][ch * 8 + 2], v[cc][ch * 8 + 3]);
-            w.z = pack_bf16(v[cc][ch * 8 + 4], v[cc][ch * 8 + 5]);
-            w.w = pack_bf16(v[cc][ch * 8 + 6], v[cc][ch * 8 + 7]);
-            *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = w;
-          }
-        }
-        if (tr) { GF_STAMP(0, i, 6); }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is for the tensor core
+        if (tr) { GF_STAMP(0, i, 3); }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        mbar_arrive(&bars->p_ready);
-        if (tr) { GF_STAMP(0, i, 7); }
+        mbar_arrive(&bars->p_ready[s]);
+        if (tr) { GF_STAMP(0, i, 4); }
       }
-      cnt = c0 + it.ntiles;
-      // epilogue: O / l -> out; the two halves of a row add up their sums first
-      if (ok) ok = mbar_wait(&bars->pv_done, (cnt - 1) & 1, abort_flag, err, 7);
-      if (ok) {
-        bars->row_max[mr & 1][half][r] = l;
-        mbar_arrive(&bars->max_ready);
-        ok = mbar_wait(&bars->max_ready, mr & 1, abort_flag, err, 11);
+      if (!ok) break;
+      // ---- end of the item: the stream's last P V, then both streams' (maximum, sum) of the row
+      if (mine > 0) {
+        ok = mbar_wait(&bars->pv_done[s], had & 1, abort_flag, err, 7);
+        ++had;
       }
-      if (ok) {
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        l += bars->row_max[mr & 1][half ^ 1][r];
-        ++mr;
-        const float inv = l > 0.f ? 1.f / l : 0.f;
-        bf16* orow = out + ((size_t)(it.q_begin + it.r0 + r) * nh + it.head) * HD + half * (HD / 2);
-        float o[HD / 2];
-#pragma unroll
-        for (int cc = 0; cc < HD / 2; cc += 32)
-          tmem_ld32(tmem_o + lane_addr + half * (HD / 2) + cc,
-                    *reinterpret_cast<float(*)[32]>(o + cc));
+      if (!ok) break;
+      // (the item before has been read out by every thread, so its figures are not needed any more)
+      if (seq > 0) ok = mbar_wait(&bars->o_free, (uint32_t)(seq - 1) & 1u, abort_flag, err, 15);
+      if (!ok) break;
+      bars->stat_m[s][r] = m_used;
+      bars->stat_l[s][r] = l;
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(&bars->stat_ready);
+      ok = mbar_wait(&bars->stat_ready, seq & 1, abort_flag, err, 11);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const float m_o = bars->stat_m[s ^ 1][r], l_o = bars->stat_l[s ^ 1][r];
+      const float m_all = fmaxf(m_used, m_o);
+      const float f_me = m_used == -INFINITY ? 0.f : fast_exp2(m_used - m_all);
+      const float f_o = m_o == -INFINITY ? 0.f : fast_exp2(m_o - m_all);
+      const float l_all = l * f_me + l_o * f_o;
+      const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+      // this stream writes channels s * HD / 2 .. of the row: from O_0 and (if stream 1 had a
+      // tile at all) O_1, each with its stream's factor
+      const float f0 = (s == 0 ? f_me : f_o) * inv, f1 = (s == 0 ? f_o : f_me) * inv;
+      const bool two = ntiles > 1;
+      const uint32_t o0 = tmem_o + lane_addr + s * (HD / 2), o1 = o0 + HD;
+      bf16* orow = out + ((size_t)(row0 + r) * nh + head) * HD + s * (HD / 2);
+#pragma unroll 1
+      for (int cc = 0; cc < HD / 2; cc += 16) {
+        float a[16], b[16];
+        tmem_ld16(o0 + cc, a);
+        if (two) tmem_ld16(o1 + cc, b);
         tmem_ld_wait();
-        // O is read: the next item's first P V may overwrite it while this one is stored
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        mbar_arrive(&bars->o_free);
+        if (cc + 16 >= HD / 2) {
+          // O is read: the next item's first P V may overwrite it while this one is stored
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          mbar_arrive(&bars->o_free);
+        }
         if (live) {
 #pragma unroll
-          for (int k = 0; k < HD / 2; k += 8) {
+          for (int k = 0; k < 16; ++k) a[k] = two ? fmaf(b[k], f1, a[k] * f0) : a[k] * f0;
+#pragma unroll
+          for (int k = 0; k < 16; k += 8) {
             uint4 w;
-            w.x = pack_bf16(o[k] * inv, o[k + 1] * inv);
-            w.y = pack_bf16(o[k + 2] * inv, o[k + 3] * inv);
-            w.z = pack_bf16(o[k + 4] * inv, o[k + 5] * inv);
-            w.w = pack_bf16(o[k + 6] * inv, o[k + 7] * inv);
-            *reinterpret_cast<uint4*>(orow + k) = w;
+            w.x = pack_bf16(a[k], a[k + 1]);
+            w.y = pack_bf16(a[k + 2], a[k + 3]);
+            w.z = pack_bf16(a[k + 4], a[k + 5]);
+            w.w = pack_bf16(a[k + 6], a[k + 7]);
+            *reinterpret_cast<uint4*>(orow + cc + k) = w;
           }
         }
       }
+      ++seq;
+#ifdef GF_TRACE
       trace = false;
+#endif
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -730,8 +917,7 @@ GF_EXPORT int gf_attn_prefill_tc(const void* q, int q_row_stride, const void* kp
   if (!make_map(&mq, q, T, nh * HD, q_row_stride, QT)) return -6;
   if (!make_map(&mk, kpages, slots, nkv * HD, (long long)nkv * HD, page_size)) return -6;
   if (!make_map(&mv, vpages, slots, nkv * HD, (long long)nkv * HD, page_size)) return -6;
-  const size_t smem = Q_BYTES + K_STAGES * K_BYTES + V_STAGES * V_BYTES + P_BYTES +
-                      sizeof(Barriers);
+  const size_t smem = Q_BYTES + K_STAGES * K_BYTES + V_STAGES * V_BYTES + sizeof(Barriers);
   static bool attr_done = false;
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel,

@@ -140,7 +140,9 @@ def prefill_tc(qkv, pages, block_table, cu_seqlens_q, kv_lens, B, max_q_len, nh,
                window, page_size, trace=None, out=None, poly_exp_every: int | None = None):
     """Prefill attention on tcgen05 (``csrc/attention_tc.cu``); ``None`` if it cannot serve the
     shapes.  ``trace``: an int64 tensor of ``768 + 4 * CTAs`` slots that receives clock stamps of
-    the first CTA's phases and, behind them, every CTA's (start ns, end ns, SM) (for tuning).
+    the first CTA's phases ([role 0 softmax (by tile), 1 MMA (by a stream's tile), 2 loader][32][8])
+    and, behind them, every CTA's (start ns, end ns, SM) (for tuning; compiled into a build of its
+    own).
     ``poly_exp_every``: see ``POLY_EXP_EVERY`` (``None``: that default)."""
     from ctypes import c_float, c_int, c_void_p
 
@@ -153,6 +155,8 @@ def prefill_tc(qkv, pages, block_table, cu_seqlens_q, kv_lens, B, max_q_len, nh,
         out = torch.empty((T, nh * hd), dtype=torch.bfloat16, device=qkv.device)
     every = POLY_EXP_EVERY if poly_exp_every is None else int(poly_exp_every)
     defines = (f"GF_HEAD_DIM={hd}",) + ((f"GF_POLY_EXP_EVERY={every}",) if every > 0 else ())
+    if trace is not None:
+        defines += ("GF_TRACE",)          # a build of its own: the phase stamps cost the issuing thread time
     f = _fn("attention_tc", "gf_attn_prefill_tc",
             [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
