@@ -46,7 +46,8 @@ template <int MAXC>
 __device__ __forceinline__ void cluster_merge(float* cpart, float* cpart_m, float* cpart_l,
                                               float* cw, float* cinv, bf16* __restrict__ out,
                                               int nrows, int splits, int split, int row, int nh,
-                                              int h0, bool active = true) {
+                                              int h0, bool active = true, float* part_o = nullptr,
+                                              float* part_ml = nullptr, int parts = 1) {
   // Loads from the peers are issued eight at a time without branches (the peer index is
   // clamped, a clamped load's weight is zero); the additions stay in split order.
   // (`active` false: a thread beyond the NTHREADS that work here; it only joins the barrier)
@@ -71,6 +72,13 @@ __device__ __forceinline__ void cluster_merge(float* cpart, float* cpart_m, floa
       lsum += wgt * lp[p];
     }
     cinv[r] = lsum > 0.f ? 1.f / lsum : 0.f;
+    // part_o / part_ml: this cluster holds only a part of the request's keys; it leaves its
+    // unnormalised result with the maximum and the sum for the kernel that merges the parts
+    // (both pointers stand at this cluster's part of its first head; a head has `parts` parts)
+    if (part_ml && split == 0) {
+      part_ml[(size_t)r * parts * 2] = mm;
+      part_ml[(size_t)r * parts * 2 + 1] = lsum;
+    }
   }
   __syncthreads();
   const int total = nrows * HD, share = (total + splits - 1) / splits;
@@ -83,7 +91,8 @@ __device__ __forceinline__ void cluster_merge(float* cpart, float* cpart_m, floa
     float acc = 0.f;
 #pragma unroll
     for (int p = 0; p < MAXC; ++p) acc += p < splits ? cw[r * 16 + p] * v[p] : 0.f;
-    out[((size_t)row * nh + h0 + r) * HD + d] = __float2bfloat16_rn(acc * cinv[r]);
+    if (part_o) part_o[(size_t)r * parts * HD + d] = acc;
+    else out[((size_t)row * nh + h0 + r) * HD + d] = __float2bfloat16_rn(acc * cinv[r]);
   }
 }
 
@@ -451,7 +460,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap,
                        const int* __restrict__ cu_seqlens_q, const int* __restrict__ positions,
                        bf16* __restrict__ out, int nh, int nkv, int page_size, int window,
                        float scale_log2, int splits, int oob_row, int tbl_cap, int nst,
-                       int* err, const RopeArgs rope) {
+                       int* err, const RopeArgs rope, int parts, float* __restrict__ po,
+                       float* __restrict__ pml) {
   // No static shared memory in this kernel: the dynamic part then starts at the aligned base,
   // which the swizzled tiles need (checked below: a misaligned base ends the CTA with code 5).
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -462,7 +472,9 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap,
   bf16* qs = reinterpret_cast<bf16*>(stbl + tbl_cap);           // [8][HD] rotated q, then new k, v
   bf16* knew = qs + 8 * HD;
   bf16* vnew = knew + HD;
-  const int split = blockIdx.x, b = blockIdx.z;
+  // grid z = request * parts + part: with `parts` > 1 several clusters share a request's keys,
+  // each leaves an unnormalised result in po / pml, and attn_decode_merge_kernel adds them up
+  const int split = blockIdx.x, b = blockIdx.z / parts, part = blockIdx.z - b * parts;
   const int G = nh / nkv;
   const int chunks = (G + 7) / 8;
   const int kvh = blockIdx.y / chunks, chunk = blockIdx.y - kvh * chunks;
@@ -491,9 +503,10 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap,
   const int lo = window > 0 ? max(0, p - window + 1) : 0;
   const int lo_al = lo / KT * KT;                               // tiles start on tile boundaries
   const int nkeys = p - lo_al + 1;
-  int per = (nkeys + splits - 1) / splits;
+  const int pieces = splits * parts;
+  int per = (nkeys + pieces - 1) / pieces;
   per = (per + KT - 1) / KT * KT;
-  const int begin = lo_al + split * per;
+  const int begin = lo_al + (part * splits + split) * per;
   const int end = min(p + 1, begin + per);
   const int first = max(begin, lo);                             // first visible key of this split
   const int ntiles = first < end ? (end - begin + KT - 1) / KT : 0;
@@ -757,7 +770,14 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap,
         lsum += cw[w * 8 + r] * sl[w * 8 + r];
       }
     }
-    if (splits == 1) {
+    if (splits == 1 && parts > 1) {
+      const size_t at = ((size_t)b * nh + h0 + r) * parts + part;
+      po[at * HD + d] = acc;
+      if (d == 0) {
+        pml[at * 2] = mm;
+        pml[at * 2 + 1] = lsum;
+      }
+    } else if (splits == 1) {
       out[((size_t)row * nh + h0 + r) * HD + d] =
           __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
     } else {
@@ -769,13 +789,15 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap,
     }
   }
   if (splits > 1) {
+    float* part_o = parts > 1 ? po + (((size_t)b * nh + h0) * parts + part) * HD : nullptr;
+    float* part_ml = parts > 1 ? pml + (((size_t)b * nh + h0) * parts + part) * 2 : nullptr;
     cluster_sync_all();          // also orders the weights above before they are overwritten
     if (splits <= 8)
       cluster_merge<8>(cpart, cpart_m, cpart_l, cw, cinv, out, nrows, splits, split, row, nh, h0,
-                       consumer);
+                       consumer, part_o, part_ml, parts);
     else
       cluster_merge<16>(cpart, cpart_m, cpart_l, cw, cinv, out, nrows, splits, split, row, nh, h0,
-                        consumer);
+                        consumer, part_o, part_ml, parts);
     cluster_sync_all();          // nobody leaves while a peer reads it
   }
 }
@@ -799,7 +821,7 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ po,
     acc += wgt * po[(base + s) * HD + d];
     lsum += wgt * pml[(base + s) * 2 + 1];
   }
-  const int row = cu_seqlens_q[b];
+  const int row = cu_seqlens_q ? cu_seqlens_q[b] : b;
   out[((size_t)row * nh + head) * HD + d] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
 }
 
@@ -1078,10 +1100,12 @@ GF_EXPORT int gf_attn_decode_tma(const void* q, int q_row_stride, void* kpages, 
                                  const int* cu_seqlens_q, const int* positions, void* out, int B,
                                  int nh, int nkv, int page_size, int window, float scale,
                                  int splits, int stages, const float* rope_table, int rot,
-                                 int fused, int write_kv, int* err, void* stream) {
+                                 int fused, int write_kv, int* err, void* stream, int parts,
+                                 void* scratch) {
 #if GF_HEAD_DIM % 64 == 0
   if (B <= 0) return 0;
-  if (nh % nkv || splits < 1) return -3;
+  if (nh % nkv || splits < 1 || parts < 1 || (parts > 1 && !scratch)) return -3;
+  if ((long long)B * parts > 65535) return -6;
   if (fused && (rot < 0 || rot > HD || rot % 2 || (!rope_table && rot))) return -3;
   if (splits != 1 && splits != 2 && splits != 4 && splits != 8 && splits != 16) return -6;
   if (page_size % 8 || (KT % page_size && page_size % KT) || num_pages <= 0) return -6;
@@ -1115,12 +1139,21 @@ GF_EXPORT int gf_attn_decode_tma(const void* q, int q_row_stride, void* kpages, 
   }
   const RopeArgs rope{fused ? rope_table : nullptr, fused ? rot : 0, fused ? 1 : 0,
                       fused && write_kv ? 1 : 0};
-  dim3 grid(splits, nkv * chunks, B);
-  return launch_kernel_cluster_dims(attn_decode_tma_kernel, grid, dim3(TMA_THREADS), smem, st, splits,
-                                    true, mk, mv, (const bf16*)q, q_row_stride, (bf16*)kpages,
-                                    (bf16*)vpages, block_table, table_stride, cu_seqlens_q,
-                                    positions, (bf16*)out, nh, nkv, page_size, window,
-                                    scale * LOG2E, splits, (int)slots, tbl_cap, nst, err, rope);
+  // `parts` > 1 (few requests with many keys): that many clusters share a request's keys; they
+  // leave their results in `scratch` (gf_attn_decode_scratch_bytes(B, nh, parts) bytes) and a
+  // second kernel adds them up
+  float* po = (float*)scratch;
+  float* pml = po ? po + (size_t)B * nh * parts * HD : nullptr;
+  dim3 grid(splits, nkv * chunks, B * parts);
+  int rc = launch_kernel_cluster_dims(attn_decode_tma_kernel, grid, dim3(TMA_THREADS), smem, st,
+                                      splits, true, mk, mv, (const bf16*)q, q_row_stride,
+                                      (bf16*)kpages, (bf16*)vpages, block_table, table_stride,
+                                      cu_seqlens_q, positions, (bf16*)out, nh, nkv, page_size,
+                                      window, scale * LOG2E, splits, (int)slots, tbl_cap, nst, err,
+                                      rope, parts, po, pml);
+  if (rc || parts == 1) return rc;
+  return launch_kernel(attn_decode_merge_kernel, dim3(nh, B), dim3(HD), 0, st, (const float*)po,
+                       (const float*)pml, cu_seqlens_q, (bf16*)out, nh, parts);
 #else
   return -6;
 #endif

@@ -41,11 +41,14 @@
 // on 32 scores.  The whole row in registers: 2,250.  The three waits of a group made by three
 // lanes at once: 1,950 (a wait costs its thread 300 cycles while the tensor core reads its
 // operands from shared memory, 60 otherwise).  The 16 products of a tile take 1,350 of them.
-// Tried and slower: a thread for each stream (the streams fall into step: both wait for the
-// tensor core, then both for the exponentials), the same with a token that makes them take turns,
-// the K and V waits moved to a softmax thread, a second warp that waits ahead and meets the
-// issuing warp at a hardware barrier (faster on long rows of tiles, slower on short ones), and a
-// share of the exponentials by polynomial (the exponential unit is not what the tile waits for).
+// Tried and not faster: a thread for each stream (the streams fall into step: both wait for the
+// tensor core, then both for the exponentials), the same with turns handed over through barriers
+// in shared memory (slower) or through a hardware barrier of the two warps (the same), the K and V
+// waits moved to a softmax thread, a second warp that waits ahead and meets the issuing warp at
+// a hardware barrier (4 % faster on long rows of tiles, 6 % slower on short ones), and a share of
+// the exponentials by polynomial.  What a tile waits for now is the chain of one stream: softmax
+// of a tile (2,150 cycles, 1,024 of them the exponential unit's), the wait of the issuing thread
+// (300 to 500), the 16 products (1,350); two streams make two tiles in that time.
 //
 // Every wait on an mbarrier is bounded; when one runs out, the waiter records a code in *err, an
 // abort flag in shared memory tells the other roles to leave their loops, all meet at the final

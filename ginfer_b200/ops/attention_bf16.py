@@ -35,6 +35,31 @@ def decode_splits(batch: int, nh: int, nkv: int, max_keys: int, sms: int | None 
     return splits
 
 
+MAX_PARTS = 16                 # clusters that may share one request's keys
+# the fewest keys a CTA should be left with: where one cluster a request leaves more than half of
+# the SMs idle, and otherwise (the kernel that adds the parts up costs 3 us: 8 requests of 4,096
+# keys measured 16.5 us in two parts against 12.0 in one, of 32,768 keys 46.9 against 58.2)
+MIN_KEYS_PER_CTA_IDLE, MIN_KEYS_PER_CTA = 256, 1024
+
+
+def decode_partition(batch: int, nh: int, nkv: int, max_keys: int,
+                     sms: int | None = None) -> tuple[int, int]:
+    """(splits, parts): how many CTAs form the cluster that merges through distributed shared
+    memory, and how many such clusters share a request's keys (their results are added up by a
+    second kernel).  More than one cluster only where 8 CTAs a request and kv head leave most of
+    the GPU idle: few requests with many keys."""
+    from .gemm_bf16 import num_sms
+    splits = decode_splits(batch, nh, nkv, max_keys, sms)
+    if splits < 8:
+        return splits, 1
+    chunks = (nh // nkv + 15) // 16
+    base = max(1, batch * nkv * chunks)
+    n_sms = sms or num_sms()
+    least = MIN_KEYS_PER_CTA_IDLE if 2 * base * splits <= n_sms else MIN_KEYS_PER_CTA
+    want = min(n_sms * CTAS_PER_SM // (base * splits), max_keys // (least * splits), MAX_PARTS)
+    return splits, max(1, want)
+
+
 def tma_serves(hd: int, page_size: int, splits: int) -> bool:
     """Whether decode attention takes the kernel that loads its tiles by TMA."""
     return (hd % 64 == 0 and page_size % 8 == 0 and splits in (1, 2, 4, 8, 16)
@@ -52,7 +77,7 @@ def _scratch_for(nbytes: int, device) -> torch.Tensor:
 
 def decode(qkv, pages, block_table, cu_seqlens_q, positions, B, nh, nkv, hd, scale, window,
            page_size, splits, out=None, scratch=None, through_scratch=False, rope=None,
-           use_tma=True, stages=3):
+           use_tma=True, stages=3, parts=1):
     """Split-KV decode attention.  ``splits`` of 2, 4, 8 or 16 merge inside a thread-block cluster
     (no scratch memory) unless ``through_scratch``; any other number goes through scratch.
     ``rope = (table or None, rotary_dim, write)``: q and k arrive unrotated and the kernel
@@ -60,7 +85,9 @@ def decode(qkv, pages, block_table, cu_seqlens_q, positions, B, nh, nkv, hd, sca
     ``use_tma``: take the kernel that loads its tiles by TMA where it serves the case (head sizes
     64, 128, 192 and 256, page sizes 8, 16, 32, 64 and multiples of 64, cluster merge), with a
     ring of ``stages`` tiles (2 .. 6; three let two CTAs share an SM, and with clusters of 8 only
-    that fits a grid of 128 CTAs in one wave: four and six stages measured half as fast)."""
+    that fits a grid of 128 CTAs in one wave: four and six stages measured half as fast).
+    ``parts`` > 1 (TMA kernel only): that many clusters share a request's keys and a second kernel
+    adds their results up (see :func:`decode_partition`)."""
     from . import _fn, _ok, _p, _stream
     defines = (f"GF_HEAD_DIM={hd}",)
     if out is None:
@@ -76,16 +103,27 @@ def decode(qkv, pages, block_table, cu_seqlens_q, positions, B, nh, nkv, hd, sca
     if use_tma and hd % 64 == 0 and scratch is None and not through_scratch:
         from .gemm_bf16 import error_word
         table, rot, write = rope if rope is not None else (None, 0, False)
+        parts = max(1, int(parts))
+        part_scratch = None
+        if parts > 1:
+            nbytes = B * nh * parts * (hd + 2) * 4
+            if torch.cuda.is_current_stream_capturing():
+                part_scratch = torch.empty(nbytes // 4, dtype=torch.float32, device=qkv.device)
+            else:
+                part_scratch = _scratch_for(nbytes, qkv.device)
         f = _fn("attention_bf16", "gf_attn_decode_tma",
                 [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
-                 c_int, c_int, c_int, c_void_p, c_void_p], defines, kernels=1)
+                 c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p], defines, kernels=1)
         rc = f(_p(qkv), qkv.stride(0), _p(pages[0]), _p(pages[1]), pages.shape[1],
                _p(block_table), block_table.stride(0), _p(cu_seqlens_q), _p(positions), _p(out), B,
                nh, nkv, page_size, int(window), float(scale), int(splits),
                int(stages), _p(table),
                int(rot) if table is not None else 0, 1 if rope is not None else 0,
-               int(bool(write)), _p(error_word(qkv.device)), _stream())
+               int(bool(write)), _p(error_word(qkv.device)), _stream(), parts, _p(part_scratch))
+        if rc == 0 and parts > 1:
+            from . import _Counter
+            _Counter.launches += 1                     # the kernel that adds the parts up
         if rc != -6:
             _ok(rc, "attn_decode_tma")
             return out
@@ -187,9 +225,13 @@ def try_run(qkv, pages, block_table, ctx, nh, nkv, hd, scale, window, page_size,
         return None
     if ctx.decode_only:
         keys = ctx.max_kv_len if window <= 0 else min(window, ctx.max_kv_len)
-        splits = ctx.extras.get("decode_splits") or decode_splits(ctx.num_seqs, nh, nkv, keys)
+        splits, parts = decode_partition(ctx.num_seqs, nh, nkv, keys)
+        if ctx.extras.get("decode_splits"):
+            splits, parts = ctx.extras["decode_splits"], 1
+        if not tma_serves(hd, page_size, splits):
+            parts = 1
         return decode(qkv, pages, block_table, ctx.cu_seqlens_q, ctx.positions, ctx.num_seqs, nh,
-                      nkv, hd, scale, window, page_size, splits, rope=rope)
+                      nkv, hd, scale, window, page_size, splits, rope=rope, parts=parts)
     assert rope is None, "only decode steps rotate inside the attention kernel"
     # A mixed step whose single tokens come first (as the scheduler orders them): those requests
     # go to the decode kernel, the portions behind them to a prefill kernel.  (A single token as a
@@ -202,8 +244,9 @@ def try_run(qkv, pages, block_table, ctx, nh, nkv, hd, scale, window, page_size,
     if 0 < nd < B and len(q_lens) == B:
         keys = ctx.max_kv_len if window <= 0 else min(window, ctx.max_kv_len)
         out = torch.empty((qkv.shape[0], nh * hd), dtype=torch.bfloat16, device=qkv.device)
+        splits, parts = decode_partition(nd, nh, nkv, keys)
         decode(qkv, pages, block_table[:nd], None, ctx.positions, nd, nh, nkv, hd, scale, window,
-               page_size, decode_splits(nd, nh, nkv, keys), out=out)
+               page_size, splits, out=out, parts=parts if tma_serves(hd, page_size, splits) else 1)
         cu, kv_lens, table, B = cu[nd:], kv_lens[nd:], block_table[nd:], B - nd
         max_q = max(q_lens[nd:])
     if max_q >= TC_MIN_QUERY_ROWS:

@@ -351,6 +351,25 @@ def test_attention_bf16_decode_with_tiles_by_tma(case, splits):
     torch.testing.assert_close(out.float(), other.float(), atol=1e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("case", [DEC_TMA_CASES[0], DEC_TMA_CASES[2], DEC_TMA_CASES[4],
+                                  DEC_TMA_CASES[5], ([9000, 300, 2100], 12, 2, 128, 16, 0)])
+@pytest.mark.parametrize("splits,parts", [(8, 2), (8, 5), (4, 3), (1, 4), (8, 16)])
+def test_attention_bf16_decode_with_several_clusters_a_request(case, splits, parts):
+    """Few requests with many keys: several clusters share a request's keys and a second kernel
+    adds their results up.  Against the oracle and against one cluster a request; parts that get
+    no key at all (more pieces than tiles) count for nothing."""
+    from ginfer_b200.ops import attention_bf16, gemm_bf16
+    lens, nh, nkv, hd, P, window = case
+    dev, want, scale = _paged_case(lens, [1] * len(lens), nh, nkv, hd, P, window, torch.bfloat16)
+    args = (_qkv(dev, nh, nkv, hd), dev["pages"], dev["table"], dev["cu"], dev["positions"],
+            len(lens), nh, nkv, hd, scale, window, P, splits)
+    out = attention_bf16.decode(*args, parts=parts)
+    gemm_bf16.check_errors()
+    torch.testing.assert_close(out.double().cpu(), want, atol=1e-2, rtol=2e-2)
+    one = attention_bf16.decode(*args)
+    torch.testing.assert_close(out.float(), one.float(), atol=1e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("case", DEC_CASES)
 @pytest.mark.parametrize("splits", [1, 4, 8, -3])
 @pytest.mark.parametrize("rot_frac", [1.0, 0.5])

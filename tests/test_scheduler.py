@@ -376,6 +376,22 @@ def test_split_choices_of_the_kernels():
     assert gemm_bf16.split_k_for(8, 17920, 1536, sms=64) == 1        # 140 tiles on 64 SMs: none
     assert gemm_bf16.split_k_for(8, 1536, 8960, sms=64) == 4         # fewer SMs, fewer splits
     assert attention_bf16.decode_splits(64, 12, 2, 576, sms=32) == 1
+    # several clusters a request: only where one cluster leaves most of the GPU idle (few requests,
+    # many keys), and never so many that a CTA is left with less than 256 keys (1,024 where one
+    # cluster a request fills half of the SMs already)
+    P = attention_bf16.decode_partition
+    assert P(1, 12, 2, 576) == (8, 1)
+    assert P(1, 12, 2, 4096) == (8, 2)
+    assert P(1, 12, 2, 32768) == (8, 16)
+    assert P(8, 12, 2, 4096) == (8, 1)               # 128 CTAs already
+    assert P(8, 12, 2, 32768) == (8, 2)
+    assert P(64, 12, 2, 32768) == (2, 1)
+    assert P(1, 28, 4, 32768) == (8, 9)              # 4 kv heads: 296 // 32
+    for b in (1, 2, 5, 8, 33, 64):
+        for keys in (1, 70, 600, 5000, 40000):
+            splits, parts = P(b, 12, 2, keys)
+            assert parts == 1 or (splits == 8 and keys // (splits * parts) >= 256)
+            assert 1 <= parts <= attention_bf16.MAX_PARTS
 
 
 def test_pages_a_cache_group_can_hold_at_once():

@@ -162,3 +162,27 @@ def test_a_step_of_many_tokens_agrees_with_portions_plain_and_the_32_bit_path(
     for name, got in (("one step", whole), ("a later portion", second), ("portions", cut)):
         err = np.abs(got.double().numpy() - ref)
         assert (err <= atol + rtol * np.abs(ref)).all(), (name, float(err.max()), atol)
+
+
+def test_decoding_one_request_with_thousands_of_keys_agrees_with_plain(tmp_path):
+    """One request of 4,600 tokens, its last tokens decoded one by one from CUDA graphs: so few
+    requests with so many keys take several thread-block clusters a request and a kernel that
+    adds their results up.  Every decoded row against the plain implementation, with a query and
+    key sharpened so that a far key carries weight."""
+    from ginfer_b200.engine import ModelRunner
+    from ginfer_b200.engine.loading import load_model
+    from ginfer_b200.ops import attention_bf16
+    cfg = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": 1,
+           "vocab_size": 300, "rope_theta": 1e6, "rms_norm_eps": 1e-6, "hidden_size": 128,
+           "num_attention_heads": 2, "num_key_value_heads": 1, "head_dim": 64,
+           "intermediate_size": 256, "max_position_embeddings": 8192,
+           "tie_word_embeddings": False, "use_sliding_window": False, "torch_dtype": "bfloat16"}
+    d = make_folder(tmp_path, "long_context", seed=3, storage="bfloat16", config=cfg)
+    reqs = {"far": prompt(4600, 300, seed=9)}
+    steps = replay.cut_tail_decode(reqs, tail=5)
+    assert attention_bf16.decode_partition(1, 2, 1, 5120)[1] > 1
+    model, _ = load_model(d, "bfloat16")
+    runner = ModelRunner(model, page_size=16, max_num_seqs=2, max_seq_len=4800, num_pages=320,
+                         max_num_batched_tokens=8192, enforce_eager=False)
+    rows = replay.run_in_process(runner, steps)
+    replay.compare(rows, replay.plain_logits(d, reqs, "bfloat16"), "bfloat16", reqs)
