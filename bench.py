@@ -334,12 +334,95 @@ def run_micro(name: str) -> int:
 
 
 # ----------------------------------------------------------------------------- scenarios
-SCENARIOS = ("serve64", "chunked", "ref256")
+SCENARIOS = ("serve64", "chunked", "ref256", "longctx")
 
 # what 11Aln0/ginfer publishes for its own throughput run (README.md:51-53 and the log under
 # media/): one A40, a 1.5B Qwen2-architecture model in bf16
 REF256_PUBLISHED = {"hardware": "A40", "prefill_tok_s": 31590.0, "decode_tok_s": 5457.0,
                     "total_tok_s": 16138.0}
+
+
+def run_long_context(shape: str, layers: int | None, context: int = 32768) -> int:
+    """One prompt of ``context`` tokens fed in portions of 2,048 (each portion timed on the device
+    with CUDA events; the whole prompt three times, the last pass reported: the first two let the
+    portions' CUDA graphs be captured), then single tokens decoded
+    at that context for one request and for eight: where attention over the cache, not the
+    products, decides the time.  Fractions: a portion's flops (products and the attention over
+    the keys before and inside it) over the measured tensor peak; a decode step's bytes (weights
+    once, the cache of the live requests) over the measured copy bandwidth.  One JSON line."""
+    import torch
+
+    from ginfer_b200 import ops
+    from ginfer_b200.engine import StepEntry
+    from ginfer_b200.engine.llm import Engine
+    cfg = dict(SHAPES[shape])
+    full_layers = cfg["num_hidden_layers"]
+    L = cfg["num_hidden_layers"] = layers or full_layers
+    cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], context + 256)
+    V, portion, B = cfg["vocab_size"], PREFILL_TOKENS, 8
+    eng = Engine(config=cfg, dtype="bfloat16", max_num_seqs=B, max_seq_len=context + 128,
+                 max_num_batched_tokens=portion, kvcache_block_size=PAGE,
+                 num_kvcache_blocks=B * ((context + 128) // PAGE + 2))
+    runner = eng.runner
+    peaks, peaks_from = load_peaks()
+    g = torch.Generator().manual_seed(1)
+    prompts = torch.randint(0, V, (B, context), generator=g).tolist()
+    # ---- the prompt in portions
+    per_portion = []
+    for rep in range(3):
+        per_portion = []
+        for at in range(0, context, portion):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            start.record()
+            last = at + portion >= context
+            runner.step([StepEntry("long", prompts[0][at:at + portion], [portion - 1] if last else [])])
+            stop.record()
+            torch.cuda.synchronize()
+            per_portion.append(start.elapsed_time(stop))
+        if rep < 2:
+            runner.end("long")
+    lin = 2.0 * portion * L * linear_params_per_layer(cfg)
+
+    def portion_flops(at):
+        keys = portion * at + portion * (portion + 1) / 2
+        return lin + L * 4.0 * cfg["num_attention_heads"] * cfg["head_dim"] * keys
+    total_ms = sum(per_portion)
+    flops = sum(portion_flops(at) for at in range(0, context, portion))
+    prefill = {"tokens": context, "portion": portion, "ms": round(total_ms, 3),
+               "value": round(context / (total_ms * 1e-3), 1),
+               "frac": round(flops / (total_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4),
+               "first_portion_ms": round(per_portion[0], 3),
+               "last_portion_ms": round(per_portion[-1], 3),
+               "last_portion_frac": round(portion_flops(context - portion) / (per_portion[-1] * 1e-3) /
+                                          (peaks["bf16_tflops"] * 1e12), 4)}
+    # ---- decoding at that context: the request above, then eight of them
+    decode = {}
+    ids = ["long"]
+    for batch in (1, B):
+        for b in range(len(ids), batch):
+            rid = f"long{b}"
+            for at in range(0, context, portion):
+                runner.step([StepEntry(rid, prompts[b][at:at + portion], [])])
+            ids.append(rid)
+        feed = torch.randint(0, V, (8 + 32, batch), generator=g).tolist()
+        for s_ in range(8):
+            ops.argmax(runner.step([StepEntry(ids[b], [feed[s_][b]], [0]) for b in range(batch)]))
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for s_ in range(8, 40):
+            ops.argmax(runner.step([StepEntry(ids[b], [feed[s_][b]], [0]) for b in range(batch)]))
+        stop.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(stop) / 32
+        nbytes = weight_bytes(cfg, L) + batch * (context + 24) * kv_bytes_per_token(cfg, L)
+        decode[f"b{batch}"] = {"tok_s": round(batch / (ms * 1e-3), 1), "ms": round(ms, 4),
+                               "frac": round(nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)}
+    print(json.dumps({"scenario": "longctx", "model": SHAPE_NAMES[shape], "layers_run": L,
+                      "layers_config": full_layers, "context": context, "kv_block": PAGE,
+                      "prefill": prefill, "decode": decode, "peaks": peaks_from}))
+    return 0
 
 
 def run_scenario(name: str, shape: str, layers: int | None) -> int:
@@ -454,6 +537,8 @@ def main() -> int:
         if args.gpus != 1:
             print(json.dumps({"error": "this engine runs on one GPU", "n_gpus": args.gpus}))
             return 2
+        if args.scenario == "longctx":
+            return run_long_context(args.shape, args.layers)
         return run_scenario(args.scenario, args.shape, args.layers)
 
     if args.impl == "reference":

@@ -199,8 +199,14 @@ class ModelRunner:
         graphable = decode_only or (B <= PORTION_GRAPH_MAX_SEQS and T >= PORTION_GRAPH_MIN_TOKENS)
         if graphable and not self.enforce_eager:
             # such steps are replayed from CUDA graphs, one per (shape, table width): widths come
-            # in steps of GRAPH_WIDTH_STEP pages so that few graphs are needed
-            width = min(cache.table_width, -(-width // GRAPH_WIDTH_STEP) * GRAPH_WIDTH_STEP)
+            # in steps of GRAPH_WIDTH_STEP pages so that few graphs are needed.  Steps with
+            # portions take the next power of two of such steps (the portions of one long prompt
+            # then share a handful of graphs; nothing in such a step is chosen by the width, while
+            # a decode step splits its keys by it).
+            steps = -(-width // GRAPH_WIDTH_STEP)
+            if not decode_only:
+                steps = 1 << (steps - 1).bit_length()
+            width = min(cache.table_width, steps * GRAPH_WIDTH_STEP)
         slots_of_token = slot_ids[seq_of_token]
         slot_maps = [cache.slot_mapping(g, slots_of_token, positions)
                      for g in range(cache.num_groups)]
