@@ -1126,17 +1126,17 @@ GF_EXPORT int gf_attn_decode_tma(const void* q, int q_row_stride, void* kpages, 
   const int most = (int)(room / STAGE_BYTES) < TMAX_STAGES ? (int)(room / STAGE_BYTES) : TMAX_STAGES;
   const int nst = stages < 2 ? 2 : stages > most ? most : stages;
   const size_t smem = (size_t)nst * STAGE_BYTES + small + (size_t)tbl_cap * sizeof(int);
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(
-        attn_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-        (int)((size_t)most * STAGE_BYTES + small + kMaxTableCopyTma * sizeof(int)));
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attn_decode_tma_kernel,
-                               cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-    if (e != cudaSuccess) return (int)e;
-    attr_done = true;
-  }
+  static OncePerDevice attrs;
+  if (int rc = attrs.run([&] {
+        cudaError_t e = cudaFuncSetAttribute(
+            attn_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            (int)((size_t)most * STAGE_BYTES + small + kMaxTableCopyTma * sizeof(int)));
+        if (e == cudaSuccess)
+          e = cudaFuncSetAttribute(attn_decode_tma_kernel,
+                                   cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        return e;
+      }))
+    return rc;
   const RopeArgs rope{fused ? rope_table : nullptr, fused ? rot : 0, fused ? 1 : 0,
                       fused && write_kv ? 1 : 0};
   // `parts` > 1 (few requests with many keys): that many clusters share a request's keys; they
@@ -1195,14 +1195,13 @@ GF_EXPORT int gf_attn_prefill(const void* q, int q_row_stride, const void* kpage
   const size_t work = (size_t)(QT + 2 * PRE_STAGES * KT) * ROW * sizeof(bf16);
   const int tbl_cap = table_stride < kMaxTableCopy ? table_stride : kMaxTableCopy;
   const size_t smem = work + (size_t)tbl_cap * sizeof(int);
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)(work + kMaxTableCopy * sizeof(int)));
-    if (e != cudaSuccess) return (int)e;
-    attr_done = true;
-  }
+  static OncePerDevice attrs;
+  if (int rc = attrs.run([&] {
+        return cudaFuncSetAttribute(attn_prefill_kernel,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)(work + kMaxTableCopy * sizeof(int)));
+      }))
+    return rc;
   dim3 grid((max_q_len + QT - 1) / QT, nh, B);
   return launch_kernel(attn_prefill_kernel, grid, dim3(NTHREADS), smem, st, (const bf16*)q,
                        q_row_stride, (const bf16*)kpages, (const bf16*)vpages, block_table,

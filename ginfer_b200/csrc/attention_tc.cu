@@ -921,13 +921,12 @@ GF_EXPORT int gf_attn_prefill_tc(const void* q, int q_row_stride, const void* kp
   if (!make_map(&mk, kpages, slots, nkv * HD, (long long)nkv * HD, page_size)) return -6;
   if (!make_map(&mv, vpages, slots, nkv * HD, (long long)nkv * HD, page_size)) return -6;
   const size_t smem = Q_BYTES + K_STAGES * K_BYTES + V_STAGES * V_BYTES + sizeof(Barriers);
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    attr_done = true;
-  }
+  static OncePerDevice attrs;
+  if (int rc = attrs.run([&] {
+        return cudaFuncSetAttribute(attn_prefill_tc_kernel,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      }))
+    return rc;
   const int q_tiles = (max_q_len + QT - 1) / QT;
   const long long items = (long long)nh * q_tiles * B;
   if (items >= (1ll << 30)) return -6;

@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #define GF_EXPORT extern "C" __attribute__((visibility("default")))
 
 // dtype codes used across the C interface
@@ -117,5 +119,25 @@ inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t
 }  // namespace gf
 
 // Every library exports this switch for programmatic dependent launch (on by default).
+// A kernel's attributes (dynamic shared memory, cluster sizes) belong to a device: `set` runs once
+// on each device a launcher is used on.  Returns `set`'s error, -9 for a device that cannot be
+// told, else 0.  One object per launcher and attribute set (a function-local static).
+struct OncePerDevice {
+  static constexpr int kMaxDevices = 64;
+  std::mutex lock;
+  bool done[kMaxDevices] = {};
+  template <typename F>
+  int run(F&& set) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -9;
+    std::lock_guard<std::mutex> hold(lock);
+    if (done[dev]) return 0;
+    const cudaError_t e = set();
+    if (e != cudaSuccess) return (int)e;
+    done[dev] = true;
+    return 0;
+  }
+};
+
 #define GF_DEFINE_PDL_SWITCH \
   GF_EXPORT void gf_set_pdl(int on) { gf::pdl_flag() = on ? 1 : 0; }

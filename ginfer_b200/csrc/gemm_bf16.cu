@@ -632,19 +632,16 @@ static int launch_mode(const CUtensorMap& mw, const CUtensorMap& mx, const float
   const size_t smem = 1024 + (ring > red ? ring : red) + (2 * STAGES + 1) * sizeof(uint64_t) + 16 +
                       5 * BN * sizeof(float);
   auto k = gemm_tc_kernel<BN, EPI, OUT, CLUSTER>;
-  static bool done = false;
-  if (!done) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    done = true;
-  }
+  static OncePerDevice attrs, np_attrs;              // (of this instantiation of the launcher)
+  if (int rc = attrs.run([&] {
+        return cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      }))
+    return rc;
   if (CLUSTER && split_k > 8) {                       // clusters of more than 8 CTAs are opt-in
-    static bool np_done = false;
-    if (!np_done) {
-      cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-      if (e != cudaSuccess) return (int)e;
-      np_done = true;
-    }
+    if (int rc = np_attrs.run([&] {
+          return cudaFuncSetAttribute(k, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        }))
+      return rc;
   }
   dim3 grid((N + BM - 1) / BM, (M + BN - 1) / BN, split_k);
   return launch_kernel_cluster(k, grid, dim3(NTHREADS), smem, st, CLUSTER ? split_k : 1, mw, mx,

@@ -309,12 +309,11 @@ static int launch_prefill(const CUtensorMap& mx, const CUtensorMap& mw, const fl
   const size_t smem = 1024 + (size_t)PSTAGES * (PA_BYTES + PB_BYTES) +
                       (2 * PSTAGES + 4) * sizeof(uint64_t) + 16;
   auto k = gemm_prefill_kernel<EPI, OUT>;
-  static bool done = false;
-  if (!done) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    done = true;
-  }
+  static OncePerDevice attrs;                        // (of this instantiation of the launcher)
+  if (int rc = attrs.run([&] {
+        return cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      }))
+    return rc;
   return launch_kernel(k, dim3(ctas), dim3(P_THREADS), smem, st, mx, mw, bias, (OUT*)out, ldo, M,
                        N, K, qkv, err);
 }
