@@ -39,6 +39,61 @@ static_assert(PN % 32 == 0 && PN <= 256 && PSTAGES >= 2, "tile width");
 constexpr int EPI_WARPS = 8;
 constexpr int P_THREADS = (2 + EPI_WARPS) * 32;
 constexpr uint32_t P_TMEM_COLS = 512;
+// The same on CTA pairs (a cluster of two; tcgen05 .cta_group::2): a tile of 256 tokens x PN weight
+// rows.  Each CTA brings its 128 tokens and HALF of the weight rows of a K block; one thread of
+// the pair's first CTA issues products of 256 x PN x 16 that read both CTAs' shared memory and
+// write 128 token rows into each CTA's tensor memory.  A CTA's tensor core then reads 8 KB of
+// operands a product from shared memory instead of 12 KB (which is what bounds the single-CTA
+// kernel), and a weight tile crosses from L2 to an SM once for 256 tokens instead of 128.
+constexpr uint32_t PB_BYTES_PAIR = (PN / 2) * BK * 2;       // this CTA's half of the W tile
+constexpr int PSTAGES_PAIR = (220 * 1024) / (PM * BK * 2 + (PN / 2) * BK * 2);
+
+__device__ __forceinline__ uint32_t peer_addr(uint32_t local, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+  return remote;
+}
+// (addresses in the cluster's shared window: the barrier may be another CTA's)
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// A TMA load into this CTA's shared memory whose bytes are counted by a barrier of the pair's
+// first CTA (no multicast: each CTA fetches what it holds).
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar,
+                                                 int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.cta_group::2 "
+      "[%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrives on the barrier at this offset in both CTAs of the pair once the products issued so far
+// are complete
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  const uint16_t both = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+      "[%0], %1;"
+      ::"r"(smem_u32(bar)), "h"(both)
+      : "memory");
+}
+// D fp32, A and B bf16, both K-major, M = 256 over the pair, N = bn
+__host__ __device__ constexpr uint32_t umma_idesc_pair(int bn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) |
+         ((uint32_t)(256 >> 4) << 24);
+}
 
 constexpr int PEPI_STORE = 0;                 // out[m, n] = acc (+ bias[n])
 constexpr int PEPI_GATED = 2;                 // out[m, n / 2] = silu(acc[m, n]) * acc[m, n + 1], n even
@@ -71,7 +126,7 @@ __device__ __forceinline__ void store16_bf16(bf16* dst, const float (&v)[16]) {
   }
 }
 
-template <int EPI, typename OUT>
+template <int EPI, typename OUT, bool PAIR = false>
 __global__ void __launch_bounds__(P_THREADS)
 gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
                     const __grid_constant__ CUtensorMap tmap_w, const float* __restrict__ bias,
@@ -79,39 +134,55 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
                     int* __restrict__ err) {
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* tiles = (unsigned char*)(((uintptr_t)smem + 1023) & ~(uintptr_t)1023);
-  uint64_t* full = (uint64_t*)(tiles + PSTAGES * (PA_BYTES + PB_BYTES));
-  uint64_t* empty = full + PSTAGES;
-  uint64_t* acc_full = empty + PSTAGES;       // [2]
+  constexpr int NST = PAIR ? PSTAGES_PAIR : PSTAGES;
+  constexpr uint32_t B_BYTES = PAIR ? PB_BYTES_PAIR : PB_BYTES;
+  constexpr uint32_t STAGE = PA_BYTES + B_BYTES;
+  uint64_t* full = (uint64_t*)(tiles + NST * STAGE);
+  uint64_t* empty = full + NST;
+  uint64_t* acc_full = empty + NST;           // [2]
   uint64_t* acc_empty = acc_full + 2;         // [2]
   uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m_tiles = (M + PM - 1) / PM, n_tiles = (N + PN - 1) / PN;
+  // a pair: the cluster walks over tiles of 2 * PM tokens, this CTA has rows rank * PM .. of them
+  const uint32_t rank = PAIR ? cluster_rank() : 0u;
+  const int walker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int walkers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  constexpr int TM = PAIR ? 2 * PM : PM;
+  const int m_tiles = (M + TM - 1) / TM, n_tiles = (N + PN - 1) / PN;
   const int ntiles = m_tiles * n_tiles;
   const int nkb = (K + BK - 1) / BK;
 
   pdl_trigger();
   if (threadIdx.x == 0) {
-    for (int s = 0; s < PSTAGES; ++s) {
-      mbar_init(full + s, 1);
+    for (int s = 0; s < NST; ++s) {
+      mbar_init(full + s, PAIR ? 2 : 1);      // a pair: the first CTA's counts both CTAs' loads
       mbar_init(empty + s, 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full + b, 1);
-      mbar_init(acc_empty + b, EPI_WARPS * 32);
+      mbar_init(acc_empty + b, (PAIR ? 2 : 1) * EPI_WARPS * 32);   // both CTAs' epilogue threads
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_x) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_w) : "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 ::"r"(smem_u32(tmem_slot)), "r"(P_TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                   ::"r"(smem_u32(tmem_slot)), "r"(P_TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                   ::"r"(smem_u32(tmem_slot)), "r"(P_TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (PAIR) cluster_sync();                    // the peer's barriers exist before anything signals them
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *tmem_slot;
 
@@ -120,52 +191,92 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
       pdl_wait();                                      // x comes from the kernel in front
       int it = 0;                                      // K blocks issued so far, over all tiles
       bool ok = true;
-      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-        const int n0 = (tile / m_tiles) * PN, m0 = (tile % m_tiles) * PM;
+      for (int tile = walker; tile < ntiles && ok; tile += walkers) {
+        const int n0 = (tile / m_tiles) * PN + (PAIR ? (int)rank * (PN / 2) : 0);
+        const int m0 = (tile % m_tiles) * TM + (int)rank * PM;
         for (int kb = 0; kb < nkb; ++kb, ++it) {
-          const int s = it % PSTAGES;
-          if (!mbar_wait(empty + s, ((it / PSTAGES) & 1) ^ 1, err, 1)) { ok = false; break; }
-          mbar_expect_tx(full + s, PA_BYTES + PB_BYTES);
-          unsigned char* a = tiles + s * (PA_BYTES + PB_BYTES);
-          tma_load_2d(a, &tmap_x, full + s, kb * BK, m0);
-          tma_load_2d(a + PA_BYTES, &tmap_w, full + s, kb * BK, n0);
+          const int s = it % NST;
+          if (!mbar_wait(empty + s, ((it / NST) & 1) ^ 1, err, 1)) { ok = false; break; }
+          unsigned char* a = tiles + s * STAGE;
+          if (PAIR) {
+            const uint32_t bar = peer_addr(smem_u32(full + s), 0);     // the first CTA's
+            mbar_expect_tx_cluster(bar, STAGE);
+            tma_load_2d_pair(a, &tmap_x, bar, kb * BK, m0);
+            tma_load_2d_pair(a + PA_BYTES, &tmap_w, bar, kb * BK, n0);
+          } else {
+            mbar_expect_tx(full + s, STAGE);
+            tma_load_2d(a, &tmap_x, full + s, kb * BK, m0);
+            tma_load_2d(a + PA_BYTES, &tmap_w, full + s, kb * BK, n0);
+          }
         }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc(PN);
+    if (rank == 0) {                            // a pair: its first CTA issues for both
+      // The whole warp walks through the K blocks; lane 0 issues the products.  The waits for
+      // the stages are made AHEAD stages at a time, each by a lane of its own (see
+      // mbar_wait_lanes): one after the other they took as long as the products themselves.
+      constexpr uint32_t idesc = PAIR ? umma_idesc_pair(PN) : umma_idesc(PN);
+      constexpr int AHEAD = PAIR ? NST / 2 : 1;      // (single CTAs: four stages, no gain measured)
       int it = 0, t = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++t) {
+      for (int tile = walker; tile < ntiles && ok; tile += walkers, ++t) {
         const int buf = t & 1, use = t >> 1;
         // the epilogue must have read this accumulator's last tile (passes at once the first time)
         if (!mbar_wait(acc_empty + buf, (uint32_t)(use & 1) ^ 1u, err, 2)) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t acc = tmem + (uint32_t)(buf * 256);
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
-          const int s = it % PSTAGES;
-          if (!mbar_wait(full + s, (it / PSTAGES) & 1, err, 2)) { ok = false; break; }
+        for (int kb0 = 0; kb0 < nkb && ok; kb0 += AHEAD) {
+          const int n = min(AHEAD, nkb - kb0);
+          {
+            const int mine = it + min(lane, n - 1);
+            ok = mbar_wait_lanes(full + mine % NST, (uint32_t)(mine / NST) & 1u, lane < n, err, 2);
+          }
+          if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a = smem_u32(tiles + s * (PA_BYTES + PB_BYTES));
-          const uint64_t ad = umma_desc(a), bd = umma_desc(a + PA_BYTES);
+          if (lane == 0) {
+            for (int j = 0; j < n; ++j) {
+              const int s = (it + j) % NST;
+              const uint32_t a = smem_u32(tiles + s * STAGE);
+              const uint64_t ad = umma_desc(a), bd = umma_desc(a + PA_BYTES);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
-            umma(acc, ad + (uint64_t)(k * UMMA_K * 2 >> 4), bd + (uint64_t)(k * UMMA_K * 2 >> 4),
-                 idesc, (kb > 0 || k > 0) ? 1u : 0u);
-          umma_commit(empty + s);                      // the stage is free once these have read it
+              for (int k = 0; k < BK / UMMA_K; ++k) {
+                const uint32_t accumulate = (kb0 + j > 0 || k > 0) ? 1u : 0u;
+                if (PAIR)
+                  umma_pair(acc, ad + (uint64_t)(k * UMMA_K * 2 >> 4),
+                            bd + (uint64_t)(k * UMMA_K * 2 >> 4), idesc, accumulate);
+                else
+                  umma(acc, ad + (uint64_t)(k * UMMA_K * 2 >> 4),
+                       bd + (uint64_t)(k * UMMA_K * 2 >> 4), idesc, accumulate);
+              }
+              // the stage is free (in both CTAs of a pair) once these have read it
+              if (PAIR) umma_commit_pair(empty + s);
+              else umma_commit(empty + s);
+            }
+          }
+          it += n;
         }
-        if (ok) umma_commit(acc_full + buf);           // the tile's accumulator is complete
+        if (ok && lane == 0) {                         // the tile's accumulator is complete
+          if (PAIR) umma_commit_pair(acc_full + buf);
+          else umma_commit(acc_full + buf);
+        }
       }
     }
   } else {
     // epilogue: TMEM lanes (warp % 4) * 32 .. + 31 = tokens, columns half * 128 .. + 127
     const int e = warp - 2, q = warp & 3, half = e >> 2;
     pdl_wait();                                        // nothing is written before the kernel ahead is done
+    // this thread has read its part of an accumulator (a pair: the first CTA's thread that
+    // issues the products counts both CTAs' epilogue threads)
+    auto acc_read = [&](int buf) {
+      if (PAIR) mbar_arrive_cluster(peer_addr(smem_u32(acc_empty + buf), 0));
+      else mbar_arrive(acc_empty + buf);
+    };
     int t = 0;
-    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++t) {
+    for (int tile = walker; tile < ntiles; tile += walkers, ++t) {
       const int buf = t & 1, use = t >> 1;
-      const int n0 = (tile / m_tiles) * PN + half * (PN / 2), m = (tile % m_tiles) * PM + q * 32 + lane;
+      const int n0 = (tile / m_tiles) * PN + half * (PN / 2);
+      const int m = (tile % m_tiles) * TM + (int)rank * PM + q * 32 + lane;
       if (!mbar_wait(acc_full + buf, (uint32_t)(use & 1), err, 3)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 256 + half * (PN / 2));
@@ -231,7 +342,7 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
           }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        mbar_arrive(acc_empty + buf);
+        acc_read(buf);
         continue;
       }
 #pragma unroll 1
@@ -246,7 +357,7 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
         }
         if (c == PN / 2 - 16) {                        // the last read of this accumulator
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-          mbar_arrive(acc_empty + buf);
+          acc_read(buf);
         }
         const int n = n0 + c;
         if (m >= M || n >= N) continue;
@@ -295,25 +406,35 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (PAIR) cluster_sync();                    // neither CTA leaves while the other may still signal it
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem),
-                 "r"(P_TMEM_COLS)
-                 : "memory");
+    if (PAIR)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem),
+                   "r"(P_TMEM_COLS)
+                   : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem),
+                   "r"(P_TMEM_COLS)
+                   : "memory");
   }
 }
 
-template <int EPI, typename OUT>
+template <int EPI, typename OUT, bool PAIR = false>
 static int launch_prefill(const CUtensorMap& mx, const CUtensorMap& mw, const float* bias, void* out,
                           int ldo, int M, int N, int K, int* err, int ctas, cudaStream_t st,
                           const QkvArgs& qkv = QkvArgs{}) {
-  const size_t smem = 1024 + (size_t)PSTAGES * (PA_BYTES + PB_BYTES) +
-                      (2 * PSTAGES + 4) * sizeof(uint64_t) + 16;
-  auto k = gemm_prefill_kernel<EPI, OUT>;
+  constexpr int NST = PAIR ? PSTAGES_PAIR : PSTAGES;
+  const size_t smem = 1024 + (size_t)NST * (PA_BYTES + (PAIR ? PB_BYTES_PAIR : PB_BYTES)) +
+                      (2 * NST + 4) * sizeof(uint64_t) + 16;
+  auto k = gemm_prefill_kernel<EPI, OUT, PAIR>;
   static OncePerDevice attrs;                        // (of this instantiation of the launcher)
   if (int rc = attrs.run([&] {
         return cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       }))
     return rc;
+  if (PAIR)
+    return launch_kernel_cluster_dims(k, dim3(ctas & ~1), dim3(P_THREADS), smem, st, 2, true, mx, mw,
+                                      bias, (OUT*)out, ldo, M, N, K, qkv, err);
   return launch_kernel(k, dim3(ctas), dim3(P_THREADS), smem, st, mx, mw, bias, (OUT*)out, ldo, M,
                        N, K, qkv, err);
 }
@@ -328,9 +449,10 @@ GF_DEFINE_PDL_SWITCH
 // epi 0: out [M, N] (row stride ldo) bf16 or fp32 = x w^T (+ bias); epi 2: w rows interleaved
 // (gate_i, up_i), out [M, N / 2] bf16 = silu(gate) * up.  `ctas`: CTAs to launch (0: one an SM).
 // -6: a shape or alignment this kernel does not take (the caller uses another product).
+// `pair`: on CTA pairs (tiles of 256 tokens; see the top of the file).
 GF_EXPORT int gf_gemm_prefill(const void* x, int ldx, const void* w, const void* bias, void* out,
                               int ldo, int M, int N, int K, int epi, int out_f32, int ctas,
-                              int* err, void* stream) {
+                              int* err, void* stream, int pair) {
   if (M <= 0 || N <= 0) return 0;
   if (K < 8 || K % 8 || ldx % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) ||
       ((uintptr_t)out & 15))
@@ -340,8 +462,9 @@ GF_EXPORT int gf_gemm_prefill(const void* x, int ldx, const void* w, const void*
     return -6;
   CUtensorMap mx, mw;
   if (!make_map(&mx, x, M, K, ldx, PM)) return -6;
-  if (!make_map(&mw, w, N, K, K, PN)) return -6;
-  const int ntiles = ((M + PM - 1) / PM) * ((N + PN - 1) / PN);
+  if (!make_map(&mw, w, N, K, K, pair ? PN / 2 : PN)) return -6;
+  const int tm = pair ? 2 * PM : PM;
+  const int ntiles = ((M + tm - 1) / tm) * ((N + PN - 1) / PN);
   int sms = 148;
   {
     int dev = 0, v = 0;
@@ -350,8 +473,24 @@ GF_EXPORT int gf_gemm_prefill(const void* x, int ldx, const void* w, const void*
       sms = v;
   }
   if (ctas <= 0 || ctas > sms) ctas = sms;
-  if (ctas > ntiles) ctas = ntiles;
+  if (pair) {
+    if (ctas > 2 * ntiles) ctas = 2 * ntiles;
+    ctas &= ~1;
+    if (ctas < 2) return -6;
+  } else if (ctas > ntiles) {
+    ctas = ntiles;
+  }
   auto st = (cudaStream_t)stream;
+  if (pair) {
+    if (epi == PEPI_GATED)
+      return launch_prefill<PEPI_GATED, bf16, true>(mx, mw, nullptr, out, ldo, M, N, K, err, ctas,
+                                                    st);
+    if (out_f32)
+      return launch_prefill<PEPI_STORE, float, true>(mx, mw, (const float*)bias, out, ldo, M, N, K,
+                                                     err, ctas, st);
+    return launch_prefill<PEPI_STORE, bf16, true>(mx, mw, (const float*)bias, out, ldo, M, N, K,
+                                                  err, ctas, st);
+  }
   if (epi == PEPI_GATED)
     return launch_prefill<PEPI_GATED, bf16>(mx, mw, nullptr, out, ldo, M, N, K, err, ctas, st);
   if (out_f32)

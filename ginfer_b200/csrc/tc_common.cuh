@@ -44,6 +44,32 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* e
   if (err) atomicCAS(err, 0, code);      // the first wait that ran out names the role
   return false;
 }
+// The same for a whole warp, each lane with a barrier of its own (lanes without one pass `active`
+// = false): true when all of them are complete.  A wait on a barrier in shared memory costs its
+// thread 300 to 500 cycles while the tensor core reads its operands from there, complete or not,
+// and the thread that issues products cannot hide it behind them (a product keeps its thread
+// until the one before it has run): several lanes make several waits in the time of one.
+__device__ __forceinline__ bool mbar_wait_lanes(uint64_t* bar, uint32_t parity, bool active,
+                                                int* err, int code) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    uint32_t done = 1;
+    if (active) {
+      asm volatile(
+          "{\n\t.reg .pred p;\n\t"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(done)
+          : "r"(addr), "r"(parity)
+          : "memory");
+    }
+    if (__all_sync(0xffffffffu, done != 0)) return true;
+    active = active && !done;
+    if (spin > 1024) __nanosleep(64);
+  }
+  if (err && (threadIdx.x & 31) == 0) atomicCAS(err, 0, code);
+  return false;
+}
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar,
                                             int c0, int c1) {
   asm volatile(

@@ -16,10 +16,17 @@ def supports(x: torch.Tensor, weight: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and weight.is_contiguous())
 
 
-def gemm(x, weight, bias_f32=None, out_dtype=torch.bfloat16, epi: int = 0, ctas: int = 0):
+# GINFER_B200_GEMM_PAIR=0: the products of many tokens on single CTAs instead of CTA pairs
+PAIR = os.environ.get("GINFER_B200_GEMM_PAIR", "1") != "0"
+
+
+def gemm(x, weight, bias_f32=None, out_dtype=torch.bfloat16, epi: int = 0, ctas: int = 0,
+         pair: bool | None = None):
     """``x [M, K] @ weight[N, K]^T``; ``epi`` 0: (+ bias) -> ``[M, N]``; ``epi`` 2: weight rows
     are interleaved (gate_i, up_i) and the result is ``silu(gate) * up`` -> ``[M, N / 2]``.
-    ``ctas``: CTAs to launch (0: one an SM).  ``None`` if the kernel cannot serve the shape."""
+    ``ctas``: CTAs to launch (0: one an SM).  ``pair``: on CTA pairs (tiles of 256 tokens x 256
+    weight rows, tcgen05 ``cta_group::2``; ``None``: the default).  ``None`` if the kernel cannot
+    serve the shape."""
     from . import _cuda, _fn, _ok, _p, _stream
     from .gemm_bf16 import error_word
     if not supports(x, weight):
@@ -33,9 +40,10 @@ def gemm(x, weight, bias_f32=None, out_dtype=torch.bfloat16, epi: int = 0, ctas:
         return out
     f = _fn("gemm_prefill", "gf_gemm_prefill",
             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-             c_int, c_int, c_void_p, c_void_p])
+             c_int, c_int, c_void_p, c_void_p, c_int])
     rc = f(_p(x), x.stride(0), _p(weight), _p(bias_f32), _p(out), cols, M, N, K, int(epi),
-           1 if out_dtype == torch.float32 else 0, int(ctas), _p(error_word(x.device)), _stream())
+           1 if out_dtype == torch.float32 else 0, int(ctas), _p(error_word(x.device)), _stream(),
+           1 if (PAIR if pair is None else pair) else 0)
     if rc == -6:
         return None
     _ok(rc, "gemm_prefill")
