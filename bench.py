@@ -427,8 +427,8 @@ def run_long_context(shape: str, layers: int | None, context: int = 32768) -> in
 
 def run_scenario(name: str, shape: str, layers: int | None) -> int:
     """The serving workloads the baseline names beside the headline, through the Python entry
-    point (scheduler, chunked prompts, decode graphs), wall clock, second pass reported (the first
-    one captures graphs).  ``serve64``: continuous batching of 64 requests, prompts of 128..2048
+    point (scheduler, chunked prompts, decode graphs), wall clock, third pass reported (the first
+    two capture graphs: of decode steps at first sight, of steps with portions at second).  ``serve64``: continuous batching of 64 requests, prompts of 128..2048
     tokens, 64..256 generated each.  ``chunked``: 8 prompts of 8,192 tokens fed in 2,048-token
     portions beside 32 requests that generate 256 tokens each.  ``ref256``: the reference's own
     throughput run (``ginfer/test/test_engine.cc:57-112``): 256 prompts of 512 random ids, 128
@@ -470,7 +470,7 @@ def run_scenario(name: str, shape: str, layers: int | None) -> int:
                      max_num_batched_tokens=2048 + 32, kvcache_block_size=PAGE,
                      num_kvcache_blocks=8 * (8200 // PAGE + 2) + 32 * (288 // PAGE + 2))
     result = None
-    for _ in range(2):
+    for _ in range(3):
         torch.cuda.synchronize()
         t0, s0 = time.perf_counter(), eng.runner.steps_run
         st0 = dict(vars(eng.stats))
