@@ -19,8 +19,8 @@ def supports(hd: int, nh: int, nkv: int) -> bool:
 
 
 def decode_splits(batch: int, nh: int, nkv: int, max_keys: int, sms: int | None = None) -> int:
-    """How many ways to split each request's keys so that the grid fills the GPU: a power of two
-    up to 8, so that the splits of a request can form a thread-block cluster.  ``sms``: the
+    """How many ways to split each request's keys so that the grid fills the GPU without a second
+    wave: a power of two up to 8, so that the splits of a request can form a thread-block cluster.  ``sms``: the
     device's SM count (asked of the current device if ``None``)."""
     from .gemm_bf16 import num_sms
     chunks = (nh // nkv + 15) // 16
@@ -30,8 +30,8 @@ def decode_splits(batch: int, nh: int, nkv: int, max_keys: int, sms: int | None 
     splits = 1
     while splits * 2 <= min(want, 8):                 # clusters of 16 schedule badly: 8 at most
         splits *= 2
-    if splits < 8 and splits < want and splits * 2 - want <= want - splits:
-        splits *= 2                                   # round to the nearer power of two
+    # (never more CTAs than fit at once: 48 requests in 4 splits, 384 CTAs for 296 places, measured
+    # 17.3 us against 10.6 in 2)
     return splits
 
 

@@ -359,6 +359,8 @@ def test_split_choices_of_the_kernels():
     assert attention_bf16.decode_splits(64, 12, 2, 576) == 2
     assert attention_bf16.decode_splits(512, 12, 2, 576) == 1
     assert attention_bf16.decode_splits(1, 12, 2, 40) == 1           # one tile of keys
+    assert attention_bf16.decode_splits(48, 12, 2, 576) == 2         # 4 would not fit at once
+    assert attention_bf16.decode_splits(24, 12, 2, 576) == 4
     for b in (1, 3, 8, 20, 64, 200):
         for keys in (10, 600, 5000):
             assert attention_bf16.decode_splits(b, 28, 4, keys) in (1, 2, 4, 8)
