@@ -99,10 +99,12 @@ def add_to(linear: "Linear", x: torch.Tensor, residual: torch.Tensor, gamma=None
 
 
 # From this many tokens on the gated product runs on the persistent tcgen05 kernel of
-# csrc/gemm_prefill.cu (SiLU*mul in its epilogue).  On a B200 at the 1.5B shape (17920 x 1536):
-# 2,048 tokens 87.7 us against 96.0 for cuBLAS + SiLU*mul, 8,192 tokens 336 against 386, 512 tokens
-# 27.4 against 27.1; at the 7B shape (37888 x 3584) 383 against 392.
-PREFILL_GATED_MIN_TOKENS = 1024
+# csrc/gemm_prefill.cu (on CTA pairs, SiLU*mul in its epilogue).  On a B200 in a CUDA graph, against
+# cuBLAS + the SiLU*mul kernel: at the 1.5B shape (17920 x 1536) 512 tokens 26.9 against 26.6 us,
+# 768 tokens 36.2 against 37.9, 1,024 tokens 45.8 against 48.8, 2,048 tokens 84.6 against 96.0,
+# 8,192 tokens 304 against 386; at the 7B shape (37888 x 3584) 768 tokens 151 against 153, 1,024
+# tokens 193 against 210, 2,048 tokens 367 against 392.
+PREFILL_GATED_MIN_TOKENS = 768
 
 
 def _gemm_bf16():
