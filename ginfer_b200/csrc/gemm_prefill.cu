@@ -20,6 +20,10 @@
 //               at a time: tcgen05.ld, bias, SiLU*mul or rotation in fp32, bf16 / fp32 stores.
 //               The epilogue of a tile runs while the next tile's products go into the other
 //               accumulator.
+// The gated product runs on CTA pairs (template parameter PAIR; see PB_BYTES_PAIR below): a
+// cluster of two CTAs on a tile of 256 tokens, every role as above in both CTAs except that only
+// the first CTA's warp 1 issues products (tcgen05.mma.cta_group::2, 256 x 256 x 16) and that its
+// barriers count both CTAs' loads and both CTAs' epilogue threads.
 // Every wait is bounded; a wait that runs out sets *err (1 producer, 2 MMA issuer, 3 epilogue)
 // and the roles leave their loops, after which the CTA frees its tensor memory and returns.
 #include "tc_common.cuh"
