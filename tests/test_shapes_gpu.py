@@ -164,10 +164,10 @@ def test_a_step_of_many_tokens_agrees_with_portions_plain_and_the_32_bit_path(
         assert (err <= atol + rtol * np.abs(ref)).all(), (name, float(err.max()), atol)
 
 
-def test_decoding_one_request_with_thousands_of_keys_agrees_with_plain(tmp_path):
-    """One request of 4,600 tokens, its last tokens decoded one by one from CUDA graphs: so few
-    requests with so many keys take several thread-block clusters a request and a kernel that
-    adds their results up.  Every decoded row against the plain implementation, with a query and
+def test_decoding_few_requests_with_thousands_of_keys_agrees_with_plain(tmp_path):
+    """A request of 4,600 tokens (and one of 41), their last tokens decoded one by one from CUDA
+    graphs: so few requests with so many keys take several thread-block clusters a request and a
+    kernel that adds their results up.  Every decoded row against the plain implementation, with a query and
     key sharpened so that a far key carries weight."""
     from ginfer_b200.engine import ModelRunner
     from ginfer_b200.engine.loading import load_model
@@ -178,9 +178,16 @@ def test_decoding_one_request_with_thousands_of_keys_agrees_with_plain(tmp_path)
            "intermediate_size": 256, "max_position_embeddings": 8192,
            "tie_word_embeddings": False, "use_sliding_window": False, "torch_dtype": "bfloat16"}
     d = make_folder(tmp_path, "long_context", seed=3, storage="bfloat16", config=cfg)
-    reqs = {"far": prompt(4600, 300, seed=9)}
-    steps = replay.cut_tail_decode(reqs, tail=5)
-    assert attention_bf16.decode_partition(1, 2, 1, 5120)[1] > 1
+    # (a second, short request beside it: most of the parts hold none of its keys)
+    reqs = {"far": prompt(4600, 300, seed=9), "near": prompt(41, 300, seed=10)}
+    tail = 5
+    steps = [{"step": i, "end": [], "entries": [
+        {"id": rid, "tokens": toks[:-tail], "want": list(range(len(toks) - tail))}]}
+        for i, (rid, toks) in enumerate(reqs.items())]
+    for k in range(tail, 0, -1):                         # then both decode side by side
+        steps.append({"step": len(steps), "end": list(reqs) if k == 1 else [], "entries": [
+            {"id": rid, "tokens": [toks[-k]], "want": [0]} for rid, toks in reqs.items()]})
+    assert attention_bf16.decode_partition(2, 2, 1, 5120)[1] > 1
     model, _ = load_model(d, "bfloat16")
     runner = ModelRunner(model, page_size=16, max_num_seqs=2, max_seq_len=4800, num_pages=320,
                          max_num_batched_tokens=8192, enforce_eager=False)
