@@ -342,8 +342,9 @@ REF256_PUBLISHED = {"hardware": "A40", "prefill_tok_s": 31590.0, "decode_tok_s":
                     "total_tok_s": 16138.0}
 
 
-def run_long_context(shape: str, layers: int | None, context: int = 32768) -> int:
-    """One prompt of ``context`` tokens fed in portions of 2,048 (each portion timed on the device
+def run_long_context(shape: str, layers: int | None, context: int = 32768,
+                     portion: int | None = None) -> int:
+    """One prompt of ``context`` tokens fed in portions of 2,048 (``--portion``: another size; each portion timed on the device
     with CUDA events; the whole prompt three times, the last pass reported: the first two let the
     portions' CUDA graphs be captured), then single tokens decoded
     at that context for one request and for eight: where attention over the cache, not the
@@ -359,7 +360,7 @@ def run_long_context(shape: str, layers: int | None, context: int = 32768) -> in
     full_layers = cfg["num_hidden_layers"]
     L = cfg["num_hidden_layers"] = layers or full_layers
     cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], context + 256)
-    V, portion, B = cfg["vocab_size"], PREFILL_TOKENS, 8
+    V, portion, B = cfg["vocab_size"], int(portion or PREFILL_TOKENS), 8
     eng = Engine(config=cfg, dtype="bfloat16", max_num_seqs=B, max_seq_len=context + 128,
                  max_num_batched_tokens=portion, kvcache_block_size=PAGE,
                  num_kvcache_blocks=B * ((context + 128) // PAGE + 2))
@@ -528,6 +529,8 @@ def main() -> int:
     ap.add_argument("--enforce-eager", action="store_true")
     ap.add_argument("--micro", choices=MICRO, default=None,
                     help="run one small kernel workload (for profiling) instead of the benchmark")
+    ap.add_argument("--portion", type=int, default=None,
+                    help="tokens a step of the long prompt in --scenario longctx (default 2,048)")
     ap.add_argument("--scenario", choices=SCENARIOS, default=None,
                     help="run a serving workload through the entry point instead of the benchmark")
     args = ap.parse_args()
@@ -538,7 +541,7 @@ def main() -> int:
             print(json.dumps({"error": "this engine runs on one GPU", "n_gpus": args.gpus}))
             return 2
         if args.scenario == "longctx":
-            return run_long_context(args.shape, args.layers)
+            return run_long_context(args.shape, args.layers, portion=args.portion)
         return run_scenario(args.scenario, args.shape, args.layers)
 
     if args.impl == "reference":
