@@ -260,7 +260,7 @@ def prefill_timed(eng, tokens: int, reps: int, warmup: int, seed: int):
 
 # ----------------------------------------------------------------------------- small workloads
 MICRO = ("gemm_gateup_m8", "gemm_down_m8", "gemm_lmhead_m8", "gemm_gateup_m2048", "attn_decode_b8",
-         "attn_decode_b64", "prefill_2layers")
+         "attn_decode_b64", "attn_decode_b1_ctx32768", "prefill_2layers")
 
 
 def run_micro(name: str) -> int:
@@ -301,20 +301,21 @@ def run_micro(name: str) -> int:
         print(json.dumps({"micro": name, "out": list(y.shape)}))
         return 0
     if name.startswith("attn_decode"):
-        B = 8 if name.endswith("b8") else 64
-        ctx = PROMPT + 64
+        B = 1 if "_b1_" in name else 8 if name.endswith("b8") else 64
+        ctx = 32768 if name.endswith("ctx32768") else PROMPT + 64
         pages_n = B * (ctx // PAGE + 2)
         pages = torch.randn(2, pages_n, PAGE, nkv, hd, device=dev).to(torch.bfloat16)
         table = torch.randperm(pages_n, device=dev).to(torch.int32).reshape(B, -1).contiguous()
         qkv = torch.randn(B, (nh + 2 * nkv) * hd, device=dev).to(torch.bfloat16)
         cu = torch.arange(B + 1, dtype=torch.int32, device=dev)
         pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
-        splits = attention_bf16.decode_splits(B, nh, nkv, ctx)
+        # few requests with many keys: several clusters a request and a kernel that adds them up
+        splits, parts = attention_bf16.decode_partition(B, nh, nkv, ctx)
         for _ in range(6):
             y = attention_bf16.decode(qkv, pages, table, cu, pos, B, nh, nkv, hd,
-                                      1 / math.sqrt(hd), 0, PAGE, splits)
+                                      1 / math.sqrt(hd), 0, PAGE, splits, parts=parts)
         torch.cuda.synchronize()
-        print(json.dumps({"micro": name, "splits": splits, "out": list(y.shape)}))
+        print(json.dumps({"micro": name, "splits": splits, "parts": parts, "out": list(y.shape)}))
         return 0
     if name == "prefill_2layers":
         from ginfer_b200.engine import StepEntry

@@ -812,9 +812,12 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ po,
   pdl_trigger();
   pdl_wait();
   const size_t base = ((size_t)b * nh + head) * splits;
+  // (eight parts' loads under way at a time: one after the other they were most of this kernel)
   float mm = -INFINITY;
+#pragma unroll 8
   for (int s = 0; s < splits; ++s) mm = fmaxf(mm, pml[(base + s) * 2]);
   float acc = 0.f, lsum = 0.f;
+#pragma unroll 8
   for (int s = 0; s < splits; ++s) {
     const float ms = pml[(base + s) * 2];
     const float wgt = ms == -INFINITY ? 0.f : exp2f(ms - mm);
