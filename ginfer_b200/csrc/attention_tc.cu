@@ -583,7 +583,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
         if (kind == 0) break;
         if (kind == 2) continue;
         const int ntiles = it.ntiles;
-        ok = mbar_wait(&bars->q_full, (uint32_t)(seq & 1), abort_flag, err, 2);
+        // (every lane makes the waits of this loop; what they saw is made one answer for the warp,
+        // since the waits by lanes below want every lane to take part)
+        ok = __all_sync(0xffffffffu, mbar_wait(&bars->q_full, (uint32_t)(seq & 1), abort_flag, err, 2));
         // S_s = Q K^T for the stream's next tile; `last`: the item's last tile
         auto issue_qk = [&](int s, bool last) {
           int& ck = s ? ck1 : ck0;
@@ -607,7 +609,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
         for (int s = 0; s < NS; ++s) {
           if (s >= ntiles || !ok) continue;
           const int ck = s ? ck1 : ck0;
-          ok = mbar_wait<true>(&bars->k_full[s * KS + ck % KS], (ck / KS) & 1, abort_flag, err, 3);
+          ok = __all_sync(0xffffffffu, mbar_wait<true>(&bars->k_full[s * KS + ck % KS], (ck / KS) & 1,
+                                                    abort_flag, err, 3));
           if (!ok) continue;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           issue_qk(s, s == ntiles - 1);
@@ -624,7 +627,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
             if (lane == 0) { GF_STAMP(1, t, 4 * s); }
             // the item's first P V overwrites O: the item before must have been read out
             if (i == 0)
-              ok = mbar_wait(&bars->o_free, (uint32_t)(seq & 1) ^ 1u, abort_flag, err, 14);
+              ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_free, (uint32_t)(seq & 1) ^ 1u, abort_flag,
+                                                     err, 14));
             if (lane == 0) { GF_STAMP(1, t, 4 * s + 1); }
             // lane 0: P of this tile; lane 1: its V tile; lane 2: the K tile of the next S product
             {
