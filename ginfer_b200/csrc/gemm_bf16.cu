@@ -427,7 +427,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     const int e = threadIdx.x - 64, sub = e & (tpt - 1);
     float part[SCALE_BATCH];
     if (ex.in_sumsq) {
-      const int tok = e / tpt;                           // the first round's token of this thread
+      const int tok = e / tpt;                           // this thread's token in the first pass of the loop
       const float* src = ex.in_sumsq + m0 + min(tok, live - 1);
 #pragma unroll
       for (int u = 0; u < SCALE_BATCH; ++u)
