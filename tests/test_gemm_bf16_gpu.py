@@ -59,6 +59,27 @@ def test_gated_epilogue(M, I, K):
     gemm_bf16.check_errors()
 
 
+@pytest.mark.parametrize("M,N,K,split_k", [
+    (8, 2048, 1536, 8), (1, 1536, 1536, 8), (16, 392, 512, 4), (13, 1000, 256, 2),   # partials pushed
+    (30, 1536, 512, 4), (8, 1536, 1536, 12),
+    (8, 1536, 8960, 12), (8, 640, 3072, 4), (40, 512, 1536, 8),                      # partials pulled
+])
+def test_cluster_split_adds_up_like_the_workspace_split(M, N, K, split_k):
+    """The K splits of a cluster are summed in rank order, whether the partials are sent to the
+    band owners (K ranges that leave stages of the ring free) or fetched by them: bit for bit what
+    the workspace mode gives, which sums in split order too."""
+    from ginfer_b200.ops import gemm_bf16
+    g = torch.Generator(device="cpu").manual_seed(N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    b = torch.randn(N, generator=g).to(DEV)
+    cluster = gemm_bf16.gemm(x, w, b, torch.float32, split_k=split_k)
+    through = gemm_bf16.gemm(x, w, b, torch.float32, split_k=split_k, through_workspace=True)
+    assert torch.equal(cluster, through)
+    torch.testing.assert_close(cluster.double(), _ref(x, w, b), atol=1e-3, rtol=1e-4)
+    gemm_bf16.check_errors()
+
+
 def test_refuses_what_tma_cannot_address():
     from ginfer_b200.ops import gemm_bf16
     x = torch.randn(4, 100, device=DEV).to(torch.bfloat16)        # K = 100: rows of 200 bytes
