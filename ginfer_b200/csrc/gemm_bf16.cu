@@ -379,7 +379,7 @@ __host__ __device__ constexpr bool push_fits(int K, int split_k) {
 }
 
 template <int BN, int EPI, typename OUT, bool CLUSTER, bool PUSH = false>
-__global__ void __launch_bounds__(NTHREADS)
+__global__ void __launch_bounds__(NTHREADS, 4)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                const float* __restrict__ bias, OUT* __restrict__ out, int ldo, int M, int N, int K,
                int split_k, float* __restrict__ workspace, int* __restrict__ err,
@@ -501,25 +501,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       cluster_wait();
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc(BN);
-      bool ok = true;
-      for (int i = 0; i < nkb && ok; ++i) {
-        const int s = i % STAGES;
-        ok = mbar_wait(full + s, (i / STAGES) & 1, err, 2);
-        if (!ok) {
-          gave_up = 1;
-          break;
-        }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a = smem_u32(tiles + s * (A_BYTES + B_BYTES));
-        const uint64_t ad = umma_desc(a), bd = umma_desc(a + A_BYTES);
+    // The whole warp walks through the K blocks; lane 0 issues the products.  The waits for the
+    // stages are made AHEAD stages at a time, each by a lane of its own (mbar_wait_lanes): one
+    // after the other they cost the issuing thread more than the products of a stage.
+    constexpr uint32_t idesc = umma_idesc(BN);
+#ifndef GF_MMA_AHEAD
+    constexpr int AHEAD = BN <= 64 ? (STAGES >= 6 ? 3 : 2) : 1;
+#else
+    constexpr int AHEAD = GF_MMA_AHEAD;
+#endif
+    bool ok = true;
+    for (int i0 = 0; i0 < nkb && ok; i0 += AHEAD) {
+      const int n = min(AHEAD, nkb - i0);
+      const int mine = i0 + min(lane, n - 1);
+      ok = mbar_wait_lanes(full + mine % STAGES, (uint32_t)(mine / STAGES) & 1u, lane < n, err, 2);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (lane == 0) {
+        for (int i = i0; i < i0 + n; ++i) {
+          const int s = i % STAGES;
+          const uint32_t a = smem_u32(tiles + s * (A_BYTES + B_BYTES));
+          const uint64_t ad = umma_desc(a), bd = umma_desc(a + A_BYTES);
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k)
-          umma(tmem, ad + (uint64_t)(k * UMMA_K * 2 >> 4), bd + (uint64_t)(k * UMMA_K * 2 >> 4),
-               idesc, (i > 0 || k > 0) ? 1u : 0u);
-        umma_commit(empty + s);            // the stage is free once these MMAs have read it
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma(tmem, ad + (uint64_t)(k * UMMA_K * 2 >> 4), bd + (uint64_t)(k * UMMA_K * 2 >> 4),
+                 idesc, (i > 0 || k > 0) ? 1u : 0u);
+          umma_commit(empty + s);          // the stage is free once these MMAs have read it
+        }
       }
+      __syncwarp();
+    }
+    if (lane == 0) {
+      if (!ok) gave_up = 1;
       umma_commit(acc_full);               // the accumulator is complete
     }
   } else {
