@@ -146,6 +146,10 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
   uint64_t* acc_full = empty + NST;           // [2]
   uint64_t* acc_empty = acc_full + 2;         // [2]
   uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+  // the bias of a tile's PN columns, for the tile in either accumulator: with nearly all of the
+  // SM's memory carved out as shared memory, a bias read from global memory in the epilogue's
+  // inner loop goes to L2 every time
+  float* bias_s = (float*)(tmem_slot + 4);    // [2][PN]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // a pair: the cluster walks over tiles of 2 * PM tokens, this CTA has rows rank * PM .. of them
@@ -281,6 +285,14 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const int buf = t & 1, use = t >> 1;
       const int n0 = (tile / m_tiles) * PN + half * (PN / 2);
       const int m = (tile % m_tiles) * TM + (int)rank * PM + q * 32 + lane;
+      const float* bias_t = bias_s + buf * PN + half * (PN / 2);     // of this thread's columns
+      if (EPI != PEPI_GATED && bias) {
+        const int tn0 = (tile / m_tiles) * PN;
+        for (int i = e * 32 + lane; i < PN; i += EPI_WARPS * 32)
+          bias_s[buf * PN + i] = tn0 + i < N ? bias[tn0 + i] : 0.f;
+        // the epilogue warps; they are at most a tile apart, and the tiles alternate buffers
+        asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
+      }
       if (!mbar_wait(acc_full + buf, (uint32_t)(use & 1), err, 3)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 256 + half * (PN / 2));
@@ -306,7 +318,7 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
               tmem_ld16(taddr + hb + j, v);
               if (bias) {
 #pragma unroll
-                for (int u = 0; u < 16; ++u) v[u] += bias[n0 + hb + j + u];
+                for (int u = 0; u < 16; ++u) v[u] += bias_t[hb + j + u];
               }
               if (row_ok) store16_bf16(dst + j, v);
               if (cache_ok) store16_bf16(page + j, v);
@@ -329,8 +341,8 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
               }
 #pragma unroll
               for (int u = 0; u < 16; ++u) {
-                const float x = round_bf16(a[u] + (bias ? bias[n0 + hb + j + u] : 0.f));
-                const float y = round_bf16(b[u] + (bias ? bias[n0 + hb + hh + j + u] : 0.f));
+                const float x = round_bf16(a[u] + (bias ? bias_t[hb + j + u] : 0.f));
+                const float y = round_bf16(b[u] + (bias ? bias_t[hb + hh + j + u] : 0.f));
                 a[u] = x * cc[u] - y * ss[u];
                 b[u] = x * ss[u] + y * cc[u];
               }
@@ -368,7 +380,7 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
         if (EPI == PEPI_STORE) {
           if (bias) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] += (n + j < N) ? bias[n + j] : 0.f;
+            for (int j = 0; j < 16; ++j) v[j] += bias_t[c + j];
           }
           OUT* dst = out + (size_t)m * ldo + n;
           if (sizeof(OUT) == 2) {
@@ -429,7 +441,7 @@ static int launch_prefill(const CUtensorMap& mx, const CUtensorMap& mw, const fl
                           const QkvArgs& qkv = QkvArgs{}) {
   constexpr int NST = PAIR ? PSTAGES_PAIR : PSTAGES;
   const size_t smem = 1024 + (size_t)NST * (PA_BYTES + (PAIR ? PB_BYTES_PAIR : PB_BYTES)) +
-                      (2 * NST + 4) * sizeof(uint64_t) + 16;
+                      (2 * NST + 4) * sizeof(uint64_t) + 16 + 2 * PN * sizeof(float);
   auto k = gemm_prefill_kernel<EPI, OUT, PAIR>;
   static OncePerDevice attrs;                        // (of this instantiation of the launcher)
   if (int rc = attrs.run([&] {
