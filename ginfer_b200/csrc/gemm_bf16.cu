@@ -801,9 +801,12 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* bia
                   int ldo, int M, int N, int K, int split_k, float* workspace, int* err,
                   cudaStream_t st, const GemmExtra& ex) {
 #ifndef GF_NO_PUSH                                   // (a build to compare the two ways with)
-  if (split_k > 1 && !workspace && push_fits<BN, EPI>(K, split_k))
-    return launch_mode<BN, EPI, OUT, true, true>(mw, mx, bias, out, ldo, M, N, K, split_k,
-                                                 workspace, err, st, ex);
+  // (token tiles above 32 have no stages to spare but for very short reductions: not compiled)
+  if constexpr (BN <= 32) {
+    if (split_k > 1 && !workspace && push_fits<BN, EPI>(K, split_k))
+      return launch_mode<BN, EPI, OUT, true, true>(mw, mx, bias, out, ldo, M, N, K, split_k,
+                                                   workspace, err, st, ex);
+  }
 #endif
   if (split_k > 1 && !workspace)
     return launch_mode<BN, EPI, OUT, true>(mw, mx, bias, out, ldo, M, N, K, split_k, workspace,
