@@ -102,6 +102,8 @@ __host__ __device__ constexpr uint32_t umma_idesc_pair(int bn) {
 constexpr int PEPI_STORE = 0;                 // out[m, n] = acc (+ bias[n])
 constexpr int PEPI_GATED = 2;                 // out[m, n / 2] = silu(acc[m, n]) * acc[m, n + 1], n even
 constexpr int PEPI_QKV = 3;                   // + bias, q and k heads rotated, k and v to the cache
+constexpr int QKV_SCRATCH_PITCH = 80;         // bytes between a warp's scratch rows (64 used)
+constexpr int QKV_SCRATCH_WARP = 32 * QKV_SCRATCH_PITCH;
 
 // What the q/k/v epilogue needs beside the product: rows [q heads | k heads | v heads] of `hd`
 // channels; q and k are rotated by the angles of the token's position (table row: cos | sin over
@@ -150,6 +152,9 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
   // SM's memory carved out as shared memory, a bias read from global memory in the epilogue's
   // inner loop goes to L2 every time
   float* bias_s = (float*)(tmem_slot + 4);    // [2][PN]
+  // the q/k/v epilogue's scratch: 32 rows of 64 bytes (80 apart) for each epilogue warp, through
+  // which it turns "a thread a token" into "four threads a token" and back (see there)
+  unsigned char* scratch_s = (unsigned char*)(bias_s + 2 * PN);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // a pair: the cluster walks over tiles of 2 * PM tokens, this CTA has rows rank * PM .. of them
@@ -293,24 +298,52 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
         // the epilogue warps; they are at most a tile apart, and the tiles alternate buffers
         asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
       }
+      // q/k/v: what the epilogue reads beside the accumulator is asked for before the wait for it
+      const int rr = lane >> 2, pc = lane & 3;         // four threads a token: token rr (+ 8 i), piece pc
+      int pos_t[4] = {0, 0, 0, 0}, slot_t[4] = {-1, -1, -1, -1}, slot_v[2] = {-1, -1};
+      float4 tc[4], ts[4];                             // cos and sin of the chunk of channels to come
+      auto load_table = [&](int j) {                   // channels j + 4 pc .. + 3 of tokens rr + 8 i
+        const int hd = qkv.hd;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float* trow = qkv.rope + (size_t)pos_t[i] * hd + j + 4 * pc;
+          tc[i] = __ldg(reinterpret_cast<const float4*>(trow));
+          ts[i] = __ldg(reinterpret_cast<const float4*>(trow + (hd >> 1)));
+        }
+      };
+      if (EPI == PEPI_QKV) {
+        const int mm = m < M ? m : M - 1;
+        const int pos_mine = qkv.positions[mm];
+        const int slot_mine = m < M ? qkv.slot_mapping[mm] : -1;     // negative: nothing is cached
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          pos_t[i] = __shfl_sync(0xffffffffu, pos_mine, 8 * i + rr);
+          slot_t[i] = __shfl_sync(0xffffffffu, slot_mine, 8 * i + rr);
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) slot_v[i] = __shfl_sync(0xffffffffu, slot_mine, 16 * i + (lane >> 1));
+        if (n0 / qkv.hd < qkv.nh + qkv.nkv) load_table(0);           // the first head is rotated
+      }
       if (!mbar_wait(acc_full + buf, (uint32_t)(use & 1), err, 3)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 256 + half * (PN / 2));
       if (EPI == PEPI_QKV) {
-        // whole heads of this thread's token: hd divides the half tile's 128 columns
+        // Whole heads of this thread's token: hd divides the half tile's 128 columns.  The
+        // accumulator gives a thread one token's row, but a warp that reads the table or writes
+        // `out` and the cache that way touches 32 lines with every instruction, and these, not
+        // the bytes, are what the epilogue then waits for.  So the table is read, and the
+        // results are written, with four threads a token (8 tokens x 64 bytes an instruction),
+        // and the warp's scratch in shared memory turns one lay-out into the other.
         const int hd = qkv.hd, hh = hd >> 1;
-        const bool row_ok = m < M;
-        const int mm = row_ok ? m : M - 1;
-        const float* cs = qkv.rope + (size_t)qkv.positions[mm] * hd;
-        const int slot_i = qkv.slot_mapping[mm];
-        const bool cache_ok = row_ok && slot_i >= 0;       // a negative slot: nothing is cached
-        const size_t slot = (size_t)(slot_i >= 0 ? slot_i : 0);
+        unsigned char* scr = scratch_s + (size_t)e * QKV_SCRATCH_WARP;
+        unsigned char* scr_mine = scr + lane * QKV_SCRATCH_PITCH;
+        const int m_w0 = m - lane;                     // the warp's first token
+        bf16* outb = reinterpret_cast<bf16*>(out);
 #pragma unroll 1
         for (int hb = 0; hb < PN / 2 && n0 + hb < N; hb += hd) {
           const int head = (n0 + hb) / hd;
-          bf16* dst = reinterpret_cast<bf16*>(out) + (size_t)mm * ldo + n0 + hb;
           if (head >= qkv.nh + qkv.nkv) {             // a v head: bias, to `out` and to the cache
-            bf16* page = qkv.vpages + (slot * qkv.nkv + (head - qkv.nh - qkv.nkv)) * hd;
+            const int vh = head - qkv.nh - qkv.nkv;
 #pragma unroll 1
             for (int j = 0; j < hd; j += 16) {
               float v[16];
@@ -320,25 +353,52 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
 #pragma unroll
                 for (int u = 0; u < 16; ++u) v[u] += bias_t[hb + j + u];
               }
-              if (row_ok) store16_bf16(dst + j, v);
-              if (cache_ok) store16_bf16(page + j, v);
+              store16_bf16(reinterpret_cast<bf16*>(scr_mine), v);
+              __syncwarp();
+              // two threads a token: 16 tokens x 32 bytes an instruction
+#pragma unroll
+              for (int i = 0; i < 2; ++i) {
+                const int row = 16 * i + (lane >> 1), mr = m_w0 + row, col = j + 8 * (lane & 1);
+                const uint4 piece = *reinterpret_cast<const uint4*>(scr + row * QKV_SCRATCH_PITCH +
+                                                                    (lane & 1) * 16);
+                if (mr < M) {
+                  *reinterpret_cast<uint4*>(outb + (size_t)mr * ldo + n0 + hb + col) = piece;
+                  if (slot_v[i] >= 0)
+                    *reinterpret_cast<uint4*>(qkv.vpages +
+                                              ((size_t)slot_v[i] * qkv.nkv + vh) * hd + col) = piece;
+                }
+              }
             }
           } else {                                    // a q or k head: bias, round, rotate
-            bf16* page = head >= qkv.nh ? qkv.kpages + (slot * qkv.nkv + (head - qkv.nh)) * hd
-                                        : nullptr;
+            const bool k_head = head >= qkv.nh;
 #pragma unroll 1
             for (int j = 0; j < hh; j += 16) {
+              // (cos and sin of this chunk were asked for a chunk ago, or before the accumulator
+              // was waited for)
               float a[16], b[16];
               __syncwarp();
-              tmem_ld16(taddr + hb + j, a);
-              tmem_ld16(taddr + hb + hh + j, b);
-              float cc[16], ss[16];                    // rows of the table are 16-byte aligned
+              tmem_ld16_async(taddr + hb + j, a);
+              tmem_ld16_async(taddr + hb + hh + j, b);
+              tmem_ld_wait();
+              float cc[16], ss[16];
 #pragma unroll
-              for (int u = 0; u < 16; u += 4) {
-                *reinterpret_cast<float4*>(cc + u) = *reinterpret_cast<const float4*>(cs + j + u);
-                *reinterpret_cast<float4*>(ss + u) =
-                    *reinterpret_cast<const float4*>(cs + hh + j + u);
-              }
+              for (int i = 0; i < 4; ++i)
+                *reinterpret_cast<float4*>(scr + (8 * i + rr) * QKV_SCRATCH_PITCH + pc * 16) = tc[i];
+              __syncwarp();
+#pragma unroll
+              for (int u = 0; u < 16; u += 4)
+                *reinterpret_cast<float4*>(cc + u) = *reinterpret_cast<const float4*>(scr_mine + u * 4);
+              __syncwarp();
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                *reinterpret_cast<float4*>(scr + (8 * i + rr) * QKV_SCRATCH_PITCH + pc * 16) = ts[i];
+              __syncwarp();
+#pragma unroll
+              for (int u = 0; u < 16; u += 4)
+                *reinterpret_cast<float4*>(ss + u) = *reinterpret_cast<const float4*>(scr_mine + u * 4);
+              __syncwarp();
+              // the next chunk's, or (the table is the same for every head) the next head's first
+              load_table(j + 16 < hh ? j + 16 : 0);
 #pragma unroll
               for (int u = 0; u < 16; ++u) {
                 const float x = round_bf16(a[u] + (bias ? bias_t[hb + j + u] : 0.f));
@@ -346,12 +406,22 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
                 a[u] = x * cc[u] - y * ss[u];
                 b[u] = x * ss[u] + y * cc[u];
               }
-              if (row_ok) {
-                store16_bf16(dst + j, a);
-                store16_bf16(dst + hh + j, b);
-                if (page && cache_ok) {
-                  store16_bf16(page + j, a);
-                  store16_bf16(page + hh + j, b);
+              // this token's 16 + 16 results as 64 bytes of its scratch row, then four threads a
+              // token: pieces 0, 1 are channels j .. j + 15, pieces 2, 3 channels hh + j .. + 15
+              store16_bf16(reinterpret_cast<bf16*>(scr_mine), a);
+              store16_bf16(reinterpret_cast<bf16*>(scr_mine) + 16, b);
+              __syncwarp();
+              const int col = pc < 2 ? j + 8 * pc : hh + j + 8 * (pc - 2);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int row = 8 * i + rr, mr = m_w0 + row;
+                const uint4 piece =
+                    *reinterpret_cast<const uint4*>(scr + row * QKV_SCRATCH_PITCH + pc * 16);
+                if (mr < M) {
+                  *reinterpret_cast<uint4*>(outb + (size_t)mr * ldo + n0 + hb + col) = piece;
+                  if (k_head && slot_t[i] >= 0)
+                    *reinterpret_cast<uint4*>(qkv.kpages + ((size_t)slot_t[i] * qkv.nkv +
+                                                            (head - qkv.nh)) * hd + col) = piece;
                 }
               }
             }
@@ -441,7 +511,8 @@ static int launch_prefill(const CUtensorMap& mx, const CUtensorMap& mw, const fl
                           const QkvArgs& qkv = QkvArgs{}) {
   constexpr int NST = PAIR ? PSTAGES_PAIR : PSTAGES;
   const size_t smem = 1024 + (size_t)NST * (PA_BYTES + (PAIR ? PB_BYTES_PAIR : PB_BYTES)) +
-                      (2 * NST + 4) * sizeof(uint64_t) + 16 + 2 * PN * sizeof(float);
+                      (2 * NST + 4) * sizeof(uint64_t) + 16 + 2 * PN * sizeof(float) +
+                      (EPI == PEPI_QKV ? EPI_WARPS * QKV_SCRATCH_WARP : 0);
   auto k = gemm_prefill_kernel<EPI, OUT, PAIR>;
   static OncePerDevice attrs;                        // (of this instantiation of the launcher)
   if (int rc = attrs.run([&] {
