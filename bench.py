@@ -259,7 +259,8 @@ def prefill_timed(eng, tokens: int, reps: int, warmup: int, seed: int):
 
 
 # ----------------------------------------------------------------------------- small workloads
-MICRO = ("gemm_gateup_m8", "gemm_down_m8", "gemm_lmhead_m8", "gemm_gateup_m2048", "attn_decode_b8",
+MICRO = ("gemm_gateup_m8", "gemm_down_m8", "gemm_lmhead_m8", "gemm_gateup_m2048", "gemm_qkv_m2048",
+         "attn_decode_b8",
          "attn_decode_b64", "attn_decode_b1_ctx32768", "prefill_2layers")
 
 
@@ -283,6 +284,25 @@ def run_micro(name: str) -> int:
         ws = [(torch.randn(2 * I, H, device=dev) * 0.05).to(torch.bfloat16) for _ in range(3)]
         for i in range(6):
             y = gemm_prefill.gemm(x, ws[i % 3], None, torch.bfloat16, epi=2)
+        torch.cuda.synchronize()
+        gemm_bf16.check_errors()
+        print(json.dumps({"micro": name, "out": list(y.shape)}))
+        return 0
+    if name == "gemm_qkv_m2048":
+        # the joined q/k/v product of a 2,048-token prompt: bias, rotation and cache write in its
+        # epilogue
+        from ginfer_b200.ops import gemm_prefill
+        T, N = PREFILL_TOKENS, (nh + 2 * nkv) * hd
+        x = torch.randn(T, H, device=dev).to(torch.bfloat16)
+        ws = [(torch.randn(N, H, device=dev) * 0.05).to(torch.bfloat16) for _ in range(3)]
+        bias = torch.randn(N, device=dev)
+        table = torch.randn(CONTEXT, hd, device=dev)
+        pos = torch.arange(T, dtype=torch.int32, device=dev)
+        slots = torch.randperm(2 * T, device=dev)[:T].to(torch.int32)
+        pages = torch.zeros(2, 2 * T // PAGE + 1, PAGE, nkv, hd, dtype=torch.bfloat16, device=dev)
+        for i in range(6):
+            y = gemm_prefill.qkv_rope_write(x, ws[i % 3], bias, table, hd, pos, slots, pages, nh,
+                                            nkv, hd)
         torch.cuda.synchronize()
         gemm_bf16.check_errors()
         print(json.dumps({"micro": name, "out": list(y.shape)}))

@@ -102,8 +102,12 @@ __host__ __device__ constexpr uint32_t umma_idesc_pair(int bn) {
 constexpr int PEPI_STORE = 0;                 // out[m, n] = acc (+ bias[n])
 constexpr int PEPI_GATED = 2;                 // out[m, n / 2] = silu(acc[m, n]) * acc[m, n + 1], n even
 constexpr int PEPI_QKV = 3;                   // + bias, q and k heads rotated, k and v to the cache
-constexpr int QKV_SCRATCH_PITCH = 80;         // bytes between a warp's scratch rows (64 used)
-constexpr int QKV_SCRATCH_WARP = 32 * QKV_SCRATCH_PITCH;
+// A warp's scratch: 32 rows of 64 bytes; the 16-byte pieces of a row are swapped by bits 1 and 2 of
+// the row, so that neither a thread a row nor four threads a row meet a bank twice in one access.
+constexpr int QKV_SCRATCH_WARP = 32 * 64;
+__device__ __forceinline__ int scr_at(int row, int piece) {
+  return row * 64 + ((piece ^ ((row >> 1) & 3)) << 4);
+}
 
 // What the q/k/v epilogue needs beside the product: rows [q heads | k heads | v heads] of `hd`
 // channels; q and k are rotated by the angles of the token's position (table row: cos | sin over
@@ -130,6 +134,14 @@ __device__ __forceinline__ void store16_bf16(bf16* dst, const float (&v)[16]) {
     for (int u = 0; u < 4; ++u) p[u] = __floats2bfloat162_rn(v[j + 2 * u], v[j + 2 * u + 1]);
     *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<const uint4*>(p);
   }
+}
+
+// eight of sixteen values, from `first`, as 16 bytes of bf16
+__device__ __forceinline__ void store8_bf16(void* dst, const float (&v)[16], int first) {
+  __nv_bfloat162 p[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) p[u] = __floats2bfloat162_rn(v[first + 2 * u], v[first + 2 * u + 1]);
+  *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(p);
 }
 
 template <int EPI, typename OUT, bool PAIR = false>
@@ -336,7 +348,6 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
         // and the warp's scratch in shared memory turns one lay-out into the other.
         const int hd = qkv.hd, hh = hd >> 1;
         unsigned char* scr = scratch_s + (size_t)e * QKV_SCRATCH_WARP;
-        unsigned char* scr_mine = scr + lane * QKV_SCRATCH_PITCH;
         const int m_w0 = m - lane;                     // the warp's first token
         bf16* outb = reinterpret_cast<bf16*>(out);
 #pragma unroll 1
@@ -353,14 +364,17 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
 #pragma unroll
                 for (int u = 0; u < 16; ++u) v[u] += bias_t[hb + j + u];
               }
-              store16_bf16(reinterpret_cast<bf16*>(scr_mine), v);
+              // (a row's two pieces go to its first or second half by bit 1 of the row: with two
+              // threads a row, four rows are read at once)
+              store8_bf16(scr + scr_at(lane, (lane & 2) + 0), v, 0);
+              store8_bf16(scr + scr_at(lane, (lane & 2) + 1), v, 8);
               __syncwarp();
               // two threads a token: 16 tokens x 32 bytes an instruction
 #pragma unroll
               for (int i = 0; i < 2; ++i) {
                 const int row = 16 * i + (lane >> 1), mr = m_w0 + row, col = j + 8 * (lane & 1);
-                const uint4 piece = *reinterpret_cast<const uint4*>(scr + row * QKV_SCRATCH_PITCH +
-                                                                    (lane & 1) * 16);
+                const uint4 piece =
+                    *reinterpret_cast<const uint4*>(scr + scr_at(row, (row & 2) + (lane & 1)));
                 if (mr < M) {
                   *reinterpret_cast<uint4*>(outb + (size_t)mr * ldo + n0 + hb + col) = piece;
                   if (slot_v[i] >= 0)
@@ -383,19 +397,21 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
               float cc[16], ss[16];
 #pragma unroll
               for (int i = 0; i < 4; ++i)
-                *reinterpret_cast<float4*>(scr + (8 * i + rr) * QKV_SCRATCH_PITCH + pc * 16) = tc[i];
+                *reinterpret_cast<float4*>(scr + scr_at(8 * i + rr, pc)) = tc[i];
               __syncwarp();
 #pragma unroll
-              for (int u = 0; u < 16; u += 4)
-                *reinterpret_cast<float4*>(cc + u) = *reinterpret_cast<const float4*>(scr_mine + u * 4);
+              for (int u = 0; u < 4; ++u)
+                *reinterpret_cast<float4*>(cc + 4 * u) =
+                    *reinterpret_cast<const float4*>(scr + scr_at(lane, u));
               __syncwarp();
 #pragma unroll
               for (int i = 0; i < 4; ++i)
-                *reinterpret_cast<float4*>(scr + (8 * i + rr) * QKV_SCRATCH_PITCH + pc * 16) = ts[i];
+                *reinterpret_cast<float4*>(scr + scr_at(8 * i + rr, pc)) = ts[i];
               __syncwarp();
 #pragma unroll
-              for (int u = 0; u < 16; u += 4)
-                *reinterpret_cast<float4*>(ss + u) = *reinterpret_cast<const float4*>(scr_mine + u * 4);
+              for (int u = 0; u < 4; ++u)
+                *reinterpret_cast<float4*>(ss + 4 * u) =
+                    *reinterpret_cast<const float4*>(scr + scr_at(lane, u));
               __syncwarp();
               // the next chunk's, or (the table is the same for every head) the next head's first
               load_table(j + 16 < hh ? j + 16 : 0);
@@ -408,15 +424,16 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
               }
               // this token's 16 + 16 results as 64 bytes of its scratch row, then four threads a
               // token: pieces 0, 1 are channels j .. j + 15, pieces 2, 3 channels hh + j .. + 15
-              store16_bf16(reinterpret_cast<bf16*>(scr_mine), a);
-              store16_bf16(reinterpret_cast<bf16*>(scr_mine) + 16, b);
+              store8_bf16(scr + scr_at(lane, 0), a, 0);
+              store8_bf16(scr + scr_at(lane, 1), a, 8);
+              store8_bf16(scr + scr_at(lane, 2), b, 0);
+              store8_bf16(scr + scr_at(lane, 3), b, 8);
               __syncwarp();
               const int col = pc < 2 ? j + 8 * pc : hh + j + 8 * (pc - 2);
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
                 const int row = 8 * i + rr, mr = m_w0 + row;
-                const uint4 piece =
-                    *reinterpret_cast<const uint4*>(scr + row * QKV_SCRATCH_PITCH + pc * 16);
+                const uint4 piece = *reinterpret_cast<const uint4*>(scr + scr_at(row, pc));
                 if (mr < M) {
                   *reinterpret_cast<uint4*>(outb + (size_t)mr * ldo + n0 + hb + col) = piece;
                   if (k_head && slot_t[i] >= 0)
