@@ -302,7 +302,7 @@ def run_micro(name: str) -> int:
         pages = torch.zeros(2, 2 * T // PAGE + 1, PAGE, nkv, hd, dtype=torch.bfloat16, device=dev)
         for i in range(6):
             y = gemm_prefill.qkv_rope_write(x, ws[i % 3], bias, table, hd, pos, slots, pages, nh,
-                                            nkv, hd)
+                                            nkv, hd, min_tokens=1)
         torch.cuda.synchronize()
         gemm_bf16.check_errors()
         print(json.dumps({"micro": name, "out": list(y.shape)}))

@@ -50,9 +50,17 @@ def gemm(x, weight, bias_f32=None, out_dtype=torch.bfloat16, epi: int = 0, ctas:
     return out
 
 
-QKV_MIN_TOKENS = 1024     # below this cuBLAS and the rotation kernel behind it are the faster pair
-# GINFER_B200_QKV_EPILOGUE=0 keeps the plain product and the rotation kernel at every size
-QKV_EPILOGUE = os.environ.get("GINFER_B200_QKV_EPILOGUE", "1") != "0"
+# The joined q/k/v product with the rotation and the cache write in its epilogue is an option
+# (GINFER_B200_QKV_EPILOGUE=1, then from QKV_MIN_TOKENS tokens on), not the default: cuBLAS with the
+# rotation kernel behind it is the faster pair.  On a B200, in a prompt step of 4 layers and the head
+# from a CUDA graph (us, epilogue / cuBLAS + rotation kernel): 1.5B shape 1,024 tokens 793 / 759,
+# 1,536 tokens 909 / 887, 2,048 tokens 1,092 / 1,083, 4,096 tokens 1,914 / 1,895; 7B shape 1,024 tokens
+# 1,960 / 1,942, 2,048 tokens 3,373 / 3,381, 4,096 tokens 6,623 / 6,575; the whole step of 2,048 tokens
+# at the 1.5B shape 5.70 / 5.65 ms.  Alone at 2,048 tokens the kernel takes 19.3 us against 11.7 + 4.6:
+# its 128 tiles are one round for 148 CTAs, so its epilogue hides behind nothing, and where it has
+# several rounds its products are behind cuBLAS's (44 against 37.5 us at 8,192 tokens).
+QKV_MIN_TOKENS = 1024
+QKV_EPILOGUE = os.environ.get("GINFER_B200_QKV_EPILOGUE", "0") != "0"
 
 
 def qkv_epilogue_serves(x, weight, table, rot, positions, slot_mapping, pages, nh, nkv, hd,

@@ -473,7 +473,8 @@ def test_the_q_k_v_epilogue_is_only_offered_what_it_takes():
                        pages=torch.zeros(2, 4, 16, 4, 32, dtype=torch.bfloat16))
     assert not offered(weight=w[:-hd]) and not offered(weight=w.float())    # rows that are no heads
     with pytest.raises(RuntimeError, match="CUDA device only"):
-        gemm_prefill.qkv_rope_write(x, w, None, table, hd, pos, pos, pages, nh, nkv, hd)
+        gemm_prefill.qkv_rope_write(x, w, None, table, hd, pos, pos, pages, nh, nkv, hd,
+                                    min_tokens=1)
     with pytest.raises(RuntimeError, match="CUDA device only"):
         gemm_prefill.gemm(x, w)
 

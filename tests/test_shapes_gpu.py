@@ -99,8 +99,8 @@ def test_bfloat16_path_agrees_with_the_32_bit_path_at_large_layer_sizes(name):
 @pytest.mark.parametrize("head_dim,heads,kv_heads", [(64, 6, 2), (128, 3, 1)])
 def test_a_step_of_many_tokens_agrees_with_portions_plain_and_the_32_bit_path(
         tmp_path, head_dim, heads, kv_heads, monkeypatch):
-    """From 1,024 tokens on a step's joined q/k/v product rotates q and k and writes the cache in
-    its own epilogue (and the gated product joins SiLU*mul).  The same prompt in one step, as a
+    """Where it is switched on, from 1,024 tokens on a step's joined q/k/v product rotates q and k
+    and writes the cache in its own epilogue (and the gated product joins SiLU*mul).  The same prompt in one step, as a
     short portion followed by one of 1,030 tokens (the epilogue then works at positions and cache
     slots offset from its rows), in two portions below that size (plain products, the rotation
     kernel) and on the 32-bit path must give the same logits, for the prompt's last token and for
@@ -118,6 +118,8 @@ def test_a_step_of_many_tokens_agrees_with_portions_plain_and_the_32_bit_path(
                     config=cfg)
     toks = prompt(1100, 643, 5)
     tail = prompt(3, 643, 6)
+    from ginfer_b200.ops import gemm_prefill
+    monkeypatch.setattr(gemm_prefill, "QKV_EPILOGUE", True)      # (an option: off by default)
     served = []
     inner = ops.qkv_rope_write
 
