@@ -159,14 +159,16 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
   uint64_t* empty = full + NST;
   uint64_t* acc_full = empty + NST;           // [2]
   uint64_t* acc_empty = acc_full + 2;         // [2]
-  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+  uint64_t* bias_ready = acc_empty + 2;       // the epilogue threads have staged a tile's bias
+  uint32_t* tmem_slot = (uint32_t*)(bias_ready + 1);
   // the bias of a tile's PN columns, for the tile in either accumulator: with nearly all of the
   // SM's memory carved out as shared memory, a bias read from global memory in the epilogue's
   // inner loop goes to L2 every time
   float* bias_s = (float*)(tmem_slot + 4);    // [2][PN]
   // the q/k/v epilogue's scratch: 32 rows of 64 bytes (80 apart) for each epilogue warp, through
   // which it turns "a thread a token" into "four threads a token" and back (see there)
-  unsigned char* scratch_s = (unsigned char*)(bias_s + 2 * PN);
+  unsigned char* scratch_s =
+      (unsigned char*)(((uintptr_t)(bias_s + 2 * PN) + 15) & ~(uintptr_t)15);   // 16-byte pieces
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // a pair: the cluster walks over tiles of 2 * PM tokens, this CTA has rows rank * PM .. of them
@@ -188,6 +190,7 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
       mbar_init(acc_full + b, 1);
       mbar_init(acc_empty + b, (PAIR ? 2 : 1) * EPI_WARPS * 32);   // both CTAs' epilogue threads
     }
+    mbar_init(bias_ready, EPI_WARPS * 32);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_x) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_w) : "memory");
@@ -307,8 +310,11 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
         const int tn0 = (tile / m_tiles) * PN;
         for (int i = e * 32 + lane; i < PN; i += EPI_WARPS * 32)
           bias_s[buf * PN + i] = tn0 + i < N ? bias[tn0 + i] : 0.f;
-        // the epilogue warps; they are at most a tile apart, and the tiles alternate buffers
-        asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
+        // every epilogue thread has written its part (a bounded wait like the others: a warp
+        // that gave up does not leave the rest at a barrier); the warps are then at most a tile
+        // apart, and the tiles alternate buffers
+        mbar_arrive(bias_ready);
+        if (!mbar_wait(bias_ready, (uint32_t)t & 1u, err, 3)) break;
       }
       // q/k/v: what the epilogue reads beside the accumulator is asked for before the wait for it
       const int rr = lane >> 2, pc = lane & 3;         // four threads a token: token rr (+ 8 i), piece pc
@@ -528,7 +534,7 @@ static int launch_prefill(const CUtensorMap& mx, const CUtensorMap& mw, const fl
                           const QkvArgs& qkv = QkvArgs{}) {
   constexpr int NST = PAIR ? PSTAGES_PAIR : PSTAGES;
   const size_t smem = 1024 + (size_t)NST * (PA_BYTES + (PAIR ? PB_BYTES_PAIR : PB_BYTES)) +
-                      (2 * NST + 4) * sizeof(uint64_t) + 16 + 2 * PN * sizeof(float) +
+                      (2 * NST + 5) * sizeof(uint64_t) + 32 + 2 * PN * sizeof(float) +
                       (EPI == PEPI_QKV ? EPI_WARPS * QKV_SCRATCH_WARP : 0);
   auto k = gemm_prefill_kernel<EPI, OUT, PAIR>;
   static OncePerDevice attrs;                        // (of this instantiation of the launcher)
