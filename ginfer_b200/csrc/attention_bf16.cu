@@ -468,7 +468,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap,
   unsigned char* ring = smem_raw;                               // [nst][K tile | V tile]
   uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw + (size_t)nst * STAGE_BYTES);
   uint64_t* empty = full + TMAX_STAGES;
-  int* stbl = reinterpret_cast<int*>(full + 2 * TMAX_STAGES);
+  uint64_t* patched = full + 2 * TMAX_STAGES;                   // the new key and value are in their tile
+  int* stbl = reinterpret_cast<int*>(full + 2 * TMAX_STAGES + 1);
   bf16* qs = reinterpret_cast<bf16*>(stbl + tbl_cap);           // [8][HD] rotated q, then new k, v
   bf16* knew = qs + 8 * HD;
   bf16* vnew = knew + HD;
@@ -492,6 +493,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap,
       mbar_init(&full[i], 1);
       mbar_init(&empty[i], 4);                                  // one arrival per consumer warp
     }
+    mbar_init(patched, NTHREADS);                               // the consumer threads
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&kmap) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&vmap) : "memory");
@@ -651,7 +653,9 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap,
           *reinterpret_cast<bf16*>(kt + off) = knew[j];
           *reinterpret_cast<bf16*>(vt + off) = vnew[j];
         }
-        consumer_sync();
+        // (a wait with a limit, like the one above: a warp that gave up there is not waited for)
+        mbar_arrive(patched);
+        if (!mbar_wait(patched, 0u, err, 4)) break;
       }
       const int col0 = begin + it * KT + warp * 16;
       if (col0 < end && col0 + 16 > first) {
@@ -1124,7 +1128,7 @@ GF_EXPORT int gf_attn_decode_tma(const void* q, int q_row_stride, void* kpages, 
   auto st = (cudaStream_t)stream;
   const int G = nh / nkv, chunks = (G + 7) / 8;
   const int tbl_cap = table_stride < kMaxTableCopyTma ? table_stride : kMaxTableCopyTma;
-  const size_t small = 2 * TMAX_STAGES * sizeof(uint64_t) + (size_t)10 * HD * sizeof(bf16);
+  const size_t small = (2 * TMAX_STAGES + 1) * sizeof(uint64_t) + (size_t)10 * HD * sizeof(bf16);
   const size_t room = (size_t)227 * 1024 - small - kMaxTableCopyTma * sizeof(int);
   const int most = (int)(room / STAGE_BYTES) < TMAX_STAGES ? (int)(room / STAGE_BYTES) : TMAX_STAGES;
   const int nst = stages < 2 ? 2 : stages > most ? most : stages;
