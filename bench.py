@@ -484,6 +484,8 @@ def run_scenario(name: str, shape: str, layers: int | None) -> int:
                      max_num_batched_tokens=16384, kvcache_block_size=PAGE,
                      num_kvcache_blocks=256 * (640 // PAGE + 2))
     else:
+        # (prompts of 8,192 tokens: the position table has to reach that far)
+        cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], 16384)
         prompts = ([[rng.randrange(V) for _ in range(32)] for _ in range(32)] +
                    [[rng.randrange(V) for _ in range(8192)] for _ in range(8)])
         params = ([SamplingParams(max_tokens=256, ignore_eos=True)] * 32 +
