@@ -57,8 +57,8 @@ def gemm(x, weight, bias_f32=None, out_dtype=torch.bfloat16, epi: int = 0, ctas:
 # 1,536 tokens 909 / 887, 2,048 tokens 1,092 / 1,083, 4,096 tokens 1,914 / 1,895; 7B shape 1,024 tokens
 # 1,960 / 1,942, 2,048 tokens 3,373 / 3,381, 4,096 tokens 6,623 / 6,575; the whole step of 2,048 tokens
 # at the 1.5B shape 5.70 / 5.65 ms, a 32,768-token prompt in portions 216 / 214 ms, the reference's
-# throughput run level; only the serving run of 64 mixed requests, whose steps are launched one kernel
-# at a time, is faster with it (0.676 / 0.686 s).  Alone at 2,048 tokens the kernel takes 19.3 us against 11.7 + 4.6:
+# throughput run level; only the serving run of 64 requests, whose steps mix portions of prompts
+# with decoded tokens, is faster with it (0.676 / 0.686 s).  Alone at 2,048 tokens the kernel takes 19.3 us against 11.7 + 4.6:
 # its 128 tiles are one round for 148 CTAs, so its epilogue hides behind nothing, and where it has
 # several rounds its products are behind cuBLAS's (44 against 37.5 us at 8,192 tokens).
 QKV_MIN_TOKENS = 1024
