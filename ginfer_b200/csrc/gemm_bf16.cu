@@ -20,12 +20,18 @@
 // multiplies its accumulator by 1 / rms[token] = rsqrt(sum of the partials / K + eps) (`in_sumsq`;
 // every epilogue takes it), since (s gamma / rms) W^T = (s gamma) W^T / rms.
 // Products whose tiles alone would leave most SMs idle (the small-N products of a decode step) split
-// the K range, deterministically, in one of two ways.  Cluster mode (split_k 2, 4 or 8): the splits
-// of a tile form a thread-block cluster, park their fp32 partial tiles in their own shared memory,
-// and after a cluster barrier each CTA sums a band of rows over all peers through distributed
-// shared memory, in rank order, and runs the epilogue for it.  Workspace mode (any split_k): the
-// partials go to global memory and the split that finishes a tile last (counted with an atomic it
-// resets) sums them in split order.
+// the K range, deterministically, in one of two ways.  Cluster mode (split_k 2, 4, 8 or 12): the
+// splits of a tile form a thread-block cluster and each CTA sums a band of the tile's rows over all
+// peers, in rank order, and runs the epilogue for it.  Where a split's K range leaves stages of the
+// ring unused (the q/k/v and output products of decode steps) the partials are pushed: every thread
+// sends its row's partial sums into the band owner's shared memory (st.async, counted by the
+// owner's mbarrier), the owner waits for the bytes, and nobody waits for a barrier of the cluster
+// after the set-up; in a decode step of 4 layers at the 1.5B shape 258.4 us against 260.4.
+// Otherwise they are pulled: every CTA parks its partial tile in its own shared memory, and after
+// a cluster barrier the owners read their bands through distributed shared memory (and a second
+// barrier keeps everyone until the reads are done).  Workspace mode (any split_k): the partials
+// go to global memory and the split that finishes a tile last (counted with an atomic it resets)
+// sums them in split order.
 //
 // The reference calls cuBLASLt for every product (ginfer/core/op/kernels/cuda/gemm_kernel/
 // gemm_kernel.cu:93-156, bias in the epilogue :112-121, fp32 compute :100) and has a separate
@@ -66,6 +72,7 @@ __device__ unsigned int g_tile_done[kMaxTiles];
 constexpr unsigned int kStampCap = 1 << 15;
 __device__ unsigned long long g_stamps[kStampCap * 8];
 __device__ unsigned int g_stamp_next;
+__shared__ unsigned int stamp_slot;
 __device__ __forceinline__ unsigned long long gtime() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -180,8 +187,21 @@ __device__ __forceinline__ void store4(bf16* p, const float (&v)[4]) {
   *reinterpret_cast<uint2*>(p) = w;
 }
 
-template <int BN, int EPI, typename OUT, int SPLIT>
-__device__ __forceinline__ void cluster_reduce(uint32_t red, const float* __restrict__ bias,
+// Where the partial of (chunk of 16 tokens, split `src`, row of the band, token) lies in a band
+// owner's receive area, in floats.  A sender writes four tokens at a time; the pieces of a row are
+// swapped by the row's quad so that readers of one token in neighbouring quads meet no bank twice.
+__device__ __forceinline__ int recv_at(int chunk, int src, int row, int tok16, int split, int band) {
+  return ((chunk * split + src) * band + row) * 16 + ((((tok16 >> 2) ^ (row >> 2)) & 3) << 2) +
+         (tok16 & 3);
+}
+
+// PUSH = false: `red` is the parked tile's address (see above), the peers are read after the
+// cluster's barrier, all NTHREADS threads work.  PUSH = true: the peers have sent their rows of
+// this CTA's band into `recv` (recv_at), counted by `recv_bar`; the 128 epilogue threads wait
+// for it and work, and nothing of a peer is touched.
+template <int BN, int EPI, typename OUT, int SPLIT, bool PUSH>
+__device__ __forceinline__ void cluster_reduce(uint32_t red, const float* recv, uint64_t* recv_bar,
+                                               int* err, const float* __restrict__ bias,
                                                OUT* __restrict__ out, int ldo, int M, int N,
                                                int n0, int m0, const float* scale,
                                                const GemmExtra& ex, float* sqs) {
@@ -189,29 +209,52 @@ __device__ __forceinline__ void cluster_reduce(uint32_t red, const float* __rest
   constexpr int band = Band<SPLIT>::rows;
   constexpr int QUADS = band / 4;                     // a unit of work: four rows of one token
   constexpr int UNITS = QUADS * BN;
+  constexpr int GROUP = PUSH ? 128 : NTHREADS;
+  const int uid = PUSH ? (int)threadIdx.x - 64 : (int)threadIdx.x;
   const bool active = rank * band < BM;
   // vector stores need four rows that exist and an aligned row of the output
   const bool vec = (ldo & 3) == 0 && (N & 3) == 0;
   // EPI_RESID: the residual of this thread's first unit (the only one when the band's units are
-  // no more than the threads, as in decode steps) is asked for before the cluster meets
+  // no more than the threads, as in decode steps) is asked for before the partials are waited for
   float rs0[4] = {0.f, 0.f, 0.f, 0.f};
-  if (EPI == EPI_RESID && active && threadIdx.x < UNITS) {
-    const int tok = threadIdx.x / QUADS, n = n0 + rank * band + (threadIdx.x % QUADS) * 4;
+  if (EPI == EPI_RESID && active && uid < UNITS) {
+    const int tok = uid / QUADS, n = n0 + rank * band + (uid % QUADS) * 4;
     const float* src = ex.resid + (size_t)min(m0 + tok, M - 1) * ldo;
 #pragma unroll
     for (int j = 0; j < 4; ++j) rs0[j] = __ldcg(src + min(n + j, N - 1));
   }
-  cluster_sync();                                     // every peer's partial tile is parked
-  if (active) {
-    for (int u = threadIdx.x; u < UNITS; u += NTHREADS) {
-      const int tok = u / QUADS, row = rank * band + (u % QUADS) * 4;
+  // the bias of the first unit likewise: it may come from memory, and nothing it waits for
+  float b0[4] = {0.f, 0.f, 0.f, 0.f};
+  if (EPI != EPI_SILU && bias && active && uid < UNITS) {
+    const int n = n0 + rank * band + (uid % QUADS) * 4;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) b0[j] = __ldg(bias + min(n + j, N - 1));
+  }
+  bool have = true;
+  if (PUSH) {
+    if (active) have = mbar_wait(recv_bar, 0, err, 3);
+  } else {
+    cluster_sync();                                   // every peer's partial tile is parked
+  }
+  if (active && have) {
+    for (int u = uid; u < UNITS; u += GROUP) {
+      const int tok = u / QUADS, brow = (u % QUADS) * 4, row = rank * band + brow;
       const int n = n0 + row, m = m0 + tok;
       float hh = 0.f;
       if (m < M && n < N) {
         float4 t[SPLIT];
+        if (PUSH) {
+          const float* src = recv + recv_at(tok >> 4, 0, brow, tok & 15, SPLIT, band);
 #pragma unroll
-        for (int p = 0; p < SPLIT; ++p)
-          t[p] = ld_dsmem_f4(red + (uint32_t)((tok * RED_LD + row) * 4), p);
+          for (int p = 0; p < SPLIT; ++p) {
+            const float* q = src + p * band * 16;
+            t[p] = make_float4(q[0], q[16], q[32], q[48]);
+          }
+        } else {
+#pragma unroll
+          for (int p = 0; p < SPLIT; ++p)
+            t[p] = ld_dsmem_f4(red + (uint32_t)((tok * RED_LD + row) * 4), p);
+        }
         float4 a4 = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int p = 0; p < SPLIT; ++p)
@@ -230,13 +273,18 @@ __device__ __forceinline__ void cluster_reduce(uint32_t red, const float* __rest
           if (n + 3 < N) store_out<OUT>(dst + 1, r1);
         } else {
           if (bias) {
+            if (u < GROUP) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] += bias[min(n + j, N - 1)];
+              for (int j = 0; j < 4; ++j) v[j] += b0[j];
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) v[j] += bias[min(n + j, N - 1)];
+            }
           }
           const size_t at = (size_t)m * ldo + n;
           if (EPI == EPI_RESID) {
             float rs[4] = {rs0[0], rs0[1], rs0[2], rs0[3]};
-            if (u >= NTHREADS) {
+            if (u >= GROUP) {
 #pragma unroll
               for (int j = 0; j < 4; ++j) rs[j] = __ldcg(ex.resid + (size_t)m * ldo + min(n + j, N - 1));
             }
@@ -275,10 +323,13 @@ __device__ __forceinline__ void cluster_reduce(uint32_t red, const float* __rest
     }
   }
   if (EPI == EPI_RESID) {
-    __syncthreads();
-    for (int tok = threadIdx.x; tok < BN; tok += NTHREADS) {
+    if (PUSH)
+      asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps
+    else
+      __syncthreads();
+    for (int tok = uid; tok < BN; tok += GROUP) {
       float sum = 0.f;
-      if (active)
+      if (active && have)
         for (int qd = 0; qd < QUADS; ++qd) sum += sqs[tok * QUADS + qd];
       if (m0 + tok < M)
         ex.out_sumsq[(size_t)(blockIdx.x * SPLIT + rank) * ex.ss_ld + m0 + tok] = sum;
@@ -286,8 +337,49 @@ __device__ __forceinline__ void cluster_reduce(uint32_t red, const float* __rest
   }
 }
 
-template <int BN, int EPI, typename OUT, bool CLUSTER>
-__global__ void __launch_bounds__(NTHREADS)
+template <int BN, int EPI, typename OUT>
+struct ReduceBySplit {
+  template <bool PUSH>
+  static __device__ __forceinline__ void run(int split_k, uint32_t red, const float* recv,
+                                             uint64_t* recv_bar, int* err, const float* bias,
+                                             OUT* out, int ldo, int M, int N, int n0, int m0,
+                                             const float* scale, const GemmExtra& ex, float* sqs) {
+    if (split_k == 2)
+      cluster_reduce<BN, EPI, OUT, 2, PUSH>(red, recv, recv_bar, err, bias, out, ldo, M, N, n0, m0,
+                                            scale, ex, sqs);
+    else if (split_k == 4)
+      cluster_reduce<BN, EPI, OUT, 4, PUSH>(red, recv, recv_bar, err, bias, out, ldo, M, N, n0, m0,
+                                            scale, ex, sqs);
+    else if (split_k == 8)
+      cluster_reduce<BN, EPI, OUT, 8, PUSH>(red, recv, recv_bar, err, bias, out, ldo, M, N, n0, m0,
+                                            scale, ex, sqs);
+    else
+      cluster_reduce<BN, EPI, OUT, 12, PUSH>(red, recv, recv_bar, err, bias, out, ldo, M, N, n0, m0,
+                                             scale, ex, sqs);
+  }
+};
+
+// Rows of a band of a cluster split at run time (Band<SPLIT>::rows).
+__host__ __device__ constexpr int band_rows(int split) {
+  return (BM / split + 15) / 16 * 16 < 16 ? 16 : (BM / split + 15) / 16 * 16;
+}
+// Bytes a band owner receives from its cluster (all splits, every chunk of 16 tokens of the tile).
+__host__ __device__ constexpr uint32_t recv_bytes(int bn, int split) {
+  return (uint32_t)(bn / 16) * split * band_rows(split) * 16 * 4;
+}
+
+// Whether a cluster split adds up in push mode: the stages that no split's K range reaches have
+// to hold the receive area (and the squares of an EPI_RESID band behind it).
+template <int BN, int EPI>
+__host__ __device__ constexpr bool push_fits(int K, int split_k) {
+  const int per = ((K + BK - 1) / BK + split_k - 1) / split_k;
+  const uint32_t stage = BM * BK * 2 + BN * BK * 2;
+  const uint32_t need = recv_bytes(BN, split_k) + (EPI == EPI_RESID ? 16u * BN * sizeof(float) : 0u);
+  return split_k > 1 && per + (int)((need + stage - 1) / stage) <= stages_for(BN);
+}
+
+template <int BN, int EPI, typename OUT, bool CLUSTER, bool PUSH = false>
+__global__ void __launch_bounds__(NTHREADS, 4)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                const float* __restrict__ bias, OUT* __restrict__ out, int ldo, int M, int N, int K,
                int split_k, float* __restrict__ workspace, int* __restrict__ err,
@@ -300,7 +392,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   uint64_t* full = (uint64_t*)(tiles + STAGES * (A_BYTES + B_BYTES));
   uint64_t* empty = full + STAGES;
   uint64_t* acc_full = empty + STAGES;
-  uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
+  uint64_t* recv_bar = acc_full + 1;                  // counts what the cluster's peers send here
+  uint32_t* tmem_slot = (uint32_t*)(recv_bar + 1);
   float* scale_s = (float*)(tmem_slot + 2);           // [BN] factors of a deferred normalisation
   float* sq_s = scale_s + BN;                         // [4][BN] squares per epilogue warp (EPI_RESID)
   __shared__ bool is_last;
@@ -318,10 +411,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   const int per = (nkb_all + split_k - 1) / split_k;
   const int kb0 = split * per, kb1 = min(nkb_all, kb0 + per);
   const int nkb = max(0, kb1 - kb0);
+  // Cluster split-K in push mode: the stages that no split's K range reaches take what the peers
+  // send.
+  constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr bool push = CLUSTER && PUSH;              // (the launcher asked push_fits)
+  float* recv = reinterpret_cast<float*>(tiles + (size_t)per * STAGE_BYTES);
 
   pdl_trigger();
 #ifdef GF_STAMPS
-  __shared__ unsigned int stamp_slot;
   if (threadIdx.x == 0) {
     stamp_slot = atomicAdd(&g_stamp_next, 1u) % kStampCap;
     unsigned int smid;
@@ -340,6 +437,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       mbar_init(empty + s, 1);
     }
     mbar_init(acc_full, 1);
+    mbar_init(recv_bar, 1);
+    if (push && (int)cluster_rank() * band_rows(split_k) < BM) {
+      const int live = min(BN, M - m0);
+      mbar_expect_tx(recv_bar, (uint32_t)((live + 15) / 16) * split_k * band_rows(split_k) * 64u);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_w) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_x) : "memory");
@@ -354,6 +456,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *tmem_slot;
+  // push mode: nobody sends before every CTA of the cluster has set its barrier up.  The producer
+  // asks for its weights first and waits afterwards.
+  if (push) {
+    cluster_arrive();
+    if (warp != 0) cluster_wait();
+  }
 
   if (warp == 0) {
     if (lane == 0) {
@@ -388,26 +496,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       }
       issued_s = issued;
     }
+    if (push) {
+      __syncwarp();
+      cluster_wait();
+    }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc(BN);
-      bool ok = true;
-      for (int i = 0; i < nkb && ok; ++i) {
-        const int s = i % STAGES;
-        ok = mbar_wait(full + s, (i / STAGES) & 1, err, 2);
-        if (!ok) {
-          gave_up = 1;
-          break;
-        }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a = smem_u32(tiles + s * (A_BYTES + B_BYTES));
-        const uint64_t ad = umma_desc(a), bd = umma_desc(a + A_BYTES);
+    // The whole warp walks through the K blocks; lane 0 issues the products.  The waits for the
+    // stages are made AHEAD stages at a time, each by a lane of its own (mbar_wait_lanes): one
+    // after the other they cost the issuing thread more than the products of a stage.
+    constexpr uint32_t idesc = umma_idesc(BN);
+#ifndef GF_MMA_AHEAD
+    constexpr int AHEAD = BN <= 64 ? (STAGES >= 6 ? 3 : 2) : 1;
+#else
+    constexpr int AHEAD = GF_MMA_AHEAD;
+#endif
+    bool ok = true;
+    for (int i0 = 0; i0 < nkb && ok; i0 += AHEAD) {
+      const int n = min(AHEAD, nkb - i0);
+      const int mine = i0 + min(lane, n - 1);
+      ok = mbar_wait_lanes(full + mine % STAGES, (uint32_t)(mine / STAGES) & 1u, lane < n, err, 2);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (lane == 0) {
+        for (int i = i0; i < i0 + n; ++i) {
+          const int s = i % STAGES;
+          const uint32_t a = smem_u32(tiles + s * (A_BYTES + B_BYTES));
+          const uint64_t ad = umma_desc(a), bd = umma_desc(a + A_BYTES);
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k)
-          umma(tmem, ad + (uint64_t)(k * UMMA_K * 2 >> 4), bd + (uint64_t)(k * UMMA_K * 2 >> 4),
-               idesc, (i > 0 || k > 0) ? 1u : 0u);
-        umma_commit(empty + s);            // the stage is free once these MMAs have read it
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma(tmem, ad + (uint64_t)(k * UMMA_K * 2 >> 4), bd + (uint64_t)(k * UMMA_K * 2 >> 4),
+                 idesc, (i > 0 || k > 0) ? 1u : 0u);
+          umma_commit(empty + s);          // the stage is free once these MMAs have read it
+        }
       }
+      __syncwarp();
+    }
+    if (lane == 0) {
+      if (!ok) gave_up = 1;
       umma_commit(acc_full);               // the accumulator is complete
     }
   } else {
@@ -487,6 +612,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             }
           }
         }
+      } else if (CLUSTER && push) {
+        // send every row's partial sums to the CTA that owns the row's band
+        const int band = band_rows(split_k), row = q * 32 + lane;
+        const uint32_t owner = (uint32_t)(row / band), me = cluster_rank();
+        const uint32_t bar = dsmem_addr(smem_u32(recv_bar), owner);
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+          if (m0 + c >= M) break;
+          float v[16];
+          if (nkb > 0) {
+            tmem_ld16(taddr + c, v);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = 0.f;
+          }
+#pragma unroll
+          for (int j = 0; j < 16; j += 4)
+            st_async_f4(dsmem_addr(smem_u32(recv + recv_at(c >> 4, (int)me, row % band, j, split_k,
+                                                           band)),
+                                   owner),
+                        v[j], v[j + 1], v[j + 2], v[j + 3], bar);
+        }
       } else if (CLUSTER) {
         // park this split's partial tile in shared memory (the ring is drained by now):
         // red[token][RED_LD], a warp's lanes writing neighbouring rows
@@ -525,6 +672,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         }
       }
     }
+    if (CLUSTER && push) {
+      // this CTA's band, summed over what the peers sent, in rank order
+      float* sqs = recv + recv_bytes(BN, split_k) / sizeof(float);
+      ReduceBySplit<BN, EPI, OUT>::template run<true>(split_k, 0u, recv, recv_bar, err, bias, out,
+                                                      ldo, M, N, n0, m0, scale, ex, sqs);
+      if (threadIdx.x == 64) GF_STAMP(6);
+    }
     if (EPI == EPI_RESID && split_k == 1) {
       // every epilogue warp arrives, also one whose wait ran out
       asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -554,8 +708,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                  "r"(TMEM_COLS)
                  : "memory");
   }
-  if (split_k == 1) {
-    if (threadIdx.x == 0) GF_STAMP(6);
+  if (split_k == 1 || push) {
+    if (threadIdx.x == 0) GF_STAMP(push ? 7 : 6);
     return;
   }
   const float* scale = ex.in_sumsq ? scale_s : nullptr;
@@ -566,14 +720,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     pdl_wait();
     const uint32_t red = smem_u32(tiles);
     float* sqs = reinterpret_cast<float*>(tiles) + (size_t)BN * RED_LD;    // behind the parked tile
-    if (split_k == 2)
-      cluster_reduce<BN, EPI, OUT, 2>(red, bias, out, ldo, M, N, n0, m0, scale, ex, sqs);
-    else if (split_k == 4)
-      cluster_reduce<BN, EPI, OUT, 4>(red, bias, out, ldo, M, N, n0, m0, scale, ex, sqs);
-    else if (split_k == 8)
-      cluster_reduce<BN, EPI, OUT, 8>(red, bias, out, ldo, M, N, n0, m0, scale, ex, sqs);
-    else
-      cluster_reduce<BN, EPI, OUT, 12>(red, bias, out, ldo, M, N, n0, m0, scale, ex, sqs);
+    ReduceBySplit<BN, EPI, OUT>::template run<false>(split_k, red, nullptr, nullptr, err, bias, out,
+                                                     ldo, M, N, n0, m0, scale, ex, sqs);
     if (threadIdx.x == 0) GF_STAMP(6);
     cluster_sync();                                   // nobody leaves while a peer still reads it
     if (threadIdx.x == 0) GF_STAMP(7);
@@ -618,7 +766,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   }
 }
 
-template <int BN, int EPI, typename OUT, bool CLUSTER>
+template <int BN, int EPI, typename OUT, bool CLUSTER, bool PUSH = false>
 static int launch_mode(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* out,
                        int ldo, int M, int N, int K, int split_k, float* workspace, int* err,
                        cudaStream_t st, const GemmExtra& ex) {
@@ -629,9 +777,9 @@ static int launch_mode(const CUtensorMap& mw, const CUtensorMap& mx, const float
   const size_t red = CLUSTER ? (size_t)BN * RED_LD * sizeof(float) +
                                    (EPI == EPI_RESID ? (size_t)16 * BN * sizeof(float) : 0)
                              : 0;
-  const size_t smem = 1024 + (ring > red ? ring : red) + (2 * STAGES + 1) * sizeof(uint64_t) + 16 +
+  const size_t smem = 1024 + (ring > red ? ring : red) + (2 * STAGES + 2) * sizeof(uint64_t) + 16 +
                       5 * BN * sizeof(float);
-  auto k = gemm_tc_kernel<BN, EPI, OUT, CLUSTER>;
+  auto k = gemm_tc_kernel<BN, EPI, OUT, CLUSTER, PUSH>;
   static OncePerDevice attrs, np_attrs;              // (of this instantiation of the launcher)
   if (int rc = attrs.run([&] {
         return cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -652,6 +800,14 @@ template <int BN, int EPI, typename OUT>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* out,
                   int ldo, int M, int N, int K, int split_k, float* workspace, int* err,
                   cudaStream_t st, const GemmExtra& ex) {
+#ifndef GF_NO_PUSH                                   // (a build to compare the two ways with)
+  // (token tiles above 32 have no stages to spare but for very short reductions: not compiled)
+  if constexpr (BN <= 32) {
+    if (split_k > 1 && !workspace && push_fits<BN, EPI>(K, split_k))
+      return launch_mode<BN, EPI, OUT, true, true>(mw, mx, bias, out, ldo, M, N, K, split_k,
+                                                   workspace, err, st, ex);
+  }
+#endif
   if (split_k > 1 && !workspace)
     return launch_mode<BN, EPI, OUT, true>(mw, mx, bias, out, ldo, M, N, K, split_k, workspace,
                                            err, st, ex);

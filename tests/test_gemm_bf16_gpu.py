@@ -60,12 +60,13 @@ def test_gated_epilogue(M, I, K):
 
 
 @pytest.mark.parametrize("M,N,K,split_k", [
-    (8, 2048, 1536, 8), (1, 1536, 1536, 8), (16, 392, 512, 4), (13, 1000, 256, 2),
+    (8, 2048, 1536, 8), (1, 1536, 1536, 8), (16, 392, 512, 4), (13, 1000, 256, 2),   # partials pushed
     (30, 1536, 512, 4), (8, 1536, 1536, 12),
-    (8, 1536, 8960, 12), (8, 640, 3072, 4), (40, 512, 1536, 8),
+    (8, 1536, 8960, 12), (8, 640, 3072, 4), (40, 512, 1536, 8),                      # partials pulled
 ])
 def test_cluster_split_adds_up_like_the_workspace_split(M, N, K, split_k):
-    """The K splits of a cluster are summed in rank order by the band owners: bit for bit what
+    """The K splits of a cluster are summed in rank order, whether the partials are sent to the
+    band owners (K ranges that leave stages of the ring free) or fetched by them: bit for bit what
     the workspace mode gives, which sums in split order too."""
     from ginfer_b200.ops import gemm_bf16
     g = torch.Generator(device="cpu").manual_seed(N + K)
