@@ -447,6 +447,43 @@ def run_long_context(shape: str, layers: int | None, context: int = 32768,
     return 0
 
 
+def scenario_plan(name: str, shape: str, layers: int | None):
+    """A serving workload without the engine: ``(config, layers of the whole model, prompts,
+    sampling parameters, the engine's sizes)``.  Every prompt with its output fits the engine's
+    longest sequence and the model's position table (a host test checks that)."""
+    import random
+
+    from ginfer_b200.sampling import SamplingParams
+    cfg = dict(SHAPES[shape])
+    full_layers = cfg["num_hidden_layers"]
+    cfg["num_hidden_layers"] = layers or full_layers
+    rng = random.Random(0)
+    V = cfg["vocab_size"]
+    if name == "serve64":
+        prompts = [[rng.randrange(V) for _ in range(rng.randint(128, 2048))] for _ in range(64)]
+        params = [SamplingParams(max_tokens=rng.randint(64, 256), ignore_eos=True)
+                  for _ in range(64)]
+        kwargs = dict(max_num_seqs=64, max_seq_len=8192, max_num_batched_tokens=2048,
+                      num_kvcache_blocks=64 * (2304 // PAGE + 2))
+    elif name == "ref256":
+        prompts = [[rng.randrange(V) for _ in range(512)] for _ in range(256)]
+        params = [SamplingParams(max_tokens=128, ignore_eos=True)] * 256
+        kwargs = dict(max_num_seqs=256, max_seq_len=CONTEXT, max_num_batched_tokens=16384,
+                      num_kvcache_blocks=256 * (640 // PAGE + 2))
+    elif name == "chunked":
+        # (prompts of 8,192 tokens: the position table has to reach that far)
+        cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], 16384)
+        prompts = ([[rng.randrange(V) for _ in range(32)] for _ in range(32)] +
+                   [[rng.randrange(V) for _ in range(8192)] for _ in range(8)])
+        params = ([SamplingParams(max_tokens=256, ignore_eos=True)] * 32 +
+                  [SamplingParams(max_tokens=8, ignore_eos=True)] * 8)
+        kwargs = dict(max_num_seqs=40, max_seq_len=16384, max_num_batched_tokens=2048 + 32,
+                      num_kvcache_blocks=8 * (8200 // PAGE + 2) + 32 * (288 // PAGE + 2))
+    else:
+        raise SystemExit(f"unknown scenario {name!r}")
+    return cfg, full_layers, prompts, params, kwargs
+
+
 def run_scenario(name: str, shape: str, layers: int | None) -> int:
     """The serving workloads the baseline names beside the headline, through the Python entry
     point (scheduler, chunked prompts, decode graphs), wall clock, third pass reported (the first
@@ -458,41 +495,13 @@ def run_scenario(name: str, shape: str, layers: int | None) -> int:
     time, pages of 16; prefill and decode tok/s counted as the reference counts them (a step with
     a prompt portion counts its tokens, another step its requests, each over its own wall time:
     ``ginfer/engine/engine.cc:73-121``) beside the figures it publishes.  One JSON line."""
-    import random
     import time
 
     import torch
 
     from ginfer_b200.engine.llm import Engine
-    from ginfer_b200.sampling import SamplingParams
-    cfg = dict(SHAPES[shape])
-    full_layers = cfg["num_hidden_layers"]
-    cfg["num_hidden_layers"] = layers or full_layers
-    rng = random.Random(0)
-    V = cfg["vocab_size"]
-    if name == "serve64":
-        prompts = [[rng.randrange(V) for _ in range(rng.randint(128, 2048))] for _ in range(64)]
-        params = [SamplingParams(max_tokens=rng.randint(64, 256), ignore_eos=True)
-                  for _ in range(64)]
-        eng = Engine(config=cfg, dtype="bfloat16", max_num_seqs=64, max_seq_len=8192,
-                     max_num_batched_tokens=2048, kvcache_block_size=PAGE,
-                     num_kvcache_blocks=64 * (2304 // PAGE + 2))
-    elif name == "ref256":
-        prompts = [[rng.randrange(V) for _ in range(512)] for _ in range(256)]
-        params = [SamplingParams(max_tokens=128, ignore_eos=True)] * 256
-        eng = Engine(config=cfg, dtype="bfloat16", max_num_seqs=256, max_seq_len=CONTEXT,
-                     max_num_batched_tokens=16384, kvcache_block_size=PAGE,
-                     num_kvcache_blocks=256 * (640 // PAGE + 2))
-    else:
-        # (prompts of 8,192 tokens: the position table has to reach that far)
-        cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], 16384)
-        prompts = ([[rng.randrange(V) for _ in range(32)] for _ in range(32)] +
-                   [[rng.randrange(V) for _ in range(8192)] for _ in range(8)])
-        params = ([SamplingParams(max_tokens=256, ignore_eos=True)] * 32 +
-                  [SamplingParams(max_tokens=8, ignore_eos=True)] * 8)
-        eng = Engine(config=cfg, dtype="bfloat16", max_num_seqs=40, max_seq_len=16384,
-                     max_num_batched_tokens=2048 + 32, kvcache_block_size=PAGE,
-                     num_kvcache_blocks=8 * (8200 // PAGE + 2) + 32 * (288 // PAGE + 2))
+    cfg, full_layers, prompts, params, kwargs = scenario_plan(name, shape, layers)
+    eng = Engine(config=cfg, dtype="bfloat16", kvcache_block_size=PAGE, **kwargs)
     result = None
     for _ in range(3):
         torch.cuda.synchronize()

@@ -511,3 +511,26 @@ def test_the_reference_benchmark_workload_is_scheduled_in_nine_prompt_steps():
     assert all(len(r.output) == 128 and r.finish_reason == "max_tokens" for r in reqs)
     assert sched.num_preemptions == 0
     assert cache.free_pages() == [256 * (640 // page + 2)] and cache.slots.num_free == 256
+
+
+def test_the_bench_scenarios_fit_the_engines_they_ask_for():
+    """Every prompt of a serving workload of ``bench.py``, with the tokens it generates, fits the
+    engine's longest sequence and the model's position table, at every shape (the runner takes
+    the smaller of the two as its limit and refuses longer requests)."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import bench
+    for name in bench.SCENARIOS:
+        if name == "longctx":
+            continue                                     # (one prompt, sized from its arguments)
+        for shape in bench.SHAPES:
+            cfg, full_layers, prompts, params, kwargs = bench.scenario_plan(name, shape, 2)
+            limit = min(kwargs["max_seq_len"], cfg["max_position_embeddings"])
+            longest = max(len(p) + q.max_tokens for p, q in zip(prompts, params))
+            assert longest <= limit, (name, shape, longest, limit)
+            assert len(prompts) == len(params) and cfg["num_hidden_layers"] == 2
+            assert full_layers == bench.SHAPES[shape]["num_hidden_layers"]
+            # pages for every request at its full length, so that nobody is preempted
+            pages = sum(-(-(len(p) + q.max_tokens) // bench.PAGE) for p, q in zip(prompts, params))
+            assert pages <= kwargs["num_kvcache_blocks"], (name, shape, pages)
