@@ -8,7 +8,11 @@
 // tokens of the 1.5B shape, goes away).  A third epilogue serves the joined q/k/v product: a
 // thread holds whole heads of its token, so it adds the bias, rotates q and k by the token's
 // angles and writes k and v into the token's slot of the paged cache as well as into `out` (no
-// rotation kernel reads and rewrites q/k/v behind the product).
+// rotation kernel reads and rewrites q/k/v behind the product); it reads the table and writes
+// its results with four threads a token, through a scratch in shared memory, since with a
+// thread a token every such access touched 32 lines.  (An option of the engine, not its default:
+// the product's tiles are one round for the SMs at 2,048 tokens, so this epilogue hides behind
+// nothing, and the library's product with the rotation kernel behind it measures faster there.)
 //
 // One CTA an SM walks over tiles (tile = blockIdx.x + i * gridDim.x; the tiles of one block of
 // weight rows are neighbours, so that block is read from HBM once and from L2 after that).  Roles:
